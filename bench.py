@@ -1,0 +1,350 @@
+#!/usr/bin/env python
+"""Benchmark of the attention KV-cache path: decode attention tokens/s and KV-read GB/s.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
+
+Default workload (the one the headline metric is quoted on): GLM-4-9B-shaped batched decode, a 40-layer
+attention stack, 32 q heads / 2 kv heads, head_dim 128, f16 caches of max_length 8192, 64 independent
+sequences per GPU with n_past drawn uniformly from [1024, 8191] by a seed.  A step is one decode step of all
+sequences through all 40 layers: 40 calls of cglm_attn_forward (fused RoPE + f16 append + attention).
+Sequences are independent, so N GPUs hold 64 sequences each and exchange nothing (weak scaling).
+
+Prints ONE JSON line (rank 0).  `value` is whole-job tokens/s with inputs resident in HBM; `e2e` is the
+same metric through cglm_attn_forward_host with pinned host activations (H2D and D2H inside the timed
+region); `roofline` is the decode kernel's KV bytes per launch over its measured duration against the
+measured HBM copy bandwidth; `cpu_baseline` is the CPU restatement of the reference path timed on this
+box's host cores on a bounded sample.  --impl reference times only that CPU path.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes as C
+import json
+import os
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+WORKLOADS = {
+    # name: H, G, D, max_length, layers, seqs per GPU, n_past range, rope, theta, interleaved, mask
+    "glm4_9b_batched_decode": dict(H=32, G=2, D=128, M=8192, layers=40, seqs=64, n_past=(1024, 8191), rope=8,
+                                   theta=10000.0, interleaved=False, mask=0, seed=1003),
+    "glm3_6b_decode_512": dict(H=32, G=2, D=128, M=2048, layers=1, seqs=1, n_past=(512, 512), rope=8, theta=10000.0,
+                               interleaved=False, mask=0, seed=1001),
+    "glm4_9b_long_131072": dict(H=32, G=2, D=128, M=131072 + 64, layers=1, seqs=1, n_past=(131072, 131072), rope=8,
+                                theta=5.0e6, interleaved=False, mask=0, seed=1004),
+    "glm1_6b_mha_decode": dict(H=32, G=32, D=128, M=4096, layers=28, seqs=4, n_past=(2048, 2048), rope=4,
+                               theta=10000.0, interleaved=True, mask=1, seed=1005),
+}
+HBM_FALLBACK_GBS = 6650.0   # earlier measurement on this pool, used only without MEASURED_PEAKS.json
+# dram__bytes_read.sum + dram__bytes_write.sum of one decode launch of the default workload (ncu capture of a
+# 1/8-size case scaled by KV bytes; see profiles/).  None until measured.
+NCU_TRAFFIC_PER_KV_BYTE = None
+
+
+def kv_bytes(w, n_past):
+    """Algorithmic bytes of one layer call: K and V^T of every attended token, f16 (4*G*D*(n_past+1))."""
+    return int(sum(4 * w["G"] * w["D"] * (p + 1) for p in n_past))
+
+
+def draw_n_past(w, rank):
+    rng = np.random.default_rng(w["seed"] + 7919 * rank)
+    lo, hi = w["n_past"]
+    return rng.integers(lo, hi + 1, w["seqs"]).astype(np.int32)
+
+
+def qkv_row(w):
+    return 3 * w["H"] * w["D"] if w["interleaved"] else (w["H"] + 2 * w["G"]) * w["D"]
+
+
+class ClockSampler(threading.Thread):
+    """Samples SM clock and throttle reasons of one GPU during the timed region (read-only NVML queries)."""
+
+    def __init__(self, index):
+        super().__init__(daemon=True)
+        self.index, self.samples, self.reasons, self.max_mhz = index, [], set(), None
+        self._stop = threading.Event()
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.nv = None
+
+    def run(self):
+        if self.nv is None:
+            return
+        nv = self.nv
+        names = {nv.nvmlClocksThrottleReasonHwSlowdown: "hw_slowdown",
+                 nv.nvmlClocksThrottleReasonHwThermalSlowdown: "hw_thermal_slowdown",
+                 nv.nvmlClocksThrottleReasonSwThermalSlowdown: "sw_thermal_slowdown",
+                 nv.nvmlClocksThrottleReasonSwPowerCap: "sw_power_cap"}
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                r = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+                for bit, name in names.items():
+                    if r & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            self._stop.wait(0.05)
+
+    def finish(self):
+        self._stop.set()
+        self.join(timeout=2)
+        med = float(np.median(self.samples)) if self.samples else None
+        return {"sm_mhz": med, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons),
+                "samples": len(self.samples)}
+
+
+def host_threads():
+    return os.cpu_count() or 1
+
+
+def cpu_leg(w, n_past, host_caches, steps, warmup):
+    """Times the CPU oracle on one layer of the workload.  Returns (tokens/s scaled to all layers, seconds/layer)."""
+    from oracle import attn_oracle as O
+    cfg = O.make_cfg(w["H"], w["G"], w["D"], w["M"], 0, w["rope"], w["theta"], w["mask"], "ggml")
+    rng = np.random.default_rng(w["seed"])
+    n, H, G, D = len(n_past), w["H"], w["G"], w["D"]
+    qkv = rng.standard_normal((n, qkv_row(w))).astype(np.float32)
+    if w["interleaved"]:
+        q = [qkv[i] for i in range(n)]; k = [qkv[i][D:] for i in range(n)]; v = [qkv[i][2 * D:] for i in range(n)]
+        hs = 3 * D
+    else:
+        q = [qkv[i] for i in range(n)]; k = [qkv[i][H * D:] for i in range(n)]; v = [qkv[i][(H + G) * D:] for i in range(n)]
+        hs = D
+    kc = [c[0] for c in host_caches]
+    vc = [c[1] for c in host_caches]
+    n_ctx = np.maximum(n_past // 2, 2).astype(np.int32)
+    thr = host_threads()
+    times = []
+    for it in range(warmup + steps):
+        t0 = time.perf_counter()
+        O.attn_decode_batch(cfg, q, k, v, hs, hs, kc, vc, n_past, n_ctx, n_threads=thr)
+        dt = time.perf_counter() - t0
+        if it >= warmup:
+            times.append(dt)
+    per_layer = float(np.mean(times))
+    return n / (per_layer * w["layers"]), per_layer, thr
+
+
+def synth_host_caches(w, n_past, seed):
+    """Host caches for the reference arm: N(0,1) f16 tiled from a 4M-value pool (fast to make, same distribution)."""
+    rng = np.random.default_rng(seed)
+    pool = rng.standard_normal(1 << 22).astype(np.float16).view(np.uint16)
+    G, M, D = w["G"], w["M"], w["D"]
+    out = []
+    for i, p in enumerate(n_past):
+        n = G * M * D
+        off = (i * 104729) % (pool.size // 2)
+        k = np.resize(pool[off:], n).reshape(G, M, D).copy()
+        v = np.resize(pool[off + 17:], n).reshape(G, D, M).copy()
+        out.append((k, v))
+    return out
+
+
+def run_reference(args, w):
+    """--impl reference: the reference's CPU path (our CPU restatement of it: the reference's own arithmetic lives
+    in the ggml submodule, which is absent and unpinned, so it cannot be compiled here)."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    n_past = draw_n_past(w, 0)
+    caches = synth_host_caches(w, n_past, w["seed"])
+    # each step: one of the workload's layers over all sequences
+    tps, per_layer, thr = cpu_leg(w, n_past, caches, args.steps, max(1, min(args.warmup, 3)))
+    sample = f"1 of {w['layers']} layers x {w['seqs']} sequences per step, scaled to {w['layers']} layers"
+    line = {
+        "impl": "reference", "metric": "decode_attention_tokens_per_s", "value": tps, "unit": "tokens/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": per_layer * w["layers"] * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+        "config": workload_config(args, w, n_past),
+        "cpu_baseline": {"value": tps, "unit": "tokens/s", "cores": thr, "kind": "port", "sample": sample},
+        "e2e": {"value": tps, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(args, w, n_past):
+    return {"workload": args.workload, "n_head": w["H"], "n_kv_head": w["G"], "head_dim": w["D"],
+            "max_length": w["M"], "layers": w["layers"], "seqs_per_gpu": w["seqs"],
+            "global_batch": w["seqs"] * args.gpus, "n_past_range": list(w["n_past"]),
+            "n_past_mean": float(np.mean(n_past)), "parallelism": f"sequence-sharded x{args.gpus}, no collective",
+            "l2_policy": "inputs larger than L2 (each launch streams its own cache slabs; a step touches every layer's)"}
+
+
+def run_ours(args, w):
+    import torch
+    import torch.distributed as dist
+
+    from chatglm_cpp_b200 import _lib
+    from chatglm_cpp_b200 import attention as A
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU fallback); use --impl reference for the CPU path")
+    torch.cuda.set_device(local)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    L = _lib.lib()
+    H, G, D, M, layers, n = w["H"], w["G"], w["D"], w["M"], w["layers"], w["seqs"]
+    desc = _lib.AttnDesc(H, G, D, M, 0, w["rope"], w["theta"], w["mask"])
+    n_past = draw_n_past(w, rank)
+    n_ctx = np.maximum(n_past // 2, 2).astype(np.int32)
+
+    # ---- state: caches for every (layer, sequence), filled with N(0,1) f16 on the device ------------------
+    arena = A.KVArena(desc, layers * n)
+    g = torch.Generator(device="cuda")
+    g.manual_seed(w["seed"] + rank)
+    for view in (arena.k_all(), arena.v_all()):
+        flat = view.view(-1)
+        step = 1 << 28
+        for o in range(0, flat.numel(), step):
+            seg = flat[o:o + step]
+            seg.copy_(torch.randn(seg.numel(), device="cuda", generator=g, dtype=torch.float32).half())
+    ws = A.Workspace(desc, n, 1)
+    row, orow = qkv_row(w), H * D
+    qkv_dev = torch.randn(layers, n, row, device="cuda", generator=g)
+    out_dev = torch.empty(layers, n, orow, device="cuda")
+    qkv_host = qkv_dev.cpu().pin_memory()
+    out_host = torch.empty(layers, n, orow).pin_memory()
+    stage_qkv = torch.empty(n, row, device="cuda")
+    stage_out = torch.empty(n, orow, device="cuda")
+
+    # one descriptor array per layer, built once: slot of (layer l, sequence i) is l*n + i
+    seq_arrays = []
+    for l in range(layers):
+        arr = (_lib.AttnSeq * n)()
+        for i in range(n):
+            call = A.SeqCall(qkv=qkv_dev[l, i:i + 1], slot=l * n + i, n_past=int(n_past[i]), n_ctx=int(n_ctx[i]),
+                             out=out_dev[l, i:i + 1])
+            A.fill_seq(arr[i], desc, call, w["interleaved"])
+        seq_arrays.append(arr)
+    stream = torch.cuda.current_stream().cuda_stream
+
+    def step_device():
+        for l in range(layers):
+            rc = L.cglm_attn_forward(arena._h, seq_arrays[l], n, ws.ptr, ws.bytes, stream)
+            if rc != 0:
+                raise _lib.CglmError(rc, "cglm_attn_forward")
+
+    def step_host():
+        for l in range(layers):
+            rc = L.cglm_attn_forward_host(arena._h, seq_arrays[l], n, int(w["interleaved"]), qkv_host[l].data_ptr(),
+                                          out_host[l].data_ptr(), stage_qkv.data_ptr(), stage_out.data_ptr(), ws.ptr,
+                                          ws.bytes, stream)
+            if rc != 0:
+                raise _lib.CglmError(rc, "cglm_attn_forward_host")
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps, warmup):
+        for _ in range(warmup):
+            fn()
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        launches0 = L.cglm_launch_count()
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        barrier()
+        ms = e0.elapsed_time(e1)
+        if world > 1:
+            t = torch.tensor([ms], device="cuda", dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms, L.cglm_launch_count() - launches0
+
+    sampler = ClockSampler(local)
+    sampler.start()
+    ms, launches = timed(step_device, args.steps, args.warmup)
+    clocks = sampler.finish()
+    if ws.status() != 0:
+        raise SystemExit("device-side status is not clean after the timed region")
+    ms_e2e, _ = timed(step_host, max(3, args.steps // 2), max(3, args.warmup))
+    e2e_steps = max(3, args.steps // 2)
+
+    tokens_per_step = n * world
+    value = tokens_per_step * args.steps / (ms * 1e-3)
+    e2e_value = tokens_per_step * e2e_steps / (ms_e2e * 1e-3)
+    bytes_per_launch = kv_bytes(w, n_past)
+    launch_ms = ms / (args.steps * layers)
+    achieved = bytes_per_launch / (launch_ms * 1e-3) / 1e9
+    peak, peak_src = HBM_FALLBACK_GBS, "fallback"
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            peak, peak_src = float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        pass
+
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        # bounded sample: layer 0 of the same workload, with the device's cache contents
+        torch.cuda.synchronize()
+        host_caches = [(arena.k_cache(i).cpu().numpy().view(np.uint16), arena.v_cache(i).cpu().numpy().view(np.uint16))
+                       for i in range(n)]
+        tps, per_layer, thr = cpu_leg(w, n_past, host_caches, 3, 1)
+        cpu = {"value": tps, "unit": "tokens/s", "cores": thr, "kind": "port",
+               "sample": f"layer 0 of {layers} x {n} sequences (same cache bits), 3 repetitions, scaled to {layers} layers"}
+
+    if rank == 0:
+        line = {
+            "metric": "decode_attention_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+            "config": workload_config(args, w, n_past),
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                         "peak_source": peak_src, "kernel": "decode_kernel",
+                         "algorithmic_bytes_per_launch": bytes_per_launch, "launch_us": launch_ms * 1e3,
+                         "traffic": (NCU_TRAFFIC_PER_KV_BYTE * bytes_per_launch
+                                     if NCU_TRAFFIC_PER_KV_BYTE is not None else None),
+                         "frac_of_nominal_8000": achieved / 8000.0},
+            "cpu_baseline": cpu,
+            "e2e": {"value": e2e_value, "unit": "tokens/s", "ms_per_step": ms_e2e / e2e_steps,
+                    "h2d_bytes_per_step": layers * n * row * 4, "d2h_bytes_per_step": layers * n * orow * 4},
+            "gpu_launches": int(launches) * world,
+            "clocks": clocks,
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--workload", choices=sorted(WORKLOADS), default="glm4_9b_batched_decode")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    w = WORKLOADS[args.workload]
+    if args.impl == "reference":
+        run_reference(args, w)
+    else:
+        run_ours(args, w)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,86 @@
+"""ctypes binding of libcglm_attn.so, the C ABI declared in include/cglm_attn.h.
+
+There is no fallback: if the CUDA library has not been built, importing this module raises.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+_PKG = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_PKG, "lib", "libcglm_attn.so")
+
+OK, ERR_INVALID_ARG, ERR_CUDA, ERR_WORKSPACE, ERR_UNSUPPORTED, ERR_TIMEOUT, ERR_NO_DEVICE = 0, -1, -2, -3, -4, -5, -6
+ROPE_GPTJ, ROPE_NEOX, ROPE_CHATGLM, ROPE_CHATGLM2, ROPE_DISABLED = 0, 2, 4, 8, 10000
+MASK_CAUSAL, MASK_CHATGLM = 0, 1
+SEQ_NO_APPEND, SEQ_PARTIAL, SEQ_USE_KV_LOCAL = 1, 2, 4
+
+
+class AttnDesc(C.Structure):
+    _fields_ = [("n_head", C.c_int), ("n_kv_head", C.c_int), ("head_dim", C.c_int), ("max_len", C.c_int),
+                ("n_virtual", C.c_int), ("rope_type", C.c_int), ("rope_theta", C.c_float), ("mask_type", C.c_int)]
+
+
+class AttnSeq(C.Structure):
+    _fields_ = [("q", C.c_void_p), ("k", C.c_void_p), ("v", C.c_void_p),
+                ("q_tok_stride", C.c_longlong), ("q_head_stride", C.c_longlong),
+                ("kv_tok_stride", C.c_longlong), ("kv_head_stride", C.c_longlong),
+                ("slot", C.c_int), ("qlen", C.c_int), ("n_past", C.c_int), ("n_ctx", C.c_int),
+                ("position_ids", C.c_void_p), ("out", C.c_void_p), ("q_roped", C.c_void_p),
+                ("k_roped", C.c_void_p), ("kv_local", C.c_int), ("flags", C.c_int), ("partial", C.c_void_p)]
+
+
+# every symbol include/cglm_attn.h declares: name -> (restype, argtypes)
+SYMBOLS = {
+    "cglm_kv_arena_create": (C.c_int, [C.POINTER(AttnDesc), C.c_int, C.POINTER(C.c_void_p)]),
+    "cglm_kv_arena_destroy": (C.c_int, [C.c_void_p]),
+    "cglm_kv_arena_k_cache": (C.c_void_p, [C.c_void_p, C.c_int]),
+    "cglm_kv_arena_v_cache": (C.c_void_p, [C.c_void_p, C.c_int]),
+    "cglm_kv_arena_n_slots": (C.c_int, [C.c_void_p]),
+    "cglm_kv_arena_desc": (C.POINTER(AttnDesc), [C.c_void_p]),
+    "cglm_kv_slot_bytes": (C.c_size_t, [C.POINTER(AttnDesc)]),
+    "cglm_kv_slot_copy": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]),
+    "cglm_attn_workspace_bytes": (C.c_size_t, [C.POINTER(AttnDesc), C.c_int, C.c_int]),
+    "cglm_attn_workspace_init": (C.c_int, [C.c_void_p, C.c_size_t, C.c_void_p]),
+    "cglm_attn_workspace_status": (C.c_int, [C.c_void_p, C.c_void_p]),
+    "cglm_attn_forward": (C.c_int, [C.c_void_p, C.POINTER(AttnSeq), C.c_int, C.c_void_p, C.c_size_t, C.c_void_p]),
+    "cglm_attn_forward_host": (C.c_int, [C.c_void_p, C.POINTER(AttnSeq), C.c_int, C.c_int, C.c_void_p, C.c_void_p,
+                                         C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]),
+    "cglm_attn_splitkv_combine": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p]),
+    "cglm_kv_load_prefix": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_void_p]),
+    "cglm_status_string": (C.c_char_p, [C.c_int]),
+    "cglm_last_error_string": (C.c_char_p, []),
+    "cglm_launch_count": (C.c_ulonglong, []),
+}
+
+_lib = None
+
+
+def lib():
+    """The loaded library with argtypes set.  Raises if the CUDA library is missing."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise RuntimeError(
+                f"{LIB_PATH} is missing: build it with `python -m chatglm_cpp_b200.build` "
+                "(this package has no CPU or PyTorch fallback)")
+        handle = C.CDLL(LIB_PATH)
+        for name, (res, args) in SYMBOLS.items():
+            fn = getattr(handle, name)
+            fn.restype = res
+            fn.argtypes = args
+        _lib = handle
+    return _lib
+
+
+class CglmError(RuntimeError):
+    def __init__(self, status: int, where: str):
+        self.status = status
+        msg = lib().cglm_status_string(status).decode()
+        detail = lib().cglm_last_error_string().decode()
+        super().__init__(f"{where}: {msg}" + (f" ({detail})" if detail and status == ERR_CUDA else ""))
+
+
+def check(status: int, where: str) -> None:
+    if status != OK:
+        raise CglmError(status, where)

@@ -1,0 +1,196 @@
+"""Python face of the C ABI (include/cglm_attn.h) for tests and benchmarks.
+
+PyTorch appears here only as the owner of device buffers and streams; every computation goes through
+libcglm_attn.so.  The classes mirror the reference's objects: ``KVArena`` is ModelContext's kv buffer
+(chatglm.h:337,345,627-628) and ``BasicAttention`` keeps the constructor arguments, public cache members
+and ``forward(qkv, n_past, n_ctx)`` call shape of chatglm::BasicAttention (chatglm.h:440-472) for the part
+between its two Linears.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass
+from typing import Optional, Sequence
+
+import torch
+
+from . import _lib
+from ._lib import (AttnDesc, AttnSeq, MASK_CAUSAL, MASK_CHATGLM, ROPE_CHATGLM, ROPE_CHATGLM2, ROPE_DISABLED,  # noqa: F401
+                   ROPE_GPTJ, ROPE_NEOX, SEQ_NO_APPEND, SEQ_PARTIAL, SEQ_USE_KV_LOCAL, check)
+
+
+def _stream_ptr() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+class _DevView:
+    """Zero-copy torch view of library-owned device memory."""
+
+    def __init__(self, ptr: int, shape, typestr: str):
+        self.__cuda_array_interface__ = {"shape": tuple(shape), "typestr": typestr, "data": (ptr, False), "version": 3}
+
+
+class KVArena:
+    """All k_cache / v_cache pairs of a model (layers x sequences) in one device allocation."""
+
+    def __init__(self, desc: AttnDesc, n_slots: int):
+        if not torch.cuda.is_available():
+            raise RuntimeError("KVArena needs a CUDA device: this package has no CPU fallback")
+        self.desc = desc
+        self.n_slots = n_slots
+        handle = C.c_void_p()
+        check(_lib.lib().cglm_kv_arena_create(C.byref(desc), n_slots, C.byref(handle)), "cglm_kv_arena_create")
+        self._h = handle
+
+    def close(self):
+        if self._h:
+            _lib.lib().cglm_kv_arena_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def k_cache(self, slot: int) -> torch.Tensor:
+        """f16 [n_kv_head, max_len, head_dim] view of the slot's k_cache (chatglm.h:470)."""
+        d = self.desc
+        ptr = _lib.lib().cglm_kv_arena_k_cache(self._h, slot)
+        return torch.as_tensor(_DevView(ptr, (d.n_kv_head, d.max_len, d.head_dim), "<f2"), device="cuda")
+
+    def v_cache(self, slot: int) -> torch.Tensor:
+        """f16 [n_kv_head, head_dim, max_len] view of the slot's transposed v_cache (chatglm.h:471)."""
+        d = self.desc
+        ptr = _lib.lib().cglm_kv_arena_v_cache(self._h, slot)
+        return torch.as_tensor(_DevView(ptr, (d.n_kv_head, d.head_dim, d.max_len), "<f2"), device="cuda")
+
+    def k_all(self) -> torch.Tensor:
+        """f16 [n_slots, n_kv_head, max_len, head_dim] view of every k_cache (the arena keeps them contiguous)."""
+        d = self.desc
+        ptr = _lib.lib().cglm_kv_arena_k_cache(self._h, 0)
+        return torch.as_tensor(_DevView(ptr, (self.n_slots, d.n_kv_head, d.max_len, d.head_dim), "<f2"), device="cuda")
+
+    def v_all(self) -> torch.Tensor:
+        """f16 [n_slots, n_kv_head, head_dim, max_len] view of every v_cache."""
+        d = self.desc
+        ptr = _lib.lib().cglm_kv_arena_v_cache(self._h, 0)
+        return torch.as_tensor(_DevView(ptr, (self.n_slots, d.n_kv_head, d.head_dim, d.max_len), "<f2"), device="cuda")
+
+    def load_prefix(self, slot: int, past_kv: torch.Tensor) -> None:
+        """past_kv: f16 [2, n_kv_head, n_virtual, head_dim] on the device (chatglm.h:580-615)."""
+        assert past_kv.is_cuda and past_kv.dtype == torch.float16 and past_kv.is_contiguous()
+        check(_lib.lib().cglm_kv_load_prefix(self._h, slot, past_kv.data_ptr(), _stream_ptr()), "cglm_kv_load_prefix")
+
+
+class Workspace:
+    def __init__(self, desc: AttnDesc, n_seq: int, max_qlen: int = 1):
+        n = _lib.lib().cglm_attn_workspace_bytes(C.byref(desc), n_seq, max_qlen)
+        if n == 0:
+            raise ValueError("bad descriptor for workspace")
+        self.buf = torch.empty(n, dtype=torch.uint8, device="cuda")
+        self.bytes = n
+        check(_lib.lib().cglm_attn_workspace_init(self.buf.data_ptr(), n, _stream_ptr()), "cglm_attn_workspace_init")
+
+    @property
+    def ptr(self) -> int:
+        return self.buf.data_ptr()
+
+    def status(self) -> int:
+        return _lib.lib().cglm_attn_workspace_status(self.ptr, _stream_ptr())
+
+
+@dataclass
+class SeqCall:
+    """One sequence of a batched forward: a fused qkv activation on the device plus its cache slot."""
+    qkv: torch.Tensor                 # f32 [qlen, (H+2G)*D] (blocked) or [qlen, 3*H*D] (interleaved)
+    slot: int
+    n_past: int
+    n_ctx: int = 0
+    out: Optional[torch.Tensor] = None        # f32 [qlen, H*D]
+    position_ids: Optional[torch.Tensor] = None
+    q_roped: Optional[torch.Tensor] = None
+    k_roped: Optional[torch.Tensor] = None
+    partial: Optional[torch.Tensor] = None
+    kv_local: int = 0
+    flags: int = 0
+
+
+def fill_seq(dst: AttnSeq, desc: AttnDesc, call: SeqCall, interleaved: bool) -> None:
+    H, G, D = desc.n_head, desc.n_kv_head, desc.head_dim
+    qkv = call.qkv
+    assert qkv.is_cuda and qkv.dtype == torch.float32 and qkv.is_contiguous() and qkv.dim() == 2
+    base, esz = qkv.data_ptr(), 4
+    row = qkv.shape[1]
+    if interleaved:   # chatglm.cpp:638-644
+        assert row == 3 * H * D and H == G
+        dst.q, dst.k, dst.v = base, base + D * esz, base + 2 * D * esz
+        dst.q_head_stride = dst.kv_head_stride = 3 * D
+    else:             # chatglm.cpp:646-652
+        assert row == (H + 2 * G) * D
+        dst.q, dst.k, dst.v = base, base + H * D * esz, base + (H + G) * D * esz
+        dst.q_head_stride = dst.kv_head_stride = D
+    dst.q_tok_stride = dst.kv_tok_stride = row
+    dst.slot, dst.qlen, dst.n_past, dst.n_ctx = call.slot, qkv.shape[0], call.n_past, call.n_ctx
+    dst.position_ids = call.position_ids.data_ptr() if call.position_ids is not None else None
+    dst.out = call.out.data_ptr() if call.out is not None else None
+    dst.q_roped = call.q_roped.data_ptr() if call.q_roped is not None else None
+    dst.k_roped = call.k_roped.data_ptr() if call.k_roped is not None else None
+    dst.partial = call.partial.data_ptr() if call.partial is not None else None
+    dst.kv_local, dst.flags = call.kv_local, call.flags
+
+
+def forward_batch(arena: KVArena, ws: Workspace, calls: Sequence[SeqCall], interleaved: bool = False,
+                  seq_array=None) -> None:
+    """cglm_attn_forward over a batch of sequences; asynchronous on the current stream."""
+    n = len(calls)
+    arr = seq_array if seq_array is not None else (AttnSeq * n)()
+    for i, c in enumerate(calls):
+        fill_seq(arr[i], arena.desc, c, interleaved)
+    check(_lib.lib().cglm_attn_forward(arena._h, arr, n, ws.ptr, ws.bytes, _stream_ptr()), "cglm_attn_forward")
+
+
+class BasicAttention:
+    """The cache-owning attention module of one layer for one sequence (chatglm.h:440-472).
+
+    ``forward`` takes what query_key_value.forward returns (chatglm.cpp:629) and returns what dense.forward
+    consumes (chatglm.cpp:719).
+    """
+
+    def __init__(self, arena: KVArena, slot: int, ws: Workspace, interleaved_qkv: bool = False):
+        d = arena.desc
+        self.arena, self.slot, self.ws = arena, slot, ws
+        self.num_attention_heads = d.n_head
+        self.num_key_value_heads = d.n_kv_head
+        self.interleaved_qkv = interleaved_qkv
+        self.rope_type = d.rope_type
+        self.rope_theta = d.rope_theta
+        self.attn_mask_type = d.mask_type
+        self.num_virtual_tokens = d.n_virtual
+        self.k_cache = arena.k_cache(slot)   # [#kvh, s, d]
+        self.v_cache = arena.v_cache(slot)   # [#kvh, d, s]
+
+    def forward(self, qkv: torch.Tensor, n_past: int, n_ctx: int = 0, position_ids: Optional[torch.Tensor] = None,
+                want_roped: bool = False):
+        d = self.arena.desc
+        qlen = qkv.shape[0]
+        out = torch.empty(qlen, d.n_head * d.head_dim, dtype=torch.float32, device="cuda")
+        qr = kr = None
+        if want_roped:
+            qr = torch.empty(qlen, d.n_head, d.head_dim, dtype=torch.float32, device="cuda")
+            kr = torch.empty(qlen, d.n_kv_head, d.head_dim, dtype=torch.float32, device="cuda")
+        call = SeqCall(qkv=qkv, slot=self.slot, n_past=n_past, n_ctx=n_ctx, out=out, position_ids=position_ids,
+                       q_roped=qr, k_roped=kr)
+        forward_batch(self.arena, self.ws, [call], self.interleaved_qkv)
+        return (out, qr, kr) if want_roped else out
+
+
+def splitkv_combine(partials: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """partials: f32 [n_part, H, D+2] (acc | m | l) on this device -> f32 [H*D]."""
+    assert partials.is_cuda and partials.dtype == torch.float32 and partials.is_contiguous()
+    n, H, Dp2 = partials.shape
+    if out is None:
+        out = torch.empty(H * (Dp2 - 2), dtype=torch.float32, device="cuda")
+    check(_lib.lib().cglm_attn_splitkv_combine(partials.data_ptr(), n, H, Dp2 - 2, out.data_ptr(), _stream_ptr()),
+          "cglm_attn_splitkv_combine")
+    return out

@@ -1,0 +1,528 @@
+// C ABI of the attention KV-cache path: argument checking, the KV arena, workspace layout, dispatch of each
+// sequence to the kernel that covers its shape.  Declarations and their reference counterparts are in
+// include/cglm_attn.h.
+#include <cmath>
+#include <cstddef>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+#include <new>
+#include <vector>
+
+#include "common.cuh"
+
+using namespace cglm;
+
+// the ctypes mirror of these structs (chatglm_cpp_b200/_lib.py) is checked against the same numbers
+static_assert(sizeof(cglm_attn_desc) == 32, "cglm_attn_desc layout");
+static_assert(sizeof(cglm_attn_seq) == 120 && offsetof(cglm_attn_seq, position_ids) == 72 &&
+                  offsetof(cglm_attn_seq, partial) == 112,
+              "cglm_attn_seq layout");
+
+struct cglm_kv_arena {
+    cglm_attn_desc desc;
+    int n_slots;
+    int device;
+    int n_sm;
+    uint8_t *base;        // one allocation: K slabs, then V slabs
+    uint16_t *k_base;
+    uint16_t *v_base;
+    size_t k_slot_elems;  // G*M*D
+    bool has_tmaps;
+    CUtensorMap k_map, v_map;
+    // pinned ring through which sequence descriptors travel to the device without a host sync
+    SeqDev *ring;
+    int ring_slots;
+    int ring_cap;         // descriptors per slot
+    int ring_next;
+    cudaEvent_t *ring_events;
+    std::mutex mu;
+};
+
+namespace {
+
+thread_local char g_err[256] = "";
+
+int fail_cuda(cudaError_t e, const char *what) {
+    std::snprintf(g_err, sizeof(g_err), "%s: %s", what, cudaGetErrorString(e));
+    return CGLM_ERR_CUDA;
+}
+#define CGLM_CUDA(call)                                  \
+    do {                                                 \
+        cudaError_t e__ = (call);                        \
+        if (e__ != cudaSuccess) return fail_cuda(e__, #call); \
+    } while (0)
+
+bool desc_ok(const cglm_attn_desc *d) {
+    if (!d) return false;
+    if (d->n_head <= 0 || d->n_kv_head <= 0 || d->n_head % d->n_kv_head) return false;
+    if (d->head_dim <= 0 || d->head_dim % 2 || d->max_len <= 0 || d->n_virtual < 0 || d->n_virtual > d->max_len)
+        return false;
+    switch (d->rope_type) {
+    case CGLM_ROPE_GPTJ: case CGLM_ROPE_NEOX: case CGLM_ROPE_DISABLED: break;
+    case CGLM_ROPE_CHATGLM: case CGLM_ROPE_CHATGLM2:
+        if (d->head_dim % 4) return false;
+        break;
+    default: return false;
+    }
+    return d->mask_type == CGLM_MASK_CAUSAL || d->mask_type == CGLM_MASK_CHATGLM;
+}
+
+AttnShape make_shape(const cglm_attn_desc &d) {
+    AttnShape s;
+    s.H = d.n_head; s.G = d.n_kv_head; s.D = d.head_dim; s.R = d.n_head / d.n_kv_head;
+    s.M = d.max_len; s.V = d.n_virtual; s.rope_type = d.rope_type; s.mask_type = d.mask_type;
+    // apply_rotary_emb_glm passes no base, i.e. ggml's default 10000 (chatglm.cpp:563-564)
+    const float base = d.rope_type == CGLM_ROPE_CHATGLM ? 10000.f : d.rope_theta;
+    s.theta_scale = powf(base, -2.0f / static_cast<float>(rope_n_dims(d.rope_type, d.head_dim)));
+    s.scale = 1.f / std::sqrt(static_cast<float>(d.head_dim));
+    return s;
+}
+
+size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+
+// ---- workspace layout (fixed regions first, so that self-resetting counters stay where they are) ------
+struct WsLayout {
+    size_t counters, partials, seqs, q_stage, total;
+};
+WsLayout ws_layout(const cglm_attn_desc &d, int n_sm, int n_seq, long long n_tokens) {
+    WsLayout w;
+    size_t off = sizeof(WsHeader);
+    w.counters = off;
+    off = align_up(off + sizeof(int) * kDecodeMaxSeqPerLaunch * static_cast<size_t>(d.n_kv_head), 256);
+    w.partials = off;
+    off = align_up(off + sizeof(float) * kDecodePartialFloats * 2 * static_cast<size_t>(decode_max_ctas(n_sm)), 256);
+    w.seqs = off;
+    off = align_up(off + sizeof(SeqDev) * static_cast<size_t>(n_seq), 256);
+    w.q_stage = off;
+    off = align_up(off + sizeof(float) * static_cast<size_t>(n_tokens) * d.n_head * d.head_dim, 256);
+    w.total = off;
+    return w;
+}
+
+int device_sm_count(int *n_sm, int *major) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) {
+        fail_cuda(e, "cudaGetDevice");
+        return CGLM_ERR_NO_DEVICE;
+    }
+    cudaDeviceProp prop;
+    e = cudaGetDeviceProperties(&prop, dev);
+    if (e != cudaSuccess) {
+        fail_cuda(e, "cudaGetDeviceProperties");
+        return CGLM_ERR_NO_DEVICE;
+    }
+    *n_sm = prop.multiProcessorCount;
+    *major = prop.major;
+    return CGLM_OK;
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static bool tried = false;
+    if (!tried) {
+        tried = true;
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess) {
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+        }
+    }
+    return fn;
+}
+
+// K: f16 [n_slots*G][M][D=128] as a 3-D tensor, box 64 dims x 64 tokens; V^T: f16 [n_slots*G*D][M] as a
+// 2-D tensor, box 64 tokens x 128 dims.  Both 128-byte swizzled; tokens past M read as zero.
+bool build_tensor_maps(cglm_kv_arena *a) {
+    EncodeTiledFn enc = encode_tiled_fn();
+    if (!enc) return false;
+    const cglm_attn_desc &d = a->desc;
+    const cuuint64_t rows = static_cast<cuuint64_t>(a->n_slots) * d.n_kv_head;
+    {
+        cuuint64_t dims[3] = {static_cast<cuuint64_t>(d.head_dim), static_cast<cuuint64_t>(d.max_len), rows};
+        cuuint64_t strides[2] = {static_cast<cuuint64_t>(d.head_dim) * 2,
+                                 static_cast<cuuint64_t>(d.head_dim) * 2 * d.max_len};
+        cuuint32_t box[3] = {64, kDecodeTile, 1};
+        cuuint32_t estr[3] = {1, 1, 1};
+        if (enc(&a->k_map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, a->k_base, dims, strides, box, estr,
+                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+            return false;
+    }
+    {
+        cuuint64_t dims[2] = {static_cast<cuuint64_t>(d.max_len), rows * d.head_dim};
+        cuuint64_t strides[1] = {static_cast<cuuint64_t>(d.max_len) * 2};
+        cuuint32_t box[2] = {kDecodeTile, 128};
+        cuuint32_t estr[2] = {1, 1};
+        if (enc(&a->v_map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, a->v_base, dims, strides, box, estr,
+                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+            return false;
+    }
+    return true;
+}
+
+bool fast_decode_shape(const cglm_kv_arena *a) {
+    const cglm_attn_desc &d = a->desc;
+    return a->has_tmaps && d.head_dim == 128 && d.n_head / d.n_kv_head <= 16 && d.max_len % 8 == 0 &&
+           (d.rope_type == CGLM_ROPE_CHATGLM2 || d.rope_type == CGLM_ROPE_CHATGLM || d.rope_type == CGLM_ROPE_DISABLED);
+}
+
+__global__ void combine_kernel(const float *__restrict__ partials, int n_part, int H, int D, float *__restrict__ out) {
+    const int h = blockIdx.x;
+    float m_star = -INFINITY;
+    for (int p = 0; p < n_part; ++p) {
+        m_star = fmaxf(m_star, partials[(static_cast<long long>(p) * H + h) * (D + 2) + D]);
+    }
+    for (int d = threadIdx.x; d < D; d += blockDim.x) {
+        float acc = 0.f, den = 0.f;
+        for (int p = 0; p < n_part; ++p) {
+            const float *pp = partials + (static_cast<long long>(p) * H + h) * (D + 2);
+            const float m = pp[D];
+            const float w = m == -INFINITY ? 0.f : __expf(m - m_star);
+            acc += w * pp[d];
+            den += w * pp[D + 1];
+        }
+        out[static_cast<long long>(h) * D + d] = acc / den;
+    }
+}
+
+__global__ void load_prefix_kernel(const uint16_t *__restrict__ past_kv, uint16_t *__restrict__ k_slot,
+                                   uint16_t *__restrict__ v_slot, int G, int V, int D, int M) {
+    const long long n = static_cast<long long>(G) * V * D;
+    for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n;
+         i += static_cast<long long>(gridDim.x) * blockDim.x) {
+        const int d = static_cast<int>(i % D);
+        const int t = static_cast<int>((i / D) % V);
+        const int g = static_cast<int>(i / (static_cast<long long>(D) * V));
+        k_slot[(static_cast<long long>(g) * M + t) * D + d] = past_kv[i];
+        v_slot[(static_cast<long long>(g) * D + d) * M + t] = past_kv[n + i];
+    }
+}
+
+int ring_reserve(cglm_kv_arena *a, int n_seq, SeqDev **slot, cudaEvent_t *ev) {
+    if (n_seq > a->ring_cap) {
+        // grow: wait for every copy in flight, then reallocate
+        for (int i = 0; i < a->ring_slots; ++i) {
+            CGLM_CUDA(cudaEventSynchronize(a->ring_events[i]));
+        }
+        if (a->ring) CGLM_CUDA(cudaFreeHost(a->ring));
+        a->ring = nullptr;
+        int cap = a->ring_cap ? a->ring_cap : 64;
+        while (cap < n_seq) cap *= 2;
+        CGLM_CUDA(cudaHostAlloc(reinterpret_cast<void **>(&a->ring), sizeof(SeqDev) * cap * a->ring_slots,
+                                cudaHostAllocDefault));
+        a->ring_cap = cap;
+    }
+    const int i = a->ring_next;
+    a->ring_next = (i + 1) % a->ring_slots;
+    CGLM_CUDA(cudaEventSynchronize(a->ring_events[i]));   // the copy that last used this slot has run
+    *slot = a->ring + static_cast<size_t>(i) * a->ring_cap;
+    *ev = a->ring_events[i];
+    return CGLM_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+size_t cglm_kv_slot_bytes(const cglm_attn_desc *desc) {
+    if (!desc_ok(desc)) return 0;
+    return static_cast<size_t>(4) * desc->n_kv_head * desc->max_len * desc->head_dim;
+}
+
+int cglm_kv_arena_create(const cglm_attn_desc *desc, int n_slots, cglm_kv_arena **out) {
+    if (!desc_ok(desc) || n_slots <= 0 || !out) return CGLM_ERR_INVALID_ARG;
+    if (desc->head_dim > 256) return CGLM_ERR_UNSUPPORTED;
+    int n_sm = 0, major = 0;
+    int rc = device_sm_count(&n_sm, &major);
+    if (rc != CGLM_OK) return rc;
+    if (major < 10) {
+        std::snprintf(g_err, sizeof(g_err), "compute capability %d.x device: this library carries sm_100a code only", major);
+        return CGLM_ERR_NO_DEVICE;
+    }
+    cglm_kv_arena *a = new (std::nothrow) cglm_kv_arena();
+    if (!a) return CGLM_ERR_INVALID_ARG;
+    a->desc = *desc;
+    a->n_slots = n_slots;
+    a->n_sm = n_sm;
+    cudaGetDevice(&a->device);
+    a->k_slot_elems = static_cast<size_t>(desc->n_kv_head) * desc->max_len * desc->head_dim;
+    const size_t k_bytes = align_up(a->k_slot_elems * 2 * n_slots, 1024);
+    const size_t v_bytes = a->k_slot_elems * 2 * n_slots;
+    cudaError_t e = cudaMalloc(reinterpret_cast<void **>(&a->base), k_bytes + v_bytes);
+    if (e != cudaSuccess) {
+        delete a;
+        return fail_cuda(e, "cudaMalloc(kv arena)");
+    }
+    a->k_base = reinterpret_cast<uint16_t *>(a->base);
+    a->v_base = reinterpret_cast<uint16_t *>(a->base + k_bytes);
+    e = cudaMemset(a->base, 0, k_bytes + v_bytes);
+    if (e != cudaSuccess) {
+        cudaFree(a->base);
+        delete a;
+        return fail_cuda(e, "cudaMemset(kv arena)");
+    }
+    a->has_tmaps = desc->head_dim == 128 && desc->max_len % 8 == 0 && build_tensor_maps(a);
+    a->ring = nullptr;
+    a->ring_slots = 64;
+    a->ring_cap = 0;
+    a->ring_next = 0;
+    a->ring_events = new cudaEvent_t[a->ring_slots];
+    for (int i = 0; i < a->ring_slots; ++i) {
+        cudaEventCreateWithFlags(&a->ring_events[i], cudaEventDisableTiming);
+    }
+    *out = a;
+    return CGLM_OK;
+}
+
+int cglm_kv_arena_destroy(cglm_kv_arena *a) {
+    if (!a) return CGLM_ERR_INVALID_ARG;
+    cudaDeviceSynchronize();
+    for (int i = 0; i < a->ring_slots; ++i) cudaEventDestroy(a->ring_events[i]);
+    delete[] a->ring_events;
+    if (a->ring) cudaFreeHost(a->ring);
+    cudaFree(a->base);
+    delete a;
+    return CGLM_OK;
+}
+
+void *cglm_kv_arena_k_cache(const cglm_kv_arena *a, int slot) {
+    if (!a || slot < 0 || slot >= a->n_slots) return nullptr;
+    return a->k_base + a->k_slot_elems * slot;
+}
+void *cglm_kv_arena_v_cache(const cglm_kv_arena *a, int slot) {
+    if (!a || slot < 0 || slot >= a->n_slots) return nullptr;
+    return a->v_base + a->k_slot_elems * slot;
+}
+int cglm_kv_arena_n_slots(const cglm_kv_arena *a) { return a ? a->n_slots : 0; }
+const cglm_attn_desc *cglm_kv_arena_desc(const cglm_kv_arena *a) { return a ? &a->desc : nullptr; }
+
+int cglm_kv_slot_copy(cglm_kv_arena *a, int slot, void *k_host, void *v_host, int to_device, void *cuda_stream) {
+    if (!a || slot < 0 || slot >= a->n_slots) return CGLM_ERR_INVALID_ARG;
+    cudaStream_t st = static_cast<cudaStream_t>(cuda_stream);
+    const size_t bytes = a->k_slot_elems * 2;
+    void *kd = cglm_kv_arena_k_cache(a, slot), *vd = cglm_kv_arena_v_cache(a, slot);
+    if (k_host) {
+        CGLM_CUDA(to_device ? cudaMemcpyAsync(kd, k_host, bytes, cudaMemcpyHostToDevice, st)
+                            : cudaMemcpyAsync(k_host, kd, bytes, cudaMemcpyDeviceToHost, st));
+    }
+    if (v_host) {
+        CGLM_CUDA(to_device ? cudaMemcpyAsync(vd, v_host, bytes, cudaMemcpyHostToDevice, st)
+                            : cudaMemcpyAsync(v_host, vd, bytes, cudaMemcpyDeviceToHost, st));
+    }
+    return CGLM_OK;
+}
+
+size_t cglm_attn_workspace_bytes(const cglm_attn_desc *desc, int n_seq, int max_qlen) {
+    if (!desc_ok(desc) || n_seq <= 0 || max_qlen <= 0) return 0;
+    int n_sm = 148, major = 0;
+    device_sm_count(&n_sm, &major);   // falls back to a B200's SM count when no device is visible
+    return ws_layout(*desc, n_sm, n_seq, static_cast<long long>(n_seq) * max_qlen).total;
+}
+
+int cglm_attn_workspace_init(void *workspace, size_t workspace_bytes, void *cuda_stream) {
+    if (!workspace || workspace_bytes < sizeof(WsHeader)) return CGLM_ERR_WORKSPACE;
+    cudaStream_t st = static_cast<cudaStream_t>(cuda_stream);
+    CGLM_CUDA(cudaMemsetAsync(workspace, 0, workspace_bytes, st));
+    const unsigned int magic = kWsMagic;
+    CGLM_CUDA(cudaMemcpyAsync(workspace, &magic, sizeof(magic), cudaMemcpyHostToDevice, st));
+    return CGLM_OK;
+}
+
+int cglm_attn_workspace_status(void *workspace, void *cuda_stream) {
+    if (!workspace) return CGLM_ERR_WORKSPACE;
+    cudaStream_t st = static_cast<cudaStream_t>(cuda_stream);
+    WsHeader h;
+    CGLM_CUDA(cudaMemcpyAsync(&h, workspace, sizeof(int) * 2, cudaMemcpyDeviceToHost, st));
+    CGLM_CUDA(cudaStreamSynchronize(st));
+    if (h.magic != kWsMagic) return CGLM_ERR_WORKSPACE;
+    if (h.status != 0) {
+        const int zero = 0;
+        CGLM_CUDA(cudaMemcpyAsync(&static_cast<WsHeader *>(workspace)->status, &zero, sizeof(int),
+                                  cudaMemcpyHostToDevice, st));
+        CGLM_CUDA(cudaStreamSynchronize(st));
+    }
+    return h.status;
+}
+
+int cglm_attn_forward(cglm_kv_arena *a, const cglm_attn_seq *seqs, int n_seq, void *workspace,
+                      size_t workspace_bytes, void *cuda_stream) {
+    if (!a || !seqs || n_seq <= 0) return CGLM_ERR_INVALID_ARG;
+    if (!workspace) return CGLM_ERR_WORKSPACE;
+    const cglm_attn_desc &d = a->desc;
+    cudaStream_t st = static_cast<cudaStream_t>(cuda_stream);
+    const bool fast_ok = fast_decode_shape(a);
+
+    // ---- validate and classify ---------------------------------------------------------------------------
+    long long gen_tokens = 0, decode_tiles = 0;
+    int n_fast = 0;
+    std::vector<unsigned char> is_fast(n_seq);
+    for (int i = 0; i < n_seq; ++i) {
+        const cglm_attn_seq &s = seqs[i];
+        if (!s.q || !s.k || !s.v || s.qlen <= 0 || s.n_past < 0 || s.slot < 0 || s.slot >= a->n_slots)
+            return CGLM_ERR_INVALID_ARG;
+        if (s.qlen > 1 && s.n_past != 0) return CGLM_ERR_INVALID_ARG;   // chatglm.cpp:689 masks only at n_past == 0
+        const bool partial = (s.flags & CGLM_SEQ_PARTIAL) != 0;
+        if (partial ? !s.partial : !s.out) return CGLM_ERR_INVALID_ARG;
+        if ((s.flags & CGLM_SEQ_NO_APPEND) && (!partial || s.qlen != 1)) return CGLM_ERR_INVALID_ARG;
+        if ((s.flags & CGLM_SEQ_USE_KV_LOCAL) && (s.kv_local < 0 || s.qlen != 1)) return CGLM_ERR_INVALID_ARG;
+        const int kv_before = (s.flags & CGLM_SEQ_USE_KV_LOCAL) ? s.kv_local : d.n_virtual + s.n_past;
+        const int appended = (s.flags & CGLM_SEQ_NO_APPEND) ? 0 : s.qlen;
+        if (static_cast<long long>(kv_before) + appended > d.max_len) return CGLM_ERR_INVALID_ARG;
+        if (d.rope_type == CGLM_ROPE_CHATGLM && !s.position_ids && s.n_ctx < 2) return CGLM_ERR_INVALID_ARG;
+        const int L = kv_before + appended;
+        is_fast[i] = fast_ok && s.qlen == 1 && L >= 1;
+        if (is_fast[i]) {
+            ++n_fast;
+            decode_tiles += static_cast<long long>((L + kDecodeTile - 1) / kDecodeTile) * d.n_kv_head;
+        } else {
+            gen_tokens += s.qlen;
+        }
+    }
+    const WsLayout lay = ws_layout(d, a->n_sm, n_seq, gen_tokens);
+    if (workspace_bytes < lay.total) return CGLM_ERR_WORKSPACE;
+
+    // ---- descriptors: fast-decode sequences first, then the generic ones -----------------------------------
+    std::lock_guard<std::mutex> lock(a->mu);
+    SeqDev *host = nullptr;
+    cudaEvent_t ev;
+    int rc = ring_reserve(a, n_seq, &host, &ev);
+    if (rc != CGLM_OK) return rc;
+    int fi = 0, gi = n_fast, tok = 0;
+    for (int i = 0; i < n_seq; ++i) {
+        const cglm_attn_seq &s = seqs[i];
+        SeqDev &o = host[is_fast[i] ? fi++ : gi++];
+        o.q = s.q; o.k = s.k; o.v = s.v;
+        o.q_tok_stride = s.q_tok_stride; o.q_head_stride = s.q_head_stride;
+        o.kv_tok_stride = s.kv_tok_stride; o.kv_head_stride = s.kv_head_stride;
+        o.position_ids = s.position_ids;
+        o.out = s.out; o.q_roped = s.q_roped; o.k_roped = s.k_roped; o.partial = s.partial;
+        o.slot = s.slot; o.qlen = s.qlen; o.n_past = s.n_past; o.n_ctx = s.n_ctx;
+        o.kv_before = (s.flags & CGLM_SEQ_USE_KV_LOCAL) ? s.kv_local : d.n_virtual + s.n_past;
+        o.flags = s.flags;
+        o.tok_begin = 0;
+        o.pad = 0;
+        if (!is_fast[i]) {
+            o.tok_begin = tok;
+            tok += s.qlen;
+        }
+    }
+    uint8_t *ws = static_cast<uint8_t *>(workspace);
+    SeqDev *seqs_dev = reinterpret_cast<SeqDev *>(ws + lay.seqs);
+    CGLM_CUDA(cudaMemcpyAsync(seqs_dev, host, sizeof(SeqDev) * n_seq, cudaMemcpyHostToDevice, st));
+    CGLM_CUDA(cudaEventRecord(ev, st));
+
+    LaunchCtx cx;
+    cx.shape = make_shape(d);
+    cx.k_base = a->k_base;
+    cx.v_base = a->v_base;
+    cx.hdr = reinterpret_cast<WsHeader *>(ws);
+    cx.counters = reinterpret_cast<int *>(ws + lay.counters);
+    cx.partials = reinterpret_cast<float *>(ws + lay.partials);
+    cx.q_stage = reinterpret_cast<float *>(ws + lay.q_stage);
+    cx.k_map = &a->k_map;
+    cx.v_map = &a->v_map;
+    cx.stream = st;
+    cx.n_sm = a->n_sm;
+
+    // the decode kernel keeps a per-launch table of kDecodeMaxSeqPerLaunch sequences
+    for (int begin = 0; begin < n_fast; begin += kDecodeMaxSeqPerLaunch) {
+        const int cnt = n_fast - begin < kDecodeMaxSeqPerLaunch ? n_fast - begin : kDecodeMaxSeqPerLaunch;
+        long long tiles = 0;
+        for (int i = begin; i < begin + cnt; ++i) {
+            const int L = host[i].kv_before + ((host[i].flags & CGLM_SEQ_NO_APPEND) ? 0 : 1);
+            tiles += static_cast<long long>((L + kDecodeTile - 1) / kDecodeTile) * d.n_kv_head;
+        }
+        CGLM_CUDA(launch_decode(cx, seqs_dev + begin, cnt, tiles));
+    }
+    if (n_seq - n_fast > 0) {
+        CGLM_CUDA(launch_generic(cx, seqs_dev + n_fast, n_seq - n_fast, static_cast<int>(gen_tokens)));
+    }
+    (void)decode_tiles;
+    return CGLM_OK;
+}
+
+int cglm_attn_forward_host(cglm_kv_arena *a, const cglm_attn_seq *seqs, int n_seq, int interleaved_qkv,
+                           const float *qkv_host, float *out_host, float *dev_qkv, float *dev_out, void *workspace,
+                           size_t workspace_bytes, void *cuda_stream) {
+    if (!a || !seqs || n_seq <= 0 || !qkv_host || !out_host || !dev_qkv || !dev_out) return CGLM_ERR_INVALID_ARG;
+    const cglm_attn_desc &d = a->desc;
+    if (interleaved_qkv && d.n_head != d.n_kv_head) return CGLM_ERR_INVALID_ARG;   // chatglm.cpp:637
+    cudaStream_t st = static_cast<cudaStream_t>(cuda_stream);
+    const long long H = d.n_head, G = d.n_kv_head, D = d.head_dim;
+    const long long row = (H + 2 * G) * D, orow = H * D;
+    long long n_tok = 0;
+    std::vector<cglm_attn_seq> dev_seqs(seqs, seqs + n_seq);
+    for (int i = 0; i < n_seq; ++i) {
+        if (seqs[i].qlen <= 0) return CGLM_ERR_INVALID_ARG;
+        cglm_attn_seq &s = dev_seqs[i];
+        const float *base = dev_qkv + n_tok * row;
+        s.q = base;
+        if (interleaved_qkv) {   // chatglm.cpp:638-644
+            s.k = base + D; s.v = base + 2 * D;
+            s.q_head_stride = s.kv_head_stride = 3 * D;
+        } else {                 // chatglm.cpp:646-652
+            s.k = base + H * D; s.v = base + (H + G) * D;
+            s.q_head_stride = s.kv_head_stride = D;
+        }
+        s.q_tok_stride = s.kv_tok_stride = row;
+        s.out = dev_out + n_tok * orow;
+        s.position_ids = nullptr; s.q_roped = nullptr; s.k_roped = nullptr; s.partial = nullptr;
+        s.flags = 0; s.kv_local = 0;
+        n_tok += seqs[i].qlen;
+    }
+    CGLM_CUDA(cudaMemcpyAsync(dev_qkv, qkv_host, sizeof(float) * n_tok * row, cudaMemcpyHostToDevice, st));
+    const int rc = cglm_attn_forward(a, dev_seqs.data(), n_seq, workspace, workspace_bytes, cuda_stream);
+    if (rc != CGLM_OK) return rc;
+    CGLM_CUDA(cudaMemcpyAsync(out_host, dev_out, sizeof(float) * n_tok * orow, cudaMemcpyDeviceToHost, st));
+    return CGLM_OK;
+}
+
+int cglm_attn_splitkv_combine(const float *partials, int n_part, int n_head, int head_dim, float *out,
+                              void *cuda_stream) {
+    if (!partials || !out || n_part <= 0 || n_head <= 0 || head_dim <= 0) return CGLM_ERR_INVALID_ARG;
+    combine_kernel<<<n_head, 128, 0, static_cast<cudaStream_t>(cuda_stream)>>>(partials, n_part, n_head, head_dim, out);
+    g_launch_count += 1;
+    CGLM_CUDA(cudaGetLastError());
+    return CGLM_OK;
+}
+
+int cglm_kv_load_prefix(cglm_kv_arena *a, int slot, const void *past_kv, void *cuda_stream) {
+    if (!a || !past_kv || slot < 0 || slot >= a->n_slots) return CGLM_ERR_INVALID_ARG;
+    const cglm_attn_desc &d = a->desc;
+    if (d.n_virtual == 0) return CGLM_OK;
+    const long long n = static_cast<long long>(d.n_kv_head) * d.n_virtual * d.head_dim;
+    const int blocks = static_cast<int>((n + 255) / 256 < 1024 ? (n + 255) / 256 : 1024);
+    load_prefix_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(cuda_stream)>>>(
+        static_cast<const uint16_t *>(past_kv), static_cast<uint16_t *>(cglm_kv_arena_k_cache(a, slot)),
+        static_cast<uint16_t *>(cglm_kv_arena_v_cache(a, slot)), d.n_kv_head, d.n_virtual, d.head_dim, d.max_len);
+    g_launch_count += 1;
+    CGLM_CUDA(cudaGetLastError());
+    return CGLM_OK;
+}
+
+const char *cglm_status_string(int status) {
+    switch (status) {
+    case CGLM_OK: return "ok";
+    case CGLM_ERR_INVALID_ARG: return "invalid argument";
+    case CGLM_ERR_CUDA: return "CUDA call failed";
+    case CGLM_ERR_WORKSPACE: return "workspace missing, too small or not initialised";
+    case CGLM_ERR_UNSUPPORTED: return "shape not supported";
+    case CGLM_ERR_TIMEOUT: return "device-side wait timed out";
+    case CGLM_ERR_NO_DEVICE: return "no usable CUDA device (sm_100a required)";
+    default: return "unknown status";
+    }
+}
+
+const char *cglm_last_error_string(void) { return g_err; }
+
+unsigned long long cglm_launch_count(void) { return g_launch_count; }
+
+}  // extern "C"

@@ -1,0 +1,250 @@
+// Shared device-side declarations of the attention KV-cache kernels (sm_100a).
+#pragma once
+
+#include <cuda.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/cglm_attn.h"
+
+namespace cglm {
+
+// ---- workspace layout -------------------------------------------------------------------------------
+// [0, 256)            control block (WsHeader)
+// [256, ...)          item counters (int per (sequence, kv head)), partial slots, device copies of the
+//                     sequence descriptors, roped/scaled q staging for the generic and prefill paths
+struct WsHeader {
+    unsigned int magic;   // kWsMagic once cglm_attn_workspace_init ran
+    int status;           // sticky device-side status (0 or CGLM_ERR_*)
+    int reserved[62];
+};
+static_assert(sizeof(WsHeader) == 256, "control block is 256 bytes");
+constexpr unsigned int kWsMagic = 0x43474c4du;  // "CGLM"
+
+// Device-side copy of one cglm_attn_seq with everything resolved that the kernels would otherwise
+// re-derive: cache row of the first kv head, attended length, rope positions.
+struct SeqDev {
+    const float *q, *k, *v;
+    long long q_tok_stride, q_head_stride, kv_tok_stride, kv_head_stride;
+    const int *position_ids;
+    float *out;
+    float *q_roped;
+    float *k_roped;
+    float *partial;
+    int slot;
+    int qlen;
+    int n_past;
+    int n_ctx;
+    int kv_before;   // cached tokens attended besides the ones appended now (n_virtual + n_past, or kv_local)
+    int flags;
+    int tok_begin;   // first row of this sequence in the staging buffers of the generic path
+    int pad;
+};
+
+struct AttnShape {
+    int H, G, D, R;       // heads, kv heads, head dim, H / G
+    int M, V;             // cache capacity in tokens, virtual tokens
+    int rope_type;
+    int mask_type;
+    float theta_scale;    // powf(base, -2 / n_dims) computed on the host with the C library's powf
+    float scale;          // 1 / sqrtf(D)
+};
+
+// ---- bounded waiting --------------------------------------------------------------------------------
+// Every device-side wait in this library gives up after kSpinLimit polls, records CGLM_ERR_TIMEOUT in the
+// workspace status word and lets the kernel run to its end with invalid results instead of hanging.
+constexpr unsigned int kSpinLimit = 1u << 22;
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) {
+    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+__device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void fence_mbar_init() {
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void fence_proxy_async() {
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t *bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
+                 : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Returns false when the wait ran out (or an earlier wait of this CTA did): the caller carries on
+// without touching the barrier again.  *abort_flag lives in shared memory.
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t *bar, uint32_t parity, volatile int *abort_flag) {
+    if (*abort_flag) {
+        return false;
+    }
+    for (unsigned int i = 0; i < kSpinLimit; ++i) {
+        if (mbar_try_wait(bar, parity)) {
+            return true;
+        }
+        if ((i & 1023u) == 1023u && *abort_flag) {
+            return false;
+        }
+    }
+    *abort_flag = 1;
+    return false;
+}
+
+// ---- TMA (non-multicast tiled loads from this GPU's memory) -----------------------------------------
+__device__ __forceinline__ void tma_load_2d(void *dst, const CUtensorMap *map, int c0, int c1, uint64_t *bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(smem_u32(dst)), "l"(map), "r"(c0), "r"(c1), "r"(smem_u32(bar))
+        : "memory");
+}
+__device__ __forceinline__ void tma_load_3d(void *dst, const CUtensorMap *map, int c0, int c1, int c2,
+                                            uint64_t *bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+        ::"r"(smem_u32(dst)), "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(smem_u32(bar))
+        : "memory");
+}
+__device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap *map) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
+}
+
+// ---- warp-level tensor-core pieces for the decode kernel ---------------------------------------------
+__device__ __forceinline__ void ldmatrix_x4(uint32_t &r0, uint32_t &r1, uint32_t &r2, uint32_t &r3, uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+                 : "r"(addr));
+}
+__device__ __forceinline__ void mma_m16n8k16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+        "{%0, %1, %2, %3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ float ex2_approx(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {
+    __half2 h = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<uint32_t *>(&h);
+}
+__device__ __forceinline__ void named_bar_sync(int id, int n_threads) {
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(n_threads) : "memory");
+}
+
+// ---- RoPE pieces shared by every kernel --------------------------------------------------------------
+// Angle i of a position: theta_0 = pos, theta_{j+1} = theta_j * theta_scale, each product rounded to f32
+// (the iterated ladder of ggml's rope cache).  cos/sin are taken in double and rounded once, which
+// reproduces a correctly rounded f32 cosf/sinf in all but near-tie cases.
+__device__ __forceinline__ void rope_cos_sin(int pos, int i, float theta_scale, float &c, float &s) {
+    float theta = static_cast<float>(pos);
+    for (int j = 0; j < i; ++j) {
+        theta = __fmul_rn(theta, theta_scale);
+    }
+    double sd, cd;
+    sincos(static_cast<double>(theta), &sd, &cd);
+    c = static_cast<float>(cd);
+    s = static_cast<float>(sd);
+}
+// The rotation keeps four products and two sums separately rounded (no FMA contraction), like the
+// host oracle built with -ffp-contract=off.
+__device__ __forceinline__ void rope_rotate(float x0, float x1, float c, float s, float &y0, float &y1) {
+    y0 = __fsub_rn(__fmul_rn(x0, c), __fmul_rn(x1, s));
+    y1 = __fadd_rn(__fmul_rn(x0, s), __fmul_rn(x1, c));
+}
+
+// Index bookkeeping of one rope mode: how many rotated pairs a head has, which two elements pair i
+// touches, and which (position stream, ladder index) drives it.
+struct RopePair {
+    int i0, i1;     // element indices inside the head
+    int stream;     // 0: position id, 1: block position id (CGLM_ROPE_CHATGLM only)
+    int ladder;     // index into the angle ladder
+};
+__device__ __forceinline__ int rope_n_pairs(int rope_type, int D) {
+    switch (rope_type) {
+    case CGLM_ROPE_GPTJ:
+    case CGLM_ROPE_NEOX:
+    case CGLM_ROPE_CHATGLM: return D / 2;
+    case CGLM_ROPE_CHATGLM2: return D / 4;
+    default: return 0;
+    }
+}
+// n_dims handed to ggml's rope for each mode: D for the basic modes, D/2 for both GLM modes.
+__host__ __device__ __forceinline__ int rope_n_dims(int rope_type, int D) {
+    return (rope_type == CGLM_ROPE_GPTJ || rope_type == CGLM_ROPE_NEOX) ? D : D / 2;
+}
+__device__ __forceinline__ RopePair rope_pair(int rope_type, int D, int p) {
+    RopePair r;
+    switch (rope_type) {
+    case CGLM_ROPE_GPTJ:      // adjacent pairs over the whole head
+    case CGLM_ROPE_CHATGLM2:  // adjacent pairs over the first half
+        r.i0 = 2 * p; r.i1 = 2 * p + 1; r.stream = 0; r.ladder = p; break;
+    case CGLM_ROPE_NEOX:      // (p, p + D/2)
+        r.i0 = p; r.i1 = p + D / 2; r.stream = 0; r.ladder = p; break;
+    default: {                // CGLM_ROPE_CHATGLM: halves of D/2, pairs (i, i + D/4) inside each
+        const int q = D / 4, half = p / q, i = p % q;
+        r.i0 = half * (D / 2) + i; r.i1 = r.i0 + q; r.stream = half; r.ladder = i; break;
+    }
+    }
+    return r;
+}
+// Position ids of token s of a sequence when the caller passed none (chatglm.cpp:1142-1153, 1319-1327).
+__device__ __forceinline__ void derive_positions(const SeqDev &sq, int rope_type, int s, int &pos, int &block) {
+    const int p = sq.n_past + s;
+    if (sq.position_ids) {
+        pos = sq.position_ids[s];
+        block = rope_type == CGLM_ROPE_CHATGLM ? sq.position_ids[sq.qlen + s] : 0;
+    } else if (rope_type == CGLM_ROPE_CHATGLM) {
+        pos = min(p, sq.n_ctx - 2);
+        block = max(p - (sq.n_ctx - 2), 0);
+    } else {
+        pos = p;
+        block = 0;
+    }
+}
+
+// ---- launchers implemented in the kernel translation units ------------------------------------------
+struct LaunchCtx {
+    AttnShape shape;
+    uint16_t *k_base;            // arena K slabs: f16 [n_slots*G][M][D]
+    uint16_t *v_base;            // arena V slabs: f16 [n_slots*G*D][M]
+    WsHeader *hdr;
+    int *counters;               // one per (sequence, kv head) of the decode list, zero between launches
+    float *partials;             // decode split partials: 2 slots per CTA
+    float *q_stage;              // generic path: roped, scaled q f32 [tokens][H][D]
+    const CUtensorMap *k_map;    // host copies of the arena's tensor maps (passed by value to kernels)
+    const CUtensorMap *v_map;
+    cudaStream_t stream;
+    int n_sm;
+};
+
+// generic path (any head_dim <= 256, any cache capacity, prefill and decode, every rope and mask mode);
+// seqs_dev[i].tok_begin indexes q_stage, total_tokens = sum of qlen
+cudaError_t launch_generic(const LaunchCtx &cx, const SeqDev *seqs_dev, int n_seq, int total_tokens);
+// fused rope + append + split-KV decode (head_dim 128, <= 16 q heads per kv head, capacity % 8 == 0)
+cudaError_t launch_decode(const LaunchCtx &cx, const SeqDev *seqs_dev, int n_seq, long long total_tiles);
+constexpr int kDecodeTile = 64;   // tokens per TMA tile of the decode kernel
+int decode_max_ctas(int n_sm);
+constexpr int kDecodeMaxSeqPerLaunch = 256;   // sized so that two decode CTAs fit the shared memory of one SM
+constexpr int kDecodePartialFloats = 16 * 128 + 32;   // acc[16][128] | m[16] | l[16]
+
+extern unsigned long long g_launch_count;
+
+}  // namespace cglm

@@ -1,0 +1,170 @@
+/*
+ * cglm_attn.h -- C ABI of the B200 (sm_100a) attention KV-cache path.
+ *
+ * The library replaces what chatglm::BasicAttention::forward records between its two Linears
+ * (li-plus/chatglm.cpp, chatglm.cpp:636-717): qkv split views, RoPE on q and k, the f16 append of K
+ * into k_cache [kv_heads, max_len, head_dim] and of V into the transposed v_cache
+ * [kv_heads, head_dim, max_len] at n_past, and scaled-dot-product attention over the cache.
+ *
+ * Conventions
+ *  - every entry point returns CGLM_OK (0) or a negative CGLM_ERR_*; nothing throws, aborts or waits
+ *    without a bound; work is enqueued on the given CUDA stream and the host never synchronises
+ *    unless the function says so;
+ *  - there is no CPU fallback: without a usable CUDA device every compute entry point fails;
+ *  - pointers named *_host are host memory, all others are device memory;
+ *  - strides are in elements, not bytes.
+ */
+#ifndef CGLM_ATTN_H
+#define CGLM_ATTN_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum {
+    CGLM_OK = 0,
+    CGLM_ERR_INVALID_ARG = -1,   /* bad shape, null pointer, n_past + qlen beyond the cache ... */
+    CGLM_ERR_CUDA = -2,          /* a CUDA runtime/driver call failed; see cglm_last_error_string */
+    CGLM_ERR_WORKSPACE = -3,     /* workspace missing, too small or not initialised */
+    CGLM_ERR_UNSUPPORTED = -4,   /* shape outside what the kernels cover (head_dim > 256, ...) */
+    CGLM_ERR_TIMEOUT = -5,       /* a bounded device-side wait ran out; results of that call are invalid */
+    CGLM_ERR_NO_DEVICE = -6      /* no CUDA device / wrong architecture */
+};
+
+/* values of chatglm::RopeType (chatglm.h:93-99) */
+enum {
+    CGLM_ROPE_GPTJ = 0,       /* full head, adjacent pairs      (apply_rotary_emb_basic, chatglm.cpp:523-537) */
+    CGLM_ROPE_NEOX = 2,       /* full head, split-half pairs    (apply_rotary_emb_basic) */
+    CGLM_ROPE_CHATGLM = 4,    /* 2-D: position / block position (apply_rotary_emb_glm,  chatglm.cpp:539-574) */
+    CGLM_ROPE_CHATGLM2 = 8,   /* first half of the head, adjacent pairs (apply_rotary_emb_glm2, chatglm.cpp:576-601) */
+    CGLM_ROPE_DISABLED = 10000
+};
+
+/* values of chatglm::AttentionMaskType (chatglm.h:101-104) */
+enum {
+    CGLM_MASK_CAUSAL = 0,     /* ggml_diag_mask_inf at n_past == 0 (chatglm.cpp:696-697) */
+    CGLM_MASK_CHATGLM = 1     /* prefix-bidirectional: scores[:, :-1, -1] = -inf at n_past == 0 (chatglm.cpp:1126-1140) */
+};
+
+/* What the BasicAttention constructor fixes per model (chatglm.h:443-455). */
+typedef struct cglm_attn_desc {
+    int n_head;        /* num_attention_heads */
+    int n_kv_head;     /* num_key_value_heads */
+    int head_dim;      /* hidden_size / num_attention_heads */
+    int max_len;       /* cache capacity in tokens = max_length + num_virtual_tokens */
+    int n_virtual;     /* num_virtual_tokens (P-Tuning v2 prefix held in cache slots [0, n_virtual)) */
+    int rope_type;     /* CGLM_ROPE_* */
+    float rope_theta;
+    int mask_type;     /* CGLM_MASK_* */
+} cglm_attn_desc;
+
+/*
+ * KV arena: one device allocation holding the k_cache / v_cache pairs ("slots") of every layer and
+ * every sequence, the counterpart of ModelContext::ctx_kv + buf_kv (chatglm.h:337,345,627-628).
+ * Slot s holds k_cache f16 [n_kv_head][max_len][head_dim] and v_cache f16 [n_kv_head][head_dim][max_len],
+ * exactly the two tensors BasicAttention owns (chatglm.h:452-455,470-471).  All K slabs are contiguous,
+ * then all V slabs, so that two TMA tensor maps cover the whole arena.
+ */
+typedef struct cglm_kv_arena cglm_kv_arena;
+
+/* Allocates and zero-fills the arena on the current CUDA device.  Synchronous. */
+int cglm_kv_arena_create(const cglm_attn_desc *desc, int n_slots, cglm_kv_arena **out);
+int cglm_kv_arena_destroy(cglm_kv_arena *arena);
+/* Device pointers of one slot's tensors (the public k_cache / v_cache members, chatglm.h:470-471). */
+void *cglm_kv_arena_k_cache(const cglm_kv_arena *arena, int slot);
+void *cglm_kv_arena_v_cache(const cglm_kv_arena *arena, int slot);
+int cglm_kv_arena_n_slots(const cglm_kv_arena *arena);
+const cglm_attn_desc *cglm_kv_arena_desc(const cglm_kv_arena *arena);
+/* Bytes of one slot (k_cache + v_cache). */
+size_t cglm_kv_slot_bytes(const cglm_attn_desc *desc);
+/* Whole-slot copies between host and device, the counterpart of ggml_backend_tensor_set/get on the cache
+ * tensors (e.g. chatglm.h:588).  k_host: f16 [n_kv_head][max_len][head_dim]; v_host: f16
+ * [n_kv_head][head_dim][max_len]; either may be NULL.  to_device != 0 uploads.  Asynchronous on cuda_stream. */
+int cglm_kv_slot_copy(cglm_kv_arena *arena, int slot, void *k_host, void *v_host, int to_device,
+                      void *cuda_stream);
+
+/*
+ * One BasicAttention::forward call for one sequence (chatglm.cpp:620-721 minus the two Linears).
+ * q/k/v point into the fused qkv activation; the (token, head) strides express both layouts of
+ * chatglm.cpp:636-653 without a copy:
+ *   blocked     (ChatGLM2/3/4): q = qkv, k = qkv + H*D, v = qkv + (H+G)*D, tok_stride = (H+2G)*D, head_stride = D
+ *   interleaved (ChatGLM-6B v1): q = qkv, k = qkv + D,  v = qkv + 2*D,     tok_stride = 3*H*D,    head_stride = 3*D
+ */
+typedef struct cglm_attn_seq {
+    const float *q, *k, *v;           /* f32 [qlen][heads][head_dim] through the strides below */
+    long long q_tok_stride, q_head_stride;
+    long long kv_tok_stride, kv_head_stride;
+    int slot;                         /* which cache pair of the arena */
+    int qlen;                         /* tokens in this call; > 1 only with n_past == 0 (chatglm.cpp:689) */
+    int n_past;
+    int n_ctx;                        /* prompt length; only CGLM_ROPE_CHATGLM derives ids from it (chatglm.cpp:1147-1151) */
+    const int *position_ids;          /* optional [qlen] (or [2*qlen] for CGLM_ROPE_CHATGLM); NULL: derived from n_past, n_ctx */
+    float *out;                       /* context_layer f32 [qlen][n_head*head_dim] (chatglm.cpp:716-717) */
+    float *q_roped;                   /* optional f32 [qlen][n_head][head_dim]: q after RoPE, before the 1/sqrt(d) scale */
+    float *k_roped;                   /* optional f32 [qlen][n_kv_head][head_dim]: k after RoPE (the reference ropes in place) */
+    /* split-KV use only (zero otherwise) */
+    int kv_local;                     /* >0: tokens of this sequence present in this arena slot before the call */
+    int flags;                        /* CGLM_SEQ_* */
+    float *partial;                   /* with CGLM_SEQ_PARTIAL: f32 [n_head][head_dim+2] = acc | m | l instead of out */
+} cglm_attn_seq;
+
+enum {
+    CGLM_SEQ_NO_APPEND = 1,   /* this rank does not own position n_past: attend only */
+    CGLM_SEQ_PARTIAL = 2,     /* emit un-normalised (acc, m, l) into .partial; .out is not written */
+    CGLM_SEQ_USE_KV_LOCAL = 4 /* attend over kv_local cached tokens (+ the appended one) instead of n_virtual + n_past */
+};
+
+/* Scratch the kernels need for n_seq sequences per call with at most max_qlen tokens each. */
+size_t cglm_attn_workspace_bytes(const cglm_attn_desc *desc, int n_seq, int max_qlen);
+/* Zeroes the control words of a workspace.  Call once before first use and after any CGLM_ERR_TIMEOUT. */
+int cglm_attn_workspace_init(void *workspace, size_t workspace_bytes, void *cuda_stream);
+/* Synchronises the stream, returns the device-side status accumulated since the last query, clears it. */
+int cglm_attn_workspace_status(void *workspace, void *cuda_stream);
+
+/*
+ * RoPE(q,k) -> f16 append -> attention for n_seq independent sequences (host array of descriptors).
+ * Replaces the graph nodes of chatglm.cpp:636-717.  Decode (qlen 1) and prefill (n_past 0) may be mixed.
+ * Asynchronous on cuda_stream.
+ */
+int cglm_attn_forward(cglm_kv_arena *arena, const cglm_attn_seq *seqs, int n_seq, void *workspace,
+                      size_t workspace_bytes, void *cuda_stream);
+
+/*
+ * The same call for callers whose activations live in host memory, as ggml_backend_tensor_set /
+ * ggml_backend_tensor_get move them in the reference (chatglm.cpp:743, 764): copies the fused qkv rows
+ * host->device, runs cglm_attn_forward, copies context_layer device->host, all on cuda_stream.
+ *   qkv_host  f32 [n_tokens][(H+2G)*D], the rows of all sequences back to back (sequence i owns rows
+ *             [tok_begin_i, tok_begin_i + qlen_i)); out_host f32 [n_tokens][H*D].
+ * interleaved_qkv selects the v1 layout.  dev_qkv / dev_out are device staging buffers of at least those sizes.
+ * Only n_past / qlen / n_ctx / slot of each descriptor are read.  Asynchronous: out_host is valid after the
+ * stream is synchronised; use pinned host memory for truly asynchronous copies.
+ */
+int cglm_attn_forward_host(cglm_kv_arena *arena, const cglm_attn_seq *seqs, int n_seq, int interleaved_qkv,
+                           const float *qkv_host, float *out_host, float *dev_qkv, float *dev_out,
+                           void *workspace, size_t workspace_bytes, void *cuda_stream);
+
+/*
+ * Split-KV combine: log-sum-exp merge of n_part partials of one query token, each laid out
+ * f32 [n_head][head_dim+2] (acc | m | l), all in this GPU's memory -> out f32 [n_head*head_dim].
+ * The per-GPU partials come from cglm_attn_forward with CGLM_SEQ_PARTIAL.
+ */
+int cglm_attn_splitkv_combine(const float *partials, int n_part, int n_head, int head_dim, float *out,
+                              void *cuda_stream);
+
+/* P-Tuning v2 prefix load for one slot (BasicModel::load_prefix_cache, chatglm.h:580-615):
+ * past_kv f16 [2][n_kv_head][n_virtual][head_dim] (device) -> cache positions [0, n_virtual), V transposed. */
+int cglm_kv_load_prefix(cglm_kv_arena *arena, int slot, const void *past_kv, void *cuda_stream);
+
+const char *cglm_status_string(int status);
+/* Text of the last CUDA error seen by this thread inside the library ("" if none). */
+const char *cglm_last_error_string(void);
+/* Number of kernels the library launched since load (all threads); for launch accounting in benchmarks. */
+unsigned long long cglm_launch_count(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* CGLM_ATTN_H */

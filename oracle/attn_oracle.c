@@ -130,8 +130,11 @@ static void rope_cache(const oracle_cfg *cfg, int pos, int n_dims, float base, f
         if (cfg->num.theta_powf) {
             t = (float)pos * powf(base, -(float)i0 / (float)n_dims);
         }
-        cs[i0] = cosf(t);
-        cs[i0 + 1] = sinf(t);
+        /* cosf/sinf taken as the correctly rounded values (evaluated in double, rounded once), so that the
+         * pin does not hang on one C library's last-bit behaviour: libm float versions differ by an ulp
+         * between platforms, and an ulp in cos is unbounded in ulps of x0*cos - x1*sin under cancellation. */
+        cs[i0] = (float)cos((double)t);
+        cs[i0 + 1] = (float)sin((double)t);
         theta *= theta_scale;
     }
 }

@@ -1,0 +1,277 @@
+"""GPU parity: the CUDA path through the C ABI against the CPU oracle and the committed golden vectors."""
+import ctypes as C
+
+import numpy as np
+import pytest
+import torch
+
+from golden_util import GOLDEN_ATOL, MODEL_FIXTURES, load_fixture, model_output, steps
+from gpu_util import (OUT_ATOL, ROPE_MAX_ULP, assert_out_close, download_cache, make_desc, oracle_cfg, qkv_width,
+                      random_cache, run_decode_batch, ulp_distance, upload_cache)
+from oracle import attn_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+
+def _A():
+    from chatglm_cpp_b200 import attention as A
+    return A
+
+
+@pytest.mark.parametrize("name", MODEL_FIXTURES)
+def test_reference_fixture_through_cuda(name):
+    """The reference's own golden vectors (prefill 3, decode, decode; chatglm_test.cpp:329-361), CUDA attention."""
+    A = _A()
+    z, meta, w = load_fixture(name)
+    desc = make_desc(meta["n_head"], meta["n_kv_head"], meta["head_dim"], meta["max_length"] + meta["n_virtual"],
+                     meta["n_virtual"], meta["rope_type"], meta["rope_theta"], meta["mask_type"])
+    arena, ws = A.KVArena(desc, 1), A.Workspace(desc, 1, 8)
+    attn = A.BasicAttention(arena, 0, ws, meta["interleaved_qkv"])
+    cfg = oracle_cfg(desc)
+    kc, vc = O.new_caches(cfg)
+    if meta["n_virtual"]:
+        arena.load_prefix(0, torch.from_numpy(z["prefix"]).cuda())
+        O.load_prefix_cache(cfg, z["prefix"], kc, vc)
+    for i, x, y, qkv, ctx_twin, n_past in steps(z):
+        ctx, qr, kr = attn.forward(torch.from_numpy(qkv).cuda(), n_past, n_ctx=meta["n_ctx"], want_roped=True)
+        torch.cuda.synchronize()
+        ctx = ctx.cpu().numpy()
+        want, oqr, okr = O.attn_forward(cfg, qkv, meta["interleaved_qkv"], kc, vc, n_past, n_ctx=meta["n_ctx"],
+                                        want_roped=True)
+        assert np.abs(model_output(meta, w, x, ctx) - y).max() < GOLDEN_ATOL, (name, i)
+        assert_out_close(ctx, want, f"{name} step {i}")
+        assert np.abs(ctx - ctx_twin).max() < OUT_ATOL
+        assert ulp_distance(qr.cpu().numpy(), oqr).max() <= ROPE_MAX_ULP
+        assert ulp_distance(kr.cpu().numpy(), okr).max() <= ROPE_MAX_ULP
+    gk, gv = download_cache(arena, 0)
+    np.testing.assert_array_equal(gk, kc)
+    np.testing.assert_array_equal(gv, vc)
+    np.testing.assert_array_equal(gk, z["k_cache_final"].view(np.uint16))
+    assert ws.status() == 0
+
+
+def test_config1_glm3_decode_n_past_512():
+    """BASELINE config 1: ChatGLM3-6B layer, one decode step at n_past 512, max_length 2048."""
+    run_decode_batch(make_desc(32, 2, 128, 2048), [512], seed=1001)
+
+
+@pytest.mark.parametrize("n_past", [0, 1, 15, 16, 17, 62, 63, 64, 65, 127, 128, 129, 1000, 2046, 2047])
+def test_decode_tile_edges(n_past):
+    """Attended lengths around the 16-token warp slice and the 64-token tile, up to a full cache."""
+    run_decode_batch(make_desc(32, 2, 128, 2048), [n_past], seed=n_past)
+
+
+def test_decode_batch_mixed_lengths_spans_and_merges():
+    """64 sequences of uniformly random length: spans cross item boundaries, items are merged from partials."""
+    rng = np.random.default_rng(1003)
+    n_past = rng.integers(1024, 8192, 64).tolist()
+    run_decode_batch(make_desc(32, 2, 128, 8192, theta=10000.0), n_past, seed=3, check_rope=False)
+
+
+def test_decode_single_long_sequence_many_parts():
+    """One long sequence: every CTA holds a part of the same two items."""
+    run_decode_batch(make_desc(32, 2, 128, 32768 + 64, theta=5.0e6), [32768], seed=4)
+
+
+def test_decode_small_batch_fewer_tiles_than_ctas():
+    run_decode_batch(make_desc(32, 2, 128, 256), [3, 70, 130], seed=5)
+
+
+def test_decode_mha_v1_2d_rope_interleaved():
+    """BASELINE config 5 shape: ChatGLM-6B v1, 32 heads with their own K/V, 2-D RoPE, interleaved qkv."""
+    run_decode_batch(make_desc(32, 32, 128, 4096, rope=O.ROPE_CHATGLM, mask=O.MASK_CHATGLM), [2048, 2048, 5, 300],
+                     seed=1005, interleaved=True, n_ctx_list=[17, 2000, 4, 300])
+
+
+def test_decode_gqa_r4_and_rope_disabled():
+    run_decode_batch(make_desc(8, 2, 128, 512), [100, 400], seed=6)
+    run_decode_batch(make_desc(16, 1, 128, 512, rope=O.ROPE_DISABLED), [77], seed=7)
+
+
+def test_decode_virtual_tokens_d128():
+    """P-Tuning prefix on the fast path: cache capacity max_length + n_virtual stays a multiple of 8."""
+    run_decode_batch(make_desc(32, 2, 128, 1024 + 8, V=8), [0, 5, 900], seed=8)
+
+
+def test_decode_generic_shapes():
+    """Shapes only the generic kernel covers: capacity not a multiple of 8, head_dim 64, 32 q heads per kv head,
+    full-head rope modes."""
+    run_decode_batch(make_desc(32, 2, 128, 1029, V=5), [0, 700], seed=9)
+    run_decode_batch(make_desc(8, 2, 64, 256), [100], seed=10)
+    run_decode_batch(make_desc(32, 1, 128, 256), [100], seed=11)
+    run_decode_batch(make_desc(4, 4, 32, 128, rope=O.ROPE_GPTJ), [50], seed=12)
+    run_decode_batch(make_desc(4, 2, 32, 128, rope=O.ROPE_NEOX, theta=50000.0), [50], seed=13)
+
+
+def test_long_context_rope_position_131072():
+    """BASELINE config 4's position: RoPE at 131072 with theta 5e6 stays within 2 ulp of the oracle."""
+    desc = make_desc(32, 2, 128, 131072 + 64, theta=5.0e6)
+    A = _A()
+    arena, ws = A.KVArena(desc, 1), A.Workspace(desc, 1, 1)
+    rng = np.random.default_rng(1004)
+    P = 131072
+    # fill the cache on the device, read it back for the oracle
+    arena.k_cache(0)[:, :P].copy_(torch.randn(2, P, 128, device="cuda").half())
+    arena.v_cache(0)[:, :, :P].copy_(torch.randn(2, 128, P, device="cuda").half())
+    k, v = download_cache(arena, 0)
+    qkv = rng.standard_normal((1, qkv_width(desc, False))).astype(np.float32)
+    attn = A.BasicAttention(arena, 0, ws)
+    out, qr, kr = attn.forward(torch.from_numpy(qkv).cuda(), P, want_roped=True)
+    torch.cuda.synchronize()
+    assert ws.status() == 0
+    k, v = k.copy(), v.copy()
+    want, oqr, okr = O.attn_forward(oracle_cfg(desc, "f32"), qkv, False, k, v, P, want_roped=True)
+    assert ulp_distance(qr.cpu().numpy(), oqr).max() <= ROPE_MAX_ULP
+    assert ulp_distance(kr.cpu().numpy(), okr).max() <= ROPE_MAX_ULP
+    assert_out_close(out.cpu().numpy(), want, "n_past 131072")
+    gk, gv = download_cache(arena, 0)
+    np.testing.assert_array_equal(gk[:, P], k[:, P])
+    np.testing.assert_array_equal(gv[:, :, P], v[:, :, P])
+    arena.close()
+
+
+@pytest.mark.parametrize("H,G,D,M,V,rope,mask,S", [
+    (32, 2, 128, 2048, 0, O.ROPE_CHATGLM2, O.MASK_CAUSAL, 37),
+    (8, 8, 128, 256, 0, O.ROPE_CHATGLM, O.MASK_CHATGLM, 19),
+    (8, 2, 64, 128, 5, O.ROPE_CHATGLM2, O.MASK_CAUSAL, 16),
+    (8, 8, 16, 77, 5, O.ROPE_CHATGLM, O.MASK_CHATGLM, 9),
+])
+def test_prefill_then_decode(H, G, D, M, V, rope, mask, S):
+    """Prefill of S tokens at n_past 0 (both mask types, with and without a prefix), then two decode steps."""
+    A = _A()
+    desc = make_desc(H, G, D, M, V, rope, 10000.0, mask)
+    inter = rope == O.ROPE_CHATGLM
+    rng = np.random.default_rng(S)
+    arena, ws = A.KVArena(desc, 1), A.Workspace(desc, 1, S)
+    attn = A.BasicAttention(arena, 0, ws, inter)
+    cfg = oracle_cfg(desc, "f32")
+    k, v = random_cache(rng, desc, V)
+    upload_cache(arena, 0, k, v)
+    n_past = 0
+    for qlen in (S, 1, 1):
+        qkv = rng.standard_normal((qlen, qkv_width(desc, inter))).astype(np.float32)
+        out, qr, kr = attn.forward(torch.from_numpy(qkv).cuda(), n_past, n_ctx=S, want_roped=True)
+        torch.cuda.synchronize()
+        want, oqr, okr = O.attn_forward(cfg, qkv, inter, k, v, n_past, n_ctx=S, want_roped=True)
+        assert_out_close(out.cpu().numpy(), want, f"qlen {qlen} n_past {n_past}")
+        assert ulp_distance(qr.cpu().numpy(), oqr).max() <= ROPE_MAX_ULP
+        assert ulp_distance(kr.cpu().numpy(), okr).max() <= ROPE_MAX_ULP
+        n_past += qlen
+    gk, gv = download_cache(arena, 0)
+    np.testing.assert_array_equal(gk, k)
+    np.testing.assert_array_equal(gv, v)
+    assert ws.status() == 0
+
+
+def test_explicit_position_ids_match_derived():
+    A = _A()
+    desc = make_desc(32, 32, 128, 512, rope=O.ROPE_CHATGLM, mask=O.MASK_CHATGLM)
+    rng = np.random.default_rng(21)
+    arena, ws = A.KVArena(desc, 2), A.Workspace(desc, 2, 1)
+    k, v = random_cache(rng, desc, 200)
+    upload_cache(arena, 0, k, v)
+    upload_cache(arena, 1, k, v)
+    qkv = torch.from_numpy(rng.standard_normal((1, qkv_width(desc, True))).astype(np.float32)).cuda()
+    ids = torch.tensor([48, 152], dtype=torch.int32, device="cuda")   # n_past 200, n_ctx 50 -> pos 48, block 152
+    outs = [torch.zeros(1, 4096, device="cuda") for _ in range(2)]
+    A.forward_batch(arena, ws, [A.SeqCall(qkv=qkv, slot=0, n_past=200, n_ctx=50, out=outs[0]),
+                                A.SeqCall(qkv=qkv, slot=1, n_past=200, n_ctx=0, out=outs[1], position_ids=ids)], True)
+    torch.cuda.synchronize()
+    assert torch.equal(outs[0], outs[1])
+    assert torch.equal(arena.k_cache(0), arena.k_cache(1))
+
+
+def test_splitkv_partials_combine_to_full_attention():
+    """A long sequence cut into 4 contiguous KV slices held in 4 slots: partials + LSE combine == one-pass result."""
+    A = _A()
+    P, n_rank = 4096 + 37, 4
+    chunk = (P + 1 + n_rank - 1) // n_rank
+    M_local = (chunk + 63) // 64 * 64 + 64
+    full = make_desc(32, 2, 128, 8192, theta=5.0e6)
+    local = make_desc(32, 2, 128, M_local, theta=5.0e6)
+    rng = np.random.default_rng(1004)
+    k, v = random_cache(rng, full, P)
+    qkv = rng.standard_normal((1, qkv_width(full, False))).astype(np.float32)
+    kf, vf = k.copy(), v.copy()
+    want = O.attn_forward(oracle_cfg(full, "f32"), qkv, False, kf, vf, P)
+    arena, ws = A.KVArena(local, n_rank), A.Workspace(local, n_rank, 1)
+    partials = torch.zeros(n_rank, 32, 130, device="cuda")
+    qkv_d = torch.from_numpy(qkv).cuda()
+    calls = []
+    for r in range(n_rank):
+        lo, hi = r * chunk, min((r + 1) * chunk, P + 1)
+        owns_new = lo <= P < hi
+        n_local = (min(hi, P) - lo)
+        kl = np.zeros((2, M_local, 128), np.uint16); vl = np.zeros((2, 128, M_local), np.uint16)
+        kl[:, :n_local] = k[:, lo:lo + n_local]; vl[:, :, :n_local] = v[:, :, lo:lo + n_local]
+        upload_cache(arena, r, kl, vl)
+        flags = A.SEQ_PARTIAL | A.SEQ_USE_KV_LOCAL | (0 if owns_new else A.SEQ_NO_APPEND)
+        calls.append(A.SeqCall(qkv=qkv_d, slot=r, n_past=P, partial=partials[r], kv_local=n_local, flags=flags))
+    A.forward_batch(arena, ws, calls)
+    out = A.splitkv_combine(partials)
+    torch.cuda.synchronize()
+    assert ws.status() == 0
+    assert_out_close(out.cpu().numpy().reshape(1, -1), want, "split-KV combine")
+    # the owner of position P appended it at its local index
+    r_own = P // chunk
+    gk, gv = download_cache(arena, r_own)
+    np.testing.assert_array_equal(gk[:, P - r_own * chunk], kf[:, P])
+    np.testing.assert_array_equal(gv[:, :, P - r_own * chunk], vf[:, :, P])
+
+
+def test_forward_host_roundtrip_matches_device_call():
+    from chatglm_cpp_b200 import _lib
+    A = _A()
+    desc = make_desc(32, 2, 128, 1024)
+    rng = np.random.default_rng(31)
+    n, n_past = 3, [10, 500, 1023]
+    arena, ws = A.KVArena(desc, 2 * n), A.Workspace(desc, n, 1)
+    qkv = rng.standard_normal((n, qkv_width(desc, False))).astype(np.float32)
+    outs = []
+    for i, P in enumerate(n_past):
+        k, v = random_cache(rng, desc, P)
+        upload_cache(arena, i, k, v)
+        upload_cache(arena, n + i, k, v)
+    calls = [A.SeqCall(qkv=torch.from_numpy(qkv[i:i + 1]).cuda(), slot=i, n_past=P, out=torch.zeros(1, 4096, device="cuda"))
+             for i, P in enumerate(n_past)]
+    A.forward_batch(arena, ws, calls)
+    qkv_pinned = torch.from_numpy(qkv).pin_memory()
+    out_pinned = torch.zeros(n, 4096).pin_memory()
+    dev_qkv, dev_out = torch.empty(n, qkv.shape[1], device="cuda"), torch.empty(n, 4096, device="cuda")
+    arr = (_lib.AttnSeq * n)()
+    for i, P in enumerate(n_past):
+        arr[i].slot, arr[i].qlen, arr[i].n_past = n + i, 1, P
+    _lib.check(_lib.lib().cglm_attn_forward_host(arena._h, arr, n, 0, qkv_pinned.data_ptr(), out_pinned.data_ptr(),
+                                                 dev_qkv.data_ptr(), dev_out.data_ptr(), ws.ptr, ws.bytes,
+                                                 torch.cuda.current_stream().cuda_stream), "forward_host")
+    torch.cuda.synchronize()
+    for i in range(n):
+        assert torch.equal(out_pinned[i], calls[i].out[0].cpu())
+        assert torch.equal(arena.k_cache(i), arena.k_cache(n + i))
+        assert torch.equal(arena.v_cache(i), arena.v_cache(n + i))
+
+
+def test_argument_errors_return_codes():
+    from chatglm_cpp_b200 import _lib
+    A = _A()
+    L = _lib.lib()
+    desc = make_desc(32, 2, 128, 256)
+    arena, ws = A.KVArena(desc, 1), A.Workspace(desc, 1, 1)
+    qkv = torch.zeros(1, qkv_width(desc, False), device="cuda")
+    out = torch.zeros(1, 4096, device="cuda")
+    with pytest.raises(_lib.CglmError) as e:   # n_past + 1 > capacity
+        A.forward_batch(arena, ws, [A.SeqCall(qkv=qkv, slot=0, n_past=256, out=out)])
+    assert e.value.status == _lib.ERR_INVALID_ARG
+    with pytest.raises(_lib.CglmError):        # slot out of range
+        A.forward_batch(arena, ws, [A.SeqCall(qkv=qkv, slot=1, n_past=0, out=out)])
+    with pytest.raises(_lib.CglmError):        # qlen > 1 with n_past > 0
+        A.forward_batch(arena, ws, [A.SeqCall(qkv=torch.zeros(2, qkv.shape[1], device="cuda"), slot=0, n_past=3,
+                                              out=torch.zeros(2, 4096, device="cuda"))])
+    arr = (_lib.AttnSeq * 1)()
+    A.fill_seq(arr[0], desc, A.SeqCall(qkv=qkv, slot=0, n_past=0, out=out), False)
+    assert L.cglm_attn_forward(arena._h, arr, 1, ws.ptr, 1024, None) == _lib.ERR_WORKSPACE
+    assert L.cglm_attn_forward(arena._h, arr, 1, None, 0, None) == _lib.ERR_WORKSPACE
+    bad = make_desc(32, 3, 128, 256)
+    h = C.c_void_p()
+    assert L.cglm_kv_arena_create(C.byref(bad), 1, C.byref(h)) == _lib.ERR_INVALID_ARG
+    assert ws.status() == 0
