@@ -1,0 +1,219 @@
+// Host side of the B200 attention KV-cache path: the chatglm:: module surface of include/chatglm_b200.h over the
+// C ABI of include/cglm_attn.h.  Host code only; compiled by nvcc for the CUDA runtime declarations.
+#include "../../include/chatglm_b200.h"
+
+#include <algorithm>
+#include <cuda_runtime.h>
+
+namespace chatglm {
+
+#define CHATGLM_CHECK_CUDA(call)                                                                   \
+    do {                                                                                           \
+        cudaError_t error__ = (call);                                                              \
+        CHATGLM_CHECK(error__ == cudaSuccess) << "CUDA error: " << cudaGetErrorString(error__);    \
+    } while (false)
+
+size_t element_size(TensorType type) {
+    switch (type) {
+    case TYPE_F32: return 4;
+    case TYPE_F16: return 2;
+    case TYPE_I32: return 4;
+    }
+    CHATGLM_THROW << "unknown tensor type " << static_cast<int>(type);
+}
+
+size_t nbytes(const Tensor *t) { return static_cast<size_t>(t->ne[0] * t->ne[1] * t->ne[2] * t->ne[3]) * element_size(t->type); }
+
+static void set_contiguous(Tensor *t, TensorType type, int64_t ne0, int64_t ne1, int64_t ne2) {
+    t->type = type;
+    t->ne[0] = ne0; t->ne[1] = ne1; t->ne[2] = ne2; t->ne[3] = 1;
+    t->nb[0] = element_size(type);
+    t->nb[1] = t->nb[0] * ne0;
+    t->nb[2] = t->nb[1] * ne1;
+    t->nb[3] = t->nb[2] * ne2;
+}
+
+ModelContext::ModelContext(void *cuda_stream) : stream_(cuda_stream) {}
+
+ModelContext::~ModelContext() {
+    cudaStreamSynchronize(static_cast<cudaStream_t>(stream_));
+    reset_scratch();
+    if (workspace_) cudaFree(workspace_);
+    if (arena_) cglm_kv_arena_destroy(arena_);
+}
+
+int ModelContext::register_attention(const cglm_attn_desc &desc, Tensor **k_cache, Tensor **v_cache) {
+    CHATGLM_CHECK(!arena_) << "kv buffer already allocated: construct every BasicAttention before alloc_kv()";
+    if (have_desc_) {
+        CHATGLM_CHECK(desc.n_head == desc_.n_head && desc.n_kv_head == desc_.n_kv_head && desc.head_dim == desc_.head_dim &&
+                      desc.max_len == desc_.max_len && desc.n_virtual == desc_.n_virtual &&
+                      desc.rope_type == desc_.rope_type && desc.rope_theta == desc_.rope_theta &&
+                      desc.mask_type == desc_.mask_type)
+            << "all attention modules of one context share one configuration";
+    } else {
+        desc_ = desc;
+        have_desc_ = true;
+    }
+    const int slot = static_cast<int>(kv_tensors_.size() / 2);
+    auto k = std::make_unique<Tensor>(), v = std::make_unique<Tensor>();
+    // chatglm.h:452-455: k_cache ne = [d, max_length + v, #kvh], v_cache ne = [max_length + v, d, #kvh], both F16
+    set_contiguous(k.get(), TYPE_F16, desc.head_dim, desc.max_len, desc.n_kv_head);
+    set_contiguous(v.get(), TYPE_F16, desc.max_len, desc.head_dim, desc.n_kv_head);
+    *k_cache = k.get();
+    *v_cache = v.get();
+    kv_tensors_.push_back(std::move(k));
+    kv_tensors_.push_back(std::move(v));
+    return slot;
+}
+
+void ModelContext::alloc_kv() {
+    CHATGLM_CHECK(!arena_) << "kv buffer already allocated";
+    CHATGLM_CHECK(have_desc_ && !kv_tensors_.empty()) << "no attention module registered";
+    const int n_slots = static_cast<int>(kv_tensors_.size() / 2);
+    CHATGLM_CHECK_CGLM(cglm_kv_arena_create(&desc_, n_slots, &arena_));
+    for (int s = 0; s < n_slots; ++s) {
+        kv_tensors_[2 * s]->data = cglm_kv_arena_k_cache(arena_, s);
+        kv_tensors_[2 * s + 1]->data = cglm_kv_arena_v_cache(arena_, s);
+    }
+}
+
+void ModelContext::ensure_workspace(int n_seq, int max_qlen) {
+    const size_t need = cglm_attn_workspace_bytes(&desc_, n_seq, max_qlen);
+    CHATGLM_CHECK(need > 0) << "invalid attention configuration";
+    if (need > workspace_bytes_) {
+        if (workspace_) {
+            CHATGLM_CHECK_CUDA(cudaStreamSynchronize(static_cast<cudaStream_t>(stream_)));
+            CHATGLM_CHECK_CUDA(cudaFree(workspace_));
+            workspace_ = nullptr;
+        }
+        CHATGLM_CHECK_CUDA(cudaMalloc(&workspace_, need));
+        workspace_bytes_ = need;
+        CHATGLM_CHECK_CGLM(cglm_attn_workspace_init(workspace_, workspace_bytes_, stream_));
+    }
+}
+
+Tensor *ModelContext::new_tensor_2d(TensorType type, int64_t ne0, int64_t ne1) {
+    auto t = std::make_unique<Tensor>();
+    set_contiguous(t.get(), type, ne0, ne1, 1);
+    CHATGLM_CHECK_CUDA(cudaMalloc(&t->data, std::max<size_t>(nbytes(t.get()), 16)));
+    t->owned = true;
+    scratch_.push_back(std::move(t));
+    return scratch_.back().get();
+}
+
+Tensor *ModelContext::new_tensor_1d(TensorType type, int64_t ne0) { return new_tensor_2d(type, ne0, 1); }
+
+void ModelContext::reset_scratch() {
+    if (!scratch_.empty()) {
+        cudaStreamSynchronize(static_cast<cudaStream_t>(stream_));
+    }
+    for (auto &t : scratch_) {
+        if (t->owned && t->data) cudaFree(t->data);
+    }
+    scratch_.clear();
+}
+
+void ModelContext::tensor_set(Tensor *t, const void *host, size_t offset, size_t size) {
+    CHATGLM_CHECK(offset + size <= nbytes(t)) << "tensor_set out of range";
+    CHATGLM_CHECK_CUDA(cudaMemcpyAsync(static_cast<char *>(t->data) + offset, host, size, cudaMemcpyHostToDevice,
+                                       static_cast<cudaStream_t>(stream_)));
+}
+
+void ModelContext::tensor_get(const Tensor *t, void *host, size_t offset, size_t size) {
+    CHATGLM_CHECK(offset + size <= nbytes(t)) << "tensor_get out of range";
+    CHATGLM_CHECK_CUDA(cudaMemcpyAsync(host, static_cast<const char *>(t->data) + offset, size, cudaMemcpyDeviceToHost,
+                                       static_cast<cudaStream_t>(stream_)));
+    CHATGLM_CHECK_CUDA(cudaStreamSynchronize(static_cast<cudaStream_t>(stream_)));
+}
+
+void ModelContext::synchronize() {
+    CHATGLM_CHECK_CUDA(cudaStreamSynchronize(static_cast<cudaStream_t>(stream_)));
+    if (workspace_) {
+        CHATGLM_CHECK_CGLM(cglm_attn_workspace_status(workspace_, stream_));
+    }
+}
+
+std::vector<int> make_position_ids_glm2(int qlen, int n_past) {
+    std::vector<int> ids(qlen);
+    for (int i = 0; i < qlen; i++) ids[i] = n_past + i;
+    return ids;
+}
+
+std::vector<int> make_position_ids_glm(int qlen, int n_past, int n_ctx) {
+    std::vector<int> ids(2 * qlen);
+    for (int i = 0; i < qlen; i++) {
+        const int p = n_past + i;
+        ids[i] = std::min(p, n_ctx - 2);
+        ids[qlen + i] = std::max(p - (n_ctx - 2), 0);
+    }
+    return ids;
+}
+
+BasicAttention::BasicAttention(ModelContext *mctx, int hidden_size, int num_attention_heads, int num_key_value_heads,
+                               int max_length, bool /*use_qkv_bias*/, bool /*use_dense_bias*/, bool interleaved_qkv,
+                               RopeType rope_type, float rope_theta, AttentionMaskType attn_mask_type,
+                               int num_virtual_tokens)
+    : num_attention_heads(num_attention_heads), num_key_value_heads(num_key_value_heads),
+      interleaved_qkv(interleaved_qkv), rope_type(rope_type), rope_theta(rope_theta), attn_mask_type(attn_mask_type),
+      num_virtual_tokens(num_virtual_tokens) {
+    CHATGLM_CHECK(mctx != nullptr) << "null context";
+    CHATGLM_CHECK(num_attention_heads > 0 && hidden_size % num_attention_heads == 0) << "invalid head count";
+    head_size_ = hidden_size / num_attention_heads;
+    cglm_attn_desc desc;
+    desc.n_head = num_attention_heads;
+    desc.n_kv_head = num_key_value_heads;
+    desc.head_dim = head_size_;
+    desc.max_len = max_length + num_virtual_tokens;
+    desc.n_virtual = num_virtual_tokens;
+    desc.rope_type = static_cast<int>(rope_type);
+    desc.rope_theta = rope_theta;
+    desc.mask_type = attn_mask_type == AttentionMaskType::CAUSAL ? CGLM_MASK_CAUSAL : CGLM_MASK_CHATGLM;
+    slot_ = mctx->register_attention(desc, &k_cache, &v_cache);
+}
+
+Tensor *BasicAttention::forward(ModelContext *mctx, Tensor *qkv, Tensor * /*attention_mask*/, Tensor *position_ids,
+                                int n_past) const {
+    CHATGLM_CHECK(mctx && mctx->kv_allocated()) << "kv buffer not allocated";
+    CHATGLM_CHECK(qkv && qkv->type == TYPE_F32 && qkv->data) << "qkv must be an f32 device tensor";
+    const int64_t hidden_size = static_cast<int64_t>(num_attention_heads) * head_size_;
+    const int64_t qkv_width = hidden_size + 2LL * head_size_ * num_key_value_heads;
+    CHATGLM_CHECK(qkv->ne[0] == qkv_width) << "qkv row is " << qkv->ne[0] << ", expected " << qkv_width;
+    const int qlen = static_cast<int>(qkv->ne[1]);
+    const int num_shared_q_heads = num_attention_heads / num_key_value_heads;
+
+    cglm_attn_seq seq{};
+    const float *base = static_cast<const float *>(qkv->data);
+    const long long row = static_cast<long long>(qkv->nb[1] / sizeof(float));
+    if (interleaved_qkv) {   // chatglm.cpp:636-644
+        CHATGLM_CHECK(num_shared_q_heads == 1) << "interleaved qkv is not supported for GQA";
+        seq.q = base; seq.k = base + head_size_; seq.v = base + 2 * head_size_;
+        seq.q_head_stride = seq.kv_head_stride = 3 * head_size_;
+    } else {                 // chatglm.cpp:646-652
+        seq.q = base; seq.k = base + hidden_size; seq.v = base + hidden_size + static_cast<long long>(head_size_) * num_key_value_heads;
+        seq.q_head_stride = seq.kv_head_stride = head_size_;
+    }
+    seq.q_tok_stride = seq.kv_tok_stride = row;
+    seq.slot = slot_;
+    seq.qlen = qlen;
+    seq.n_past = n_past;
+    seq.n_ctx = n_ctx_;
+    if (position_ids) {
+        const int64_t want = rope_type == RopeType::CHATGLM ? 2 * qlen : qlen;
+        CHATGLM_CHECK(position_ids->type == TYPE_I32 && position_ids->ne[0] == want)
+            << "invalid position ids size " << position_ids->ne[0];
+        seq.position_ids = static_cast<const int *>(position_ids->data);
+    }
+    Tensor *context_layer = mctx->new_tensor_2d(TYPE_F32, hidden_size, qlen);   // [s, #h * d]
+    seq.out = static_cast<float *>(context_layer->data);
+    mctx->ensure_workspace(1, qlen);
+    CHATGLM_CHECK_CGLM(cglm_attn_forward(mctx->arena_, &seq, 1, mctx->workspace_, mctx->workspace_bytes_, mctx->stream_));
+    return context_layer;
+}
+
+void BasicAttention::load_prefix_cache(ModelContext *mctx, const Tensor *past_kv) const {
+    CHATGLM_CHECK(mctx && mctx->kv_allocated()) << "kv buffer not allocated";
+    CHATGLM_CHECK(past_kv && past_kv->type == TYPE_F16 && past_kv->data) << "prefix must be an f16 device tensor";
+    CHATGLM_CHECK_CGLM(cglm_kv_load_prefix(mctx->arena_, slot_, past_kv->data, mctx->stream_));
+}
+
+}  // namespace chatglm
