@@ -35,6 +35,9 @@ WORKLOADS = {
     # name: H, G, D, max_length, layers, seqs per GPU, n_past range, rope, theta, interleaved, mask
     "glm4_9b_batched_decode": dict(H=32, G=2, D=128, M=8192, layers=40, seqs=64, n_past=(1024, 8191), rope=8,
                                    theta=10000.0, interleaved=False, mask=0, seed=1003),
+    # 1/20 of the default workload (2 layers, 1 GiB of caches): small enough for an ncu --set full capture
+    "glm4_9b_batched_decode_small": dict(H=32, G=2, D=128, M=8192, layers=2, seqs=64, n_past=(1024, 8191), rope=8,
+                                         theta=10000.0, interleaved=False, mask=0, seed=1003),
     "glm3_6b_decode_512": dict(H=32, G=2, D=128, M=2048, layers=1, seqs=1, n_past=(512, 512), rope=8, theta=10000.0,
                                interleaved=False, mask=0, seed=1001),
     "glm4_9b_long_131072": dict(H=32, G=2, D=128, M=131072 + 64, layers=1, seqs=1, n_past=(131072, 131072), rope=8,

@@ -176,10 +176,41 @@ decode_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__
             const bool whole_item = pos == ip.item_begin && has_last_tile;
 
             // ---- segment prologue: RoPE, scaled f16 q tile, append ---------------------------------------
-            named_bar_sync(1, kConsumerThreads);   // previous segment is done with q / newk / newv / xchg
+            // Every global load of the prologue is issued before the first barrier so that the loads and the
+            // cos/sin ladder overlap instead of queueing behind one another.
+            const int n_pairs = rope_n_pairs(sh.rope_type, kD);   // 0, 32 (CHATGLM2) or 64 (CHATGLM)
+            const int pr = tid & 63;                               // this thread's pair of the head, rows r0 + 2j
+            int i0, i1, cs_stream = 0, cs_ladder = 0;
+            if (pr < n_pairs) {
+                const RopePair rp = rope_pair(sh.rope_type, kD, pr);
+                i0 = rp.i0; i1 = rp.i1; cs_stream = rp.stream; cs_ladder = rp.ladder;
+            } else {
+                const int first_free = sh.rope_type == CGLM_ROPE_CHATGLM2 ? kD / 2 : 0;
+                i0 = first_free + 2 * (pr - n_pairs); i1 = i0 + 1;
+            }
+            const bool k_needed = appender || (has_last_tile && sq.k_roped);
+            float qx0[8], qx1[8], kx0 = 0.f, kx1 = 0.f, vx = 0.f;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const int r = (tid >> 6) + 2 * j;
+                qx0[j] = qx1[j] = 0.f;
+                if (r < R) {
+                    const float *src = sq.q + (g * R + r) * sq.q_head_stride;
+                    qx0[j] = __ldg(src + i0);
+                    qx1[j] = __ldg(src + i1);
+                }
+            }
+            if (k_needed && tid < 64) {
+                const float *src = sq.k + g * sq.kv_head_stride;
+                kx0 = __ldg(src + i0);
+                kx1 = __ldg(src + i1);
+            }
+            if (appender) {
+                vx = __ldg(sq.v + g * sq.kv_head_stride + tid);   // 128 consumer threads, 128 dims
+            }
             int pos_id, block_id;
             derive_positions(sq, sh.rope_type, 0, pos_id, block_id);
-            const int n_pairs = rope_n_pairs(sh.rope_type, kD);   // 0, 32 (CHATGLM2) or 64 (CHATGLM)
+            named_bar_sync(1, kConsumerThreads);   // previous segment is done with q / cs / newk / newv / xchg
             if (tid < 64 && n_pairs > 0) {
                 const int st = tid >> 5;
                 if (st == 0 || sh.rope_type == CGLM_ROPE_CHATGLM) {
@@ -188,26 +219,18 @@ decode_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__
                 }
             }
             named_bar_sync(1, kConsumerThreads);
+            float rc = 1.f, rs = 0.f;
+            if (pr < n_pairs) {
+                rc = sm.cs[cs_stream][cs_ladder][0];
+                rs = sm.cs[cs_stream][cs_ladder][1];
+            }
             // q: 16 rows x 64 pairs; rows >= R are zero
-            for (int idx = tid; idx < kRows * 64; idx += kConsumerThreads) {
-                const int r = idx >> 6, p = idx & 63;
-                int i0, i1;
-                float y0 = 0.f, y1 = 0.f;
-                if (p < n_pairs) {
-                    const RopePair rp = rope_pair(sh.rope_type, kD, p);
-                    i0 = rp.i0; i1 = rp.i1;
-                    if (r < R) {
-                        const float *src = sq.q + (g * R + r) * sq.q_head_stride;
-                        rope_rotate(src[i0], src[i1], sm.cs[rp.stream][rp.ladder][0], sm.cs[rp.stream][rp.ladder][1],
-                                    y0, y1);
-                    }
-                } else {
-                    const int first_free = sh.rope_type == CGLM_ROPE_CHATGLM2 ? kD / 2 : 0;
-                    i0 = first_free + 2 * (p - n_pairs); i1 = i0 + 1;
-                    if (r < R) {
-                        const float *src = sq.q + (g * R + r) * sq.q_head_stride;
-                        y0 = src[i0]; y1 = src[i1];
-                    }
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const int r = (tid >> 6) + 2 * j;
+                float y0 = qx0[j], y1 = qx1[j];
+                if (pr < n_pairs) {
+                    rope_rotate(qx0[j], qx1[j], rc, rs, y0, y1);
                 }
                 sm.q[r][i0] = __float2half_rn(__fmul_rn(y0, sh.scale));
                 sm.q[r][i1] = __float2half_rn(__fmul_rn(y1, sh.scale));
@@ -216,41 +239,27 @@ decode_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__
                     qr[i0] = y0; qr[i1] = y1;
                 }
             }
-            if (appender || (has_last_tile && sq.k_roped)) {
-                const long long cache_pos = sq.kv_before;
-                if (tid < 64) {
-                    const int p = tid;
-                    const float *src = sq.k + g * sq.kv_head_stride;
-                    int i0, i1;
-                    float y0, y1;
-                    if (p < n_pairs) {
-                        const RopePair rp = rope_pair(sh.rope_type, kD, p);
-                        i0 = rp.i0; i1 = rp.i1;
-                        rope_rotate(src[i0], src[i1], sm.cs[rp.stream][rp.ladder][0], sm.cs[rp.stream][rp.ladder][1],
-                                    y0, y1);
-                    } else {
-                        const int first_free = sh.rope_type == CGLM_ROPE_CHATGLM2 ? kD / 2 : 0;
-                        i0 = first_free + 2 * (p - n_pairs); i1 = i0 + 1;
-                        y0 = src[i0]; y1 = src[i1];
-                    }
-                    if (sq.k_roped) {
-                        float *kr = sq.k_roped + static_cast<long long>(g) * kD;
-                        kr[i0] = y0; kr[i1] = y1;
-                    }
-                    if (appender) {
-                        const __half h0 = __float2half_rn(y0), h1 = __float2half_rn(y1);
-                        sm.newk[i0] = h0; sm.newk[i1] = h1;
-                        uint16_t *krow = k_base + (static_cast<long long>(row) * M + cache_pos) * kD;
-                        krow[i0] = __half_as_ushort(h0);
-                        krow[i1] = __half_as_ushort(h1);
-                    }
+            if (k_needed && tid < 64) {
+                float y0 = kx0, y1 = kx1;
+                if (pr < n_pairs) {
+                    rope_rotate(kx0, kx1, rc, rs, y0, y1);
+                }
+                if (sq.k_roped) {
+                    float *kr = sq.k_roped + static_cast<long long>(g) * kD;
+                    kr[i0] = y0; kr[i1] = y1;
                 }
                 if (appender) {
-                    const int d = tid;   // 128 consumer threads, 128 dims
-                    const __half hv = __float2half_rn(sq.v[g * sq.kv_head_stride + d]);
-                    sm.newv[d] = hv;
-                    v_base[(static_cast<long long>(row) * kD + d) * M + cache_pos] = __half_as_ushort(hv);
+                    const __half h0 = __float2half_rn(y0), h1 = __float2half_rn(y1);
+                    sm.newk[i0] = h0; sm.newk[i1] = h1;
+                    uint16_t *krow = k_base + (static_cast<long long>(row) * M + sq.kv_before) * kD;
+                    krow[i0] = __half_as_ushort(h0);
+                    krow[i1] = __half_as_ushort(h1);
                 }
+            }
+            if (appender) {
+                const __half hv = __float2half_rn(vx);
+                sm.newv[tid] = hv;
+                v_base[(static_cast<long long>(row) * kD + tid) * M + sq.kv_before] = __half_as_ushort(hv);
             }
             named_bar_sync(1, kConsumerThreads);
             // A fragments of the q tile: 8 k-steps of 16 dims
@@ -493,30 +502,67 @@ decode_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__
                 named_bar_sync(1, kConsumerThreads);
                 if (sm.last_flag) {
                     __threadfence();
-                    // thread d merges column d of every row over all parts
-                    const int d = tid;
-                    for (int r = 0; r < R; ++r) {
+                    // thread (r, c8) merges 16 dims of row r over all parts; loads are issued in batches so that
+                    // L2 round trips overlap instead of adding up
+                    const int r = tid >> 3, d0 = (tid & 7) * 16;
+                    if (r < R) {
+                        auto part_ptr = [&](long long b) -> const float * {
+                            const int slot = span_start(b, total, nb) >= ip.item_begin ? 0 : 1;
+                            return partials + (b * 2 + slot) * kDecodePartialFloats;
+                        };
                         float m_star = -INFINITY;
-                        for (long long b = b0; b <= b1; ++b) {
-                            const int slot = span_start(b, total, nb) >= ip.item_begin ? 0 : 1;
-                            const float *pp = partials + (b * 2 + slot) * kDecodePartialFloats;
-                            m_star = fmaxf(m_star, __ldcg(&pp[kRows * kD + r]));
+                        for (long long b = b0; b <= b1; b += 8) {
+                            float mv[8];
+#pragma unroll
+                            for (int u = 0; u < 8; ++u) {
+                                mv[u] = b + u <= b1 ? __ldcg(part_ptr(b + u) + kRows * kD + r) : -INFINITY;
+                            }
+#pragma unroll
+                            for (int u = 0; u < 8; ++u) m_star = fmaxf(m_star, mv[u]);
                         }
-                        float acc = 0.f, den = 0.f;
-                        for (long long b = b0; b <= b1; ++b) {
-                            const int slot = span_start(b, total, nb) >= ip.item_begin ? 0 : 1;
-                            const float *pp = partials + (b * 2 + slot) * kDecodePartialFloats;
-                            const float w = ex2_approx(__ldcg(&pp[kRows * kD + r]) - m_star);
-                            den += w * __ldcg(&pp[kRows * kD + kRows + r]);
-                            acc += w * __ldcg(&pp[r * kD + d]);
+                        float acc[16];
+#pragma unroll
+                        for (int e = 0; e < 16; ++e) acc[e] = 0.f;
+                        float den = 0.f;
+                        for (long long b = b0; b <= b1; b += 4) {
+                            float mv[4], lv[4];
+                            float4 av[4][4];
+#pragma unroll
+                            for (int u = 0; u < 4; ++u) {
+                                const bool ok = b + u <= b1;
+                                const float *pp = part_ptr(ok ? b + u : b);
+                                mv[u] = ok ? __ldcg(pp + kRows * kD + r) : -INFINITY;
+                                lv[u] = __ldcg(pp + kRows * kD + kRows + r);
+#pragma unroll
+                                for (int e = 0; e < 4; ++e) {
+                                    av[u][e] = __ldcg(reinterpret_cast<const float4 *>(pp + r * kD + d0) + e);
+                                }
+                            }
+#pragma unroll
+                            for (int u = 0; u < 4; ++u) {
+                                const float w = ex2_approx(mv[u] - m_star);   // 0 for the padding entries
+                                den += w * lv[u];
+#pragma unroll
+                                for (int e = 0; e < 4; ++e) {
+                                    acc[4 * e + 0] += w * av[u][e].x; acc[4 * e + 1] += w * av[u][e].y;
+                                    acc[4 * e + 2] += w * av[u][e].z; acc[4 * e + 3] += w * av[u][e].w;
+                                }
+                            }
                         }
                         const int head = g * R + r;
                         if (want_partial) {
                             float *po = sq.partial + static_cast<long long>(head) * (kD + 2);
-                            po[d] = acc;
-                            if (d == 0) { po[kD] = m_star * kLn2; po[kD + 1] = den; }
+#pragma unroll
+                            for (int e = 0; e < 16; ++e) po[d0 + e] = acc[e];   // row stride 130 floats: not 16-byte aligned
+                            if (d0 == 0) { po[kD] = m_star * kLn2; po[kD + 1] = den; }
                         } else {
-                            sq.out[static_cast<long long>(head) * kD + d] = acc / den;
+                            const float inv = 1.f / den;
+                            float4 *op = reinterpret_cast<float4 *>(sq.out + static_cast<long long>(head) * kD + d0);
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) {
+                                op[e] = make_float4(acc[4 * e] * inv, acc[4 * e + 1] * inv, acc[4 * e + 2] * inv,
+                                                    acc[4 * e + 3] * inv);
+                            }
                         }
                     }
                 }
