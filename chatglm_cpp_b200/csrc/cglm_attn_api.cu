@@ -371,6 +371,11 @@ int cglm_attn_forward(cglm_kv_arena *a, const cglm_attn_seq *seqs, int n_seq, vo
         if (s.qlen > 1 && s.n_past != 0) return CGLM_ERR_INVALID_ARG;   // chatglm.cpp:689 masks only at n_past == 0
         const bool partial = (s.flags & CGLM_SEQ_PARTIAL) != 0;
         if (partial ? !s.partial : !s.out) return CGLM_ERR_INVALID_ARG;
+        // vector stores: out rows are written 16 bytes at a time, partial rows 8 bytes at a time
+        if ((reinterpret_cast<uintptr_t>(s.out) & 15) || (reinterpret_cast<uintptr_t>(s.partial) & 7) ||
+            (reinterpret_cast<uintptr_t>(s.q) & 3) || (reinterpret_cast<uintptr_t>(s.k) & 3) ||
+            (reinterpret_cast<uintptr_t>(s.v) & 3))
+            return CGLM_ERR_INVALID_ARG;
         if ((s.flags & CGLM_SEQ_NO_APPEND) && (!partial || s.qlen != 1)) return CGLM_ERR_INVALID_ARG;
         if ((s.flags & CGLM_SEQ_USE_KV_LOCAL) && (s.kv_local < 0 || s.qlen != 1)) return CGLM_ERR_INVALID_ARG;
         const int kv_before = (s.flags & CGLM_SEQ_USE_KV_LOCAL) ? s.kv_local : d.n_virtual + s.n_past;
@@ -389,16 +394,8 @@ int cglm_attn_forward(cglm_kv_arena *a, const cglm_attn_seq *seqs, int n_seq, vo
     const WsLayout lay = ws_layout(d, a->n_sm, n_seq, gen_tokens);
     if (workspace_bytes < lay.total) return CGLM_ERR_WORKSPACE;
 
-    // ---- descriptors: fast-decode sequences first, then the generic ones -----------------------------------
-    std::lock_guard<std::mutex> lock(a->mu);
-    SeqDev *host = nullptr;
-    cudaEvent_t ev;
-    int rc = ring_reserve(a, n_seq, &host, &ev);
-    if (rc != CGLM_OK) return rc;
-    int fi = 0, gi = n_fast, tok = 0;
-    for (int i = 0; i < n_seq; ++i) {
-        const cglm_attn_seq &s = seqs[i];
-        SeqDev &o = host[is_fast[i] ? fi++ : gi++];
+    // ---- descriptors ---------------------------------------------------------------------------------------
+    auto to_dev = [&](const cglm_attn_seq &s, SeqDev &o) {
         o.q = s.q; o.k = s.k; o.v = s.v;
         o.q_tok_stride = s.q_tok_stride; o.q_head_stride = s.q_head_stride;
         o.kv_tok_stride = s.kv_tok_stride; o.kv_head_stride = s.kv_head_stride;
@@ -409,16 +406,8 @@ int cglm_attn_forward(cglm_kv_arena *a, const cglm_attn_seq *seqs, int n_seq, vo
         o.flags = s.flags;
         o.tok_begin = 0;
         o.pad = 0;
-        if (!is_fast[i]) {
-            o.tok_begin = tok;
-            tok += s.qlen;
-        }
-    }
+    };
     uint8_t *ws = static_cast<uint8_t *>(workspace);
-    SeqDev *seqs_dev = reinterpret_cast<SeqDev *>(ws + lay.seqs);
-    CGLM_CUDA(cudaMemcpyAsync(seqs_dev, host, sizeof(SeqDev) * n_seq, cudaMemcpyHostToDevice, st));
-    CGLM_CUDA(cudaEventRecord(ev, st));
-
     LaunchCtx cx;
     cx.shape = make_shape(d);
     cx.k_base = a->k_base;
@@ -432,18 +421,47 @@ int cglm_attn_forward(cglm_kv_arena *a, const cglm_attn_seq *seqs, int n_seq, vo
     cx.stream = st;
     cx.n_sm = a->n_sm;
 
-    // the decode kernel keeps a per-launch table of kDecodeMaxSeqPerLaunch sequences
-    for (int begin = 0; begin < n_fast; begin += kDecodeMaxSeqPerLaunch) {
-        const int cnt = n_fast - begin < kDecodeMaxSeqPerLaunch ? n_fast - begin : kDecodeMaxSeqPerLaunch;
-        long long tiles = 0;
-        for (int i = begin; i < begin + cnt; ++i) {
-            const int L = host[i].kv_before + ((host[i].flags & CGLM_SEQ_NO_APPEND) ? 0 : 1);
-            tiles += static_cast<long long>((L + kDecodeTile - 1) / kDecodeTile) * d.n_kv_head;
+    // fused decode: descriptors and tile prefix travel as kernel parameters, kDecodeMaxSeqPerLaunch per launch
+    if (n_fast > 0) {
+        static thread_local DecodeTable tab;
+        int filled = 0;
+        tab.prefix[0] = 0;
+        for (int i = 0; i <= n_seq; ++i) {
+            if (i < n_seq && is_fast[i]) {
+                SeqDev &o = tab.seqs[filled];
+                to_dev(seqs[i], o);
+                const int L = o.kv_before + ((o.flags & CGLM_SEQ_NO_APPEND) ? 0 : 1);
+                tab.prefix[filled + 1] = tab.prefix[filled] + (L + kDecodeTile - 1) / kDecodeTile;
+                ++filled;
+            }
+            if (filled == kDecodeMaxSeqPerLaunch || (i == n_seq && filled > 0)) {
+                tab.n_seq = filled;
+                tab.pad = 0;
+                CGLM_CUDA(launch_decode(cx, tab));
+                filled = 0;
+            }
         }
-        CGLM_CUDA(launch_decode(cx, seqs_dev + begin, cnt, tiles));
     }
-    if (n_seq - n_fast > 0) {
-        CGLM_CUDA(launch_generic(cx, seqs_dev + n_fast, n_seq - n_fast, static_cast<int>(gen_tokens)));
+    // generic path: descriptors are uploaded through the pinned ring
+    const int n_gen = n_seq - n_fast;
+    if (n_gen > 0) {
+        std::lock_guard<std::mutex> lock(a->mu);
+        SeqDev *host = nullptr;
+        cudaEvent_t ev;
+        int rc = ring_reserve(a, n_gen, &host, &ev);
+        if (rc != CGLM_OK) return rc;
+        int gi = 0, tok = 0;
+        for (int i = 0; i < n_seq; ++i) {
+            if (is_fast[i]) continue;
+            SeqDev &o = host[gi++];
+            to_dev(seqs[i], o);
+            o.tok_begin = tok;
+            tok += seqs[i].qlen;
+        }
+        SeqDev *seqs_dev = reinterpret_cast<SeqDev *>(ws + lay.seqs);
+        CGLM_CUDA(cudaMemcpyAsync(seqs_dev, host, sizeof(SeqDev) * n_gen, cudaMemcpyHostToDevice, st));
+        CGLM_CUDA(cudaEventRecord(ev, st));
+        CGLM_CUDA(launch_generic(cx, seqs_dev, n_gen, static_cast<int>(gen_tokens)));
     }
     (void)decode_tiles;
     return CGLM_OK;

@@ -20,6 +20,7 @@ size_t element_size(TensorType type) {
     case TYPE_I32: return 4;
     }
     CHATGLM_THROW << "unknown tensor type " << static_cast<int>(type);
+    return 0;   // not reached
 }
 
 size_t nbytes(const Tensor *t) { return static_cast<size_t>(t->ne[0] * t->ne[1] * t->ne[2] * t->ne[3]) * element_size(t->type); }

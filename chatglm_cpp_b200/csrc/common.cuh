@@ -239,10 +239,18 @@ struct LaunchCtx {
 // seqs_dev[i].tok_begin indexes q_stage, total_tokens = sum of qlen
 cudaError_t launch_generic(const LaunchCtx &cx, const SeqDev *seqs_dev, int n_seq, int total_tokens);
 // fused rope + append + split-KV decode (head_dim 128, <= 16 q heads per kv head, capacity % 8 == 0)
-cudaError_t launch_decode(const LaunchCtx &cx, const SeqDev *seqs_dev, int n_seq, long long total_tiles);
 constexpr int kDecodeTile = 64;   // tokens per TMA tile of the decode kernel
+constexpr int kDecodeMaxSeqPerLaunch = 128;
+// Everything the decode kernel needs to know about its sequences, passed by value as a kernel parameter so
+// that no upload or load stands between the launch and its first memory request.
+struct DecodeTable {
+    int n_seq;
+    int pad;
+    int prefix[kDecodeMaxSeqPerLaunch + 2];   // prefix[i] = 64-token tiles of sequences [0, i), per kv head
+    SeqDev seqs[kDecodeMaxSeqPerLaunch];
+};
+cudaError_t launch_decode(const LaunchCtx &cx, const DecodeTable &tab);
 int decode_max_ctas(int n_sm);
-constexpr int kDecodeMaxSeqPerLaunch = 256;   // sized so that two decode CTAs fit the shared memory of one SM
 constexpr int kDecodePartialFloats = 16 * 128 + 32;   // acc[16][128] | m[16] | l[16]
 
 extern unsigned long long g_launch_count;

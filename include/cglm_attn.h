@@ -102,7 +102,7 @@ typedef struct cglm_attn_seq {
     int n_past;
     int n_ctx;                        /* prompt length; only CGLM_ROPE_CHATGLM derives ids from it (chatglm.cpp:1147-1151) */
     const int *position_ids;          /* optional [qlen] (or [2*qlen] for CGLM_ROPE_CHATGLM); NULL: derived from n_past, n_ctx */
-    float *out;                       /* context_layer f32 [qlen][n_head*head_dim] (chatglm.cpp:716-717) */
+    float *out;                       /* context_layer f32 [qlen][n_head*head_dim] (chatglm.cpp:716-717); 16-byte aligned */
     float *q_roped;                   /* optional f32 [qlen][n_head][head_dim]: q after RoPE, before the 1/sqrt(d) scale */
     float *k_roped;                   /* optional f32 [qlen][n_kv_head][head_dim]: k after RoPE (the reference ropes in place) */
     /* split-KV use only (zero otherwise) */
