@@ -332,17 +332,12 @@ __device__ __forceinline__ void prepare_segment(QBuf &qb, const AttnShape &sh, c
     }
 }
 
-// End-of-span merge by the four consumer warps: thread (row, 16-dim chunk) folds its piece of every part in one
-// pass with a running maximum, four parts in flight at a time.
-__device__ __forceinline__ void merge_item_cta(const ItemPos &ip, const SeqDev &sq, const AttnShape &sh, long long total,
-                                               long long nb, const float *partials, int tid) {
-    const int R = sh.R;
-    const int r = tid >> 3, d0 = (tid & 7) * 16;
-    if (r >= R) {
-        return;
-    }
-    long long b0, b1;
-    item_ctas(ip.item_begin, ip.item_begin + ip.n_tiles, total, nb, b0, b1);
+// Merge of a split item: 16 dims of one q row over all parts, in one pass with a running maximum, four parts
+// in flight at a time.  Both callers go through this one routine with the same part order, so the result does
+// not depend on which CTA, or which of its warps, happens to complete the item.
+__device__ __forceinline__ void merge_row_chunk(const ItemPos &ip, const SeqDev &sq, const AttnShape &sh, long long total,
+                                                long long nb, long long b0, long long b1, const float *partials, int r,
+                                                int d0) {
     float m_run = -INFINITY, den = 0.f;
     float acc[16];
 #pragma unroll
@@ -378,7 +373,7 @@ __device__ __forceinline__ void merge_item_cta(const ItemPos &ip, const SeqDev &
         }
         m_run = m_new;
     }
-    const int head = ip.g * R + r;
+    const int head = ip.g * sh.R + r;
     if (sq.flags & CGLM_SEQ_PARTIAL) {
         float *po = sq.partial + static_cast<long long>(head) * (kD + 2);   // row stride 130 floats: scalar stores
 #pragma unroll
@@ -394,25 +389,34 @@ __device__ __forceinline__ void merge_item_cta(const ItemPos &ip, const SeqDev &
     }
 }
 
+// End-of-span merge by the four consumer warps: thread (row, 16-dim chunk).
+__device__ __forceinline__ void merge_item_cta(const ItemPos &ip, const SeqDev &sq, const AttnShape &sh, long long total,
+                                               long long nb, const float *partials, int tid) {
+    const int r = tid >> 3;
+    if (r >= sh.R) {
+        return;
+    }
+    long long b0, b1;
+    item_ctas(ip.item_begin, ip.item_begin + ip.n_tiles, total, nb, b0, b1);
+    merge_row_chunk(ip, sq, sh, total, nb, b0, b1, partials, r, (tid & 7) * 16);
+}
+
 // Helper warp, after the consumers left a partial of a split item in scratch: count it, and if it was the
-// item's last outstanding part, merge all parts (one pass with a running maximum) and write the item's rows.
-// Lane (row, 64-dim half) handles 32 dims at a time so that the loads of two parts are in flight together.
-// The consumers' plain stores reach this warp through the shared-memory barrier it waited on; the fence below
-// publishes them (cumulatively) before the counter moves.
+// item's last outstanding part, merge all parts and write the item's rows; lane (row, 64-dim half) walks its
+// four 16-dim chunks.  The consumers' plain stores reach this warp through the shared-memory barrier it waited
+// on; the fence below publishes them (cumulatively) before the counter moves.
 __device__ __forceinline__ void finish_partial(const ItemPos &ip, const SeqDev &sq, const AttnShape &sh, long long total,
                                                long long nb, int *counters, const float *partials, int lane) {
-    const int R = sh.R, G = sh.G;
     long long b0, b1;
     item_ctas(ip.item_begin, ip.item_begin + ip.n_tiles, total, nb, b0, b1);
     const int n_parts = static_cast<int>(b1 - b0 + 1);
     int last = 0;
     if (lane == 0) {
         __threadfence();
-        int *ctr = counters + ip.seq * G + ip.g;
+        int *ctr = counters + ip.seq * sh.G + ip.g;
         last = atomicAdd(ctr, 1) == n_parts - 1;
         if (last) {
             atomicExch(ctr, 0);   // ready for the next launch
-            __threadfence();
         }
     }
     last = __shfl_sync(0xffffffffu, last, 0);
@@ -421,60 +425,11 @@ __device__ __forceinline__ void finish_partial(const ItemPos &ip, const SeqDev &
     }
     __threadfence();
     const int r = lane >> 1;
-    if (r >= R) {
+    if (r >= sh.R) {
         return;
     }
-    const int head = ip.g * R + r;
-    for (int quarter = 0; quarter < 2; ++quarter) {
-        const int d0 = (lane & 1) * 64 + quarter * 32;
-        float m_run = -INFINITY, den = 0.f;
-        float acc[32];
-#pragma unroll
-        for (int e = 0; e < 32; ++e) acc[e] = 0.f;
-        for (long long b = b0; b <= b1; b += 2) {
-            float mv[2], lv[2];
-            float4 av[2][8];
-#pragma unroll
-            for (int u = 0; u < 2; ++u) {
-                const bool ok = b + u <= b1;
-                const float *pp = part_ptr(partials, ok ? b + u : b, ip.item_begin, total, nb);
-                mv[u] = ok ? __ldcg(pp + kRows * kD + r) : -INFINITY;
-                lv[u] = __ldcg(pp + kRows * kD + kRows + r);
-#pragma unroll
-                for (int e = 0; e < 8; ++e) {
-                    av[u][e] = __ldcg(reinterpret_cast<const float4 *>(pp + r * kD + d0) + e);
-                }
-            }
-            const float m_new = fmaxf(m_run, fmaxf(mv[0], mv[1]));
-            const float keep = ex2_approx(m_run - m_new);   // 0 on the first batch
-            den *= keep;
-#pragma unroll
-            for (int e = 0; e < 32; ++e) acc[e] *= keep;
-#pragma unroll
-            for (int u = 0; u < 2; ++u) {
-                const float w = ex2_approx(mv[u] - m_new);   // 0 for the padding entry
-                den += w * lv[u];
-#pragma unroll
-                for (int e = 0; e < 8; ++e) {
-                    acc[4 * e + 0] += w * av[u][e].x; acc[4 * e + 1] += w * av[u][e].y;
-                    acc[4 * e + 2] += w * av[u][e].z; acc[4 * e + 3] += w * av[u][e].w;
-                }
-            }
-            m_run = m_new;
-        }
-        if (sq.flags & CGLM_SEQ_PARTIAL) {
-            float *po = sq.partial + static_cast<long long>(head) * (kD + 2);   // row stride 130 floats: scalar stores
-#pragma unroll
-            for (int e = 0; e < 32; ++e) po[d0 + e] = acc[e];
-            if (d0 == 0) { po[kD] = m_run * kLn2; po[kD + 1] = den; }
-        } else {
-            const float inv = 1.f / den;
-            float4 *op = reinterpret_cast<float4 *>(sq.out + static_cast<long long>(head) * kD + d0);
-#pragma unroll
-            for (int e = 0; e < 8; ++e) {
-                op[e] = make_float4(acc[4 * e] * inv, acc[4 * e + 1] * inv, acc[4 * e + 2] * inv, acc[4 * e + 3] * inv);
-            }
-        }
+    for (int q = 0; q < 4; ++q) {
+        merge_row_chunk(ip, sq, sh, total, nb, b0, b1, partials, r, (lane & 1) * 64 + q * 16);
     }
 }
 
