@@ -230,6 +230,17 @@ int ring_reserve(cglm_kv_arena *a, int n_seq, SeqDev **slot, cudaEvent_t *ev) {
 
 }  // namespace
 
+// read-only views of an arena for the other translation units of the library
+namespace cglm {
+const CUtensorMap *arena_k_map(const cglm_kv_arena *a) { return &a->k_map; }
+const CUtensorMap *arena_v_map(const cglm_kv_arena *a) { return &a->v_map; }
+bool arena_fast_decode(const cglm_kv_arena *a) { return fast_decode_shape(a); }
+int arena_device(const cglm_kv_arena *a) { return a->device; }
+int arena_sm_count(const cglm_kv_arena *a) { return a->n_sm; }
+AttnShape arena_shape(const cglm_kv_arena *a) { return make_shape(a->desc); }
+void set_last_error(const char *text) { std::snprintf(g_err, sizeof(g_err), "%s", text); }
+}  // namespace cglm
+
 extern "C" {
 
 size_t cglm_kv_slot_bytes(const cglm_attn_desc *desc) {

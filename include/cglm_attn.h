@@ -147,6 +147,24 @@ int cglm_attn_forward_host(cglm_kv_arena *arena, const cglm_attn_seq *seqs, int 
                            void *workspace, size_t workspace_bytes, void *cuda_stream);
 
 /*
+ * Decode step that brings its own scratch memory.  No counterpart in the reference; it exists for hosts that
+ * cannot hand the library a workspace when they call it: a server whose allocator already owns the whole GPU, a
+ * plugin sandbox where cudaMalloc is off limits, a loop that must stay clear of the allocator once it runs.
+ * Same work and same results as cglm_attn_forward for one-token sequences (qlen 1, flags 0, no partial output)
+ * on an arena with head_dim 128, at most 16 q heads per kv head and a cache capacity that is a multiple of 8;
+ * other shapes return CGLM_ERR_UNSUPPORTED.  The scratch is a fixed ~5 MiB array inside the library image, held
+ * by every GPU that loads the library until the process exits.  Limits per call: 128 sequences, 32 kv heads,
+ * a GPU of at most 148 SMs; beyond them the call fails with CGLM_ERR_WORKSPACE.
+ * The call allocates nothing.  The first call on each device looks up the array's device address (with that
+ * device current); make that first call before any stream capture begins.  All calls on a device share the
+ * array: two calls whose kernels can overlap on the GPU (different streams) race on it, so keep them on one
+ * stream or order them yourself.  wait_and_check != 0 synchronises the stream and returns the device-side
+ * status (0 or CGLM_ERR_TIMEOUT); otherwise the call is asynchronous like cglm_attn_forward.
+ */
+int cglm_attn_decode_static(cglm_kv_arena *arena, const cglm_attn_seq *seqs, int n_seq, int wait_and_check,
+                            void *cuda_stream);
+
+/*
  * Split-KV combine: log-sum-exp merge of n_part partials of one query token, each laid out
  * f32 [n_head][head_dim+2] (acc | m | l), all in this GPU's memory -> out f32 [n_head*head_dim].
  * The per-GPU partials come from cglm_attn_forward with CGLM_SEQ_PARTIAL.
