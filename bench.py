@@ -40,8 +40,9 @@ WORKLOADS = {
                                          theta=10000.0, interleaved=False, mask=0, seed=1003),
     "glm3_6b_decode_512": dict(H=32, G=2, D=128, M=2048, layers=1, seqs=1, n_past=(512, 512), rope=8, theta=10000.0,
                                interleaved=False, mask=0, seed=1001),
+    # BASELINE config 4: one sequence, KV length split over the GPUs, log-sum-exp combine after an all-gather
     "glm4_9b_long_131072": dict(H=32, G=2, D=128, M=131072 + 64, layers=1, seqs=1, n_past=(131072, 131072), rope=8,
-                                theta=5.0e6, interleaved=False, mask=0, seed=1004),
+                                theta=5.0e6, interleaved=False, mask=0, seed=1004, split_kv=True),
     "glm1_6b_mha_decode": dict(H=32, G=32, D=128, M=4096, layers=28, seqs=4, n_past=(2048, 2048), rope=4,
                                theta=10000.0, interleaved=True, mask=1, seed=1005),
 }
@@ -187,7 +188,118 @@ def workload_config(args, w, n_past):
             "l2_policy": "inputs larger than L2 (each launch streams its own cache slabs; a step touches every layer's)"}
 
 
+def run_split_kv(args, w):
+    """Config 4: strong scaling of ONE long sequence.  Rank r holds a contiguous slice of the KV length in its own
+    arena, runs the fused decode over it into an (acc, m, l) partial, the partials are all-gathered (NCCL) into
+    every rank's memory and merged by the log-sum-exp combine kernel.  Each step rotates through enough copies of
+    the slice that the working set is at least four times the L2."""
+    import torch
+    import torch.distributed as dist
+
+    from chatglm_cpp_b200 import _lib, sharding
+    from chatglm_cpp_b200 import attention as A
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    L = _lib.lib()
+    H, G, D = w["H"], w["G"], w["D"]
+    P = w["n_past"][0]
+    sl = sharding.split_kv(P, 0, world, rank)
+    cap = sharding.slice_capacity(P, 0, world) + 64
+    desc = _lib.AttnDesc(H, G, D, cap, 0, w["rope"], w["theta"], w["mask"])
+    local_bytes = 4 * G * D * (sl.n_local + (1 if sl.owns_new else 0))
+    n_rot = max(2, int(np.ceil(4 * 126e6 / max(local_bytes, 1))))
+    arena = A.KVArena(desc, n_rot)
+    g = torch.Generator(device="cuda"); g.manual_seed(w["seed"] + rank)
+    arena.k_all().view(-1).copy_(torch.randn(arena.k_all().numel(), device="cuda", generator=g).half())
+    arena.v_all().view(-1).copy_(torch.randn(arena.v_all().numel(), device="cuda", generator=g).half())
+    ws = A.Workspace(desc, 1, 1)
+    g0 = torch.Generator(device="cuda"); g0.manual_seed(w["seed"])           # q is replicated on every rank
+    qkv = torch.randn(1, qkv_row(w), device="cuda", generator=g0)
+    partial = torch.zeros(H, D + 2, device="cuda")
+    gathered = torch.zeros(world, H, D + 2, device="cuda")
+    out = torch.zeros(H * D, device="cuda")
+    flags = _lib.SEQ_PARTIAL | _lib.SEQ_USE_KV_LOCAL | (0 if sl.owns_new else _lib.SEQ_NO_APPEND)
+    arrs = []
+    for s in range(n_rot):
+        arr = (_lib.AttnSeq * 1)()
+        A.fill_seq(arr[0], desc, A.SeqCall(qkv=qkv, slot=s, n_past=P, partial=partial, kv_local=sl.n_local, flags=flags), False)
+        arrs.append(arr)
+    stream = torch.cuda.current_stream().cuda_stream
+    it = [0]
+
+    def step():
+        rc = L.cglm_attn_forward(arena._h, arrs[it[0] % n_rot], 1, ws.ptr, ws.bytes, stream)
+        if rc != 0:
+            raise _lib.CglmError(rc, "cglm_attn_forward")
+        it[0] += 1
+        if world > 1:
+            dist.all_gather_into_tensor(gathered, partial)
+            A.splitkv_combine(gathered, out)
+        else:
+            A.splitkv_combine(partial.unsqueeze(0), out)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sampler = ClockSampler(local); sampler.start()
+    launches0 = L.cglm_launch_count()
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    barrier()
+    clocks = sampler.finish()
+    launches = L.cglm_launch_count() - launches0
+    ms = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([ms], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    if ws.status() != 0:
+        raise SystemExit("device-side status is not clean after the timed region")
+    peak, peak_src = HBM_FALLBACK_GBS, "fallback"
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            peak, peak_src = float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        pass
+    if rank == 0:
+        step_ms = ms / args.steps
+        achieved = local_bytes / (step_ms * 1e-3) / 1e9
+        line = {
+            "metric": "decode_attention_tokens_per_s", "value": args.steps / (ms * 1e-3), "unit": "tokens/s",
+            "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": step_ms,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+            "config": {"workload": args.workload, "n_head": H, "n_kv_head": G, "head_dim": D, "n_past": P,
+                       "kv_bytes_total": 4 * G * D * (P + 1), "kv_bytes_this_rank": local_bytes,
+                       "parallelism": f"KV length split x{world}, all-gather of {H * (D + 2) * 4} B per rank + LSE combine",
+                       "l2_policy": f"rotates through {n_rot} copies of the slice (working set >= 4 x L2)"},
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                         "peak_source": peak_src, "kernel": "decode_kernel (+ all-gather + combine in the step time)",
+                         "algorithmic_bytes_per_launch": local_bytes, "launch_us": step_ms * 1e3, "traffic": None},
+            "cpu_baseline": None, "e2e": None, "gpu_launches": int(launches) * world, "clocks": clocks,
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
 def run_ours(args, w):
+    if w.get("split_kv"):
+        return run_split_kv(args, w)
     import torch
     import torch.distributed as dist
 
