@@ -85,7 +85,7 @@ size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 struct WsLayout {
     size_t counters, partials, seqs, q_stage, total;
 };
-WsLayout ws_layout(const cglm_attn_desc &d, int n_sm, int n_seq, long long n_tokens) {
+WsLayout ws_layout(const cglm_attn_desc &d, int n_sm, int n_seq, long long n_tokens, size_t prefill_bytes = 0) {
     WsLayout w;
     size_t off = sizeof(WsHeader);
     w.counters = off;
@@ -94,8 +94,12 @@ WsLayout ws_layout(const cglm_attn_desc &d, int n_sm, int n_seq, long long n_tok
     off = align_up(off + sizeof(float) * kDecodePartialFloats * 2 * static_cast<size_t>(decode_max_ctas(n_sm)), 256);
     w.seqs = off;
     off = align_up(off + sizeof(SeqDev) * static_cast<size_t>(n_seq), 256);
+    off = align_up(off, 1024);
     w.q_stage = off;
-    off = align_up(off + sizeof(float) * static_cast<size_t>(n_tokens) * d.n_head * d.head_dim, 256);
+    // roped, scaled q of the generic path (f32) or of one tcgen05 prefill (f16); used one launch at a time
+    size_t stage = sizeof(float) * static_cast<size_t>(n_tokens) * d.n_head * d.head_dim;
+    if (prefill_bytes > stage) stage = prefill_bytes;
+    off = align_up(off + stage, 1024);
     w.total = off;
     return w;
 }
@@ -163,6 +167,42 @@ bool build_tensor_maps(cglm_kv_arena *a) {
         if (enc(&a->v_map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, a->v_base, dims, strides, box, estr,
                 CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+            return false;
+    }
+    return true;
+}
+
+// Per-call maps of the tcgen05 prefill: q staging f16 [H][s_pad][128]; the slot's K rows and V^T rows cut at the
+// attended length L, so that tokens past it read as zero whatever the cache holds there.
+bool build_prefill_maps(const cglm_kv_arena *a, void *q_half, int s_pad, int L, CUtensorMap *q_map, CUtensorMap *k_map,
+                        CUtensorMap *v_map) {
+    EncodeTiledFn enc = encode_tiled_fn();
+    if (!enc) return false;
+    const cglm_attn_desc &d = a->desc;
+    const cuuint64_t rows = static_cast<cuuint64_t>(a->n_slots) * d.n_kv_head;
+    const cuuint32_t estr3[3] = {1, 1, 1}, estr2[2] = {1, 1};
+    {
+        cuuint64_t dims[3] = {128, static_cast<cuuint64_t>(s_pad), static_cast<cuuint64_t>(d.n_head)};
+        cuuint64_t strides[2] = {256, static_cast<cuuint64_t>(s_pad) * 256};
+        cuuint32_t box[3] = {64, 128, 1};
+        if (enc(q_map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, q_half, dims, strides, box, estr3, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+            return false;
+    }
+    {
+        cuuint64_t dims[3] = {128, static_cast<cuuint64_t>(L), rows};
+        cuuint64_t strides[2] = {256, static_cast<cuuint64_t>(d.max_len) * 256};
+        cuuint32_t box[3] = {64, 128, 1};
+        if (enc(k_map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, a->k_base, dims, strides, box, estr3, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+            return false;
+    }
+    {
+        cuuint64_t dims[2] = {static_cast<cuuint64_t>(L), rows * 128};
+        cuuint64_t strides[1] = {static_cast<cuuint64_t>(d.max_len) * 2};
+        cuuint32_t box[2] = {64, 128};
+        if (enc(v_map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, a->v_base, dims, strides, box, estr2, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
             return false;
     }
     return true;
@@ -373,8 +413,10 @@ int cglm_attn_forward(cglm_kv_arena *a, const cglm_attn_seq *seqs, int n_seq, vo
 
     // ---- validate and classify ---------------------------------------------------------------------------
     long long gen_tokens = 0, decode_tiles = 0;
-    int n_fast = 0;
-    std::vector<unsigned char> is_fast(n_seq);
+    int n_fast = 0, n_prefill = 0;
+    size_t prefill_bytes = 0;
+    std::vector<unsigned char> is_fast(n_seq);   // 0: generic path, 1: fused decode, 2: tcgen05 prefill
+    const bool prefill_ok = a->has_tmaps && d.head_dim == 128 && d.max_len % 8 == 0;
     for (int i = 0; i < n_seq; ++i) {
         const cglm_attn_seq &s = seqs[i];
         if (!s.q || !s.k || !s.v || s.qlen <= 0 || s.n_past < 0 || s.slot < 0 || s.slot >= a->n_slots)
@@ -398,11 +440,16 @@ int cglm_attn_forward(cglm_kv_arena *a, const cglm_attn_seq *seqs, int n_seq, vo
         if (is_fast[i]) {
             ++n_fast;
             decode_tiles += static_cast<long long>((L + kDecodeTile - 1) / kDecodeTile) * d.n_kv_head;
+        } else if (prefill_ok && s.qlen >= kPrefillMinTokens && s.n_past == 0 && s.flags == 0) {
+            is_fast[i] = 2;
+            ++n_prefill;
+            const size_t need = prefill_q_half_bytes(d.n_head, s.qlen);
+            if (need > prefill_bytes) prefill_bytes = need;
         } else {
             gen_tokens += s.qlen;
         }
     }
-    const WsLayout lay = ws_layout(d, a->n_sm, n_seq, gen_tokens);
+    const WsLayout lay = ws_layout(d, a->n_sm, n_seq, gen_tokens, prefill_bytes);
     if (workspace_bytes < lay.total) return CGLM_ERR_WORKSPACE;
 
     // ---- descriptors ---------------------------------------------------------------------------------------
@@ -438,7 +485,7 @@ int cglm_attn_forward(cglm_kv_arena *a, const cglm_attn_seq *seqs, int n_seq, vo
         int filled = 0;
         tab.prefix[0] = 0;
         for (int i = 0; i <= n_seq; ++i) {
-            if (i < n_seq && is_fast[i]) {
+            if (i < n_seq && is_fast[i] == 1) {
                 SeqDev &o = tab.seqs[filled];
                 to_dev(seqs[i], o);
                 const int L = o.kv_before + ((o.flags & CGLM_SEQ_NO_APPEND) ? 0 : 1);
@@ -454,7 +501,21 @@ int cglm_attn_forward(cglm_kv_arena *a, const cglm_attn_seq *seqs, int n_seq, vo
         }
     }
     // generic path: descriptors are uploaded through the pinned ring
-    const int n_gen = n_seq - n_fast;
+    // tcgen05 prefill: one pair of launches per prompt, tensor maps encoded for this call
+    for (int i = 0; i < n_seq && n_prefill > 0; ++i) {
+        if (is_fast[i] != 2) continue;
+        SeqDev sq;
+        to_dev(seqs[i], sq);
+        const int s_pad = (sq.qlen + 127) / 128 * 128;
+        CUtensorMap q_map, k_map, v_map;
+        __half *q_half = reinterpret_cast<__half *>(ws + lay.q_stage);
+        if (!build_prefill_maps(a, q_half, s_pad, d.n_virtual + sq.qlen, &q_map, &k_map, &v_map)) {
+            std::snprintf(g_err, sizeof(g_err), "cuTensorMapEncodeTiled failed for a prefill call");
+            return CGLM_ERR_CUDA;
+        }
+        CGLM_CUDA(launch_prefill(cx, sq, q_map, k_map, v_map, q_half));
+    }
+    const int n_gen = n_seq - n_fast - n_prefill;
     if (n_gen > 0) {
         std::lock_guard<std::mutex> lock(a->mu);
         SeqDev *host = nullptr;
@@ -463,7 +524,7 @@ int cglm_attn_forward(cglm_kv_arena *a, const cglm_attn_seq *seqs, int n_seq, vo
         if (rc != CGLM_OK) return rc;
         int gi = 0, tok = 0;
         for (int i = 0; i < n_seq; ++i) {
-            if (is_fast[i]) continue;
+            if (is_fast[i]) continue;   // fused decode and tcgen05 prefill sequences were launched above
             SeqDev &o = host[gi++];
             to_dev(seqs[i], o);
             o.tok_begin = tok;

@@ -250,6 +250,12 @@ struct DecodeTable {
     SeqDev seqs[kDecodeMaxSeqPerLaunch];
 };
 cudaError_t launch_decode(const LaunchCtx &cx, const DecodeTable &tab);
+// tcgen05 prefill (head_dim 128, n_past == 0, qlen >= 128): per-call tensor maps over the f16 q staging buffer
+// [H][s_pad][D] and over the slot's caches cut at the attended length
+size_t prefill_q_half_bytes(int H, int S);
+cudaError_t launch_prefill(const LaunchCtx &cx, const SeqDev &sq, const CUtensorMap &q_map, const CUtensorMap &k_map,
+                           const CUtensorMap &v_map, __half *q_half);
+constexpr int kPrefillMinTokens = 128;
 int decode_max_ctas(int n_sm);
 constexpr int kDecodePartialFloats = 16 * 128 + 32;   // acc[16][128] | m[16] | l[16]
 

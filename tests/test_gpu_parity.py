@@ -163,6 +163,48 @@ def test_prefill_then_decode(H, G, D, M, V, rope, mask, S):
     assert ws.status() == 0
 
 
+@pytest.mark.parametrize("H,G,M,V,rope,mask,S", [
+    (32, 2, 2048, 0, O.ROPE_CHATGLM2, O.MASK_CAUSAL, 1024),   # BASELINE config 2
+    (32, 2, 2048, 0, O.ROPE_CHATGLM2, O.MASK_CAUSAL, 128),
+    (8, 2, 512, 0, O.ROPE_CHATGLM2, O.MASK_CAUSAL, 129),
+    (8, 2, 512 + 8, 8, O.ROPE_CHATGLM2, O.MASK_CAUSAL, 300),  # P-Tuning prefix in front of the prompt
+    (8, 8, 512, 0, O.ROPE_CHATGLM, O.MASK_CHATGLM, 200),      # v1: MHA, interleaved qkv, 2-D rope, prefix mask
+    (4, 1, 264, 0, O.ROPE_DISABLED, O.MASK_CAUSAL, 256),
+])
+def test_prefill_tensor_core_path(H, G, M, V, rope, mask, S):
+    """Prompts of >= 128 tokens at head_dim 128 take the tcgen05 kernel: parity of output, RoPE and cache, then a
+    decode step on top of the cache it wrote."""
+    A = _A()
+    desc = make_desc(H, G, 128, M, V, rope, 10000.0, mask)
+    inter = rope == O.ROPE_CHATGLM
+    rng = np.random.default_rng(S + H)
+    arena, ws = A.KVArena(desc, 1), A.Workspace(desc, 1, S)
+    attn = A.BasicAttention(arena, 0, ws, inter)
+    cfg = oracle_cfg(desc, "f32")
+    k, v = random_cache(rng, desc, V)
+    upload_cache(arena, 0, k, v)
+    n_past = 0
+    launches = []
+    from chatglm_cpp_b200 import _lib
+    for qlen in (S, 1):
+        qkv = rng.standard_normal((qlen, qkv_width(desc, inter))).astype(np.float32)
+        before = _lib.lib().cglm_launch_count()
+        out, qr, kr = attn.forward(torch.from_numpy(qkv).cuda(), n_past, n_ctx=S, want_roped=True)
+        torch.cuda.synchronize()
+        launches.append(_lib.lib().cglm_launch_count() - before)
+        assert ws.status() == 0
+        want, oqr, okr = O.attn_forward(cfg, qkv, inter, k, v, n_past, n_ctx=S, want_roped=True)
+        assert_out_close(out.cpu().numpy(), want, f"qlen {qlen} n_past {n_past}")
+        assert ulp_distance(qr.cpu().numpy(), oqr).max() <= ROPE_MAX_ULP
+        assert ulp_distance(kr.cpu().numpy(), okr).max() <= ROPE_MAX_ULP
+        n_past += qlen
+    gk, gv = download_cache(arena, 0)
+    np.testing.assert_array_equal(gk, k)
+    np.testing.assert_array_equal(gv, v)
+    assert launches == [2, 1]   # prepare + tcgen05 attention, then one fused decode launch
+    arena.close()
+
+
 def test_explicit_position_ids_match_derived():
     A = _A()
     desc = make_desc(32, 32, 128, 512, rope=O.ROPE_CHATGLM, mask=O.MASK_CHATGLM)
