@@ -375,7 +375,9 @@ size_t cglm_attn_workspace_bytes(const cglm_attn_desc *desc, int n_seq, int max_
     if (!desc_ok(desc) || n_seq <= 0 || max_qlen <= 0) return 0;
     int n_sm = 148, major = 0;
     device_sm_count(&n_sm, &major);   // falls back to a B200's SM count when no device is visible
-    return ws_layout(*desc, n_sm, n_seq, static_cast<long long>(n_seq) * max_qlen).total;
+    // a prompt of >= 128 tokens at head_dim 128 may take the tensor-core prefill, whose staging is sized differently
+    const size_t prefill = desc->head_dim == 128 && max_qlen >= kPrefillMinTokens ? prefill_q_half_bytes(desc->n_head, max_qlen) : 0;
+    return ws_layout(*desc, n_sm, n_seq, static_cast<long long>(n_seq) * max_qlen, prefill).total;
 }
 
 int cglm_attn_workspace_init(void *workspace, size_t workspace_bytes, void *cuda_stream) {
@@ -416,7 +418,9 @@ int cglm_attn_forward(cglm_kv_arena *a, const cglm_attn_seq *seqs, int n_seq, vo
     int n_fast = 0, n_prefill = 0;
     size_t prefill_bytes = 0;
     std::vector<unsigned char> is_fast(n_seq);   // 0: generic path, 1: fused decode, 2: tcgen05 prefill
-    const bool prefill_ok = a->has_tmaps && d.head_dim == 128 && d.max_len % 8 == 0;
+    const bool prefill_ok = a->has_tmaps && d.head_dim == 128 && d.max_len % 8 == 0 &&
+                            (d.rope_type == CGLM_ROPE_CHATGLM2 || d.rope_type == CGLM_ROPE_CHATGLM ||
+                             d.rope_type == CGLM_ROPE_DISABLED);
     for (int i = 0; i < n_seq; ++i) {
         const cglm_attn_seq &s = seqs[i];
         if (!s.q || !s.k || !s.v || s.qlen <= 0 || s.n_past < 0 || s.slot < 0 || s.slot >= a->n_slots)
