@@ -38,6 +38,11 @@ WORKLOADS = {
     # 1/20 of the default workload (2 layers, 1 GiB of caches): small enough for an ncu --set full capture
     "glm4_9b_batched_decode_small": dict(H=32, G=2, D=128, M=8192, layers=2, seqs=64, n_past=(1024, 8191), rope=8,
                                          theta=10000.0, interleaved=False, mask=0, seed=1003),
+    # the default workload's layer call at other batch sizes: separates fixed per-launch cost from streaming rate
+    "glm4_9b_batched_decode_b32": dict(H=32, G=2, D=128, M=8192, layers=40, seqs=32, n_past=(1024, 8191), rope=8,
+                                       theta=10000.0, interleaved=False, mask=0, seed=1003),
+    "glm4_9b_batched_decode_b128": dict(H=32, G=2, D=128, M=8192, layers=20, seqs=128, n_past=(1024, 8191), rope=8,
+                                        theta=10000.0, interleaved=False, mask=0, seed=1003),
     "glm3_6b_decode_512": dict(H=32, G=2, D=128, M=2048, layers=1, seqs=1, n_past=(512, 512), rope=8, theta=10000.0,
                                interleaved=False, mask=0, seed=1001),
     # BASELINE config 4: one sequence, KV length split over the GPUs, log-sum-exp combine after an all-gather

@@ -63,6 +63,7 @@ struct __align__(1024) DecodeSmem {
     uint8_t stage[kStages][kStageBytes];
     QBuf qb[2];
     float xchg[kRows * kXchgStride + 2 * kRows];   // fold buffer: one 64-dim half of a warp's O, its m and l
+    int prefix[kDecodeMaxSeqPerLaunch + 2];        // copy of the launch's tile prefix sums (parameter space is slow to index)
     uint64_t full[kStages];
     uint64_t empty[kStages];
     uint64_t qfull[2];
@@ -457,11 +458,15 @@ decode_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__
         mbar_init(&sm.pdone[1], 1);
         fence_mbar_init();
     }
-    __syncthreads();
-    // The sequence descriptors and the prefix sums of their tile counts arrive as kernel parameters: no load
-    // stands between the launch and the first TMA request.
+    // The sequence descriptors and the prefix sums of their tile counts arrive as kernel parameters: no upload
+    // precedes the launch.  The prefix sums are searched by every role, so they are copied to shared memory once
+    // (dependent reads of parameter space miss the small constant cache one after another).
     const int n_seq = tab.n_seq;
-    const long long total = static_cast<long long>(tab.prefix[n_seq]) * G;
+    for (int i = tid; i <= n_seq; i += kThreads) {
+        sm.prefix[i] = tab.prefix[i];
+    }
+    __syncthreads();
+    const long long total = static_cast<long long>(sm.prefix[n_seq]) * G;
     const long long nb = gridDim.x;
     const long long span_lo = span_start(blockIdx.x, total, nb), span_hi = span_start(blockIdx.x + 1, total, nb);
     if (span_lo >= span_hi) {
@@ -473,15 +478,19 @@ decode_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__
         if (lane == 0) {
             tma_prefetch_desc(&k_map);
             tma_prefetch_desc(&v_map);
-            mbar_wait_bounded(&sm.hstart, 0, &sm.abort_flag);
             long long pos = span_lo;
             unsigned int n = 0;
             while (pos < span_hi && !sm.abort_flag) {
-                const ItemPos ip = locate(tab.prefix, n_seq, G, pos);
+                const ItemPos ip = locate(sm.prefix, n_seq, G, pos);
                 const int row = tab.seqs[ip.seq].slot * G + ip.g;
                 const long long seg_end = min(span_hi, ip.item_begin + ip.n_tiles);
                 for (int t = ip.tile; pos < seg_end; ++t, ++pos, ++n) {
                     const int st = n % kStages;
+                    if (n == 1) {
+                        // The first tile goes out at once; the rest of the ring's initial burst waits until the helper
+                        // warp has issued the first segment's few small loads, so that they do not queue behind it.
+                        mbar_wait_bounded(&sm.hstart, 0, &sm.abort_flag);
+                    }
                     if (!mbar_wait_bounded(&sm.empty[st], ((n / kStages) & 1u) ^ 1u, &sm.abort_flag)) break;
                     uint8_t *dst = sm.stage[st];
                     mbar_arrive_expect_tx(&sm.full[st], kStageBytes);
@@ -501,7 +510,7 @@ decode_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__
         ItemPos prev_ip{};
         SeqDev prev_sq{};
         while (pos < span_hi && !sm.abort_flag) {
-            const ItemPos ip = locate(tab.prefix, n_seq, G, pos);
+            const ItemPos ip = locate(sm.prefix, n_seq, G, pos);
             const SeqDev sq = tab.seqs[ip.seq];
             const long long item_end = ip.item_begin + ip.n_tiles;
             const long long seg_end = min(span_hi, item_end);
@@ -536,7 +545,7 @@ decode_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__
         unsigned int n = 0, sidx = 0;
         bool first_segment = true;
         while (pos < span_hi) {
-            const ItemPos ip = locate(tab.prefix, n_seq, G, pos);
+            const ItemPos ip = locate(sm.prefix, n_seq, G, pos);
             const int g = ip.g;
             const long long item_end = ip.item_begin + ip.n_tiles;
             const long long seg_end = min(span_hi, item_end);
@@ -599,6 +608,53 @@ decode_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__
                 l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 1);
                 l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 2);
             }
+            if (seg_end == span_hi) {
+                // Last segment of the span: the tile ring is idle (every tile has been loaded and consumed), so it
+                // serves as one exchange area per warp and the fold takes two barriers instead of twelve.
+                constexpr int kStride = 132;
+                float *area = reinterpret_cast<float *>(sm.stage[0]);   // [3 warps][16 rows * 132 + 32]
+                named_bar_sync(1, kConsumerThreads);                     // every warp has finished reading its tiles
+                if (warp > 0) {
+                    float *mine = area + (warp - 1) * (kRows * kStride + 2 * kRows);
+#pragma unroll
+                    for (int nd = 0; nd < 16; ++nd) {
+                        *reinterpret_cast<float2 *>(&mine[quad_row * kStride + 8 * nd + 2 * c]) = make_float2(o[nd][0], o[nd][1]);
+                        *reinterpret_cast<float2 *>(&mine[(quad_row + 8) * kStride + 8 * nd + 2 * c]) = make_float2(o[nd][2], o[nd][3]);
+                    }
+                    if (c == 0) {
+                        mine[kRows * kStride + quad_row] = m_run[0];
+                        mine[kRows * kStride + quad_row + 8] = m_run[1];
+                        mine[kRows * kStride + kRows + quad_row] = l_run[0];
+                        mine[kRows * kStride + kRows + quad_row + 8] = l_run[1];
+                    }
+                }
+                named_bar_sync(1, kConsumerThreads);
+                if (warp == 0) {
+                    for (int src = 1; src < kConsumerWarps; ++src) {
+                        const float *theirs = area + (src - 1) * (kRows * kStride + 2 * kRows);
+                        float a_me[2], a_src[2];
+#pragma unroll
+                        for (int h = 0; h < 2; ++h) {
+                            const float m_src = theirs[kRows * kStride + quad_row + 8 * h];
+                            const float l_src = theirs[kRows * kStride + kRows + quad_row + 8 * h];
+                            const float m_new = fmaxf(m_run[h], m_src);
+                            a_me[h] = ex2_approx(m_run[h] - m_new);
+                            a_src[h] = ex2_approx(m_src - m_new);
+                            l_run[h] = l_run[h] * a_me[h] + l_src * a_src[h];
+                            m_run[h] = m_new;
+                        }
+#pragma unroll
+                        for (int nd = 0; nd < 16; ++nd) {
+                            const float2 lo2 = *reinterpret_cast<const float2 *>(&theirs[quad_row * kStride + 8 * nd + 2 * c]);
+                            const float2 hi2 = *reinterpret_cast<const float2 *>(&theirs[(quad_row + 8) * kStride + 8 * nd + 2 * c]);
+                            o[nd][0] = o[nd][0] * a_me[0] + lo2.x * a_src[0];
+                            o[nd][1] = o[nd][1] * a_me[0] + lo2.y * a_src[0];
+                            o[nd][2] = o[nd][2] * a_me[1] + hi2.x * a_src[1];
+                            o[nd][3] = o[nd][3] * a_me[1] + hi2.y * a_src[1];
+                        }
+                    }
+                }
+            } else
             for (int src = 1; src < kConsumerWarps; ++src) {
                 float a_me[2] = {1.f, 1.f}, a_src[2] = {0.f, 0.f};
 #pragma unroll
@@ -696,9 +752,10 @@ decode_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__
                         // end of the span: nothing left to overlap with, all four warps finish the item
                         long long b0, b1;
                         item_ctas(ip.item_begin, item_end, total, nb, b0, b1);
-                        __threadfence();
                         int *ctr = counters + ip.seq * G + g;
-                        const int last = atomicAdd(ctr, 1) == static_cast<int>(b1 - b0);
+                        int old;   // release: the warp's partial stores (ordered before by __syncwarp); acquire: the others'
+                        asm volatile("atom.acq_rel.gpu.global.add.s32 %0, [%1], 1;" : "=r"(old) : "l"(ctr) : "memory");
+                        const int last = old == static_cast<int>(b1 - b0);
                         if (last) atomicExch(ctr, 0);
                         sm.last_flag = last;
                     }

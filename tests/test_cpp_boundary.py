@@ -1,0 +1,29 @@
+"""Runs the C++ test of the chatglm::BasicAttention mirror (tests/cpp/test_basic_attention.cpp) on the GPU."""
+import os
+import subprocess
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.mark.gpu
+def test_cpp_basic_attention_mirror():
+    from chatglm_cpp_b200 import build
+    from oracle import attn_oracle
+    build.build()
+    attn_oracle.build()
+    exe = build.build_cpp_test()
+    r = subprocess.run([exe], capture_output=True, text=True, timeout=600)
+    print(r.stdout, r.stderr)
+    assert r.returncode == 0, r.stdout + r.stderr
+    assert "ALL OK" in r.stdout
+
+
+def test_cpp_boundary_test_builds():
+    """CPU check: the C++ mirror's test program compiles and links against the library and the oracle."""
+    from chatglm_cpp_b200 import build
+    from oracle import attn_oracle
+    build.build()
+    attn_oracle.build()
+    assert os.path.exists(build.build_cpp_test())
