@@ -333,23 +333,47 @@ __device__ __forceinline__ void prepare_segment(QBuf &qb, const AttnShape &sh, c
     }
 }
 
-// Merge of a split item: 16 dims of one q row over all parts, in one pass with a running maximum, four parts
-// in flight at a time.  Both callers go through this one routine with the same part order, so the result does
-// not depend on which CTA, or which of its warps, happens to complete the item.
-__device__ __forceinline__ void merge_row_chunk(const ItemPos &ip, const SeqDev &sq, const AttnShape &sh, long long total,
-                                                long long nb, long long b0, long long b1, const float *partials, int r,
-                                                int d0) {
+// ---- completion of split items ------------------------------------------------------------------------------
+// An item cut across CTAs is completed by whichever CTA delivers its last part (atomic counters, nobody waits).
+// Items of up to kMergeFan parts are merged in one step.  Longer ones (one very long sequence covers hundreds of
+// CTAs) go through a two-level tree so that no thread walks hundreds of parts one batch after another: CTAs are
+// grouped kMergeFan at a time by their index; the last CTA of a group to finish merges the item's parts inside the
+// group into a group partial, and the last group to finish merges the group partials.
+constexpr int kMergeFan = kDecodeMergeFan;
+
+struct MergeCtx {
+    long long total, nb;   // tiles on the line, CTAs of the launch
+    int *counters;         // per item: parts delivered (short items) or groups delivered (long items)
+    int *gcounters;        // per (CTA group, slot): parts of the long item in that slot delivered
+    float *partials;       // per (CTA, slot)
+    float *gpartials;      // per (CTA group, slot)
+};
+// A CTA group holds parts of at most two long items: one that began in an earlier group (slot 0) and one that
+// begins inside the group (slot 1).
+__device__ __forceinline__ int group_slot(long long grp, long long b0) { return b0 < grp * kMergeFan ? 0 : 1; }
+
+// 16 dims of one q row merged over sources k0..k1 in one pass with a running maximum, four sources in flight at a
+// time.  Sources are CTA partials (level 0) or group partials (level 1).  Every caller goes through this routine
+// with the same source order, so the result does not depend on which CTA or warp happens to complete the item.
+// to_group >= 0: the result is itself a group partial (un-normalised); otherwise it is the item's output.
+__device__ __forceinline__ void merge_row_chunk(const ItemPos &ip, const SeqDev &sq, const AttnShape &sh, const MergeCtx &mc,
+                                                bool from_groups, long long b0, long long k0, long long k1, long long to_group,
+                                                int r, int d0) {
+    auto source = [&](long long k) -> const float * {
+        return from_groups ? mc.gpartials + (k * 2 + group_slot(k, b0)) * kDecodePartialFloats
+                           : part_ptr(mc.partials, k, ip.item_begin, mc.total, mc.nb);
+    };
     float m_run = -INFINITY, den = 0.f;
     float acc[16];
 #pragma unroll
     for (int e = 0; e < 16; ++e) acc[e] = 0.f;
-    for (long long b = b0; b <= b1; b += 4) {
+    for (long long k = k0; k <= k1; k += 4) {
         float mv[4], lv[4];
         float4 av[4][4];
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
-            const bool ok = b + u <= b1;
-            const float *pp = part_ptr(partials, ok ? b + u : b, ip.item_begin, total, nb);
+            const bool ok = k + u <= k1;
+            const float *pp = source(ok ? k + u : k);
             mv[u] = ok ? __ldcg(pp + kRows * kD + r) : -INFINITY;
             lv[u] = __ldcg(pp + kRows * kD + kRows + r);
 #pragma unroll
@@ -375,7 +399,15 @@ __device__ __forceinline__ void merge_row_chunk(const ItemPos &ip, const SeqDev 
         m_run = m_new;
     }
     const int head = ip.g * sh.R + r;
-    if (sq.flags & CGLM_SEQ_PARTIAL) {
+    if (to_group >= 0) {
+        float *gp = mc.gpartials + (to_group * 2 + group_slot(to_group, b0)) * kDecodePartialFloats;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            __stcg(reinterpret_cast<float4 *>(gp + r * kD + d0) + e,
+                   make_float4(acc[4 * e], acc[4 * e + 1], acc[4 * e + 2], acc[4 * e + 3]));
+        }
+        if (d0 == 0) { __stcg(gp + kRows * kD + r, m_run); __stcg(gp + kRows * kD + kRows + r, den); }
+    } else if (sq.flags & CGLM_SEQ_PARTIAL) {
         float *po = sq.partial + static_cast<long long>(head) * (kD + 2);   // row stride 130 floats: scalar stores
 #pragma unroll
         for (int e = 0; e < 16; ++e) po[d0 + e] = acc[e];
@@ -390,54 +422,53 @@ __device__ __forceinline__ void merge_row_chunk(const ItemPos &ip, const SeqDev 
     }
 }
 
-// End-of-span merge by the four consumer warps: thread (row, 16-dim chunk).
-__device__ __forceinline__ void merge_item_cta(const ItemPos &ip, const SeqDev &sq, const AttnShape &sh, long long total,
-                                               long long nb, const float *partials, int tid) {
-    const int r = tid >> 3;
-    if (r >= sh.R) {
-        return;
-    }
-    long long b0, b1;
-    item_ctas(ip.item_begin, ip.item_begin + ip.n_tiles, total, nb, b0, b1);
-    merge_row_chunk(ip, sq, sh, total, nb, b0, b1, partials, r, (tid & 7) * 16);
+__device__ __forceinline__ int count_part(int *ctr, int expected) {
+    int old;   // release: this CTA's partial stores; acquire: the other CTAs'
+    asm volatile("atom.acq_rel.gpu.global.add.s32 %0, [%1], 1;" : "=r"(old) : "l"(ctr) : "memory");
+    const int last = old == expected - 1;
+    if (last) atomicExch(ctr, 0);   // ready for the next launch
+    return last;
 }
 
-// Helper warp, after the consumers left a partial of a split item in scratch: count it, and if it was the
-// item's last outstanding part, merge all parts and write the item's rows; lane (row, 64-dim half) walks its
-// four 16-dim chunks.  The consumers' plain stores reach this warp through the shared-memory barrier it waited
-// on; the fence below publishes them (cumulatively) before the counter moves.
-__device__ __forceinline__ void finish_partial(const ItemPos &ip, const SeqDev &sq, const AttnShape &sh, long long total,
-                                               long long nb, int *counters, const float *partials, int lane) {
+// Called by a team of n_thr threads (the four consumer warps at the end of a span, or the helper warp in the
+// middle of one) after CTA `b` stored its part of item `ip`.  t: index inside the team; lead(f): synchronises the
+// team (ordering its memory operations), lets the team leader evaluate f() and hands the result to every member.
+template <class Lead>
+__device__ __forceinline__ void deliver_part(const ItemPos &ip, const SeqDev &sq, const AttnShape &sh, const MergeCtx &mc,
+                                             long long b, int t, int n_thr, Lead lead) {
     long long b0, b1;
-    item_ctas(ip.item_begin, ip.item_begin + ip.n_tiles, total, nb, b0, b1);
+    item_ctas(ip.item_begin, ip.item_begin + ip.n_tiles, mc.total, mc.nb, b0, b1);
     const int n_parts = static_cast<int>(b1 - b0 + 1);
-    int last = 0;
-    if (lane == 0) {
-        __threadfence();
-        int *ctr = counters + ip.seq * sh.G + ip.g;
-        last = atomicAdd(ctr, 1) == n_parts - 1;
-        if (last) {
-            atomicExch(ctr, 0);   // ready for the next launch
+    const int item = ip.seq * sh.G + ip.g;
+    auto merge = [&](bool from_groups, long long k0, long long k1, long long to_group) {
+        for (int chunk = t; chunk < kRows * 8; chunk += n_thr) {
+            const int r = chunk >> 3;
+            if (r < sh.R) merge_row_chunk(ip, sq, sh, mc, from_groups, b0, k0, k1, to_group, r, (chunk & 7) * 16);
         }
-    }
-    last = __shfl_sync(0xffffffffu, last, 0);
-    if (!last) {
+    };
+    if (n_parts <= kMergeFan) {
+        if (!lead([&] { return count_part(mc.counters + item, n_parts); })) return;
+        __threadfence();
+        merge(false, b0, b1, -1);
         return;
     }
+    const long long grp = b / kMergeFan;
+    const long long gb0 = max(b0, grp * kMergeFan), gb1 = min(b1, grp * kMergeFan + kMergeFan - 1);
+    if (!lead([&] { return count_part(mc.gcounters + grp * 2 + group_slot(grp, b0), static_cast<int>(gb1 - gb0 + 1)); })) return;
     __threadfence();
-    const int r = lane >> 1;
-    if (r >= sh.R) {
-        return;
-    }
-    for (int q = 0; q < 4; ++q) {
-        merge_row_chunk(ip, sq, sh, total, nb, b0, b1, partials, r, (lane & 1) * 64 + q * 16);
-    }
+    merge(false, gb0, gb1, grp);
+    __threadfence();   // every member publishes its piece of the group partial before the leader counts the group
+    const long long g0 = b0 / kMergeFan, g1 = b1 / kMergeFan;
+    if (!lead([&] { return count_part(mc.counters + item, static_cast<int>(g1 - g0 + 1)); })) return;
+    __threadfence();
+    merge(true, g0, g1, -1);
 }
 
 __global__ void __launch_bounds__(kThreads, 2)
 decode_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map,
               const __grid_constant__ DecodeTable tab, AttnShape sh, uint16_t *__restrict__ k_base,
-              uint16_t *__restrict__ v_base, WsHeader *hdr, int *counters, float *partials) {
+              uint16_t *__restrict__ v_base, WsHeader *hdr, int *counters, int *gcounters, float *partials,
+              float *gpartials) {
     extern __shared__ uint8_t smem_raw[];
     DecodeSmem &sm = *reinterpret_cast<DecodeSmem *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -503,6 +534,13 @@ decode_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__
         }
     } else if (warp == kHelperWarp) {
         // ================================ helper warp ==================================================
+        const MergeCtx mc{total, nb, counters, gcounters, partials, gpartials};
+        auto warp_lead = [&](auto f) {
+            __syncwarp();
+            int v = 0;
+            if (lane == 0) v = f();
+            return __shfl_sync(0xffffffffu, v, 0);
+        };
         long long pos = span_lo;
         unsigned int sidx = 0;
         int prev_slot = 0;   // partial slot of the previous segment: 0 for the CTA's first segment, else 1
@@ -524,7 +562,7 @@ decode_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__
             if (lane == 0) mbar_arrive(&sm.qfull[b]);
             if (prev_partial) {   // the consumers are still on the previous segment, or just left it
                 mbar_wait_bounded(&sm.pdone[prev_slot], 0, &sm.abort_flag);   // each used once: a CTA has <= 2 partials
-                finish_partial(prev_ip, prev_sq, sh, total, nb, counters, partials, lane);
+                deliver_part(prev_ip, prev_sq, sh, mc, blockIdx.x, lane, 32, warp_lead);
             }
             // the span's final segment is finished by the consumer warps themselves
             prev_partial = !(pos == ip.item_begin && has_last_tile) && seg_end < span_hi;
@@ -536,7 +574,7 @@ decode_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__
         }
         if (prev_partial && !sm.abort_flag) {
             mbar_wait_bounded(&sm.pdone[prev_slot], 0, &sm.abort_flag);
-            finish_partial(prev_ip, prev_sq, sh, total, nb, counters, partials, lane);
+            deliver_part(prev_ip, prev_sq, sh, mc, blockIdx.x, lane, 32, warp_lead);
         }
     } else {
         // ================================ consumer warps ===============================================
@@ -748,25 +786,20 @@ decode_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__
                     if (seg_end < span_hi) {
                         // more segments follow: the helper warp counts and merges while we stream on
                         if (lane == 0) mbar_arrive(&sm.pdone[first_segment ? 0 : 1]);
-                    } else if (lane == 0) {
-                        // end of the span: nothing left to overlap with, all four warps finish the item
-                        long long b0, b1;
-                        item_ctas(ip.item_begin, item_end, total, nb, b0, b1);
-                        int *ctr = counters + ip.seq * G + g;
-                        int old;   // release: the warp's partial stores (ordered before by __syncwarp); acquire: the others'
-                        asm volatile("atom.acq_rel.gpu.global.add.s32 %0, [%1], 1;" : "=r"(old) : "l"(ctr) : "memory");
-                        const int last = old == static_cast<int>(b1 - b0);
-                        if (last) atomicExch(ctr, 0);
-                        sm.last_flag = last;
                     }
                 }
             }
             if (!whole_item && seg_end == span_hi) {
-                named_bar_sync(1, kConsumerThreads);
-                if (sm.last_flag) {
-                    __threadfence();
-                    merge_item_cta(ip, tab.seqs[ip.seq], sh, total, nb, partials, tid);
-                }
+                // end of the span: nothing left to overlap with, all four warps complete the item if it is theirs to
+                // complete.  The barrier inside cta_lead also orders warp 0's partial stores before the count.
+                const MergeCtx mc{total, nb, counters, gcounters, partials, gpartials};
+                auto cta_lead = [&](auto f) {
+                    named_bar_sync(1, kConsumerThreads);
+                    if (tid == 0) sm.last_flag = f();
+                    named_bar_sync(1, kConsumerThreads);
+                    return sm.last_flag;
+                };
+                deliver_part(ip, tab.seqs[ip.seq], sh, mc, blockIdx.x, tid, kConsumerThreads, cta_lead);
             }
             first_segment = false;
             ++sidx;
@@ -796,7 +829,7 @@ cudaError_t launch_decode(const LaunchCtx &cx, const DecodeTable &tab) {
     const long long max_ctas = decode_max_ctas(cx.n_sm);
     const int grid = static_cast<int>(total_tiles < max_ctas ? total_tiles : max_ctas);
     decode_kernel<<<grid, kThreads, smem_bytes, cx.stream>>>(*cx.k_map, *cx.v_map, tab, cx.shape, cx.k_base, cx.v_base,
-                                                            cx.hdr, cx.counters, cx.partials);
+                                                            cx.hdr, cx.counters, cx.gcounters, cx.partials, cx.gpartials);
     g_launch_count += 1;
     return cudaGetLastError();
 }

@@ -83,15 +83,20 @@ size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
 // ---- workspace layout (fixed regions first, so that self-resetting counters stay where they are) ------
 struct WsLayout {
-    size_t counters, partials, seqs, q_stage, total;
+    size_t counters, gcounters, partials, gpartials, seqs, q_stage, total;
 };
 WsLayout ws_layout(const cglm_attn_desc &d, int n_sm, int n_seq, long long n_tokens, size_t prefill_bytes = 0) {
     WsLayout w;
     size_t off = sizeof(WsHeader);
     w.counters = off;
     off = align_up(off + sizeof(int) * kDecodeMaxSeqPerLaunch * static_cast<size_t>(d.n_kv_head), 256);
+    const size_t n_groups = (decode_max_ctas(n_sm) + kDecodeMergeFan - 1) / kDecodeMergeFan;
+    w.gcounters = off;
+    off = align_up(off + sizeof(int) * 2 * n_groups, 256);
     w.partials = off;
     off = align_up(off + sizeof(float) * kDecodePartialFloats * 2 * static_cast<size_t>(decode_max_ctas(n_sm)), 256);
+    w.gpartials = off;
+    off = align_up(off + sizeof(float) * kDecodePartialFloats * 2 * n_groups, 256);
     w.seqs = off;
     off = align_up(off + sizeof(SeqDev) * static_cast<size_t>(n_seq), 256);
     off = align_up(off, 1024);
@@ -476,7 +481,9 @@ int cglm_attn_forward(cglm_kv_arena *a, const cglm_attn_seq *seqs, int n_seq, vo
     cx.v_base = a->v_base;
     cx.hdr = reinterpret_cast<WsHeader *>(ws);
     cx.counters = reinterpret_cast<int *>(ws + lay.counters);
+    cx.gcounters = reinterpret_cast<int *>(ws + lay.gcounters);
     cx.partials = reinterpret_cast<float *>(ws + lay.partials);
+    cx.gpartials = reinterpret_cast<float *>(ws + lay.gpartials);
     cx.q_stage = reinterpret_cast<float *>(ws + lay.q_stage);
     cx.k_map = &a->k_map;
     cx.v_map = &a->v_map;

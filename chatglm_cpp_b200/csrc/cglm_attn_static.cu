@@ -34,9 +34,13 @@ constexpr int kStaticMaxKvHeads = 32;                    // kv heads per sequenc
 constexpr int kStaticMaxCtas = 2 * 148;                  // thread blocks of the decode launch: two per SM of a B200
 constexpr size_t kStaticCountersOff = sizeof(WsHeader);
 constexpr size_t kStaticCountersBytes = sizeof(int) * kStaticMaxSeq * kStaticMaxKvHeads;
-constexpr size_t kStaticPartialsOff = kStaticCountersOff + kStaticCountersBytes;
+constexpr size_t kStaticGroups = (kStaticMaxCtas + kDecodeMergeFan - 1) / kDecodeMergeFan;
+constexpr size_t kStaticGCountersOff = kStaticCountersOff + kStaticCountersBytes;
+constexpr size_t kStaticPartialsOff = kStaticGCountersOff + 256;   // 2 * 19 group counters fit in 256 bytes
 constexpr size_t kStaticPartialsBytes = sizeof(float) * kDecodePartialFloats * 2 * kStaticMaxCtas;
-constexpr size_t kStaticScratchBytes = kStaticPartialsOff + kStaticPartialsBytes;   // 4 942 080 bytes
+constexpr size_t kStaticGPartialsOff = kStaticPartialsOff + kStaticPartialsBytes;
+constexpr size_t kStaticScratchBytes = kStaticGPartialsOff + sizeof(float) * kDecodePartialFloats * 2 * kStaticGroups;   // 5 258 496 bytes
+static_assert(sizeof(int) * 2 * kStaticGroups <= 256, "group counters fit their region");
 static_assert(kStaticCountersOff % 256 == 0 && kStaticPartialsOff % 256 == 0, "regions stay 256-byte aligned");
 
 // The scratch itself.  In host code this name is only a handle for cudaGetSymbolAddress, never an address.
@@ -126,7 +130,9 @@ extern "C" int cglm_attn_decode_static(cglm_kv_arena *arena, const cglm_attn_seq
     cx.v_base = static_cast<uint16_t *>(cglm_kv_arena_v_cache(arena, 0));
     cx.hdr = reinterpret_cast<WsHeader *>(scratch);
     cx.counters = reinterpret_cast<int *>(scratch + kStaticCountersOff);
+    cx.gcounters = reinterpret_cast<int *>(scratch + kStaticGCountersOff);
     cx.partials = reinterpret_cast<float *>(scratch + kStaticPartialsOff);
+    cx.gpartials = reinterpret_cast<float *>(scratch + kStaticGPartialsOff);
     cx.q_stage = nullptr;
     cx.k_map = arena_k_map(arena);
     cx.v_map = arena_v_map(arena);

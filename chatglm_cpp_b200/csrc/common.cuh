@@ -227,7 +227,9 @@ struct LaunchCtx {
     uint16_t *v_base;            // arena V slabs: f16 [n_slots*G*D][M]
     WsHeader *hdr;
     int *counters;               // one per (sequence, kv head) of the decode list, zero between launches
+    int *gcounters;              // two per group of 16 decode CTAs (long items merged in two levels)
     float *partials;             // decode split partials: 2 slots per CTA
+    float *gpartials;            // decode group partials: 2 slots per group of 16 CTAs
     float *q_stage;              // generic path: roped, scaled q f32 [tokens][H][D]
     const CUtensorMap *k_map;    // host copies of the arena's tensor maps (passed by value to kernels)
     const CUtensorMap *v_map;
@@ -257,6 +259,7 @@ cudaError_t launch_prefill(const LaunchCtx &cx, const SeqDev &sq, const CUtensor
                            const CUtensorMap &v_map, __half *q_half);
 constexpr int kPrefillMinTokens = 128;
 int decode_max_ctas(int n_sm);
+constexpr int kDecodeMergeFan = 16;   // CTAs per group of the two-level merge
 constexpr int kDecodePartialFloats = 16 * 128 + 32;   // acc[16][128] | m[16] | l[16]
 
 extern unsigned long long g_launch_count;

@@ -152,7 +152,7 @@ int cglm_attn_forward_host(cglm_kv_arena *arena, const cglm_attn_seq *seqs, int 
  * plugin sandbox where cudaMalloc is off limits, a loop that must stay clear of the allocator once it runs.
  * Same work and same results as cglm_attn_forward for one-token sequences (qlen 1, flags 0, no partial output)
  * on an arena with head_dim 128, at most 16 q heads per kv head and a cache capacity that is a multiple of 8;
- * other shapes return CGLM_ERR_UNSUPPORTED.  The scratch is a fixed ~5 MiB array inside the library image, held
+ * other shapes return CGLM_ERR_UNSUPPORTED.  The scratch is a fixed ~5 MiB (5 258 496 bytes) array inside the library image, held
  * by every GPU that loads the library until the process exits.  Limits per call: 128 sequences, 32 kv heads,
  * a GPU of at most 148 SMs; beyond them the call fails with CGLM_ERR_WORKSPACE.
  * The call allocates nothing.  The first call on each device looks up the array's device address (with that
