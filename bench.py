@@ -415,8 +415,9 @@ def run_ours(args, w):
     out_dev = torch.empty(layers, n, orow, device="cuda")
     qkv_host = qkv_dev.cpu().pin_memory()
     out_host = torch.empty(layers, n, orow).pin_memory()
-    stage_qkv = torch.empty(n, row, device="cuda")
-    stage_out = torch.empty(n, orow, device="cuda")
+    n_stage = 3   # staging pairs rotated over the layers so that a layer's copies overlap its neighbours' kernels
+    stage_qkv = [torch.empty(n, row, device="cuda") for _ in range(n_stage)]
+    stage_out = [torch.empty(n, orow, device="cuda") for _ in range(n_stage)]
 
     # one descriptor array per layer, built once: slot of (layer l, sequence i) is l*n + i
     seq_arrays = []
@@ -438,10 +439,13 @@ def run_ours(args, w):
     def step_host():
         for l in range(layers):
             rc = L.cglm_attn_forward_host(arena._h, seq_arrays[l], n, int(w["interleaved"]), qkv_host[l].data_ptr(),
-                                          out_host[l].data_ptr(), stage_qkv.data_ptr(), stage_out.data_ptr(), ws.ptr,
-                                          ws.bytes, stream)
+                                          out_host[l].data_ptr(), stage_qkv[l % n_stage].data_ptr(),
+                                          stage_out[l % n_stage].data_ptr(), ws.ptr, ws.bytes, stream)
             if rc != 0:
                 raise _lib.CglmError(rc, "cglm_attn_forward_host")
+        rc = L.cglm_attn_host_drain(arena._h, stream)   # the step's results are read back here
+        if rc != 0:
+            raise _lib.CglmError(rc, "cglm_attn_host_drain")
 
     def barrier():
         if world > 1:

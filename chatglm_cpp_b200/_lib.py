@@ -46,6 +46,7 @@ SYMBOLS = {
     "cglm_attn_forward": (C.c_int, [C.c_void_p, C.POINTER(AttnSeq), C.c_int, C.c_void_p, C.c_size_t, C.c_void_p]),
     "cglm_attn_forward_host": (C.c_int, [C.c_void_p, C.POINTER(AttnSeq), C.c_int, C.c_int, C.c_void_p, C.c_void_p,
                                          C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]),
+    "cglm_attn_host_drain": (C.c_int, [C.c_void_p, C.c_void_p]),
     "cglm_attn_decode_static": (C.c_int, [C.c_void_p, C.POINTER(AttnSeq), C.c_int, C.c_int, C.c_void_p]),
     "cglm_attn_splitkv_combine": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p]),
     "cglm_kv_load_prefix": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_void_p]),

@@ -496,6 +496,11 @@ decode_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__
     for (int i = tid; i <= n_seq; i += kThreads) {
         sm.prefix[i] = tab.prefix[i];
     }
+    // Launched with programmatic stream serialization: everything above (barrier set-up, parameter reads) may run
+    // while the previous kernel of the stream is still draining; from here on this grid touches global memory, so
+    // it waits until that kernel has completed and its writes are visible.  Stream order is preserved.
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     __syncthreads();
     const long long total = static_cast<long long>(sm.prefix[n_seq]) * G;
     const long long nb = gridDim.x;
@@ -828,10 +833,20 @@ cudaError_t launch_decode(const LaunchCtx &cx, const DecodeTable &tab) {
     }
     const long long max_ctas = decode_max_ctas(cx.n_sm);
     const int grid = static_cast<int>(total_tiles < max_ctas ? total_tiles : max_ctas);
-    decode_kernel<<<grid, kThreads, smem_bytes, cx.stream>>>(*cx.k_map, *cx.v_map, tab, cx.shape, cx.k_base, cx.v_base,
-                                                            cx.hdr, cx.counters, cx.gcounters, cx.partials, cx.gpartials);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = smem_bytes;
+    cfg.stream = cx.stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;   // see griddepcontrol.wait in the kernel
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, decode_kernel, *cx.k_map, *cx.v_map, tab, cx.shape, cx.k_base, cx.v_base, cx.hdr,
+                                       cx.counters, cx.gcounters, cx.partials, cx.gpartials);
     g_launch_count += 1;
-    return cudaGetLastError();
+    return e != cudaSuccess ? e : cudaGetLastError();
 }
 
 }  // namespace cglm

@@ -36,6 +36,19 @@ struct cglm_kv_arena {
     int ring_cap;         // descriptors per slot
     int ring_next;
     cudaEvent_t *ring_events;
+    // host-buffer calls: copies run on two streams of the arena's own so that they overlap the kernels of
+    // neighbouring calls; the last kHostCalls calls are remembered to order the reuse of staging buffers
+    static constexpr int kHostCalls = 8;
+    struct HostCall {
+        const void *dev_in;
+        const void *dev_out;
+        cudaEvent_t h2d, kernel, d2h;
+        bool used;
+    };
+    cudaStream_t copy_in, copy_out;
+    HostCall host_calls[kHostCalls];
+    int host_next;
+    bool host_ready;
     std::mutex mu;
 };
 
@@ -334,6 +347,8 @@ int cglm_kv_arena_create(const cglm_attn_desc *desc, int n_slots, cglm_kv_arena 
     for (int i = 0; i < a->ring_slots; ++i) {
         cudaEventCreateWithFlags(&a->ring_events[i], cudaEventDisableTiming);
     }
+    a->host_ready = false;
+    a->host_next = 0;
     *out = a;
     return CGLM_OK;
 }
@@ -341,6 +356,13 @@ int cglm_kv_arena_create(const cglm_attn_desc *desc, int n_slots, cglm_kv_arena 
 int cglm_kv_arena_destroy(cglm_kv_arena *a) {
     if (!a) return CGLM_ERR_INVALID_ARG;
     cudaDeviceSynchronize();
+    if (a->host_ready) {
+        for (auto &c : a->host_calls) {
+            cudaEventDestroy(c.h2d); cudaEventDestroy(c.kernel); cudaEventDestroy(c.d2h);
+        }
+        cudaStreamDestroy(a->copy_in);
+        cudaStreamDestroy(a->copy_out);
+    }
     for (int i = 0; i < a->ring_slots; ++i) cudaEventDestroy(a->ring_events[i]);
     delete[] a->ring_events;
     if (a->ring) cudaFreeHost(a->ring);
@@ -579,10 +601,59 @@ int cglm_attn_forward_host(cglm_kv_arena *a, const cglm_attn_seq *seqs, int n_se
         s.flags = 0; s.kv_local = 0;
         n_tok += seqs[i].qlen;
     }
-    CGLM_CUDA(cudaMemcpyAsync(dev_qkv, qkv_host, sizeof(float) * n_tok * row, cudaMemcpyHostToDevice, st));
+    // ---- pipeline: H2D on copy_in, kernel on the caller's stream, D2H on copy_out ---------------------------------
+    std::unique_lock<std::mutex> lock(a->mu);
+    if (!a->host_ready) {
+        CGLM_CUDA(cudaStreamCreateWithFlags(&a->copy_in, cudaStreamNonBlocking));
+        CGLM_CUDA(cudaStreamCreateWithFlags(&a->copy_out, cudaStreamNonBlocking));
+        for (auto &c : a->host_calls) {
+            CGLM_CUDA(cudaEventCreateWithFlags(&c.h2d, cudaEventDisableTiming));
+            CGLM_CUDA(cudaEventCreateWithFlags(&c.kernel, cudaEventDisableTiming));
+            CGLM_CUDA(cudaEventCreateWithFlags(&c.d2h, cudaEventDisableTiming));
+            c.used = false;
+            c.dev_in = c.dev_out = nullptr;
+        }
+        a->host_ready = true;
+    }
+    cglm_kv_arena::HostCall &me = a->host_calls[a->host_next];
+    if (me.used) CGLM_CUDA(cudaEventSynchronize(me.d2h));   // the call that used this record eight calls ago
+    // the staging buffers may still be in use by earlier calls: the input buffer by a kernel, the output buffer by a
+    // device-to-host copy.  The most recent user of each is the one to wait for (earlier users precede it in order).
+    const cglm_kv_arena::HostCall *last_in = nullptr, *last_out = nullptr;
+    for (int back = 1; back < cglm_kv_arena::kHostCalls; ++back) {
+        const cglm_kv_arena::HostCall &c =
+            a->host_calls[(a->host_next - back + cglm_kv_arena::kHostCalls) % cglm_kv_arena::kHostCalls];
+        if (!c.used) continue;
+        if (!last_in && c.dev_in == dev_qkv) last_in = &c;
+        if (!last_out && c.dev_out == dev_out) last_out = &c;
+    }
+    a->host_next = (a->host_next + 1) % cglm_kv_arena::kHostCalls;
+    lock.unlock();
+    if (last_in) CGLM_CUDA(cudaStreamWaitEvent(a->copy_in, last_in->kernel, 0));
+    CGLM_CUDA(cudaMemcpyAsync(dev_qkv, qkv_host, sizeof(float) * n_tok * row, cudaMemcpyHostToDevice, a->copy_in));
+    CGLM_CUDA(cudaEventRecord(me.h2d, a->copy_in));
+    CGLM_CUDA(cudaStreamWaitEvent(st, me.h2d, 0));
+    if (last_out) CGLM_CUDA(cudaStreamWaitEvent(st, last_out->d2h, 0));
     const int rc = cglm_attn_forward(a, dev_seqs.data(), n_seq, workspace, workspace_bytes, cuda_stream);
     if (rc != CGLM_OK) return rc;
-    CGLM_CUDA(cudaMemcpyAsync(out_host, dev_out, sizeof(float) * n_tok * orow, cudaMemcpyDeviceToHost, st));
+    CGLM_CUDA(cudaEventRecord(me.kernel, st));
+    CGLM_CUDA(cudaStreamWaitEvent(a->copy_out, me.kernel, 0));
+    CGLM_CUDA(cudaMemcpyAsync(out_host, dev_out, sizeof(float) * n_tok * orow, cudaMemcpyDeviceToHost, a->copy_out));
+    CGLM_CUDA(cudaEventRecord(me.d2h, a->copy_out));
+    me.dev_in = dev_qkv;
+    me.dev_out = dev_out;
+    me.used = true;
+    return CGLM_OK;
+}
+
+int cglm_attn_host_drain(cglm_kv_arena *a, void *cuda_stream) {
+    if (!a) return CGLM_ERR_INVALID_ARG;
+    if (!a->host_ready) return CGLM_OK;
+    cudaStream_t st = static_cast<cudaStream_t>(cuda_stream);
+    std::lock_guard<std::mutex> lock(a->mu);
+    for (auto &c : a->host_calls) {
+        if (c.used) CGLM_CUDA(cudaStreamWaitEvent(st, c.d2h, 0));
+    }
     return CGLM_OK;
 }
 

@@ -139,12 +139,20 @@ int cglm_attn_forward(cglm_kv_arena *arena, const cglm_attn_seq *seqs, int n_seq
  *   qkv_host  f32 [n_tokens][(H+2G)*D], the rows of all sequences back to back (sequence i owns rows
  *             [tok_begin_i, tok_begin_i + qlen_i)); out_host f32 [n_tokens][H*D].
  * interleaved_qkv selects the v1 layout.  dev_qkv / dev_out are device staging buffers of at least those sizes.
- * Only n_past / qlen / n_ctx / slot of each descriptor are read.  Asynchronous: out_host is valid after the
- * stream is synchronised; use pinned host memory for truly asynchronous copies.
+ * Only n_past / qlen / n_ctx / slot of each descriptor are read.
+ * The two copies run on streams of the arena's own and the kernels on cuda_stream, chained by events, so that the
+ * upload of one call and the download of another overlap the kernels between them (one call per layer: give
+ * neighbouring calls different staging buffers, two or three pairs are enough; reuse of a staging buffer is ordered
+ * by the library).  out_host is valid once cglm_attn_host_drain has been enqueued on a stream and that stream has
+ * been synchronised.  Use pinned host memory for truly asynchronous copies.
  */
 int cglm_attn_forward_host(cglm_kv_arena *arena, const cglm_attn_seq *seqs, int n_seq, int interleaved_qkv,
                            const float *qkv_host, float *out_host, float *dev_qkv, float *dev_out,
                            void *workspace, size_t workspace_bytes, void *cuda_stream);
+
+/* Makes cuda_stream wait for every device-to-host copy that cglm_attn_forward_host has enqueued for this arena: the
+ * point where a step's results are read back (ggml_backend_tensor_get at the end of a step, chatglm.cpp:764). */
+int cglm_attn_host_drain(cglm_kv_arena *arena, void *cuda_stream);
 
 /*
  * Decode step that brings its own scratch memory.  No counterpart in the reference; it exists for hosts that

@@ -287,11 +287,50 @@ def test_forward_host_roundtrip_matches_device_call():
     _lib.check(_lib.lib().cglm_attn_forward_host(arena._h, arr, n, 0, qkv_pinned.data_ptr(), out_pinned.data_ptr(),
                                                  dev_qkv.data_ptr(), dev_out.data_ptr(), ws.ptr, ws.bytes,
                                                  torch.cuda.current_stream().cuda_stream), "forward_host")
-    torch.cuda.synchronize()
+    _lib.check(_lib.lib().cglm_attn_host_drain(arena._h, torch.cuda.current_stream().cuda_stream), "host_drain")
+    torch.cuda.current_stream().synchronize()
     for i in range(n):
         assert torch.equal(out_pinned[i], calls[i].out[0].cpu())
         assert torch.equal(arena.k_cache(i), arena.k_cache(n + i))
         assert torch.equal(arena.v_cache(i), arena.v_cache(n + i))
+
+
+def test_forward_host_pipeline_reuses_staging_buffers():
+    """Six host-buffer calls in a row over two staging pairs (copies overlap neighbouring kernels): every call's
+    output must equal the plain device call's, i.e. the reuse of a staging buffer is ordered correctly."""
+    from chatglm_cpp_b200 import _lib
+    A = _A()
+    desc = make_desc(32, 2, 128, 2048)
+    rng = np.random.default_rng(41)
+    n_layers, n = 6, 4
+    n_past = [1500, 20, 700, 2047]
+    arena, ws = A.KVArena(desc, 2 * n_layers * n), A.Workspace(desc, n, 1)
+    arena.k_all().normal_(); arena.v_all().normal_()
+    half = n_layers * n
+    arena.k_all()[half:].copy_(arena.k_all()[:half]); arena.v_all()[half:].copy_(arena.v_all()[:half])
+    width = qkv_width(desc, False)
+    qkv = torch.from_numpy(rng.standard_normal((n_layers, n, width)).astype(np.float32))
+    qkv_pinned, out_pinned = qkv.pin_memory(), torch.zeros(n_layers, n, 4096).pin_memory()
+    qkv_dev = qkv.cuda()
+    out_ref = torch.zeros(n_layers, n, 4096, device="cuda")
+    stage_in = [torch.empty(n, width, device="cuda") for _ in range(2)]
+    stage_out = [torch.empty(n, 4096, device="cuda") for _ in range(2)]
+    stream = torch.cuda.current_stream().cuda_stream
+    for l in range(n_layers):
+        A.forward_batch(arena, ws, [A.SeqCall(qkv=qkv_dev[l, i:i + 1], slot=l * n + i, n_past=n_past[i], out=out_ref[l, i:i + 1])
+                                    for i in range(n)])
+    for l in range(n_layers):
+        arr = (_lib.AttnSeq * n)()
+        for i in range(n):
+            arr[i].slot, arr[i].qlen, arr[i].n_past = half + l * n + i, 1, n_past[i]
+        _lib.check(_lib.lib().cglm_attn_forward_host(arena._h, arr, n, 0, qkv_pinned[l].data_ptr(), out_pinned[l].data_ptr(),
+                                                     stage_in[l % 2].data_ptr(), stage_out[l % 2].data_ptr(), ws.ptr, ws.bytes,
+                                                     stream), "forward_host")
+    _lib.check(_lib.lib().cglm_attn_host_drain(arena._h, stream), "host_drain")
+    torch.cuda.current_stream().synchronize()
+    assert ws.status() == 0
+    assert torch.equal(out_pinned, out_ref.cpu())
+    assert torch.equal(arena.k_all()[:half], arena.k_all()[half:])
 
 
 def test_argument_errors_return_codes():
