@@ -43,7 +43,6 @@ constexpr int kRows = 16;              // MMA M = q heads per kv head, zero padd
 constexpr int kKHalfBytes = kTile * 128;            // one 64-dim half of a K tile: 64 lines of 128 B
 constexpr int kVBytes = kD * 128;                   // V^T tile: 128 lines (dims) of 64 tokens
 constexpr int kStageBytes = 2 * kKHalfBytes + kVBytes;   // 32 KiB
-constexpr int kXchgStride = 68;                     // floats per row of the fold buffer (64 dims + pad)
 constexpr int kQStride = 136;                       // halfs per row of the q tile (272 B, ldmatrix conflict-free)
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
@@ -59,11 +58,43 @@ struct alignas(16) QBuf {
     int flags;
 };
 
+// A position on the line of tiles: which (sequence, kv head) item it falls in and where.
+struct ItemPos {
+    int seq, g, tile, n_tiles;
+    long long item_begin;   // line position of tile 0 of this item
+};
+
+// Where a completed item goes: the sequence's output row, or its (acc, m, l) row for a split-KV combine.
+struct ItemOut {
+    float *out, *partial;
+    int flags;
+};
+struct MergeCtx {
+    long long total, nb;   // tiles on the line, CTAs of the launch
+    int *counters;         // per item: parts delivered (short items) or groups delivered (long items)
+    int *gcounters;        // per (CTA group, slot): parts of the long item in that slot delivered
+    float *partials;       // per (CTA, slot)
+    float *gpartials;      // per (CTA group, slot)
+};
+
+// What a team hands to deliver_part, parked in shared memory: the function is kept out of line (one copy of the
+// merge code for its three callers), and a stack frame in local memory would put loads from a saturated memory
+// system on the critical path of the launch's last microseconds.
+struct DeliverArgs {
+    ItemPos ip;
+    ItemOut io;
+    MergeCtx mc;
+    int G, R;
+};
+
 struct __align__(1024) DecodeSmem {
     uint8_t stage[kStages][kStageBytes];
     QBuf qb[2];
-    float xchg[kRows * kXchgStride + 2 * kRows];   // fold buffer: one 64-dim half of a warp's O, its m and l
+    float xchg[kConsumerWarps * 2 * kRows];        // fold: every warp's row maxima and row sums
     int prefix[kDecodeMaxSeqPerLaunch + 2];        // copy of the launch's tile prefix sums (parameter space is slow to index)
+    int slot[kDecodeMaxSeqPerLaunch];              // copy of every sequence's arena slot, for the producer
+    SeqDev sq;                                     // the helper warp's copy of the descriptor it is preparing
+    DeliverArgs dargs[kConsumerWarps + 1];         // per calling warp: arguments of deliver_part
     uint64_t full[kStages];
     uint64_t empty[kStages];
     uint64_t qfull[2];
@@ -83,10 +114,6 @@ __device__ __forceinline__ long long span_start(long long b, long long total, lo
 }
 
 // Position on the line -> (sequence, kv head, tile) using the per-sequence prefix of tile counts.
-struct ItemPos {
-    int seq, g, tile, n_tiles;
-    long long item_begin;   // line position of tile 0 of this item
-};
 __device__ __forceinline__ ItemPos locate(const int *prefix, int n_seq, int G, long long pos) {
     int lo = 0, hi = n_seq - 1;
     while (lo < hi) {
@@ -96,9 +123,9 @@ __device__ __forceinline__ ItemPos locate(const int *prefix, int n_seq, int G, l
     ItemPos ip;
     ip.seq = lo;
     ip.n_tiles = prefix[lo + 1] - prefix[lo];
-    const long long off = pos - static_cast<long long>(prefix[lo]) * G;
-    ip.g = static_cast<int>(off / ip.n_tiles);
-    ip.tile = static_cast<int>(off % ip.n_tiles);
+    const int off = static_cast<int>(pos - static_cast<long long>(prefix[lo]) * G);   // < G * n_tiles
+    ip.g = off / ip.n_tiles;
+    ip.tile = off - ip.g * ip.n_tiles;
     ip.item_begin = pos - ip.tile;
     return ip;
 }
@@ -143,9 +170,9 @@ __device__ __forceinline__ void qk_slice(uint32_t kb, int warp, int lane, const 
     }
 }
 
-// Online softmax over the slice's 16 scores per row (log2 domain) and O = O * alpha + P V.
-// kFull: all 16 tokens are attended (every tile but an item's last).
-template <bool kFull>
+// Online softmax over the slice's 16 scores per row (log2 domain) and O = O * alpha + P V.  n_valid: attended
+// tokens of the slice, 16 for every tile but an item's last.  One body for both cases: code that runs once per
+// item costs more in instruction fetch than eight selects per tile do.
 __device__ __forceinline__ void softmax_pv_slice(uint32_t vb, int warp, int lane, int n_valid, float (&s)[2][4],
                                                  float (&m_run)[2], float (&l_run)[2], float (&o)[16][4]) {
     const int c = lane & 3;
@@ -154,7 +181,7 @@ __device__ __forceinline__ void softmax_pv_slice(uint32_t vb, int warp, int lane
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
             const int j = 8 * nbk + 2 * c + (e & 1);
-            s[nbk][e] = (kFull || j < n_valid) ? s[nbk][e] * kLog2e : -INFINITY;
+            s[nbk][e] = j < n_valid ? s[nbk][e] * kLog2e : -INFINITY;
         }
     }
     float mx[2];
@@ -213,123 +240,176 @@ __device__ __forceinline__ void patch_last_tile(uint32_t kb, uint32_t vb, int wa
         const uint2 val = *reinterpret_cast<const uint2 *>(&newk[ch * 8 + (lane & 1) * 4]);
         asm volatile("st.shared.v2.b32 [%0], {%1, %2};" ::"r"(addr), "r"(val.x), "r"(val.y) : "memory");
     }
+    // V^T: the slice's 16 tokens of a dim are 8 words (two 16-byte chunks of the dim's 128-byte line).  Word w
+    // keeps tokens 2w, 2w+1 below keep_n; the new token's half takes the new v.  Lane l patches dims l, l+32, ...
+    const int keep_n = ours ? new_local : n_valid;
+    uint32_t keep[8], ins[8];
+#pragma unroll
+    for (int w = 0; w < 8; ++w) {
+        keep[w] = (2 * w < keep_n ? 0x0000ffffu : 0u) | (2 * w + 1 < keep_n ? 0xffff0000u : 0u);
+        ins[w] = (ours && (new_local >> 1) == w) ? ((new_local & 1) ? 0xffff0000u : 0x0000ffffu) : 0u;
+    }
+#pragma unroll 1
     for (int d = lane; d < kD; d += 32) {
-        for (int j = ours ? new_local : n_valid; j < 16; ++j) {
-            const int tk = 16 * warp + j;
-            const uint32_t addr = vb + d * 128 + (((tk >> 3) ^ (d & 7)) << 4) + (tk & 7) * 2;
-            const uint16_t hv = j == new_local ? __half_as_ushort(newv[d]) : (uint16_t)0;
-            asm volatile("st.shared.b16 [%0], %1;" ::"r"(addr), "h"(hv) : "memory");
+        const uint32_t nv = __half_as_ushort(newv[d]) * 0x00010001u;
+        const uint32_t line = vb + d * 128;
+#pragma unroll
+        for (int hc = 0; hc < 2; ++hc) {
+            const uint32_t addr = line + (((2 * warp + hc) ^ (d & 7)) << 4);
+            uint32_t x0, x1, x2, x3;
+            asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(x0), "=r"(x1), "=r"(x2), "=r"(x3) : "r"(addr) : "memory");
+            x0 = (x0 & keep[4 * hc + 0]) | (nv & ins[4 * hc + 0]);
+            x1 = (x1 & keep[4 * hc + 1]) | (nv & ins[4 * hc + 1]);
+            x2 = (x2 & keep[4 * hc + 2]) | (nv & ins[4 * hc + 2]);
+            x3 = (x3 & keep[4 * hc + 3]) | (nv & ins[4 * hc + 3]);
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(x0), "r"(x1), "r"(x2), "r"(x3) : "memory");
         }
     }
     fence_proxy_async();
     __syncwarp();
 }
 
+// One warp copies a sequence descriptor from parameter space to shared memory, a word per lane: one trip instead
+// of one per field read.
+__device__ __forceinline__ void load_seq_desc(SeqDev &dst, const SeqDev &src, int lane) {
+    static_assert(sizeof(SeqDev) == 32 * sizeof(uint32_t), "one word per lane");
+    reinterpret_cast<uint32_t *>(&dst)[lane] = reinterpret_cast<const uint32_t *>(&src)[lane];
+    __syncwarp();
+}
+
 // ---- helper warp: everything a segment needs before its first tile -----------------------------------------
 // RoPE on the 16 q heads of the kv head and on the new k (chatglm.cpp:655-656), q * 1/sqrt(d) in f16
 // (chatglm.cpp:686), and, when the segment holds the item's last tile, the f16 append of K row and V^T column
-// (chatglm.cpp:668-675).  One warp: lane l owns pairs l and l+32 of every head.
+// (chatglm.cpp:668-675).  One warp, lane l owns dims 4l..4l+3 of every head: 18 sixteen-byte loads per lane, all
+// issued before anything depends on one (a single round trip), and as few instructions as possible, because this
+// runs between the start of the kernel and its first tile.  The callers guarantee 16-byte aligned rows.
+// dry: touch no global memory (loads and stores are predicated off); a dry pass before the real one only pulls
+// this code into the instruction cache, which the first execution of straight-line code otherwise pays for with
+// a few microseconds of fetch misses.
+//   CHATGLM2: dims [0, 64) rotate as adjacent pairs (2p, 2p+1) by ladder angle p: both pairs of lanes 0..15 stay
+//             inside the lane.
+//   CHATGLM:  each 64-dim half rotates as pairs (i, i+32) by ladder angle i, the first half by the position id and
+//             the second by the block position id: the partner of lane l sits in lane l ^ 8.
+__device__ __forceinline__ float4 ldg4(const float *p) { return __ldg(reinterpret_cast<const float4 *>(p)); }
+__device__ __forceinline__ uint2 pack_half4(float a, float b, float c, float d) {
+    return make_uint2(pack_half2(a, b), pack_half2(c, d));
+}
+// Angle of a position the arena's table does not hold (explicit position ids beyond the cache capacity): out of
+// line, so that the double-precision sincos stays out of the instruction stream of the common case.
+__device__ __noinline__ float2 rope_angle_uncached(int pos, int i, float theta_scale) {
+    float2 cs;
+    rope_cos_sin(pos, i, theta_scale, cs.x, cs.y);
+    return cs;
+}
+
 __device__ __forceinline__ void prepare_segment(QBuf &qb, const AttnShape &sh, const SeqDev &sq, int g,
                                                 int row, bool has_last_tile, bool appender, int lane,
                                                 uint16_t *__restrict__ k_base, uint16_t *__restrict__ v_base,
-                                                uint64_t *loads_issued) {
+                                                const float2 *__restrict__ rope_tab, int rope_tab_len,
+                                                uint64_t *loads_issued, bool dry) {
     const int R = sh.R, M = sh.M;
-    const int n_pairs = rope_n_pairs(sh.rope_type, kD);   // 0, 32 (CHATGLM2) or 64 (CHATGLM)
     if (lane == 0) {
         qb.out = sq.out; qb.partial = sq.partial; qb.kv_before = sq.kv_before; qb.flags = sq.flags;
     }
     const bool k_needed = appender || (has_last_tile && sq.k_roped);
-    // element indices of this lane's two pairs
-    int i0[2], i1[2];
-    bool rotated[2];
-#pragma unroll
-    for (int half = 0; half < 2; ++half) {
-        const int pr = lane + 32 * half;   // pair index inside the head
-        rotated[half] = pr < n_pairs;
-        if (rotated[half]) {
-            const RopePair rp = rope_pair(sh.rope_type, kD, pr);   // rp.ladder == lane, rp.stream == half
-            i0[half] = rp.i0; i1[half] = rp.i1;
-        } else {
-            const int first_free = sh.rope_type == CGLM_ROPE_CHATGLM2 ? kD / 2 : 0;
-            i0[half] = first_free + 2 * (pr - n_pairs); i1[half] = i0[half] + 1;
-        }
-    }
-    // every global load of the segment is issued before anything depends on one: a single round trip
-    float x0[2][kRows], x1[2][kRows], kx0[2] = {0.f, 0.f}, kx1[2] = {0.f, 0.f}, vx[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-    for (int half = 0; half < 2; ++half) {
+    const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
+    float4 x[kRows + 1], xv = zero4;   // x[kRows]: the new k row
+    {
+        const float *src = sq.q + static_cast<long long>(g) * R * sq.q_head_stride + 4 * lane;
 #pragma unroll
         for (int r = 0; r < kRows; ++r) {
-            x0[half][r] = x1[half][r] = 0.f;
-            if (r < R) {
-                const float *src = sq.q + (g * R + r) * sq.q_head_stride;
-                x0[half][r] = __ldg(src + i0[half]);
-                x1[half][r] = __ldg(src + i1[half]);
-            }
-        }
-        if (k_needed) {
-            const float *src = sq.k + g * sq.kv_head_stride;
-            kx0[half] = __ldg(src + i0[half]);
-            kx1[half] = __ldg(src + i1[half]);
+            x[r] = (r < R && !dry) ? ldg4(src) : zero4;
+            src += sq.q_head_stride;
         }
     }
-    if (appender) {
-#pragma unroll
-        for (int j = 0; j < 4; ++j) vx[j] = __ldg(sq.v + g * sq.kv_head_stride + lane + 32 * j);
+    x[kRows] = (k_needed && !dry) ? ldg4(sq.k + g * sq.kv_head_stride + 4 * lane) : zero4;
+    if (appender && !dry) xv = ldg4(sq.v + g * sq.kv_head_stride + 4 * lane);
+    // Lane l fetches ladder angle l of the position stream (and of the block-position stream in CHATGLM mode) from
+    // the arena's table in the same round trip.
+    int pos_id = 0, block_id = 0;
+    float2 cs0 = make_float2(1.f, 0.f), cs1 = make_float2(1.f, 0.f);
+    const int mode = sh.rope_type;
+    if (mode != CGLM_ROPE_DISABLED && !dry) {
+        derive_positions(sq, mode, 0, pos_id, block_id);
+        const bool tab0 = pos_id >= 0 && pos_id < rope_tab_len;
+        const bool tab1 = block_id >= 0 && block_id < rope_tab_len;
+        if (tab0) cs0 = __ldg(rope_tab + static_cast<long long>(pos_id) * 32 + lane);
+        else cs0 = rope_angle_uncached(pos_id, lane, sh.theta_scale);
+        if (mode == CGLM_ROPE_CHATGLM) {
+            if (tab1) cs1 = __ldg(rope_tab + static_cast<long long>(block_id) * 32 + lane);
+            else cs1 = rope_angle_uncached(block_id, lane, sh.theta_scale);
+        }
     }
     if (loads_issued) {   // first segment of the CTA: only now may the producer start its burst of tile loads,
         __syncwarp();     // so that these few small loads do not queue behind 96 KiB of them
         if (lane == 0) mbar_arrive(loads_issued);
     }
-    // In both GLM modes pair l and pair l+32 of a head use ladder index l (of the position stream for the first,
-    // of the block-position stream for the second), so every lane needs only its own cos/sin.
-    int pos_id, block_id;
-    derive_positions(sq, sh.rope_type, 0, pos_id, block_id);
-    float cs_c[2] = {1.f, 1.f}, cs_s[2] = {0.f, 0.f};
-    if (n_pairs > 0) {
-        rope_cos_sin(pos_id, lane, sh.theta_scale, cs_c[0], cs_s[0]);
-        if (sh.rope_type == CGLM_ROPE_CHATGLM) {
-            rope_cos_sin(block_id, lane, sh.theta_scale, cs_c[1], cs_s[1]);
+    // Rotation of the 17 rows, in place.  Every product and sum is rounded separately and in the order of
+    // rope_rotate(): y0 = x0 c - x1 s, y1 = x0 s + x1 c.
+    if (mode == CGLM_ROPE_CHATGLM2) {
+        // lanes 0..15 hold pairs 2l and 2l+1 entirely; lanes 16..31 hold dims that do not rotate
+        const int a = (2 * lane) & 31;
+        const float ca = __shfl_sync(0xffffffffu, cs0.x, a), sa = __shfl_sync(0xffffffffu, cs0.y, a);
+        const float cb = __shfl_sync(0xffffffffu, cs0.x, a + 1), sb = __shfl_sync(0xffffffffu, cs0.y, a + 1);
+        const bool rot = lane < 16;
+#pragma unroll
+        for (int r = 0; r <= kRows; ++r) {
+            float4 y;
+            rope_rotate(x[r].x, x[r].y, ca, sa, y.x, y.y);
+            rope_rotate(x[r].z, x[r].w, cb, sb, y.z, y.w);
+            if (rot) x[r] = y;
+        }
+    } else if (mode == CGLM_ROPE_CHATGLM) {
+        // lane l holds x_i (bit 3 of l clear) or x_{i+32} (set) of four pairs; the other element sits in lane l ^ 8
+        const bool second = lane >= 16, upper = (lane & 8) != 0;
+        float c[4], sg[4];   // sg: the sine with the sign this lane's element takes (-s for x_i, +s for x_{i+32})
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int a = 4 * (lane & 7) + e;
+            const float c0 = __shfl_sync(0xffffffffu, cs0.x, a), s0 = __shfl_sync(0xffffffffu, cs0.y, a);
+            const float c1 = __shfl_sync(0xffffffffu, cs1.x, a), s1 = __shfl_sync(0xffffffffu, cs1.y, a);
+            c[e] = second ? c1 : c0;
+            sg[e] = second ? s1 : s0;
+        }
+#pragma unroll
+        for (int r = 0; r <= kRows; ++r) {
+            const float ox = __shfl_xor_sync(0xffffffffu, x[r].x, 8), oy = __shfl_xor_sync(0xffffffffu, x[r].y, 8);
+            const float oz = __shfl_xor_sync(0xffffffffu, x[r].z, 8), ow = __shfl_xor_sync(0xffffffffu, x[r].w, 8);
+            // x_i:      y = x c - o s  (rope_rotate's y0 with x0 = x, x1 = o)
+            // x_{i+32}: y = o s + x c  (rope_rotate's y1 with x0 = o, x1 = x); the sum commutes exactly
+            const float px = __fmul_rn(ox, sg[0]), py = __fmul_rn(oy, sg[1]), pz = __fmul_rn(oz, sg[2]), pw = __fmul_rn(ow, sg[3]);
+            x[r].x = upper ? __fadd_rn(px, __fmul_rn(x[r].x, c[0])) : __fsub_rn(__fmul_rn(x[r].x, c[0]), px);
+            x[r].y = upper ? __fadd_rn(py, __fmul_rn(x[r].y, c[1])) : __fsub_rn(__fmul_rn(x[r].y, c[1]), py);
+            x[r].z = upper ? __fadd_rn(pz, __fmul_rn(x[r].z, c[2])) : __fsub_rn(__fmul_rn(x[r].z, c[2]), pz);
+            x[r].w = upper ? __fadd_rn(pw, __fmul_rn(x[r].w, c[3])) : __fsub_rn(__fmul_rn(x[r].w, c[3]), pw);
         }
     }
+    const bool want_q = has_last_tile && sq.q_roped != nullptr && !dry;
 #pragma unroll
-    for (int half = 0; half < 2; ++half) {
-        const float rc = cs_c[half], rs = cs_s[half];
-#pragma unroll
-        for (int r = 0; r < kRows; ++r) {
-            float y0 = x0[half][r], y1 = x1[half][r];
-            if (rotated[half]) rope_rotate(x0[half][r], x1[half][r], rc, rs, y0, y1);
-            qb.q[r][i0[half]] = __float2half_rn(__fmul_rn(y0, sh.scale));
-            qb.q[r][i1[half]] = __float2half_rn(__fmul_rn(y1, sh.scale));
-            if (has_last_tile && sq.q_roped && r < R) {
-                float *qr = sq.q_roped + static_cast<long long>(g * R + r) * kD;
-                qr[i0[half]] = y0; qr[i1[half]] = y1;
-            }
-        }
-        if (k_needed) {
-            float y0 = kx0[half], y1 = kx1[half];
-            if (rotated[half]) rope_rotate(kx0[half], kx1[half], rc, rs, y0, y1);
-            if (sq.k_roped) {
-                float *kr = sq.k_roped + static_cast<long long>(g) * kD;
-                kr[i0[half]] = y0; kr[i1[half]] = y1;
-            }
-            if (appender) {
-                const __half h0 = __float2half_rn(y0), h1 = __float2half_rn(y1);
-                qb.newk[i0[half]] = h0; qb.newk[i1[half]] = h1;
-                uint16_t *krow = k_base + (static_cast<long long>(row) * M + sq.kv_before) * kD;
-                krow[i0[half]] = __half_as_ushort(h0);
-                krow[i1[half]] = __half_as_ushort(h1);
-            }
+    for (int r = 0; r < kRows; ++r) {
+        *reinterpret_cast<uint2 *>(&qb.q[r][4 * lane]) =
+            pack_half4(__fmul_rn(x[r].x, sh.scale), __fmul_rn(x[r].y, sh.scale), __fmul_rn(x[r].z, sh.scale), __fmul_rn(x[r].w, sh.scale));
+        if (want_q && r < R) {
+            *reinterpret_cast<float4 *>(sq.q_roped + static_cast<long long>(g * R + r) * kD + 4 * lane) = x[r];
         }
     }
-    if (appender) {
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            const int d = lane + 32 * j;
-            const __half hv = __float2half_rn(vx[j]);
-            qb.newv[d] = hv;
-            v_base[(static_cast<long long>(row) * kD + d) * M + sq.kv_before] = __half_as_ushort(hv);
+    if (k_needed && !dry) {
+        const float4 y = x[kRows];
+        if (sq.k_roped) *reinterpret_cast<float4 *>(sq.k_roped + static_cast<long long>(g) * kD + 4 * lane) = y;
+        if (appender) {
+            const uint2 h = pack_half4(y.x, y.y, y.z, y.w);
+            *reinterpret_cast<uint2 *>(&qb.newk[4 * lane]) = h;
+            *reinterpret_cast<uint2 *>(k_base + (static_cast<long long>(row) * M + sq.kv_before) * kD + 4 * lane) = h;
         }
+    }
+    if (appender && !dry) {
+        const uint2 h = pack_half4(xv.x, xv.y, xv.z, xv.w);
+        *reinterpret_cast<uint2 *>(&qb.newv[4 * lane]) = h;
+        uint16_t *col = v_base + (static_cast<long long>(row) * kD + 4 * lane) * M + sq.kv_before;
+        col[0] = static_cast<uint16_t>(h.x & 0xffffu);
+        col[M] = static_cast<uint16_t>(h.x >> 16);
+        col[2 * static_cast<long long>(M)] = static_cast<uint16_t>(h.y & 0xffffu);
+        col[3 * static_cast<long long>(M)] = static_cast<uint16_t>(h.y >> 16);
     }
 }
 
@@ -341,13 +421,6 @@ __device__ __forceinline__ void prepare_segment(QBuf &qb, const AttnShape &sh, c
 // group into a group partial, and the last group to finish merges the group partials.
 constexpr int kMergeFan = kDecodeMergeFan;
 
-struct MergeCtx {
-    long long total, nb;   // tiles on the line, CTAs of the launch
-    int *counters;         // per item: parts delivered (short items) or groups delivered (long items)
-    int *gcounters;        // per (CTA group, slot): parts of the long item in that slot delivered
-    float *partials;       // per (CTA, slot)
-    float *gpartials;      // per (CTA group, slot)
-};
 // A CTA group holds parts of at most two long items: one that began in an earlier group (slot 0) and one that
 // begins inside the group (slot 1).
 __device__ __forceinline__ int group_slot(long long grp, long long b0) { return b0 < grp * kMergeFan ? 0 : 1; }
@@ -356,7 +429,7 @@ __device__ __forceinline__ int group_slot(long long grp, long long b0) { return 
 // time.  Sources are CTA partials (level 0) or group partials (level 1).  Every caller goes through this routine
 // with the same source order, so the result does not depend on which CTA or warp happens to complete the item.
 // to_group >= 0: the result is itself a group partial (un-normalised); otherwise it is the item's output.
-__device__ __forceinline__ void merge_row_chunk(const ItemPos &ip, const SeqDev &sq, const AttnShape &sh, const MergeCtx &mc,
+__device__ __forceinline__ void merge_row_chunk(const ItemPos &ip, const ItemOut &sq, const AttnShape &sh, const MergeCtx &mc,
                                                 bool from_groups, long long b0, long long k0, long long k1, long long to_group,
                                                 int r, int d0) {
     auto source = [&](long long k) -> const float * {
@@ -430,45 +503,67 @@ __device__ __forceinline__ int count_part(int *ctr, int expected) {
     return last;
 }
 
+
 // Called by a team of n_thr threads (the four consumer warps at the end of a span, or the helper warp in the
-// middle of one) after CTA `b` stored its part of item `ip`.  t: index inside the team; lead(f): synchronises the
-// team (ordering its memory operations), lets the team leader evaluate f() and hands the result to every member.
-template <class Lead>
-__device__ __forceinline__ void deliver_part(const ItemPos &ip, const SeqDev &sq, const AttnShape &sh, const MergeCtx &mc,
-                                             long long b, int t, int n_thr, Lead lead) {
+// middle of one) after CTA `b` stored its part of item da->ip.  t: index inside the team.  cta_flag: shared-memory
+// word through which a multi-warp team hears its leader's verdict; null for a team of one warp.
+__device__ __noinline__ void deliver_part(const DeliverArgs *da, long long b, int t, int n_thr, int *cta_flag) {
+    const ItemPos ip = da->ip;
+    const ItemOut sq = da->io;
+    const MergeCtx mc = da->mc;
+    AttnShape sh{};
+    sh.G = da->G;
+    sh.R = da->R;
+    // synchronises the team (ordering its memory operations), lets the leader count this part and hands the
+    // result to every member: did this team deliver the last part?
+    auto lead = [&](int *ctr, int expected) -> int {
+        if (cta_flag) {
+            named_bar_sync(1, n_thr);
+            if (t == 0) *cta_flag = count_part(ctr, expected);
+            named_bar_sync(1, n_thr);
+            return *cta_flag;
+        }
+        __syncwarp();
+        int v = 0;
+        if (t == 0) v = count_part(ctr, expected);
+        return __shfl_sync(0xffffffffu, v, 0);
+    };
     long long b0, b1;
     item_ctas(ip.item_begin, ip.item_begin + ip.n_tiles, mc.total, mc.nb, b0, b1);
     const int n_parts = static_cast<int>(b1 - b0 + 1);
     const int item = ip.seq * sh.G + ip.g;
+    // one merge loop for the three uses below (the arguments vary, the code does not)
     auto merge = [&](bool from_groups, long long k0, long long k1, long long to_group) {
+#pragma unroll 1
         for (int chunk = t; chunk < kRows * 8; chunk += n_thr) {
             const int r = chunk >> 3;
             if (r < sh.R) merge_row_chunk(ip, sq, sh, mc, from_groups, b0, k0, k1, to_group, r, (chunk & 7) * 16);
         }
     };
+    bool from_groups = false;
+    long long k0 = b0, k1 = b1, to_group = -1;
     if (n_parts <= kMergeFan) {
-        if (!lead([&] { return count_part(mc.counters + item, n_parts); })) return;
+        if (!lead(mc.counters + item, n_parts)) return;
+    } else {
+        const long long grp = b / kMergeFan;
+        const long long gb0 = max(b0, grp * kMergeFan), gb1 = min(b1, grp * kMergeFan + kMergeFan - 1);
+        if (!lead(mc.gcounters + grp * 2 + group_slot(grp, b0), static_cast<int>(gb1 - gb0 + 1))) return;
         __threadfence();
-        merge(false, b0, b1, -1);
-        return;
+        merge(false, gb0, gb1, grp);
+        __threadfence();   // every member publishes its piece of the group partial before the leader counts the group
+        const long long g0 = b0 / kMergeFan, g1 = b1 / kMergeFan;
+        if (!lead(mc.counters + item, static_cast<int>(g1 - g0 + 1))) return;
+        from_groups = true; k0 = g0; k1 = g1;
     }
-    const long long grp = b / kMergeFan;
-    const long long gb0 = max(b0, grp * kMergeFan), gb1 = min(b1, grp * kMergeFan + kMergeFan - 1);
-    if (!lead([&] { return count_part(mc.gcounters + grp * 2 + group_slot(grp, b0), static_cast<int>(gb1 - gb0 + 1)); })) return;
     __threadfence();
-    merge(false, gb0, gb1, grp);
-    __threadfence();   // every member publishes its piece of the group partial before the leader counts the group
-    const long long g0 = b0 / kMergeFan, g1 = b1 / kMergeFan;
-    if (!lead([&] { return count_part(mc.counters + item, static_cast<int>(g1 - g0 + 1)); })) return;
-    __threadfence();
-    merge(true, g0, g1, -1);
+    merge(from_groups, k0, k1, to_group);
 }
 
 __global__ void __launch_bounds__(kThreads, 2)
 decode_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map,
               const __grid_constant__ DecodeTable tab, AttnShape sh, uint16_t *__restrict__ k_base,
               uint16_t *__restrict__ v_base, WsHeader *hdr, int *counters, int *gcounters, float *partials,
-              float *gpartials) {
+              float *gpartials, const float2 *__restrict__ rope_tab, int rope_tab_len) {
     extern __shared__ uint8_t smem_raw[];
     DecodeSmem &sm = *reinterpret_cast<DecodeSmem *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -485,8 +580,8 @@ decode_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__
             mbar_init(&sm.qempty[b], kConsumerWarps);
         }
         mbar_init(&sm.hstart, 1);
-        mbar_init(&sm.pdone[0], 1);
-        mbar_init(&sm.pdone[1], 1);
+        mbar_init(&sm.pdone[0], kConsumerWarps);
+        mbar_init(&sm.pdone[1], kConsumerWarps);
         fence_mbar_init();
     }
     // The sequence descriptors and the prefix sums of their tile counts arrive as kernel parameters: no upload
@@ -495,16 +590,32 @@ decode_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__
     const int n_seq = tab.n_seq;
     for (int i = tid; i <= n_seq; i += kThreads) {
         sm.prefix[i] = tab.prefix[i];
+        if (i < n_seq) sm.slot[i] = tab.seqs[i].slot;
     }
-    // Launched with programmatic stream serialization: everything above (barrier set-up, parameter reads) may run
-    // while the previous kernel of the stream is still draining; from here on this grid touches global memory, so
-    // it waits until that kernel has completed and its writes are visible.  Stream order is preserved.
-    asm volatile("griddepcontrol.wait;" ::: "memory");
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     __syncthreads();
     const long long total = static_cast<long long>(sm.prefix[n_seq]) * G;
     const long long nb = gridDim.x;
     const long long span_lo = span_start(blockIdx.x, total, nb), span_hi = span_start(blockIdx.x + 1, total, nb);
+    // Launched with programmatic stream serialization: everything that reads only kernel parameters (barrier
+    // set-up, the tables above, the first segment's descriptor, the tensor maps) runs while the previous kernel of
+    // the stream is still draining.  A read of parameter space at a computed index costs about a microsecond when
+    // it misses, so none is left on the path between the wait below and the first tile.
+    if (span_lo < span_hi) {
+        if (warp == kHelperWarp) {
+            const ItemPos ip = locate(sm.prefix, n_seq, G, span_lo);
+            load_seq_desc(sm.sq, tab.seqs[ip.seq], lane);
+        } else if (warp == kProducerWarp && lane == 0) {
+            tma_prefetch_desc(&k_map);
+            tma_prefetch_desc(&v_map);
+        }
+    }
+    // From here on this grid touches global memory, so it waits until the previous kernel has completed and its
+    // writes are visible.  Stream order is preserved.
+    // (The helper warp of a CTA with work waits inside its loop, after a dry pass over its first segment.)
+    if (warp != kHelperWarp || span_lo >= span_hi) {
+        asm volatile("griddepcontrol.wait;" ::: "memory");
+        asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    }
     if (span_lo >= span_hi) {
         return;
     }
@@ -512,13 +623,11 @@ decode_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__
     if (warp == kProducerWarp) {
         // ================================ producer warp ================================================
         if (lane == 0) {
-            tma_prefetch_desc(&k_map);
-            tma_prefetch_desc(&v_map);
             long long pos = span_lo;
             unsigned int n = 0;
             while (pos < span_hi && !sm.abort_flag) {
                 const ItemPos ip = locate(sm.prefix, n_seq, G, pos);
-                const int row = tab.seqs[ip.seq].slot * G + ip.g;
+                const int row = sm.slot[ip.seq] * G + ip.g;
                 const long long seg_end = min(span_hi, ip.item_begin + ip.n_tiles);
                 for (int t = ip.tile; pos < seg_end; ++t, ++pos, ++n) {
                     const int st = n % kStages;
@@ -540,46 +649,64 @@ decode_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__
     } else if (warp == kHelperWarp) {
         // ================================ helper warp ==================================================
         const MergeCtx mc{total, nb, counters, gcounters, partials, gpartials};
-        auto warp_lead = [&](auto f) {
-            __syncwarp();
-            int v = 0;
-            if (lane == 0) v = f();
-            return __shfl_sync(0xffffffffu, v, 0);
-        };
         long long pos = span_lo;
         unsigned int sidx = 0;
         int prev_slot = 0;   // partial slot of the previous segment: 0 for the CTA's first segment, else 1
         bool prev_partial = false;
         ItemPos prev_ip{};
-        SeqDev prev_sq{};
+        ItemOut prev_sq{};
         while (pos < span_hi && !sm.abort_flag) {
             const ItemPos ip = locate(sm.prefix, n_seq, G, pos);
-            const SeqDev sq = tab.seqs[ip.seq];
+            if (sidx > 0) load_seq_desc(sm.sq, tab.seqs[ip.seq], lane);   // the first one was fetched before the wait
+            const SeqDev sq = sm.sq;
+            __syncwarp();
             const long long item_end = ip.item_begin + ip.n_tiles;
             const long long seg_end = min(span_hi, item_end);
             const bool has_last_tile = seg_end == item_end;
             const bool appender = has_last_tile && !(sq.flags & CGLM_SEQ_NO_APPEND);
             const int b = sidx & 1;
             mbar_wait_bounded(&sm.qempty[b], ((sidx >> 1) & 1u) ^ 1u, &sm.abort_flag);
-            prepare_segment(sm.qb[b], sh, sq, ip.g, sq.slot * G + ip.g, has_last_tile, appender, lane, k_base, v_base,
-                            sidx == 0 ? &sm.hstart : nullptr);
+            // First segment: a dry pass while the previous kernel of the stream may still be running, then the wait
+            // that every thread makes before it touches global memory, then the real pass over warm code.
+            const int n_pass = sidx == 0 ? 2 : 1;
+#pragma unroll 1
+            for (int pass = 0; pass < n_pass; ++pass) {
+                const bool dry = pass + 1 < n_pass;
+                if (sidx == 0 && !dry) {
+                    asm volatile("griddepcontrol.wait;" ::: "memory");
+                }
+                prepare_segment(sm.qb[b], sh, sq, ip.g, sq.slot * G + ip.g, has_last_tile, appender, lane, k_base, v_base,
+                                rope_tab, rope_tab_len, (sidx == 0 && !dry) ? &sm.hstart : nullptr, dry);
+            }
             __syncwarp();
             if (lane == 0) mbar_arrive(&sm.qfull[b]);
             if (prev_partial) {   // the consumers are still on the previous segment, or just left it
                 mbar_wait_bounded(&sm.pdone[prev_slot], 0, &sm.abort_flag);   // each used once: a CTA has <= 2 partials
-                deliver_part(prev_ip, prev_sq, sh, mc, blockIdx.x, lane, 32, warp_lead);
+                {
+                    DeliverArgs &da = sm.dargs[kConsumerWarps];
+                    if (lane == 0) { da.ip = prev_ip; da.io = prev_sq; da.mc = mc; da.G = G; da.R = R; }
+                    __syncwarp();
+                    deliver_part(&da, blockIdx.x, lane, 32, nullptr);
+                    __syncwarp();
+                }
             }
             // the span's final segment is finished by the consumer warps themselves
             prev_partial = !(pos == ip.item_begin && has_last_tile) && seg_end < span_hi;
             prev_slot = sidx == 0 ? 0 : 1;
             prev_ip = ip;
-            prev_sq = sq;
+            prev_sq = ItemOut{sq.out, sq.partial, sq.flags};
             pos = seg_end;
             ++sidx;
         }
         if (prev_partial && !sm.abort_flag) {
             mbar_wait_bounded(&sm.pdone[prev_slot], 0, &sm.abort_flag);
-            deliver_part(prev_ip, prev_sq, sh, mc, blockIdx.x, lane, 32, warp_lead);
+            {
+                    DeliverArgs &da = sm.dargs[kConsumerWarps];
+                    if (lane == 0) { da.ip = prev_ip; da.io = prev_sq; da.mc = mc; da.G = G; da.R = R; }
+                    __syncwarp();
+                    deliver_part(&da, blockIdx.x, lane, 32, nullptr);
+                    __syncwarp();
+                }
         }
     } else {
         // ================================ consumer warps ===============================================
@@ -625,186 +752,128 @@ decode_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__
                 mbar_wait_bounded(&sm.full[st], (n / kStages) & 1u, &sm.abort_flag);
                 const uint32_t kb = smem_u32(sm.stage[st]);
                 const uint32_t vb = kb + 2 * kKHalfBytes;
-                float s[2][4];
-                if (t != last_tile) {
-                    qk_slice(kb, warp, lane, qa, s);
-                    softmax_pv_slice<true>(vb, warp, lane, 16, s, m_run, l_run, o);
-                } else {
+                int n_valid = 16;
+                if (t == last_tile) {
                     const int tok0 = t * kTile + 16 * warp;   // first token of this warp's slice
-                    const int n_valid = min(16, L - tok0);
+                    n_valid = min(16, L - tok0);
                     if (n_valid > 0) {
                         patch_last_tile(kb, vb, warp, lane, n_valid, appender ? kv_before - tok0 : -1, qb.newk, qb.newv);
-                        qk_slice(kb, warp, lane, qa, s);
-                        softmax_pv_slice<false>(vb, warp, lane, n_valid, s, m_run, l_run, o);
                     }
                 }
+                if (n_valid > 0) {
+                    float s[2][4];
+                    qk_slice(kb, warp, lane, qa, s);
+                    softmax_pv_slice(vb, warp, lane, n_valid, s, m_run, l_run, o);
+                }
                 __syncwarp();
-                if (lane == 0) mbar_arrive(&sm.empty[st]);
+                // the stage of the segment's last tile is kept: it becomes the fold space below
+                if (lane == 0 && pos + 1 < seg_end) mbar_arrive(&sm.empty[st]);
             }
             // the q tile, newk and newv of this segment are no longer needed
             __syncwarp();
             if (lane == 0) mbar_arrive(&sm.qempty[sidx & 1]);
 
-            // ---- fold the four warps' states into warp 0, one 64-dim half at a time ----------------------
+            // ---- fold the four warps' states -----------------------------------------------------------------
+            // Each warp attended its own 16 tokens of every tile and holds (m, l, O[16][128]) for them.  The stage
+            // of the last tile (32 KiB = four O's) is borrowed before it goes back to the producer: every warp
+            // writes its O there, scaled to the common maximum; then warp w adds up dims [32w, 32w+32) of the four
+            // copies in a fixed order and writes that slice of the result itself.  Two barriers, and the output
+            // leaves through all 128 threads.
+            float *fold = reinterpret_cast<float *>(sm.stage[(n - 1) % kStages]);
+            float *stats = sm.xchg;   // [warp][m: 16 rows | l: 16 rows]
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
                 l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 1);
                 l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 2);
             }
-            if (seg_end == span_hi) {
-                // Last segment of the span: the tile ring is idle (every tile has been loaded and consumed), so it
-                // serves as one exchange area per warp and the fold takes two barriers instead of twelve.
-                constexpr int kStride = 132;
-                float *area = reinterpret_cast<float *>(sm.stage[0]);   // [3 warps][16 rows * 132 + 32]
-                named_bar_sync(1, kConsumerThreads);                     // every warp has finished reading its tiles
-                if (warp > 0) {
-                    float *mine = area + (warp - 1) * (kRows * kStride + 2 * kRows);
+            if (c == 0) {
+                stats[warp * 32 + quad_row] = m_run[0];
+                stats[warp * 32 + quad_row + 8] = m_run[1];
+                stats[warp * 32 + 16 + quad_row] = l_run[0];
+                stats[warp * 32 + 16 + quad_row + 8] = l_run[1];
+            }
+            named_bar_sync(1, kConsumerThreads);   // statistics visible; every warp has finished reading the tile
+            {
+                float a[2];
 #pragma unroll
-                    for (int nd = 0; nd < 16; ++nd) {
-                        *reinterpret_cast<float2 *>(&mine[quad_row * kStride + 8 * nd + 2 * c]) = make_float2(o[nd][0], o[nd][1]);
-                        *reinterpret_cast<float2 *>(&mine[(quad_row + 8) * kStride + 8 * nd + 2 * c]) = make_float2(o[nd][2], o[nd][3]);
-                    }
-                    if (c == 0) {
-                        mine[kRows * kStride + quad_row] = m_run[0];
-                        mine[kRows * kStride + quad_row + 8] = m_run[1];
-                        mine[kRows * kStride + kRows + quad_row] = l_run[0];
-                        mine[kRows * kStride + kRows + quad_row + 8] = l_run[1];
+                for (int h = 0; h < 2; ++h) {
+                    const int r = quad_row + 8 * h;
+                    const float m_star = fmaxf(fmaxf(stats[r], stats[32 + r]), fmaxf(stats[64 + r], stats[96 + r]));
+                    a[h] = ex2_approx(m_run[h] - m_star);   // 0 for a warp that saw no attended token (m = -inf)
+                }
+                // float2 unit u of row r lives at unit u ^ 4(r & 3): conflict-free stores here, and 16-byte reads below
+                float *mine = fold + warp * (kRows * kD);
+                const int swz = 4 * (quad_row & 3);
+#pragma unroll
+                for (int nd = 0; nd < 16; ++nd) {
+                    const int u = (4 * nd + c) ^ swz;
+                    *reinterpret_cast<float2 *>(&mine[quad_row * kD + 2 * u]) = make_float2(o[nd][0] * a[0], o[nd][1] * a[0]);
+                    *reinterpret_cast<float2 *>(&mine[(quad_row + 8) * kD + 2 * u]) = make_float2(o[nd][2] * a[1], o[nd][3] * a[1]);
+                }
+            }
+            named_bar_sync(1, kConsumerThreads);
+            {
+                // lane -> row rr, and 16 of the warp's 32 dims as four float4 (q: index of a float4 inside the row)
+                const int rr = lane >> 1, hf = lane & 1;
+                const float m0 = stats[rr], m1 = stats[32 + rr], m2 = stats[64 + rr], m3 = stats[96 + rr];
+                const float m_star = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
+                const float l_sum = ((stats[16 + rr] * ex2_approx(m0 - m_star) + stats[48 + rr] * ex2_approx(m1 - m_star)) +
+                                     stats[80 + rr] * ex2_approx(m2 - m_star)) + stats[112 + rr] * ex2_approx(m3 - m_star);
+                const bool want_partial = (flags & CGLM_SEQ_PARTIAL) != 0;
+                const int head = g * R + rr;
+                const float inv = 1.f / l_sum;
+                float *scratch = partials + (static_cast<long long>(blockIdx.x) * 2 + (first_segment ? 0 : 1)) * kDecodePartialFloats;
+#pragma unroll
+                for (int jj = 0; jj < 4; ++jj) {
+                    const int q = 8 * warp + 4 * hf + (jj ^ hf);   // the two lanes of a row start on different banks
+                    const float *src = fold + rr * kD + 4 * (q ^ (2 * (rr & 3)));
+                    const float4 v0 = *reinterpret_cast<const float4 *>(src);
+                    const float4 v1 = *reinterpret_cast<const float4 *>(src + kRows * kD);
+                    const float4 v2 = *reinterpret_cast<const float4 *>(src + 2 * kRows * kD);
+                    const float4 v3 = *reinterpret_cast<const float4 *>(src + 3 * kRows * kD);
+                    float4 acc;
+                    acc.x = ((v0.x + v1.x) + v2.x) + v3.x; acc.y = ((v0.y + v1.y) + v2.y) + v3.y;
+                    acc.z = ((v0.z + v1.z) + v2.z) + v3.z; acc.w = ((v0.w + v1.w) + v2.w) + v3.w;
+                    if (!whole_item) {
+                        __stcg(reinterpret_cast<float4 *>(scratch + rr * kD + 4 * q), acc);
+                    } else if (rr < R) {
+                        if (want_partial) {   // rows of kD + 2 floats: 8-byte aligned only
+                            float *pp = partial_ptr + static_cast<long long>(head) * (kD + 2) + 4 * q;
+                            *reinterpret_cast<float2 *>(pp) = make_float2(acc.x, acc.y);
+                            *reinterpret_cast<float2 *>(pp + 2) = make_float2(acc.z, acc.w);
+                        } else {
+                            *reinterpret_cast<float4 *>(out_ptr + static_cast<long long>(head) * kD + 4 * q) =
+                                make_float4(acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv);
+                        }
                     }
                 }
-                named_bar_sync(1, kConsumerThreads);
-                if (warp == 0) {
-                    for (int src = 1; src < kConsumerWarps; ++src) {
-                        const float *theirs = area + (src - 1) * (kRows * kStride + 2 * kRows);
-                        float a_me[2], a_src[2];
-#pragma unroll
-                        for (int h = 0; h < 2; ++h) {
-                            const float m_src = theirs[kRows * kStride + quad_row + 8 * h];
-                            const float l_src = theirs[kRows * kStride + kRows + quad_row + 8 * h];
-                            const float m_new = fmaxf(m_run[h], m_src);
-                            a_me[h] = ex2_approx(m_run[h] - m_new);
-                            a_src[h] = ex2_approx(m_src - m_new);
-                            l_run[h] = l_run[h] * a_me[h] + l_src * a_src[h];
-                            m_run[h] = m_new;
-                        }
-#pragma unroll
-                        for (int nd = 0; nd < 16; ++nd) {
-                            const float2 lo2 = *reinterpret_cast<const float2 *>(&theirs[quad_row * kStride + 8 * nd + 2 * c]);
-                            const float2 hi2 = *reinterpret_cast<const float2 *>(&theirs[(quad_row + 8) * kStride + 8 * nd + 2 * c]);
-                            o[nd][0] = o[nd][0] * a_me[0] + lo2.x * a_src[0];
-                            o[nd][1] = o[nd][1] * a_me[0] + lo2.y * a_src[0];
-                            o[nd][2] = o[nd][2] * a_me[1] + hi2.x * a_src[1];
-                            o[nd][3] = o[nd][3] * a_me[1] + hi2.y * a_src[1];
-                        }
-                    }
-                }
-            } else
-            for (int src = 1; src < kConsumerWarps; ++src) {
-                float a_me[2] = {1.f, 1.f}, a_src[2] = {0.f, 0.f};
-#pragma unroll
-                for (int half = 0; half < 2; ++half) {
-                    named_bar_sync(1, kConsumerThreads);
-                    if (warp == src) {
-#pragma unroll
-                        for (int nd = 0; nd < 8; ++nd) {
-                            *reinterpret_cast<float2 *>(&sm.xchg[quad_row * kXchgStride + 8 * nd + 2 * c]) =
-                                make_float2(o[8 * half + nd][0], o[8 * half + nd][1]);
-                            *reinterpret_cast<float2 *>(&sm.xchg[(quad_row + 8) * kXchgStride + 8 * nd + 2 * c]) =
-                                make_float2(o[8 * half + nd][2], o[8 * half + nd][3]);
-                        }
-                        if (half == 0 && c == 0) {
-                            sm.xchg[kRows * kXchgStride + quad_row] = m_run[0];
-                            sm.xchg[kRows * kXchgStride + quad_row + 8] = m_run[1];
-                            sm.xchg[kRows * kXchgStride + kRows + quad_row] = l_run[0];
-                            sm.xchg[kRows * kXchgStride + kRows + quad_row + 8] = l_run[1];
-                        }
-                    }
-                    named_bar_sync(1, kConsumerThreads);
-                    if (warp == 0) {
-                        if (half == 0) {
-#pragma unroll
-                            for (int h = 0; h < 2; ++h) {
-                                const float m_src = sm.xchg[kRows * kXchgStride + quad_row + 8 * h];
-                                const float l_src = sm.xchg[kRows * kXchgStride + kRows + quad_row + 8 * h];
-                                const float m_new = fmaxf(m_run[h], m_src);
-                                a_me[h] = ex2_approx(m_run[h] - m_new);
-                                a_src[h] = ex2_approx(m_src - m_new);
-                                l_run[h] = l_run[h] * a_me[h] + l_src * a_src[h];
-                                m_run[h] = m_new;
-                            }
-                        }
-#pragma unroll
-                        for (int nd = 0; nd < 8; ++nd) {
-                            const float2 lo2 = *reinterpret_cast<const float2 *>(&sm.xchg[quad_row * kXchgStride + 8 * nd + 2 * c]);
-                            const float2 hi2 = *reinterpret_cast<const float2 *>(&sm.xchg[(quad_row + 8) * kXchgStride + 8 * nd + 2 * c]);
-                            float(&oo)[4] = o[8 * half + nd];
-                            oo[0] = oo[0] * a_me[0] + lo2.x * a_src[0];
-                            oo[1] = oo[1] * a_me[0] + lo2.y * a_src[0];
-                            oo[2] = oo[2] * a_me[1] + hi2.x * a_src[1];
-                            oo[3] = oo[3] * a_me[1] + hi2.y * a_src[1];
-                        }
+                if (warp == 0 && hf == 0) {
+                    if (!whole_item) {
+                        __stcg(&scratch[kRows * kD + rr], m_star);
+                        __stcg(&scratch[kRows * kD + kRows + rr], l_sum);
+                    } else if (want_partial && rr < R) {
+                        float *pp = partial_ptr + static_cast<long long>(head) * (kD + 2);
+                        pp[kD] = m_star * kLn2;
+                        pp[kD + 1] = l_sum;
                     }
                 }
             }
-
-            // ---- emit: final rows, or a partial for the merge kernel --------------------------------------
-            if (warp == 0) {
-                const bool want_partial = (flags & CGLM_SEQ_PARTIAL) != 0;
-                if (whole_item) {
-#pragma unroll
-                    for (int h = 0; h < 2; ++h) {
-                        const int r = quad_row + 8 * h;
-                        if (r < R) {
-                            const int head = g * R + r;
-                            if (want_partial) {
-                                float *pp = partial_ptr + static_cast<long long>(head) * (kD + 2);
-#pragma unroll
-                                for (int nd = 0; nd < 16; ++nd) {
-                                    *reinterpret_cast<float2 *>(&pp[8 * nd + 2 * c]) =
-                                        make_float2(o[nd][2 * h], o[nd][2 * h + 1]);
-                                }
-                                if (c == 0) { pp[kD] = m_run[h] * kLn2; pp[kD + 1] = l_run[h]; }
-                            } else {
-                                const float inv = 1.f / l_run[h];
-                                float *op = out_ptr + static_cast<long long>(head) * kD;
-#pragma unroll
-                                for (int nd = 0; nd < 16; ++nd) {
-                                    *reinterpret_cast<float2 *>(&op[8 * nd + 2 * c]) =
-                                        make_float2(o[nd][2 * h] * inv, o[nd][2 * h + 1] * inv);
-                                }
-                            }
-                        }
-                    }
-                } else {
-                    float *pp = partials + (static_cast<long long>(blockIdx.x) * 2 + (first_segment ? 0 : 1)) * kDecodePartialFloats;
-#pragma unroll
-                    for (int nd = 0; nd < 16; ++nd) {
-                        __stcg(reinterpret_cast<float2 *>(&pp[quad_row * kD + 8 * nd + 2 * c]), make_float2(o[nd][0], o[nd][1]));
-                        __stcg(reinterpret_cast<float2 *>(&pp[(quad_row + 8) * kD + 8 * nd + 2 * c]), make_float2(o[nd][2], o[nd][3]));
-                    }
-                    if (c == 0) {
-                        __stcg(&pp[kRows * kD + quad_row], m_run[0]);
-                        __stcg(&pp[kRows * kD + quad_row + 8], m_run[1]);
-                        __stcg(&pp[kRows * kD + kRows + quad_row], l_run[0]);
-                        __stcg(&pp[kRows * kD + kRows + quad_row + 8], l_run[1]);
-                    }
-                    __syncwarp();
-                    if (seg_end < span_hi) {
-                        // more segments follow: the helper warp counts and merges while we stream on
-                        if (lane == 0) mbar_arrive(&sm.pdone[first_segment ? 0 : 1]);
-                    }
-                }
+            // hand the stage back: generic-proxy writes above, TMA writes next
+            fence_proxy_async();
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive(&sm.empty[(n - 1) % kStages]);
+                // more segments follow and this one left a partial: the helper warp counts and merges it
+                if (!whole_item && seg_end < span_hi) mbar_arrive(&sm.pdone[first_segment ? 0 : 1]);
             }
             if (!whole_item && seg_end == span_hi) {
                 // end of the span: nothing left to overlap with, all four warps complete the item if it is theirs to
-                // complete.  The barrier inside cta_lead also orders warp 0's partial stores before the count.
+                // complete.  The team barrier inside deliver_part also orders every warp's partial stores before the count.
                 const MergeCtx mc{total, nb, counters, gcounters, partials, gpartials};
-                auto cta_lead = [&](auto f) {
-                    named_bar_sync(1, kConsumerThreads);
-                    if (tid == 0) sm.last_flag = f();
-                    named_bar_sync(1, kConsumerThreads);
-                    return sm.last_flag;
-                };
-                deliver_part(ip, tab.seqs[ip.seq], sh, mc, blockIdx.x, tid, kConsumerThreads, cta_lead);
+                DeliverArgs &da = sm.dargs[warp];   // every warp parks its own copy: no barrier needed before the call
+                if (lane == 0) { da.ip = ip; da.io = ItemOut{out_ptr, partial_ptr, flags}; da.mc = mc; da.G = G; da.R = R; }
+                __syncwarp();
+                deliver_part(&da, blockIdx.x, tid, kConsumerThreads, &sm.last_flag);
             }
             first_segment = false;
             ++sidx;
@@ -844,7 +913,7 @@ cudaError_t launch_decode(const LaunchCtx &cx, const DecodeTable &tab) {
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     cudaError_t e = cudaLaunchKernelEx(&cfg, decode_kernel, *cx.k_map, *cx.v_map, tab, cx.shape, cx.k_base, cx.v_base, cx.hdr,
-                                       cx.counters, cx.gcounters, cx.partials, cx.gpartials);
+                                       cx.counters, cx.gcounters, cx.partials, cx.gpartials, cx.rope_tab, cx.rope_tab_len);
     g_launch_count += 1;
     return e != cudaSuccess ? e : cudaGetLastError();
 }

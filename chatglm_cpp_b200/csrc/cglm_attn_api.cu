@@ -27,6 +27,8 @@ struct cglm_kv_arena {
     uint8_t *base;        // one allocation: K slabs, then V slabs
     uint16_t *k_base;
     uint16_t *v_base;
+    float2 *rope_tab;     // GLM rope modes at head_dim 128: (cos, sin) of ladder step i at position p, [max_len][32]
+    int rope_tab_len;
     size_t k_slot_elems;  // G*M*D
     bool has_tmaps;
     CUtensorMap k_map, v_map;
@@ -232,6 +234,17 @@ bool fast_decode_shape(const cglm_kv_arena *a) {
            (d.rope_type == CGLM_ROPE_CHATGLM2 || d.rope_type == CGLM_ROPE_CHATGLM || d.rope_type == CGLM_ROPE_DISABLED);
 }
 
+// Angle table of an arena: entry [p][i] = (cos, sin) of ladder step i at position p, the same values the kernels
+// would compute on the fly (rope_cos_sin).  The decode kernel reads 256 bytes of it per segment instead of
+// evaluating a double-precision sincos between its start and its first tile.
+__global__ void rope_arena_table_kernel(float theta_scale, int n_pos, float2 *__restrict__ table) {
+    const long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+    if (i >= static_cast<long long>(n_pos) * 32) return;
+    float c, s;
+    rope_cos_sin(static_cast<int>(i >> 5), static_cast<int>(i & 31), theta_scale, c, s);
+    table[i] = make_float2(c, s);
+}
+
 __global__ void combine_kernel(const float *__restrict__ partials, int n_part, int H, int D, float *__restrict__ out) {
     const int h = blockIdx.x;
     float m_star = -INFINITY;
@@ -296,6 +309,7 @@ bool arena_fast_decode(const cglm_kv_arena *a) { return fast_decode_shape(a); }
 int arena_device(const cglm_kv_arena *a) { return a->device; }
 int arena_sm_count(const cglm_kv_arena *a) { return a->n_sm; }
 AttnShape arena_shape(const cglm_kv_arena *a) { return make_shape(a->desc); }
+const float2 *arena_rope_tab(const cglm_kv_arena *a, int *len) { *len = a->rope_tab_len; return a->rope_tab; }
 void set_last_error(const char *text) { std::snprintf(g_err, sizeof(g_err), "%s", text); }
 }  // namespace cglm
 
@@ -324,8 +338,11 @@ int cglm_kv_arena_create(const cglm_attn_desc *desc, int n_slots, cglm_kv_arena 
     cudaGetDevice(&a->device);
     a->k_slot_elems = static_cast<size_t>(desc->n_kv_head) * desc->max_len * desc->head_dim;
     const size_t k_bytes = align_up(a->k_slot_elems * 2 * n_slots, 1024);
-    const size_t v_bytes = a->k_slot_elems * 2 * n_slots;
-    cudaError_t e = cudaMalloc(reinterpret_cast<void **>(&a->base), k_bytes + v_bytes);
+    const size_t v_bytes = align_up(a->k_slot_elems * 2 * n_slots, 1024);
+    const bool glm_rope = desc->rope_type == CGLM_ROPE_CHATGLM2 || desc->rope_type == CGLM_ROPE_CHATGLM;
+    a->rope_tab_len = desc->head_dim == 128 && glm_rope ? desc->max_len : 0;
+    const size_t tab_bytes = static_cast<size_t>(a->rope_tab_len) * 32 * sizeof(float2);
+    cudaError_t e = cudaMalloc(reinterpret_cast<void **>(&a->base), k_bytes + v_bytes + tab_bytes);
     if (e != cudaSuccess) {
         delete a;
         return fail_cuda(e, "cudaMalloc(kv arena)");
@@ -337,6 +354,20 @@ int cglm_kv_arena_create(const cglm_attn_desc *desc, int n_slots, cglm_kv_arena 
         cudaFree(a->base);
         delete a;
         return fail_cuda(e, "cudaMemset(kv arena)");
+    }
+    a->rope_tab = nullptr;
+    if (a->rope_tab_len > 0) {
+        a->rope_tab = reinterpret_cast<float2 *>(a->base + k_bytes + v_bytes);
+        const long long n = static_cast<long long>(a->rope_tab_len) * 32;
+        rope_arena_table_kernel<<<static_cast<unsigned>((n + 255) / 256), 256>>>(make_shape(*desc).theta_scale, a->rope_tab_len,
+                                                                               a->rope_tab);
+        e = cudaGetLastError();
+        if (e == cudaSuccess) e = cudaDeviceSynchronize();
+        if (e != cudaSuccess) {
+            cudaFree(a->base);
+            delete a;
+            return fail_cuda(e, "rope table");
+        }
     }
     a->has_tmaps = desc->head_dim == 128 && desc->max_len % 8 == 0 && build_tensor_maps(a);
     a->ring = nullptr;
@@ -467,7 +498,8 @@ int cglm_attn_forward(cglm_kv_arena *a, const cglm_attn_seq *seqs, int n_seq, vo
         if (static_cast<long long>(kv_before) + appended > d.max_len) return CGLM_ERR_INVALID_ARG;
         if (d.rope_type == CGLM_ROPE_CHATGLM && !s.position_ids && s.n_ctx < 2) return CGLM_ERR_INVALID_ARG;
         const int L = kv_before + appended;
-        is_fast[i] = fast_ok && s.qlen == 1 && L >= 1;
+        is_fast[i] = fast_ok && s.qlen == 1 && L >= 1 &&
+                     decode_rows_aligned(s.q, s.k, s.v, s.q_head_stride, s.kv_head_stride, s.q_roped, s.k_roped);
         if (is_fast[i]) {
             ++n_fast;
             decode_tiles += static_cast<long long>((L + kDecodeTile - 1) / kDecodeTile) * d.n_kv_head;
@@ -509,6 +541,8 @@ int cglm_attn_forward(cglm_kv_arena *a, const cglm_attn_seq *seqs, int n_seq, vo
     cx.q_stage = reinterpret_cast<float *>(ws + lay.q_stage);
     cx.k_map = &a->k_map;
     cx.v_map = &a->v_map;
+    cx.rope_tab = a->rope_tab;
+    cx.rope_tab_len = a->rope_tab_len;
     cx.stream = st;
     cx.n_sm = a->n_sm;
 

@@ -23,6 +23,7 @@ bool arena_fast_decode(const cglm_kv_arena *a);
 int arena_device(const cglm_kv_arena *a);
 int arena_sm_count(const cglm_kv_arena *a);
 AttnShape arena_shape(const cglm_kv_arena *a);
+const float2 *arena_rope_tab(const cglm_kv_arena *a, int *len);
 void set_last_error(const char *text);   // what cglm_last_error_string returns on this thread
 }  // namespace cglm
 
@@ -103,6 +104,10 @@ extern "C" int cglm_attn_decode_static(cglm_kv_arena *arena, const cglm_attn_seq
         if ((reinterpret_cast<uintptr_t>(s.out) & 15) || (reinterpret_cast<uintptr_t>(s.q) & 3) ||
             (reinterpret_cast<uintptr_t>(s.k) & 3) || (reinterpret_cast<uintptr_t>(s.v) & 3))
             return CGLM_ERR_INVALID_ARG;
+        if (!decode_rows_aligned(s.q, s.k, s.v, s.q_head_stride, s.kv_head_stride, s.q_roped, s.k_roped)) {
+            set_last_error("q, k, v rows must be 16-byte aligned (pointers and head strides)");
+            return CGLM_ERR_UNSUPPORTED;
+        }
         if (shape.V + s.n_past + 1 > shape.M) return CGLM_ERR_INVALID_ARG;
         if (shape.rope_type == CGLM_ROPE_CHATGLM && !s.position_ids && s.n_ctx < 2) return CGLM_ERR_INVALID_ARG;
         SeqDev &o = tab.seqs[i];
@@ -136,6 +141,7 @@ extern "C" int cglm_attn_decode_static(cglm_kv_arena *arena, const cglm_attn_seq
     cx.q_stage = nullptr;
     cx.k_map = arena_k_map(arena);
     cx.v_map = arena_v_map(arena);
+    cx.rope_tab = arena_rope_tab(arena, &cx.rope_tab_len);
     cx.stream = st;
     cx.n_sm = arena_sm_count(arena);
     e = launch_decode(cx, tab);

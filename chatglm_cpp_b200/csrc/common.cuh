@@ -233,6 +233,8 @@ struct LaunchCtx {
     float *q_stage;              // generic path: roped, scaled q f32 [tokens][H][D]
     const CUtensorMap *k_map;    // host copies of the arena's tensor maps (passed by value to kernels)
     const CUtensorMap *v_map;
+    const float2 *rope_tab;      // arena's angle table: [rope_tab_len positions][32 ladder steps] (cos, sin); may be null
+    int rope_tab_len;
     cudaStream_t stream;
     int n_sm;
 };
@@ -252,6 +254,13 @@ struct DecodeTable {
     SeqDev seqs[kDecodeMaxSeqPerLaunch];
 };
 cudaError_t launch_decode(const LaunchCtx &cx, const DecodeTable &tab);
+// The decode kernel reads q/k/v head rows (and writes the optional roped copies) sixteen bytes at a time.
+inline bool decode_rows_aligned(const float *q, const float *k, const float *v, long long q_head_stride,
+                                long long kv_head_stride, const float *q_roped, const float *k_roped) {
+    const uintptr_t bits = reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v) |
+                           reinterpret_cast<uintptr_t>(q_roped) | reinterpret_cast<uintptr_t>(k_roped);
+    return (bits & 15) == 0 && q_head_stride % 4 == 0 && kv_head_stride % 4 == 0;
+}
 // tcgen05 prefill (head_dim 128, n_past == 0, qlen >= 128): per-call tensor maps over the f16 q staging buffer
 // [H][s_pad][D] and over the slot's caches cut at the attended length
 size_t prefill_q_half_bytes(int H, int S);
