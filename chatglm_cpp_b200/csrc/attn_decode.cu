@@ -143,11 +143,6 @@ __device__ __forceinline__ void item_ctas(long long item_begin, long long item_e
     while (span_start(b1 + 1, total, nb) <= item_end - 1) ++b1;
 }
 // A CTA keeps at most two partials: slot 0 for its first segment, slot 1 for its last.
-__device__ __forceinline__ const float *part_ptr(const float *partials, long long b, long long item_begin,
-                                                 long long total, long long nb) {
-    const int slot = span_start(b, total, nb) >= item_begin ? 0 : 1;
-    return partials + (b * 2 + slot) * kDecodePartialFloats;
-}
 
 // ---- per-warp tile math ---------------------------------------------------------------------------------
 // A consumer warp owns 16 tokens of every 64-token tile: tokens 16*warp .. 16*warp+15.
@@ -426,27 +421,26 @@ constexpr int kMergeFan = kDecodeMergeFan;
 __device__ __forceinline__ int group_slot(long long grp, long long b0) { return b0 < grp * kMergeFan ? 0 : 1; }
 
 // 16 dims of one q row merged over sources k0..k1 in one pass with a running maximum, four sources in flight at a
-// time.  Sources are CTA partials (level 0) or group partials (level 1).  Every caller goes through this routine
-// with the same source order, so the result does not depend on which CTA or warp happens to complete the item.
-// to_group >= 0: the result is itself a group partial (un-normalised); otherwise it is the item's output.
-__device__ __forceinline__ void merge_row_chunk(const ItemPos &ip, const ItemOut &sq, const AttnShape &sh, const MergeCtx &mc,
-                                                bool from_groups, long long b0, long long k0, long long k1, long long to_group,
-                                                int r, int d0) {
-    auto source = [&](long long k) -> const float * {
-        return from_groups ? mc.gpartials + (k * 2 + group_slot(k, b0)) * kDecodePartialFloats
-                           : part_ptr(mc.partials, k, ip.item_begin, mc.total, mc.nb);
-    };
+// time.  Sources are CTA partials (level 0) or group partials (level 1): source k sits at base + 2k slots, except
+// that source k_first uses its second slot when first_slot is 1 (the CTA or group in which the item begins holds
+// the end of the previous item in its first slot).  Every caller goes through this routine with the same source
+// order, so the result does not depend on which CTA or warp happens to complete the item.
+// dst_kind 0: the result is a group partial (un-normalised) at dst; 1: the sequence's (acc, m, l) row; 2: its output.
+__device__ __forceinline__ void merge_row_chunk(const float *base, long long k_first, int first_slot, long long k0,
+                                                long long k1, float *dst, int dst_kind, int r, int d0) {
     float m_run = -INFINITY, den = 0.f;
     float acc[16];
 #pragma unroll
     for (int e = 0; e < 16; ++e) acc[e] = 0.f;
+#pragma unroll 1
     for (long long k = k0; k <= k1; k += 4) {
         float mv[4], lv[4];
         float4 av[4][4];
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
             const bool ok = k + u <= k1;
-            const float *pp = source(ok ? k + u : k);
+            const long long ks = ok ? k + u : k;
+            const float *pp = base + (ks * 2 + (ks == k_first ? first_slot : 0)) * kDecodePartialFloats;
             mv[u] = ok ? __ldcg(pp + kRows * kD + r) : -INFINITY;
             lv[u] = __ldcg(pp + kRows * kD + kRows + r);
 #pragma unroll
@@ -471,23 +465,21 @@ __device__ __forceinline__ void merge_row_chunk(const ItemPos &ip, const ItemOut
         }
         m_run = m_new;
     }
-    const int head = ip.g * sh.R + r;
-    if (to_group >= 0) {
-        float *gp = mc.gpartials + (to_group * 2 + group_slot(to_group, b0)) * kDecodePartialFloats;
+    if (dst_kind == 0) {
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-            __stcg(reinterpret_cast<float4 *>(gp + r * kD + d0) + e,
+            __stcg(reinterpret_cast<float4 *>(dst + r * kD + d0) + e,
                    make_float4(acc[4 * e], acc[4 * e + 1], acc[4 * e + 2], acc[4 * e + 3]));
         }
-        if (d0 == 0) { __stcg(gp + kRows * kD + r, m_run); __stcg(gp + kRows * kD + kRows + r, den); }
-    } else if (sq.flags & CGLM_SEQ_PARTIAL) {
-        float *po = sq.partial + static_cast<long long>(head) * (kD + 2);   // row stride 130 floats: scalar stores
+        if (d0 == 0) { __stcg(dst + kRows * kD + r, m_run); __stcg(dst + kRows * kD + kRows + r, den); }
+    } else if (dst_kind == 1) {
+        float *po = dst + static_cast<long long>(r) * (kD + 2);   // row stride 130 floats: 8-byte aligned only
 #pragma unroll
-        for (int e = 0; e < 16; ++e) po[d0 + e] = acc[e];
+        for (int e = 0; e < 8; ++e) *reinterpret_cast<float2 *>(po + d0 + 2 * e) = make_float2(acc[2 * e], acc[2 * e + 1]);
         if (d0 == 0) { po[kD] = m_run * kLn2; po[kD + 1] = den; }
     } else {
         const float inv = 1.f / den;
-        float4 *op = reinterpret_cast<float4 *>(sq.out + static_cast<long long>(head) * kD + d0);
+        float4 *op = reinterpret_cast<float4 *>(dst + static_cast<long long>(r) * kD + d0);
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
             op[e] = make_float4(acc[4 * e] * inv, acc[4 * e + 1] * inv, acc[4 * e + 2] * inv, acc[4 * e + 3] * inv);
@@ -532,16 +524,25 @@ __device__ __noinline__ void deliver_part(const DeliverArgs *da, long long b, in
     item_ctas(ip.item_begin, ip.item_begin + ip.n_tiles, mc.total, mc.nb, b0, b1);
     const int n_parts = static_cast<int>(b1 - b0 + 1);
     const int item = ip.seq * sh.G + ip.g;
+    // Slot of the first source at each level: the CTA (group) in which the item begins holds it in its second slot
+    // unless the item begins exactly where the CTA's span (the group's first span) does.
+    const int first_cta_slot = span_start(b0, mc.total, mc.nb) >= ip.item_begin ? 0 : 1;
+    const long long g0 = b0 / kMergeFan, g1 = b1 / kMergeFan;
+    const int first_grp_slot = group_slot(g0, b0);
+    float *final_dst = (sq.flags & CGLM_SEQ_PARTIAL) ? sq.partial + static_cast<long long>(ip.g) * sh.R * (kD + 2)
+                                                      : sq.out + static_cast<long long>(ip.g) * sh.R * kD;
+    const int final_kind = (sq.flags & CGLM_SEQ_PARTIAL) ? 1 : 2;
     // one merge loop for the three uses below (the arguments vary, the code does not)
-    auto merge = [&](bool from_groups, long long k0, long long k1, long long to_group) {
+    auto merge = [&](const float *base, long long k_first, int first_slot, long long k0, long long k1, float *dst, int kind) {
 #pragma unroll 1
         for (int chunk = t; chunk < kRows * 8; chunk += n_thr) {
             const int r = chunk >> 3;
-            if (r < sh.R) merge_row_chunk(ip, sq, sh, mc, from_groups, b0, k0, k1, to_group, r, (chunk & 7) * 16);
+            if (r < sh.R) merge_row_chunk(base, k_first, first_slot, k0, k1, dst, kind, r, (chunk & 7) * 16);
         }
     };
-    bool from_groups = false;
-    long long k0 = b0, k1 = b1, to_group = -1;
+    const float *base = mc.partials;
+    long long k_first = b0, k0 = b0, k1 = b1;
+    int first_slot = first_cta_slot;
     if (n_parts <= kMergeFan) {
         if (!lead(mc.counters + item, n_parts)) return;
     } else {
@@ -549,14 +550,14 @@ __device__ __noinline__ void deliver_part(const DeliverArgs *da, long long b, in
         const long long gb0 = max(b0, grp * kMergeFan), gb1 = min(b1, grp * kMergeFan + kMergeFan - 1);
         if (!lead(mc.gcounters + grp * 2 + group_slot(grp, b0), static_cast<int>(gb1 - gb0 + 1))) return;
         __threadfence();
-        merge(false, gb0, gb1, grp);
+        merge(mc.partials, b0, first_cta_slot, gb0, gb1,
+              mc.gpartials + (grp * 2 + group_slot(grp, b0)) * kDecodePartialFloats, 0);
         __threadfence();   // every member publishes its piece of the group partial before the leader counts the group
-        const long long g0 = b0 / kMergeFan, g1 = b1 / kMergeFan;
         if (!lead(mc.counters + item, static_cast<int>(g1 - g0 + 1))) return;
-        from_groups = true; k0 = g0; k1 = g1;
+        base = mc.gpartials; k_first = g0; first_slot = first_grp_slot; k0 = g0; k1 = g1;
     }
     __threadfence();
-    merge(from_groups, k0, k1, to_group);
+    merge(base, k_first, first_slot, k0, k1, final_dst, final_kind);
 }
 
 __global__ void __launch_bounds__(kThreads, 2)
