@@ -16,11 +16,17 @@
 //   producer warp   issues the TMA tile loads (two 64x64 K boxes, one 128x64 V^T box, 128-byte swizzle, no
 //                   multicast) into a 3-stage ring guarded by mbarriers, running ahead across segments;
 //   helper warp     prepares the NEXT segment while the consumers stream the current one (RoPE of q and of
-//                   the new k, the scaled f16 q tile, the f16 append into the cache) and finishes the PREVIOUS
-//                   one (completion counter, merge of a split item), so that a segment switch costs the
-//                   consumers no global-memory round trip;
+//                   the new k with angles from the arena's table, the scaled f16 q tile, the f16 append into the
+//                   cache) and finishes the PREVIOUS one (completion counter, merge of a split item), so that a
+//                   segment switch costs the consumers no global-memory round trip;
 //   4 consumer warps take 16 tokens of each tile, run QK^T and PV on tensor cores (mma.sync m16n8k16, the
-//                   <=16 q heads of the kv head are the M rows) with a warp-shuffle online softmax.
+//                   <=16 q heads of the kv head are the M rows) with a warp-shuffle online softmax; at the end
+//                   of a segment they fold their four states through the stage of the segment's last tile.
+// What shaped the code around the tile loop: straight-line code that runs once per launch (or once per item) is
+// paid for in instruction-fetch misses, about a microsecond per 5 KiB, while every other SM waits.  Hence one body
+// for full and partial tiles, the merge code out of line in a single copy, reads of parameter space and a dry pass
+// of the helper's first segment placed before the programmatic-dependency wait, and no sincos between the start of
+// the kernel and its first tile.
 // Both caches are already contraction-contiguous for the B operand: K is [token][d] for QK^T and V^T is
 // [d][token] for PV.
 #include "common.cuh"

@@ -28,7 +28,10 @@ constexpr int kD = 128;
 constexpr int kQTile = 128;        // q rows per CTA = TMEM lanes
 constexpr int kKvTile = 128;       // tokens per KV tile
 constexpr int kSoftmaxThreads = 128;
-constexpr int kThreads = kSoftmaxThreads + 32;   // + one control warp
+constexpr int kLoadWarp = kSoftmaxThreads / 32;       // issues every TMA load
+constexpr int kScoreWarp = kLoadWarp + 1;             // issues the S = Q K^T MMAs
+constexpr int kPvWarp = kLoadWarp + 2;                // issues the O += P V MMAs
+constexpr int kThreads = kSoftmaxThreads + 96;
 constexpr int kHalfBytes = 128 * 128;          // one 128-row x 128-byte swizzled half tile (16 KiB)
 constexpr int kTileBytes = 2 * kHalfBytes;     // a 128 x 128 f16 operand tile
 constexpr int kTmemCols = 512;                 // S[2]: columns [0,256), O: columns [256,384)
@@ -118,7 +121,10 @@ rope_table_kernel(AttnShape sh, SeqDev sq, float2 *__restrict__ table) {
 
 __global__ void __launch_bounds__(kPrepThreads)
 prefill_prepare_kernel(AttnShape sh, SeqDev sq, uint16_t *__restrict__ k_base, uint16_t *__restrict__ v_base,
-                       __half *__restrict__ q_half, int s_pad, const float2 *__restrict__ table) {
+                       __half *__restrict__ q_half, int s_pad, const float2 *__restrict__ table, int table_by_position) {
+    // the attention kernel that follows is launched as a programmatic dependent: let its CTAs take their places
+    // (shared memory, tensor memory, barriers) while this grid runs; it waits for this grid before its first load
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     __shared__ __half tile_mem[kD][kPrepTokens + 2];       // v CTAs: [dim][token] transpose tile
     const int S = sq.qlen, H = sh.H, G = sh.G, M = sh.M;
     const int t_begin = blockIdx.x * kPrepTokens;
@@ -172,7 +178,11 @@ prefill_prepare_kernel(AttnShape sh, SeqDev sq, uint16_t *__restrict__ k_base, u
         i0 = first_free + 2 * (p - n_pairs); i1 = i0 + 1;
     }
     constexpr int kBatch = 8;
-    const float2 *tab = table + (static_cast<long long>(cs_stream) * S + t_begin) * 32 + cs_ladder;
+    const bool v1 = sh.rope_type == CGLM_ROPE_CHATGLM;
+    const int v1_lim = sq.n_ctx - 2;
+    // table_by_position: the arena's table, row = position (or block position) of the token; otherwise the table
+    // rope_table_kernel wrote for this call, row = (stream, token)
+    const float2 *tab = table_by_position ? table + cs_ladder : table + (static_cast<long long>(cs_stream) * S + t_begin) * 32 + cs_ladder;
     for (int hi = 0; hi < n_heads; ++hi) {
         const int hh = head0 + hi;
         const float *src_head = is_q ? sq.q + hh * sq.q_head_stride : sq.k + hh * sq.kv_head_stride;
@@ -189,7 +199,14 @@ prefill_prepare_kernel(AttnShape sh, SeqDev sq, uint16_t *__restrict__ k_base, u
                     const float *src = src_head + (t_begin + t) * tok_stride;
                     x0[u] = __ldg(src + i0);
                     x1[u] = __ldg(src + i1);
-                    if (rotated) cs[u] = __ldg(tab + t * 32);
+                    if (rotated) {
+                        // derived ids (chatglm.cpp:1142-1153, 1319-1327 with n_past = 0), as selects: a branch here
+                        // would split the batch of loads into one round trip per token
+                        const int s_tok = t_begin + t;
+                        const int by_pos = v1 ? (cs_stream ? max(s_tok - v1_lim, 0) : min(s_tok, v1_lim)) : s_tok;
+                        const int row = table_by_position ? by_pos : t;
+                        cs[u] = __ldg(tab + row * 32);
+                    }
                 }
             }
 #pragma unroll
@@ -283,82 +300,42 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = sm.tmem_base;
+    // Launched as a programmatic dependent of the prepare kernel: everything above overlapped its tail; its q, K and
+    // V^T are read from here on.
+    asm volatile("griddepcontrol.wait;" ::: "memory");
 
-    if (warp == kSoftmaxThreads / 32) {
-        // ================================ control warp: TMA and MMA issue ====================================
-        {
-            // j: running tile count of the CTA (buffer, parity); jl: KV tile index inside the current pass
-            auto load_k = [&](int j, int jl) {
-                const int b = j & 1;
-                mbar_arrive_expect_tx(&sm.k_full[b], kTileBytes);
-                tma_load_3d(sm.k[b], &k_map, 0, jl * kKvTile, kv_row, &sm.k_full[b]);
-                tma_load_3d(sm.k[b] + kHalfBytes, &k_map, 64, jl * kKvTile, kv_row, &sm.k_full[b]);
-            };
-            auto load_v = [&](int j, int jl) {
-                const int b = j & 1;
-                mbar_arrive_expect_tx(&sm.v_full[b], kTileBytes);
-                tma_load_2d(sm.v[b], &v_map, jl * kKvTile, kv_row * kD, &sm.v_full[b]);
-                tma_load_2d(sm.v[b] + kHalfBytes, &v_map, jl * kKvTile + 64, kv_row * kD, &sm.v_full[b]);
-            };
-            auto issue_pv = [&](int j, int jl) {   // O (+)= P[j&1] V^T[j&1]; any rescale of O for the tile precedes p_ready
-                const int b = j & 1;
-                mbar_wait_bounded(&sm.p_ready[b], (j >> 1) & 1u, &sm.abort_flag);
-                mbar_wait_bounded(&sm.v_full[b], (j >> 1) & 1u, &sm.abort_flag);
-                tc_fence_after();
-#pragma unroll
-                for (int th = 0; th < 2; ++th) {
-#pragma unroll
-                    for (int ks = 0; ks < 4; ++ks) {
-                        umma_f16(tmem + 256, smem_desc(smem_u32(sm.p[b]) + th * kHalfBytes + ks * 32),
-                                 smem_desc(smem_u32(sm.v[b]) + th * kHalfBytes + ks * 32), (jl | th | ks) != 0);
-                    }
-                }
-                umma_commit(&sm.o_done[b]);
-            };
-            if (lane == 0) {
-                tma_prefetch_desc(&q_map);
-                tma_prefetch_desc(&k_map);
-                tma_prefetch_desc(&v_map);
-            }
-          int jt0 = 0;   // tiles issued by earlier passes: buffer indices and barrier parities run on across passes
-          for (int pass = 0; pass < n_pass; ++pass) {
+    // j: running tile count of the CTA (buffer j & 1, barrier parity (j >> 1) & 1); jl: KV tile index inside a pass.
+    // Loads, score MMAs and P V MMAs are issued by three different warps, each a plain loop over the tiles that
+    // waits only for what its own step needs: the next score tile is computed while the softmax warps work on the
+    // current one, P V(j) follows as soon as they are done, and no step queues behind another step's barrier.
+    if (warp == kLoadWarp) {
+        // ================================ load warp: TMA ===================================================
+        if (lane == 0) {
+            tma_prefetch_desc(&q_map);
+            tma_prefetch_desc(&k_map);
+            tma_prefetch_desc(&v_map);
+        }
+        int jt0 = 0;
+        for (int pass = 0; pass < n_pass; ++pass) {
             const int s0 = q_tiles[pass] * kQTile;
             const int n_kv = kv_tiles_of(q_tiles[pass]);
-           if (lane == 0) {   // one thread issues every TMA load and every MMA
-            mbar_arrive_expect_tx(&sm.q_full, kTileBytes);
-            tma_load_3d(sm.q, &q_map, 0, s0, h, &sm.q_full);
-            tma_load_3d(sm.q + kHalfBytes, &q_map, 64, s0, h, &sm.q_full);
-            load_k(jt0, 0);
-            load_v(jt0, 0);
-            mbar_wait_bounded(&sm.q_full, pass & 1u, &sm.abort_flag);
-            for (int jl = 0; jl < n_kv; ++jl) {
-                const int j = jt0 + jl;
-                const int b = j & 1;
-                mbar_wait_bounded(&sm.k_full[b], (j >> 1) & 1u, &sm.abort_flag);
-                if (jl >= 2) mbar_wait_bounded(&sm.p_ready[b], ((j - 2) >> 1) & 1u, &sm.abort_flag);   // S[b] has been read
-                tc_fence_after();
-#pragma unroll
-                for (int kh = 0; kh < 2; ++kh) {
-#pragma unroll
-                    for (int ks = 0; ks < 4; ++ks) {
-                        umma_f16(tmem + 128 * b, smem_desc(smem_u32(sm.q) + kh * kHalfBytes + ks * 32),
-                                 smem_desc(smem_u32(sm.k[b]) + kh * kHalfBytes + ks * 32), (kh | ks) != 0);
-                    }
-                }
-                umma_commit(&sm.s_done[b]);
-                // prefetch one tile ahead of each consumer: K(j+1) for the next S, V^T(j) for the next P V
-                if (jl + 1 < n_kv) {
-                    if (jl >= 1) mbar_wait_bounded(&sm.s_done[(j - 1) & 1], ((j - 1) >> 1) & 1u, &sm.abort_flag);   // K[(j+1)&1] read
-                    load_k(j + 1, jl + 1);
-                }
-                if (jl >= 1) {
-                    if (jl >= 2) mbar_wait_bounded(&sm.o_done[b], ((j - 2) >> 1) & 1u, &sm.abort_flag);   // V^T[b] read by P V(j-2)
-                    load_v(j, jl);
-                    issue_pv(j - 1, jl - 1);
+            if (lane == 0) {
+                mbar_arrive_expect_tx(&sm.q_full, kTileBytes);
+                tma_load_3d(sm.q, &q_map, 0, s0, h, &sm.q_full);
+                tma_load_3d(sm.q + kHalfBytes, &q_map, 64, s0, h, &sm.q_full);
+                for (int jl = 0; jl < n_kv; ++jl) {
+                    const int j = jt0 + jl, b = j & 1;
+                    // K[b] was read by S(j-2), V^T[b] by P V(j-2); at the start of a pass both buffers are free
+                    if (jl >= 2) mbar_wait_bounded(&sm.s_done[b], ((j - 2) >> 1) & 1u, &sm.abort_flag);
+                    mbar_arrive_expect_tx(&sm.k_full[b], kTileBytes);
+                    tma_load_3d(sm.k[b], &k_map, 0, jl * kKvTile, kv_row, &sm.k_full[b]);
+                    tma_load_3d(sm.k[b] + kHalfBytes, &k_map, 64, jl * kKvTile, kv_row, &sm.k_full[b]);
+                    if (jl >= 2) mbar_wait_bounded(&sm.o_done[b], ((j - 2) >> 1) & 1u, &sm.abort_flag);
+                    mbar_arrive_expect_tx(&sm.v_full[b], kTileBytes);
+                    tma_load_2d(sm.v[b], &v_map, jl * kKvTile, kv_row * kD, &sm.v_full[b]);
+                    tma_load_2d(sm.v[b] + kHalfBytes, &v_map, jl * kKvTile + 64, kv_row * kD, &sm.v_full[b]);
                 }
             }
-            issue_pv(jt0 + n_kv - 1, n_kv - 1);
-           }
             jt0 += n_kv;
             __syncwarp();
             if (pass + 1 < n_pass) {
@@ -366,7 +343,65 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
                 // warps must be done with the output staging tile that overlays the K/V^T buffers
                 named_bar_sync(2, kThreads);
             }
-          }
+        }
+    } else if (warp == kScoreWarp) {
+        // ================================ score warp: one thread issues S(j) = Q K(j)^T ======================
+        int jt0 = 0;
+        for (int pass = 0; pass < n_pass; ++pass) {
+            const int n_kv = kv_tiles_of(q_tiles[pass]);
+            if (lane == 0) {
+                mbar_wait_bounded(&sm.q_full, pass & 1u, &sm.abort_flag);
+                for (int jl = 0; jl < n_kv; ++jl) {
+                    const int j = jt0 + jl, b = j & 1;
+                    mbar_wait_bounded(&sm.k_full[b], (j >> 1) & 1u, &sm.abort_flag);
+                    // S[b] was last read by the softmax of tile j-2
+                    if (jl >= 2) mbar_wait_bounded(&sm.p_ready[b], ((j - 2) >> 1) & 1u, &sm.abort_flag);
+                    tc_fence_after();
+#pragma unroll
+                    for (int kh = 0; kh < 2; ++kh) {
+#pragma unroll
+                        for (int ks = 0; ks < 4; ++ks) {
+                            umma_f16(tmem + 128 * b, smem_desc(smem_u32(sm.q) + kh * kHalfBytes + ks * 32),
+                                     smem_desc(smem_u32(sm.k[b]) + kh * kHalfBytes + ks * 32), (kh | ks) != 0);
+                        }
+                    }
+                    umma_commit(&sm.s_done[b]);
+                }
+            }
+            jt0 += n_kv;
+            __syncwarp();
+            if (pass + 1 < n_pass) {
+                named_bar_sync(2, kThreads);
+            }
+        }
+    } else if (warp == kPvWarp) {
+        // ================================ PV warp: one thread issues O (+)= P(j) V(j) =========================
+        int jt0 = 0;
+        for (int pass = 0; pass < n_pass; ++pass) {
+            const int n_kv = kv_tiles_of(q_tiles[pass]);
+            if (lane == 0) {
+                for (int jl = 0; jl < n_kv; ++jl) {
+                    const int j = jt0 + jl, b = j & 1;
+                    // any rescale of O for the tile precedes p_ready
+                    mbar_wait_bounded(&sm.v_full[b], (j >> 1) & 1u, &sm.abort_flag);
+                    mbar_wait_bounded(&sm.p_ready[b], (j >> 1) & 1u, &sm.abort_flag);
+                    tc_fence_after();
+#pragma unroll
+                    for (int th = 0; th < 2; ++th) {
+#pragma unroll
+                        for (int ks = 0; ks < 4; ++ks) {
+                            umma_f16(tmem + 256, smem_desc(smem_u32(sm.p[b]) + th * kHalfBytes + ks * 32),
+                                     smem_desc(smem_u32(sm.v[b]) + th * kHalfBytes + ks * 32), (jl | th | ks) != 0);
+                        }
+                    }
+                    umma_commit(&sm.o_done[b]);
+                }
+            }
+            jt0 += n_kv;
+            __syncwarp();
+            if (pass + 1 < n_pass) {
+                named_bar_sync(2, kThreads);
+            }
         }
     } else {
         // ================================ softmax warps: one q row per thread =================================
@@ -454,8 +489,8 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
             }
             const float m_base = m_new == -INFINITY ? 0.f : m_new;   // a row that has seen nothing yet: every p is 0
             float sum4[4] = {0.f, 0.f, 0.f, 0.f};
-            // P[b] was last read by P V(j-2); its completion is implied by s_done(j): commits complete in issue order
-            // and S(j) was issued after P V(j-2)
+            // P[b] was last read by P V(j-2), issued by another thread than S(j): wait for it explicitly
+            if (jl >= 2) mbar_wait_bounded(&sm.o_done[b], ((j - 2) >> 1) & 1u, &sm.abort_flag);
 #pragma unroll
             for (int ch = 0; ch < 4; ++ch) {
                 uint32_t packed[16];
@@ -549,23 +584,37 @@ cudaError_t launch_prefill(const LaunchCtx &cx, const SeqDev &sq, const CUtensor
         if (e != cudaSuccess) return e;
         configured = true;
     }
-    float2 *table = reinterpret_cast<float2 *>(reinterpret_cast<uint8_t *>(q_half) + prefill_q_bytes(cx.shape.H, S));
+    // Angles: positions derived from the token index lie inside the arena's table (one row per cache position);
+    // explicit position ids may not, so a call that brings them gets a table of its own first.
+    const float2 *table = cx.rope_tab;
+    int table_by_position = 1;
     int launched = 2;
-    if (rope_n_pairs_host(cx.shape.rope_type) > 0) {
+    if (rope_n_pairs_host(cx.shape.rope_type) > 0 && (sq.position_ids || !cx.rope_tab || S > cx.rope_tab_len)) {
+        float2 *own = reinterpret_cast<float2 *>(reinterpret_cast<uint8_t *>(q_half) + prefill_q_bytes(cx.shape.H, S));
         const int n_entries = (cx.shape.rope_type == CGLM_ROPE_CHATGLM ? 2 : 1) * S * 32;
-        rope_table_kernel<<<(n_entries + 255) / 256, 256, 0, cx.stream>>>(cx.shape, sq, table);
+        rope_table_kernel<<<(n_entries + 255) / 256, 256, 0, cx.stream>>>(cx.shape, sq, own);
+        table = own;
+        table_by_position = 0;
         ++launched;
     }
     dim3 prep_grid((S + kPrepTokens - 1) / kPrepTokens, (cx.shape.H + 1) / 2 + 2 * cx.shape.G);
     prefill_prepare_kernel<<<prep_grid, kPrepThreads, 0, cx.stream>>>(cx.shape, sq, cx.k_base, cx.v_base, q_half, s_pad,
-                                                                     table);
+                                                                     table, table_by_position);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return e;
-    dim3 grid((s_pad / kQTile + 1) / 2, cx.shape.H);   // each CTA takes q tiles (n_q - 1 - x) and x
-    prefill_attn_kernel<<<grid, kThreads, smem_bytes, cx.stream>>>(q_map, k_map, v_map, cx.shape, S, sq.slot * cx.shape.G,
-                                                                  sq.out, cx.hdr);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((s_pad / kQTile + 1) / 2, cx.shape.H);   // each CTA takes q tiles (n_q - 1 - x) and x
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = smem_bytes;
+    cfg.stream = cx.stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;   // see griddepcontrol.wait in the kernel
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    e = cudaLaunchKernelEx(&cfg, prefill_attn_kernel, q_map, k_map, v_map, cx.shape, S, sq.slot * cx.shape.G, sq.out, cx.hdr);
     g_launch_count += launched;
-    return cudaGetLastError();
+    return e != cudaSuccess ? e : cudaGetLastError();
 }
 
 }  // namespace cglm

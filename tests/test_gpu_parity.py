@@ -201,8 +201,33 @@ def test_prefill_tensor_core_path(H, G, M, V, rope, mask, S):
     gk, gv = download_cache(arena, 0)
     np.testing.assert_array_equal(gk, k)
     np.testing.assert_array_equal(gv, v)
-    # rope table (unless rope is disabled) + prepare + tcgen05 attention, then one fused decode launch
-    assert launches == [2 if rope == O.ROPE_DISABLED else 3, 1]
+    # prepare + tcgen05 attention (angles come from the arena's table), then one fused decode launch
+    assert launches == [2, 1]
+    arena.close()
+
+
+def test_prefill_explicit_position_ids_take_their_own_angle_table():
+    """Prefill with caller-supplied position ids (which need not lie inside the cache capacity) builds a table for
+    the call (one more launch) and must agree bit for bit with ids derived from the token index."""
+    A = _A()
+    from chatglm_cpp_b200 import _lib
+    S = 200
+    desc = make_desc(8, 2, 128, 256, rope=O.ROPE_CHATGLM2, mask=O.MASK_CAUSAL)
+    rng = np.random.default_rng(77)
+    arena, ws = A.KVArena(desc, 2), A.Workspace(desc, 1, S)
+    qkv = torch.from_numpy(rng.standard_normal((S, qkv_width(desc, False))).astype(np.float32)).cuda()
+    ids = torch.arange(S, dtype=torch.int32, device="cuda")
+    outs, counts = [], []
+    for slot, pid in ((0, None), (1, ids)):
+        before = _lib.lib().cglm_launch_count()
+        outs.append(A.BasicAttention(arena, slot, ws).forward(qkv, 0, position_ids=pid))
+        torch.cuda.synchronize()
+        counts.append(_lib.lib().cglm_launch_count() - before)
+    assert ws.status() == 0
+    assert counts == [2, 3]
+    assert torch.equal(outs[0], outs[1])
+    assert torch.equal(arena.k_cache(0), arena.k_cache(1))
+    assert torch.equal(arena.v_cache(0), arena.v_cache(1))
     arena.close()
 
 
