@@ -94,14 +94,14 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
 }
 
 // ---- launch 1: RoPE, append, f16 q ---------------------------------------------------------------------------
-// Grid: (64-token blocks, roles).  Roles along y: pairs of q heads, then one CTA per k head, then one CTA per v head.
-//   q / k CTAs  rotate their heads for the block's 64 tokens with cos/sin from a table that rope_table_kernel filled
-//               just before (one double-precision sincos per (token, ladder step, position stream) in total);
-//   v CTAs      transpose [64 tokens][128 dims] through shared memory so that the V^T cache rows are written as
+// Grid: (16-token blocks, roles).  Roles along y: pairs of q heads, then one CTA per k head, then one CTA per v head.
+//   q / k CTAs  rotate their heads for the block's tokens with cos/sin from the arena's angle table (or, for
+//               caller-supplied position ids, from a table rope_table_kernel filled just before);
+//   v CTAs      transpose [16 tokens][128 dims] through shared memory so that the V^T cache rows are written as
 //               contiguous runs of tokens instead of one 2-byte store per (token, dim).
 // q_half: f16 [H][s_pad][D]; rows >= S are never read for an output.  Rope modes: the two GLM modes or none.
 static int rope_n_pairs_host(int rope_type) { return rope_type == CGLM_ROPE_DISABLED ? 0 : 1; }
-constexpr int kPrepTokens = 64;
+constexpr int kPrepTokens = 16;   // tokens per CTA: one batch of loads per thread (64 measured 2.4 us slower per call)
 constexpr int kPrepThreads = 256;
 
 // table: f32 [stream][token][32 ladder steps][cos, sin]
@@ -154,7 +154,7 @@ prefill_prepare_kernel(AttnShape sh, SeqDev sq, uint16_t *__restrict__ k_base, u
         __syncthreads();
         uint16_t *vrow0 = v_base + static_cast<long long>(sq.slot * G + g) * kD * M + sq.kv_before + t_begin;
         for (int idx = tid; idx < kD * kPrepTokens; idx += kPrepThreads) {
-            const int d = idx >> 6, t = idx & 63;
+            const int d = idx / kPrepTokens, t = idx % kPrepTokens;
             if (t < n_tok) vrow0[static_cast<long long>(d) * M + t] = __half_as_ushort(tile[d][t]);
         }
         return;
