@@ -231,6 +231,18 @@ def run_split_kv(args, w):
     qkv = torch.randn(1, qkv_row(w), device="cuda", generator=g0)
     partial = torch.zeros(H, D + 2, device="cuda")
     gathered = torch.zeros(world, H, D + 2, device="cuda")
+    # Exchange of the partials: "p2p" = every rank stores its partial into every peer's exchange buffer over NVLink
+    # (buffers mapped with CUDA IPC) and the combine waits for the arrival words; "nccl" = all-gather + combine.
+    xchg = None
+    if world > 1 and args.exchange == "p2p":
+        from torch.multiprocessing.reductions import reduce_tensor
+        mine = A.SplitKVExchange.new_buffer(world, H, D)
+        torch.cuda.synchronize()
+        handles = [None] * world
+        dist.all_gather_object(handles, reduce_tensor(mine))
+        peers = [mine if r == rank else handles[r][0](*handles[r][1]) for r in range(world)]
+        xchg = A.SplitKVExchange(peers, rank, H, D)
+        dist.barrier()
     out = torch.zeros(H * D, device="cuda")
     flags = _lib.SEQ_PARTIAL | _lib.SEQ_USE_KV_LOCAL | (0 if sl.owns_new else _lib.SEQ_NO_APPEND)
     arrs = []
@@ -238,15 +250,18 @@ def run_split_kv(args, w):
         arr = (_lib.AttnSeq * 1)()
         A.fill_seq(arr[0], desc, A.SeqCall(qkv=qkv, slot=s, n_past=P, partial=partial, kv_local=sl.n_local, flags=flags), False)
         arrs.append(arr)
-    stream = torch.cuda.current_stream().cuda_stream
     it = [0]
 
     def step():
+        stream = torch.cuda.current_stream().cuda_stream
         rc = L.cglm_attn_forward(arena._h, arrs[it[0] % n_rot], 1, ws.ptr, ws.bytes, stream)
         if rc != 0:
             raise _lib.CglmError(rc, "cglm_attn_forward")
         it[0] += 1
-        if world > 1:
+        if xchg is not None:
+            xchg.push(partial)
+            xchg.combine_arrived(out, ws)
+        elif world > 1:
             dist.all_gather_into_tensor(gathered, partial)
             A.splitkv_combine(gathered, out)
         else:
@@ -260,16 +275,44 @@ def run_split_kv(args, w):
     for _ in range(max(args.warmup, 3)):
         step()
     barrier()
+    # A step is three launches (decode over the slice, all-gather, combine) of 20-50 us in total: issued one by one
+    # from Python the host is the bottleneck, so one pass over the rotating slices is captured in a CUDA graph and
+    # the timed region replays it.  --no-graph times the eager loop instead.
+    graph = None
+    steps = args.steps
+    launches_per_step = 3 if xchg is not None else 2   # this library's kernels: decode, (push,) combine
+    if not args.no_graph:
+        it[0] = 0
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(2):
+                step()
+        torch.cuda.current_stream().wait_stream(side)
+        barrier()
+        it[0] = 0
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for _ in range(n_rot):
+                step()
+        replays = max(1, (args.steps + n_rot - 1) // n_rot)
+        steps = replays * n_rot
+        for _ in range(2):
+            graph.replay()
+        barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     sampler = ClockSampler(local); sampler.start()
-    launches0 = L.cglm_launch_count()
     e0.record()
-    for _ in range(args.steps):
-        step()
+    if graph is not None:
+        for _ in range(replays):
+            graph.replay()
+    else:
+        for _ in range(steps):
+            step()
     e1.record()
     barrier()
     clocks = sampler.finish()
-    launches = L.cglm_launch_count() - launches0
+    launches = steps * launches_per_step
     ms = e0.elapsed_time(e1)
     if world > 1:
         t = torch.tensor([ms], device="cuda", dtype=torch.float64)
@@ -284,16 +327,18 @@ def run_split_kv(args, w):
     except Exception:
         pass
     if rank == 0:
-        step_ms = ms / args.steps
+        step_ms = ms / steps
         achieved = local_bytes / (step_ms * 1e-3) / 1e9
         line = {
-            "metric": "decode_attention_tokens_per_s", "value": args.steps / (ms * 1e-3), "unit": "tokens/s",
-            "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": step_ms,
+            "metric": "decode_attention_tokens_per_s", "value": steps / (ms * 1e-3), "unit": "tokens/s",
+            "n_gpus": world, "steps": steps, "warmup": max(args.warmup, 3), "ms_per_step": step_ms,
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
             "config": {"workload": args.workload, "n_head": H, "n_kv_head": G, "head_dim": D, "n_past": P,
                        "kv_bytes_total": 4 * G * D * (P + 1), "kv_bytes_this_rank": local_bytes,
-                       "parallelism": f"KV length split x{world}, all-gather of {H * (D + 2) * 4} B per rank + LSE combine",
-                       "l2_policy": f"rotates through {n_rot} copies of the slice (working set >= 4 x L2)"},
+                       "parallelism": (f"KV length split x{world}, " + ("peer stores" if xchg is not None else "NCCL all-gather") +
+                                       f" of {H * (D + 2) * 4} B per rank + LSE combine"),
+                       "l2_policy": f"rotates through {n_rot} copies of the slice (working set >= 4 x L2)",
+                       "issue": "eager" if graph is None else f"CUDA graph of {n_rot} steps, replayed"},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "peak_source": peak_src, "kernel": "decode_kernel (+ all-gather + combine in the step time)",
                          "algorithmic_bytes_per_launch": local_bytes, "launch_us": step_ms * 1e3, "traffic": None},
@@ -301,8 +346,16 @@ def run_split_kv(args, w):
         }
         print(json.dumps(line), flush=True)
     if world > 1:
+        # a captured graph holds the communicator's resources: release it before the group goes away, and do not let
+        # a slow teardown outlive the measurement
+        graph = None
+        torch.cuda.synchronize()
+        killer = threading.Timer(30.0, lambda: os._exit(0))
+        killer.daemon = True
+        killer.start()
         dist.barrier()
         dist.destroy_process_group()
+        killer.cancel()
 
 
 def run_prefill(args, w):
@@ -534,6 +587,8 @@ def main():
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--workload", choices=sorted(WORKLOADS), default="glm4_9b_batched_decode")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-graph", action="store_true", help="split-KV workload: issue every step eagerly")
+    ap.add_argument("--exchange", choices=["p2p", "nccl"], default="p2p", help="split-KV workload: how partials travel")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     w = WORKLOADS[args.workload]

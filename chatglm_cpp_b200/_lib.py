@@ -49,6 +49,10 @@ SYMBOLS = {
     "cglm_attn_host_drain": (C.c_int, [C.c_void_p, C.c_void_p]),
     "cglm_attn_decode_static": (C.c_int, [C.c_void_p, C.POINTER(AttnSeq), C.c_int, C.c_int, C.c_void_p]),
     "cglm_attn_splitkv_combine": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p]),
+    "cglm_attn_splitkv_xchg_bytes": (C.c_size_t, [C.c_int, C.c_int, C.c_int]),
+    "cglm_attn_splitkv_push": (C.c_int, [C.c_void_p, C.POINTER(C.c_void_p), C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p]),
+    "cglm_attn_splitkv_combine_arrived": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_uint,
+                                                    C.c_void_p]),
     "cglm_kv_load_prefix": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_void_p]),
     "cglm_status_string": (C.c_char_p, [C.c_int]),
     "cglm_last_error_string": (C.c_char_p, []),

@@ -185,6 +185,39 @@ class BasicAttention:
         return (out, qr, kr) if want_roped else out
 
 
+class SplitKVExchange:
+    """One rank's side of the peer-memory exchange of split-KV partials (cglm_attn_splitkv_push /
+    cglm_attn_splitkv_combine_arrived).  ``buffers`` holds every rank's exchange buffer as a tensor valid on this
+    device (entry ``rank`` is the local one); how the peers' buffers were mapped (CUDA IPC between processes, plain
+    tensors inside one process) is the caller's business."""
+
+    def __init__(self, buffers: Sequence[torch.Tensor], rank: int, n_head: int, head_dim: int):
+        self.n_rank, self.rank, self.n_head, self.head_dim = len(buffers), rank, n_head, head_dim
+        need = self.bytes(self.n_rank, n_head, head_dim)
+        for b in buffers:
+            assert b.is_cuda and b.is_contiguous() and b.numel() * b.element_size() >= need
+        self.buffers = list(buffers)
+        self._ptrs = (C.c_void_p * self.n_rank)(*[b.data_ptr() for b in buffers])
+
+    @staticmethod
+    def bytes(n_rank: int, n_head: int, head_dim: int) -> int:
+        return int(_lib.lib().cglm_attn_splitkv_xchg_bytes(n_rank, n_head, head_dim))
+
+    @staticmethod
+    def new_buffer(n_rank: int, n_head: int, head_dim: int) -> torch.Tensor:
+        return torch.zeros((SplitKVExchange.bytes(n_rank, n_head, head_dim) + 3) // 4, dtype=torch.int32, device="cuda")
+
+    def push(self, partial: torch.Tensor) -> None:
+        assert partial.is_cuda and partial.dtype == torch.float32 and partial.is_contiguous()
+        check(_lib.lib().cglm_attn_splitkv_push(partial.data_ptr(), self._ptrs, self.n_rank, self.rank, self.n_head,
+                                                self.head_dim, _stream_ptr()), "cglm_attn_splitkv_push")
+
+    def combine_arrived(self, out: torch.Tensor, ws: "Workspace", timeout_us: int = 0) -> None:
+        check(_lib.lib().cglm_attn_splitkv_combine_arrived(self.buffers[self.rank].data_ptr(), self.n_rank, self.n_head,
+                                                           self.head_dim, out.data_ptr(), ws.ptr, timeout_us, _stream_ptr()),
+              "cglm_attn_splitkv_combine_arrived")
+
+
 def splitkv_combine(partials: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """partials: f32 [n_part, H, D+2] (acc | m | l) on this device -> f32 [H*D]."""
     assert partials.is_cuda and partials.dtype == torch.float32 and partials.is_contiguous()

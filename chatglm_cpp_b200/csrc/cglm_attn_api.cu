@@ -264,6 +264,81 @@ __global__ void combine_kernel(const float *__restrict__ partials, int n_part, i
     }
 }
 
+// ---- split-KV exchange over peer memory ----------------------------------------------------------------------
+// Exchange buffer: [0] step counter, [1..15] unused, then 2 sets of n_rank arrival words (padded to 16 words per
+// set), then 2 sets of n_rank partial slots of n_head * (head_dim + 2) floats.
+constexpr int kXchgMaxRanks = 16;
+struct XchgPeers {
+    void *buf[kXchgMaxRanks];
+};
+__host__ __device__ inline size_t xchg_flag_word(int set, int rank) { return 16 + static_cast<size_t>(set) * kXchgMaxRanks + rank; }
+__host__ __device__ inline size_t xchg_slot_word(int set, int rank, int n_rank, int slot_words) {
+    return 16 + 2 * kXchgMaxRanks + (static_cast<size_t>(set) * n_rank + rank) * slot_words;
+}
+
+// one CTA per destination rank: plain (peer) stores of the partial, then the arrival word with release semantics
+__global__ void xchg_push_kernel(const float *__restrict__ partial, XchgPeers peers, int n_rank, int rank, int slot_words) {
+    const unsigned int e = *reinterpret_cast<volatile unsigned int *>(peers.buf[rank]) + 1u;   // local counter
+    unsigned int *dst = static_cast<unsigned int *>(peers.buf[blockIdx.x]);
+    float2 *slot = reinterpret_cast<float2 *>(dst + xchg_slot_word(e & 1u, rank, n_rank, slot_words));
+    const float2 *src = reinterpret_cast<const float2 *>(partial);
+    for (int i = threadIdx.x; i < slot_words / 2; i += blockDim.x) slot[i] = src[i];
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(dst + xchg_flag_word(e & 1u, rank)), "r"(e) : "memory");
+    }
+}
+
+// one CTA: bounded wait for the n_rank arrival words, log-sum-exp merge of the slots, counter advance
+__global__ void __launch_bounds__(1024)
+xchg_combine_kernel(unsigned int *__restrict__ local, int n_rank, int H, int D, float *__restrict__ out, WsHeader *hdr,
+                    unsigned int timeout_us) {
+    __shared__ int ok;
+    const unsigned int e = local[0] + 1u;
+    const int slot_words = H * (D + 2);
+    if (threadIdx.x == 0) ok = 1;
+    __syncthreads();
+    if (threadIdx.x < n_rank) {
+        const unsigned int *flag = local + xchg_flag_word(e & 1u, threadIdx.x);
+        long long t0, t;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+        const long long limit = static_cast<long long>(timeout_us ? timeout_us : 1000000u) * 1000;
+        bool seen = false;
+        for (unsigned int spin = 0; spin < (1u << 28); ++spin) {   // the timer bounds the wait; the count bounds the loop
+            unsigned int v;
+            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+            if (v == e) { seen = true; break; }
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+            if (t - t0 > limit) break;
+            __nanosleep(200);
+        }
+        if (!seen) ok = 0;
+    }
+    __syncthreads();
+    if (ok) {
+        const float *slots = reinterpret_cast<const float *>(local + xchg_slot_word(e & 1u, 0, n_rank, slot_words));
+        for (int i = threadIdx.x; i < H * D; i += blockDim.x) {
+            const int h = i / D, d = i - h * D;
+            float m_star = -INFINITY;
+            for (int p = 0; p < n_rank; ++p) m_star = fmaxf(m_star, __ldcg(slots + static_cast<size_t>(p) * slot_words + h * (D + 2) + D));
+            float acc = 0.f, den = 0.f;
+            for (int p = 0; p < n_rank; ++p) {
+                const float *pp = slots + static_cast<size_t>(p) * slot_words + h * (D + 2);
+                const float m = __ldcg(pp + D);
+                const float w = m == -INFINITY ? 0.f : __expf(m - m_star);
+                acc += w * __ldcg(pp + d);
+                den += w * __ldcg(pp + D + 1);
+            }
+            out[i] = acc / den;
+        }
+    } else if (threadIdx.x == 0) {
+        atomicExch(&hdr->status, static_cast<int>(CGLM_ERR_TIMEOUT));
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) local[0] = e;
+}
+
 __global__ void load_prefix_kernel(const uint16_t *__restrict__ past_kv, uint16_t *__restrict__ k_slot,
                                    uint16_t *__restrict__ v_slot, int G, int V, int D, int M) {
     const long long n = static_cast<long long>(G) * V * D;
@@ -695,6 +770,40 @@ int cglm_attn_splitkv_combine(const float *partials, int n_part, int n_head, int
                               void *cuda_stream) {
     if (!partials || !out || n_part <= 0 || n_head <= 0 || head_dim <= 0) return CGLM_ERR_INVALID_ARG;
     combine_kernel<<<n_head, 128, 0, static_cast<cudaStream_t>(cuda_stream)>>>(partials, n_part, n_head, head_dim, out);
+    g_launch_count += 1;
+    CGLM_CUDA(cudaGetLastError());
+    return CGLM_OK;
+}
+
+size_t cglm_attn_splitkv_xchg_bytes(int n_rank, int n_head, int head_dim) {
+    if (n_rank <= 0 || n_rank > kXchgMaxRanks || n_head <= 0 || head_dim <= 0) return 0;
+    return sizeof(unsigned int) * xchg_slot_word(2, 0, n_rank, n_head * (head_dim + 2));
+}
+
+int cglm_attn_splitkv_push(const float *partial, void *const *xchg, int n_rank, int rank, int n_head, int head_dim,
+                           void *cuda_stream) {
+    if (!partial || !xchg || n_rank <= 0 || n_rank > kXchgMaxRanks || rank < 0 || rank >= n_rank || n_head <= 0 ||
+        head_dim <= 0 || (head_dim & 1) || (reinterpret_cast<uintptr_t>(partial) & 7))
+        return CGLM_ERR_INVALID_ARG;
+    XchgPeers peers = {};
+    for (int r = 0; r < n_rank; ++r) {
+        if (!xchg[r] || (reinterpret_cast<uintptr_t>(xchg[r]) & 15)) return CGLM_ERR_INVALID_ARG;
+        peers.buf[r] = xchg[r];
+    }
+    xchg_push_kernel<<<n_rank, 256, 0, static_cast<cudaStream_t>(cuda_stream)>>>(partial, peers, n_rank, rank,
+                                                                              n_head * (head_dim + 2));
+    g_launch_count += 1;
+    CGLM_CUDA(cudaGetLastError());
+    return CGLM_OK;
+}
+
+int cglm_attn_splitkv_combine_arrived(void *xchg_local, int n_rank, int n_head, int head_dim, float *out,
+                                      void *workspace, unsigned int timeout_us, void *cuda_stream) {
+    if (!xchg_local || !out || n_rank <= 0 || n_rank > kXchgMaxRanks || n_head <= 0 || head_dim <= 0)
+        return CGLM_ERR_INVALID_ARG;
+    if (!workspace) return CGLM_ERR_WORKSPACE;
+    xchg_combine_kernel<<<1, 1024, 0, static_cast<cudaStream_t>(cuda_stream)>>>(
+        static_cast<unsigned int *>(xchg_local), n_rank, n_head, head_dim, out, static_cast<WsHeader *>(workspace), timeout_us);
     g_launch_count += 1;
     CGLM_CUDA(cudaGetLastError());
     return CGLM_OK;

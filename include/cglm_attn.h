@@ -180,6 +180,32 @@ int cglm_attn_decode_static(cglm_kv_arena *arena, const cglm_attn_seq *seqs, int
 int cglm_attn_splitkv_combine(const float *partials, int n_part, int n_head, int head_dim, float *out,
                               void *cuda_stream);
 
+/*
+ * Split-KV exchange over peer memory instead of an all-gather.  (The reference runs on one device; this is the
+ * "P2P" variant of the exchange step of a KV length split over the GPUs of one NVLink box.)
+ *
+ * Every rank owns an exchange buffer of cglm_attn_splitkv_xchg_bytes(n_rank, n_head, head_dim) bytes in its own
+ * memory, zero-filled once, and mapped into its peers by the host (CUDA IPC, or plain pointers when the ranks are
+ * contexts of one process).  The buffer holds a step counter, two sets (alternating by step) of n_rank partial
+ * slots [n_head][head_dim+2], and two sets of n_rank arrival words.
+ *
+ * cglm_attn_splitkv_push: step e = the local buffer's counter + 1.  Copies this rank's partial into slot `rank` of
+ *   set e & 1 of EVERY rank's buffer (xchg[0..n_rank), device pointers valid on this GPU, entry `rank` its own) with
+ *   plain stores, then publishes e in arrival word `rank` of each (release at system scope).
+ * cglm_attn_splitkv_combine_arrived: waits until all n_rank arrival words of set e & 1 of the LOCAL buffer hold e,
+ *   merges the n_rank partials like cglm_attn_splitkv_combine into out, and advances the local counter to e.  The
+ *   wait is bounded: after timeout_us (0: one second) the kernel records CGLM_ERR_TIMEOUT in the workspace status
+ *   word (cglm_attn_workspace_status reads it), leaves out untouched and still advances the counter.
+ * Each rank calls push then combine_arrived once per step, on one stream.  Because the step counter lives on the
+ * device, a captured CUDA graph of the step can be replayed.  Two sets suffice: a rank cannot push step e+2 before
+ * its own combine of step e+1, which needs every peer's push of e+1, which follows that peer's combine of e.
+ */
+size_t cglm_attn_splitkv_xchg_bytes(int n_rank, int n_head, int head_dim);
+int cglm_attn_splitkv_push(const float *partial, void *const *xchg, int n_rank, int rank, int n_head, int head_dim,
+                           void *cuda_stream);
+int cglm_attn_splitkv_combine_arrived(void *xchg_local, int n_rank, int n_head, int head_dim, float *out,
+                                      void *workspace, unsigned int timeout_us, void *cuda_stream);
+
 /* P-Tuning v2 prefix load for one slot (BasicModel::load_prefix_cache, chatglm.h:580-615):
  * past_kv f16 [2][n_kv_head][n_virtual][head_dim] (device) -> cache positions [0, n_virtual), V transposed. */
 int cglm_kv_load_prefix(cglm_kv_arena *arena, int slot, const void *past_kv, void *cuda_stream);

@@ -249,6 +249,47 @@ def test_explicit_position_ids_match_derived():
     assert torch.equal(arena.k_cache(0), arena.k_cache(1))
 
 
+def test_splitkv_peer_exchange_matches_combine_and_reports_a_missing_rank():
+    """The peer-memory exchange (push into every rank's buffer, combine once all arrival words hold the step) on one
+    device: four rank buffers, pushes issued before the combines on one stream, so no kernel ever waits for a later
+    one.  Two steps (both slot sets).  Then a step in which one rank never pushes: the bounded wait must run out,
+    set the status word and leave the context usable."""
+    A = _A()
+    n_rank, H, D = 4, 32, 128
+    desc = make_desc(H, 2, D, 256)
+    ws = A.Workspace(desc, 1, 1)
+    rng = np.random.default_rng(5)
+    bufs = [A.SplitKVExchange.new_buffer(n_rank, H, D) for _ in range(n_rank)]
+    ranks = [A.SplitKVExchange(bufs, r, H, D) for r in range(n_rank)]
+    for step in range(2):
+        parts = rng.standard_normal((n_rank, H, D + 2)).astype(np.float32)
+        parts[:, :, D + 1] = np.abs(parts[:, :, D + 1]) + 0.5            # l > 0
+        if step == 1:
+            parts[2, :, D] = -np.inf; parts[2, :, D + 1] = 0.0; parts[2, :, :D] = 0.0   # a rank that attended nothing
+        dev = torch.from_numpy(parts).cuda()
+        want = A.splitkv_combine(dev)
+        outs = [torch.zeros(H * D, device="cuda") for _ in range(n_rank)]
+        for r in range(n_rank):
+            ranks[r].push(dev[r])
+        for r in range(n_rank):
+            ranks[r].combine_arrived(outs[r], ws)
+        torch.cuda.synchronize()
+        assert ws.status() == 0
+        for r in range(n_rank):
+            assert torch.allclose(outs[r], want, rtol=1e-5, atol=1e-6), f"step {step} rank {r}"
+    # rank 3 stays silent: rank 0's combine gives up after 2 ms
+    out = torch.full((H * D,), 7.0, device="cuda")
+    for r in range(3):
+        ranks[r].push(dev[r])
+    ranks[0].combine_arrived(out, ws, timeout_us=2000)
+    torch.cuda.synchronize()
+    from chatglm_cpp_b200 import _lib
+    assert ws.status() == _lib.ERR_TIMEOUT
+    assert ws.status() == 0                      # reading the status clears it
+    assert torch.all(out == 7.0)                 # out untouched
+    assert float(torch.ones(4, device="cuda").sum()) == 4.0   # the context still works
+
+
 def test_splitkv_partials_combine_to_full_attention():
     """A long sequence cut into 4 contiguous KV slices held in 4 slots: partials + LSE combine == one-pass result."""
     A = _A()
