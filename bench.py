@@ -235,12 +235,11 @@ def run_split_kv(args, w):
     # (buffers mapped with CUDA IPC) and the combine waits for the arrival words; "nccl" = all-gather + combine.
     xchg = None
     if world > 1 and args.exchange == "p2p":
-        from torch.multiprocessing.reductions import reduce_tensor
-        mine = A.SplitKVExchange.new_buffer(world, H, D)
-        torch.cuda.synchronize()
+        mine, handle = A.SplitKVExchange.alloc_exported(world, H, D)
         handles = [None] * world
-        dist.all_gather_object(handles, reduce_tensor(mine))
-        peers = [mine if r == rank else handles[r][0](*handles[r][1]) for r in range(world)]
+        dist.all_gather_object(handles, (local, handle))
+        # imported with this rank's device current (the mapping must belong to the context whose kernels use it)
+        peers = [mine if r == rank else A.SplitKVExchange.import_handle(handles[r][1], handles[r][0]) for r in range(world)]
         xchg = A.SplitKVExchange(peers, rank, H, D)
         dist.barrier()
     out = torch.zeros(H * D, device="cuda")

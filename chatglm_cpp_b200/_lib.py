@@ -50,6 +50,10 @@ SYMBOLS = {
     "cglm_attn_decode_static": (C.c_int, [C.c_void_p, C.POINTER(AttnSeq), C.c_int, C.c_int, C.c_void_p]),
     "cglm_attn_splitkv_combine": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p]),
     "cglm_attn_splitkv_xchg_bytes": (C.c_size_t, [C.c_int, C.c_int, C.c_int]),
+    "cglm_xchg_alloc": (C.c_int, [C.c_size_t, C.POINTER(C.c_void_p)]),
+    "cglm_xchg_free": (C.c_int, [C.c_void_p]),
+    "cglm_xchg_export": (C.c_int, [C.c_void_p, C.c_char_p]),
+    "cglm_xchg_import": (C.c_int, [C.c_char_p, C.c_int, C.POINTER(C.c_void_p)]),
     "cglm_attn_splitkv_push": (C.c_int, [C.c_void_p, C.POINTER(C.c_void_p), C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p]),
     "cglm_attn_splitkv_combine_arrived": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_uint,
                                                     C.c_void_p]),

@@ -191,13 +191,36 @@ class SplitKVExchange:
     device (entry ``rank`` is the local one); how the peers' buffers were mapped (CUDA IPC between processes, plain
     tensors inside one process) is the caller's business."""
 
-    def __init__(self, buffers: Sequence[torch.Tensor], rank: int, n_head: int, head_dim: int):
+    def __init__(self, buffers: Sequence, rank: int, n_head: int, head_dim: int):
+        """buffers: per rank a tensor on this device, or a raw device pointer (int) valid on this device."""
         self.n_rank, self.rank, self.n_head, self.head_dim = len(buffers), rank, n_head, head_dim
         need = self.bytes(self.n_rank, n_head, head_dim)
+        ptrs = []
         for b in buffers:
-            assert b.is_cuda and b.is_contiguous() and b.numel() * b.element_size() >= need
-        self.buffers = list(buffers)
-        self._ptrs = (C.c_void_p * self.n_rank)(*[b.data_ptr() for b in buffers])
+            if isinstance(b, torch.Tensor):
+                assert b.is_cuda and b.is_contiguous() and b.numel() * b.element_size() >= need
+                ptrs.append(b.data_ptr())
+            else:
+                ptrs.append(int(b))
+        self.buffers = list(buffers)   # keeps tensors alive
+        self._local = ptrs[rank]
+        self._ptrs = (C.c_void_p * self.n_rank)(*ptrs)
+
+    @staticmethod
+    def alloc_exported(n_rank: int, n_head: int, head_dim: int):
+        """Allocates this rank's zero-filled buffer outside torch's allocator and returns (pointer, 64-byte IPC handle)."""
+        ptr = C.c_void_p()
+        check(_lib.lib().cglm_xchg_alloc(SplitKVExchange.bytes(n_rank, n_head, head_dim), C.byref(ptr)), "cglm_xchg_alloc")
+        handle = C.create_string_buffer(64)
+        check(_lib.lib().cglm_xchg_export(ptr, handle), "cglm_xchg_export")
+        return ptr.value, handle.raw
+
+    @staticmethod
+    def import_handle(handle: bytes, owner_device: int) -> int:
+        """Maps a peer's buffer into the current device's context; returns the device pointer."""
+        ptr = C.c_void_p()
+        check(_lib.lib().cglm_xchg_import(handle, owner_device, C.byref(ptr)), "cglm_xchg_import")
+        return ptr.value
 
     @staticmethod
     def bytes(n_rank: int, n_head: int, head_dim: int) -> int:
@@ -213,7 +236,7 @@ class SplitKVExchange:
                                                 self.head_dim, _stream_ptr()), "cglm_attn_splitkv_push")
 
     def combine_arrived(self, out: torch.Tensor, ws: "Workspace", timeout_us: int = 0) -> None:
-        check(_lib.lib().cglm_attn_splitkv_combine_arrived(self.buffers[self.rank].data_ptr(), self.n_rank, self.n_head,
+        check(_lib.lib().cglm_attn_splitkv_combine_arrived(self._local, self.n_rank, self.n_head,
                                                            self.head_dim, out.data_ptr(), ws.ptr, timeout_us, _stream_ptr()),
               "cglm_attn_splitkv_combine_arrived")
 

@@ -780,6 +780,53 @@ size_t cglm_attn_splitkv_xchg_bytes(int n_rank, int n_head, int head_dim) {
     return sizeof(unsigned int) * xchg_slot_word(2, 0, n_rank, n_head * (head_dim + 2));
 }
 
+int cglm_xchg_alloc(size_t bytes, void **ptr) {
+    if (!ptr || bytes == 0) return CGLM_ERR_INVALID_ARG;
+    CGLM_CUDA(cudaMalloc(ptr, bytes));
+    CGLM_CUDA(cudaMemset(*ptr, 0, bytes));
+    CGLM_CUDA(cudaDeviceSynchronize());
+    return CGLM_OK;
+}
+
+int cglm_xchg_free(void *ptr) {
+    if (!ptr) return CGLM_ERR_INVALID_ARG;
+    CGLM_CUDA(cudaFree(ptr));
+    return CGLM_OK;
+}
+
+int cglm_xchg_export(void *ptr, unsigned char handle[64]) {
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "handle size is part of the ABI");
+    if (!ptr || !handle) return CGLM_ERR_INVALID_ARG;
+    cudaIpcMemHandle_t h;
+    CGLM_CUDA(cudaIpcGetMemHandle(&h, ptr));
+    std::memcpy(handle, &h, sizeof(h));
+    return CGLM_OK;
+}
+
+int cglm_xchg_import(const unsigned char handle[64], int owner_device, void **ptr) {
+    if (!handle || !ptr) return CGLM_ERR_INVALID_ARG;
+    int dev = -1, can = 0;
+    CGLM_CUDA(cudaGetDevice(&dev));
+    if (owner_device != dev) {
+        CGLM_CUDA(cudaDeviceCanAccessPeer(&can, dev, owner_device));
+        if (!can) return CGLM_ERR_UNSUPPORTED;
+    }
+    cudaIpcMemHandle_t h;
+    std::memcpy(&h, handle, sizeof(h));
+    // opened with the importing device current: the mapping belongs to this device's context
+    CGLM_CUDA(cudaIpcOpenMemHandle(ptr, h, cudaIpcMemLazyEnablePeerAccess));
+    // the mapping must work for plain accesses from this device before a kernel is pointed at it: the runtime
+    // reports a broken mapping as an error code here, a kernel would fault
+    unsigned int probe = 0xffffffffu;
+    CGLM_CUDA(cudaMemcpy(&probe, *ptr, sizeof(probe), cudaMemcpyDeviceToHost));
+    void *scratch = nullptr;
+    CGLM_CUDA(cudaMalloc(&scratch, 256));
+    cudaError_t e = cudaMemcpy(scratch, *ptr, 256, cudaMemcpyDeviceToDevice);
+    cudaFree(scratch);
+    CGLM_CUDA(e);
+    return CGLM_OK;
+}
+
 int cglm_attn_splitkv_push(const float *partial, void *const *xchg, int n_rank, int rank, int n_head, int head_dim,
                            void *cuda_stream) {
     if (!partial || !xchg || n_rank <= 0 || n_rank > kXchgMaxRanks || rank < 0 || rank >= n_rank || n_head <= 0 ||

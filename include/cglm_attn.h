@@ -201,6 +201,16 @@ int cglm_attn_splitkv_combine(const float *partials, int n_part, int n_head, int
  * its own combine of step e+1, which needs every peer's push of e+1, which follows that peer's combine of e.
  */
 size_t cglm_attn_splitkv_xchg_bytes(int n_rank, int n_head, int head_dim);
+/* Host plumbing for ranks that are separate processes (one per GPU): the owner allocates its zero-filled buffer
+ * and exports a 64-byte CUDA IPC handle, which travels to the peers by any host channel; a peer imports it WITH ITS
+ * OWN DEVICE CURRENT, which maps the owner's memory into the importing device's context (peer access is enabled
+ * as part of the import; CGLM_ERR_UNSUPPORTED when the two devices have no peer path) and checks the mapping with
+ * a 4-byte copy through the runtime before any kernel touches it.  Imported mappings live until the process
+ * exits. */
+int cglm_xchg_alloc(size_t bytes, void **ptr);
+int cglm_xchg_free(void *ptr);
+int cglm_xchg_export(void *ptr, unsigned char handle[64]);
+int cglm_xchg_import(const unsigned char handle[64], int owner_device, void **ptr);
 int cglm_attn_splitkv_push(const float *partial, void *const *xchg, int n_rank, int rank, int n_head, int head_dim,
                            void *cuda_stream);
 int cglm_attn_splitkv_combine_arrived(void *xchg_local, int n_rank, int n_head, int head_dim, float *out,
