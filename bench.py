@@ -55,9 +55,9 @@ WORKLOADS = {
                                theta=10000.0, interleaved=True, mask=1, seed=1005),
 }
 HBM_FALLBACK_GBS = 6650.0   # earlier measurement on this pool, used only without MEASURED_PEAKS.json
-# dram__bytes_read.sum + dram__bytes_write.sum of one decode launch of the default workload (ncu capture of a
-# 1/8-size case scaled by KV bytes; see profiles/).  None until measured.
-NCU_TRAFFIC_PER_KV_BYTE = None
+# (dram__bytes_read.sum + dram__bytes_write.sum) / algorithmic KV bytes of one decode launch, from the ncu capture of
+# the _small workload, whose launches are identical to the default workload's (see profiles/): 316.5 MB / 303.5 MB.
+NCU_TRAFFIC_PER_KV_BYTE = 1.043
 
 
 def kv_bytes(w, n_past):
