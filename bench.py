@@ -274,6 +274,9 @@ def run_split_kv(args, w):
     for _ in range(max(args.warmup, 3)):
         step()
     barrier()
+    st = ws.status()
+    if st != 0:   # e.g. a peer's partial never arrived: every further step would run into the same bounded wait
+        raise SystemExit(f"[rank {rank}] device-side status {st} after the warm-up steps")
     # A step is three launches (decode over the slice, all-gather, combine) of 20-50 us in total: issued one by one
     # from Python the host is the bottleneck, so one pass over the rotating slices is captured in a CUDA graph and
     # the timed region replays it.  --no-graph times the eager loop instead.
