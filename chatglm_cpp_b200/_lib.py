@@ -13,7 +13,7 @@ LIB_PATH = os.path.join(_PKG, "lib", "libcglm_attn.so")
 OK, ERR_INVALID_ARG, ERR_CUDA, ERR_WORKSPACE, ERR_UNSUPPORTED, ERR_TIMEOUT, ERR_NO_DEVICE = 0, -1, -2, -3, -4, -5, -6
 ROPE_GPTJ, ROPE_NEOX, ROPE_CHATGLM, ROPE_CHATGLM2, ROPE_DISABLED = 0, 2, 4, 8, 10000
 MASK_CAUSAL, MASK_CHATGLM = 0, 1
-SEQ_NO_APPEND, SEQ_PARTIAL, SEQ_USE_KV_LOCAL = 1, 2, 4
+SEQ_NO_APPEND, SEQ_PARTIAL, SEQ_USE_KV_LOCAL, SEQ_N_PAST_DEVICE = 1, 2, 4, 8
 
 
 class AttnDesc(C.Structure):
@@ -27,7 +27,8 @@ class AttnSeq(C.Structure):
                 ("kv_tok_stride", C.c_longlong), ("kv_head_stride", C.c_longlong),
                 ("slot", C.c_int), ("qlen", C.c_int), ("n_past", C.c_int), ("n_ctx", C.c_int),
                 ("position_ids", C.c_void_p), ("out", C.c_void_p), ("q_roped", C.c_void_p),
-                ("k_roped", C.c_void_p), ("kv_local", C.c_int), ("flags", C.c_int), ("partial", C.c_void_p)]
+                ("k_roped", C.c_void_p), ("kv_local", C.c_int), ("flags", C.c_int), ("partial", C.c_void_p),
+                ("n_past_dev", C.c_void_p)]
 
 
 # every symbol include/cglm_attn.h declares: name -> (restype, argtypes)
@@ -44,6 +45,7 @@ SYMBOLS = {
     "cglm_attn_workspace_init": (C.c_int, [C.c_void_p, C.c_size_t, C.c_void_p]),
     "cglm_attn_workspace_status": (C.c_int, [C.c_void_p, C.c_void_p]),
     "cglm_attn_forward": (C.c_int, [C.c_void_p, C.POINTER(AttnSeq), C.c_int, C.c_void_p, C.c_size_t, C.c_void_p]),
+    "cglm_seq_advance": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_void_p]),
     "cglm_attn_forward_host": (C.c_int, [C.c_void_p, C.POINTER(AttnSeq), C.c_int, C.c_int, C.c_void_p, C.c_void_p,
                                          C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]),
     "cglm_attn_host_drain": (C.c_int, [C.c_void_p, C.c_void_p]),

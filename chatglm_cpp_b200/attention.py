@@ -16,7 +16,7 @@ import torch
 
 from . import _lib
 from ._lib import (AttnDesc, AttnSeq, MASK_CAUSAL, MASK_CHATGLM, ROPE_CHATGLM, ROPE_CHATGLM2, ROPE_DISABLED,  # noqa: F401
-                   ROPE_GPTJ, ROPE_NEOX, SEQ_NO_APPEND, SEQ_PARTIAL, SEQ_USE_KV_LOCAL, check)
+                   ROPE_GPTJ, ROPE_NEOX, SEQ_NO_APPEND, SEQ_N_PAST_DEVICE, SEQ_PARTIAL, SEQ_USE_KV_LOCAL, check)
 
 
 def _stream_ptr() -> int:
@@ -114,6 +114,7 @@ class SeqCall:
     partial: Optional[torch.Tensor] = None
     kv_local: int = 0
     flags: int = 0
+    n_past_dev: Optional[torch.Tensor] = None  # int32 device word(s); with SEQ_N_PAST_DEVICE the kernel reads n_past here
 
 
 def fill_seq(dst: AttnSeq, desc: AttnDesc, call: SeqCall, interleaved: bool) -> None:
@@ -138,6 +139,7 @@ def fill_seq(dst: AttnSeq, desc: AttnDesc, call: SeqCall, interleaved: bool) -> 
     dst.k_roped = call.k_roped.data_ptr() if call.k_roped is not None else None
     dst.partial = call.partial.data_ptr() if call.partial is not None else None
     dst.kv_local, dst.flags = call.kv_local, call.flags
+    dst.n_past_dev = call.n_past_dev.data_ptr() if call.n_past_dev is not None else None
 
 
 def forward_batch(arena: KVArena, ws: Workspace, calls: Sequence[SeqCall], interleaved: bool = False,

@@ -100,6 +100,7 @@ struct __align__(1024) DecodeSmem {
     int prefix[kDecodeMaxSeqPerLaunch + 2];        // copy of the launch's tile prefix sums (parameter space is slow to index)
     int slot[kDecodeMaxSeqPerLaunch];              // copy of every sequence's arena slot, for the producer
     SeqDev sq;                                     // the helper warp's copy of the descriptor it is preparing
+    int npast[kDecodeMaxSeqPerLaunch];             // kDynPast: every sequence's n_past as read from the device
     DeliverArgs dargs[kConsumerWarps + 1];         // per calling warp: arguments of deliver_part
     uint64_t full[kStages];
     uint64_t empty[kStages];
@@ -566,6 +567,10 @@ __device__ __noinline__ void deliver_part(const DeliverArgs *da, long long b, in
     merge(base, k_first, first_slot, k0, k1, final_dst, final_kind);
 }
 
+// kDynPast: sequences may carry CGLM_SEQ_N_PAST_DEVICE.  Their position is read from device memory once the previous
+// kernel of the stream has completed, the tile prefix is rebuilt from it, and nothing runs ahead of the dependency
+// wait (the spans are not known before).  A second instantiation, so that the common case pays nothing for it.
+template <bool kDynPast>
 __global__ void __launch_bounds__(kThreads, 2)
 decode_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map,
               const __grid_constant__ DecodeTable tab, AttnShape sh, uint16_t *__restrict__ k_base,
@@ -595,14 +600,43 @@ decode_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__
     // precedes the launch.  The prefix sums are searched by every role, so they are copied to shared memory once
     // (dependent reads of parameter space miss the small constant cache one after another).
     const int n_seq = tab.n_seq;
-    for (int i = tid; i <= n_seq; i += kThreads) {
-        sm.prefix[i] = tab.prefix[i];
-        if (i < n_seq) sm.slot[i] = tab.seqs[i].slot;
+    if (kDynPast) {
+        asm volatile("griddepcontrol.wait;" ::: "memory");
+        asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+        for (int i = tid; i < n_seq; i += kThreads) {
+            int np = tab.seqs[i].n_past;
+            if (tab.seqs[i].flags & CGLM_SEQ_N_PAST_DEVICE) {
+                np = *reinterpret_cast<const volatile int *>(tab.seqs[i].n_past_dev);
+                const int np_max = sh.M - sh.V - 1;   // the appended token must fit the cache
+                if (np < 0 || np > np_max) {
+                    np = np < 0 ? 0 : np_max;
+                    atomicExch(&hdr->status, static_cast<int>(CGLM_ERR_INVALID_ARG));
+                }
+            }
+            sm.npast[i] = np;
+            sm.slot[i] = tab.seqs[i].slot;
+            const int L = sh.V + np + ((tab.seqs[i].flags & CGLM_SEQ_NO_APPEND) ? 0 : 1);
+            sm.prefix[i + 1] = (L + kTile - 1) / kTile;
+        }
+        __syncthreads();
+        if (tid == 0) {
+            sm.prefix[0] = 0;
+            for (int i = 0; i < n_seq; ++i) sm.prefix[i + 1] += sm.prefix[i];
+        }
+    } else {
+        for (int i = tid; i <= n_seq; i += kThreads) {
+            sm.prefix[i] = tab.prefix[i];
+            if (i < n_seq) sm.slot[i] = tab.seqs[i].slot;
+        }
     }
     __syncthreads();
     const long long total = static_cast<long long>(sm.prefix[n_seq]) * G;
-    const long long nb = gridDim.x;
-    const long long span_lo = span_start(blockIdx.x, total, nb), span_hi = span_start(blockIdx.x + 1, total, nb);
+    // never more spans than tiles (the grid of a launch with device-side positions is sized from upper bounds): an
+    // empty span between two parts of an item would be counted as a part that never arrives
+    const long long nb = min(static_cast<long long>(gridDim.x), total);
+    const bool idle = blockIdx.x >= nb;
+    const long long span_lo = idle ? 0 : span_start(blockIdx.x, total, nb);
+    const long long span_hi = idle ? 0 : span_start(blockIdx.x + 1, total, nb);
     // Launched with programmatic stream serialization: everything that reads only kernel parameters (barrier
     // set-up, the tables above, the first segment's descriptor, the tensor maps) runs while the previous kernel of
     // the stream is still draining.  A read of parameter space at a computed index costs about a microsecond when
@@ -619,7 +653,7 @@ decode_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__
     // From here on this grid touches global memory, so it waits until the previous kernel has completed and its
     // writes are visible.  Stream order is preserved.
     // (The helper warp of a CTA with work waits inside its loop, after a dry pass over its first segment.)
-    if (warp != kHelperWarp || span_lo >= span_hi) {
+    if (!kDynPast && (warp != kHelperWarp || span_lo >= span_hi)) {
         asm volatile("griddepcontrol.wait;" ::: "memory");
         asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     }
@@ -665,8 +699,12 @@ decode_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__
         while (pos < span_hi && !sm.abort_flag) {
             const ItemPos ip = locate(sm.prefix, n_seq, G, pos);
             if (sidx > 0) load_seq_desc(sm.sq, tab.seqs[ip.seq], lane);   // the first one was fetched before the wait
-            const SeqDev sq = sm.sq;
+            SeqDev sq = sm.sq;
             __syncwarp();
+            if (kDynPast) {
+                sq.n_past = sm.npast[ip.seq];
+                sq.kv_before = sh.V + sq.n_past;   // CGLM_SEQ_USE_KV_LOCAL is not combined with a device-side position
+            }
             const long long item_end = ip.item_begin + ip.n_tiles;
             const long long seg_end = min(span_hi, item_end);
             const bool has_last_tile = seg_end == item_end;
@@ -675,11 +713,11 @@ decode_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__
             mbar_wait_bounded(&sm.qempty[b], ((sidx >> 1) & 1u) ^ 1u, &sm.abort_flag);
             // First segment: a dry pass while the previous kernel of the stream may still be running, then the wait
             // that every thread makes before it touches global memory, then the real pass over warm code.
-            const int n_pass = sidx == 0 ? 2 : 1;
+            const int n_pass = (sidx == 0 && !kDynPast) ? 2 : 1;
 #pragma unroll 1
             for (int pass = 0; pass < n_pass; ++pass) {
                 const bool dry = pass + 1 < n_pass;
-                if (sidx == 0 && !dry) {
+                if (sidx == 0 && !dry && !kDynPast) {
                     asm volatile("griddepcontrol.wait;" ::: "memory");
                 }
                 prepare_segment(sm.qb[b], sh, sq, ip.g, sq.slot * G + ip.g, has_last_tile, appender, lane, k_base, v_base,
@@ -895,7 +933,8 @@ decode_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__
 
 int decode_max_ctas(int n_sm) { return 2 * n_sm; }   // bound used to size scratch; launch_decode picks the grid
 
-cudaError_t launch_decode(const LaunchCtx &cx, const DecodeTable &tab) {
+cudaError_t launch_decode(const LaunchCtx &cx, const DecodeTable &tab, bool n_past_on_device) {
+    // with device-side positions tab.prefix holds the tile counts of the host's upper bounds: good for sizing only
     const long long total_tiles = static_cast<long long>(tab.prefix[tab.n_seq]) * cx.shape.G;
     if (tab.n_seq == 0 || total_tiles == 0) {
         return cudaSuccess;
@@ -903,7 +942,8 @@ cudaError_t launch_decode(const LaunchCtx &cx, const DecodeTable &tab) {
     static bool configured = false;
     const int smem_bytes = static_cast<int>(sizeof(DecodeSmem)) + 1024;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
+        cudaError_t e = cudaFuncSetAttribute(decode_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(decode_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
         if (e != cudaSuccess) return e;
         configured = true;
     }
@@ -925,8 +965,12 @@ cudaError_t launch_decode(const LaunchCtx &cx, const DecodeTable &tab) {
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, decode_kernel, *cx.k_map, *cx.v_map, tab, cx.shape, cx.k_base, cx.v_base, cx.hdr,
-                                       cx.counters, cx.gcounters, cx.partials, cx.gpartials, cx.rope_tab, cx.rope_tab_len);
+    cudaError_t e =
+        n_past_on_device
+            ? cudaLaunchKernelEx(&cfg, decode_kernel<true>, *cx.k_map, *cx.v_map, tab, cx.shape, cx.k_base, cx.v_base, cx.hdr,
+                                 cx.counters, cx.gcounters, cx.partials, cx.gpartials, cx.rope_tab, cx.rope_tab_len)
+            : cudaLaunchKernelEx(&cfg, decode_kernel<false>, *cx.k_map, *cx.v_map, tab, cx.shape, cx.k_base, cx.v_base, cx.hdr,
+                                 cx.counters, cx.gcounters, cx.partials, cx.gpartials, cx.rope_tab, cx.rope_tab_len);
     g_launch_count += 1;
     return e != cudaSuccess ? e : cudaGetLastError();
 }

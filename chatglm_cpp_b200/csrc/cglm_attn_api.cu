@@ -15,7 +15,7 @@ using namespace cglm;
 
 // the ctypes mirror of these structs (chatglm_cpp_b200/_lib.py) is checked against the same numbers
 static_assert(sizeof(cglm_attn_desc) == 32, "cglm_attn_desc layout");
-static_assert(sizeof(cglm_attn_seq) == 120 && offsetof(cglm_attn_seq, position_ids) == 72 &&
+static_assert(sizeof(cglm_attn_seq) == 128 && offsetof(cglm_attn_seq, position_ids) == 72 &&
                   offsetof(cglm_attn_seq, partial) == 112,
               "cglm_attn_seq layout");
 
@@ -339,6 +339,11 @@ xchg_combine_kernel(unsigned int *__restrict__ local, int n_rank, int H, int D, 
     if (threadIdx.x == 0) local[0] = e;
 }
 
+__global__ void seq_advance_kernel(int *__restrict__ n_past, int n, int delta) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) n_past[i] += delta;
+}
+
 __global__ void load_prefix_kernel(const uint16_t *__restrict__ past_kv, uint16_t *__restrict__ k_slot,
                                    uint16_t *__restrict__ v_slot, int G, int V, int D, int M) {
     const long long n = static_cast<long long>(G) * V * D;
@@ -568,6 +573,10 @@ int cglm_attn_forward(cglm_kv_arena *a, const cglm_attn_seq *seqs, int n_seq, vo
             return CGLM_ERR_INVALID_ARG;
         if ((s.flags & CGLM_SEQ_NO_APPEND) && (!partial || s.qlen != 1)) return CGLM_ERR_INVALID_ARG;
         if ((s.flags & CGLM_SEQ_USE_KV_LOCAL) && (s.kv_local < 0 || s.qlen != 1)) return CGLM_ERR_INVALID_ARG;
+        const bool dyn_past = (s.flags & CGLM_SEQ_N_PAST_DEVICE) != 0;
+        if (dyn_past && (!s.n_past_dev || (reinterpret_cast<uintptr_t>(s.n_past_dev) & 3) || s.qlen != 1 ||
+                         (s.flags & CGLM_SEQ_USE_KV_LOCAL)))
+            return CGLM_ERR_INVALID_ARG;
         const int kv_before = (s.flags & CGLM_SEQ_USE_KV_LOCAL) ? s.kv_local : d.n_virtual + s.n_past;
         const int appended = (s.flags & CGLM_SEQ_NO_APPEND) ? 0 : s.qlen;
         if (static_cast<long long>(kv_before) + appended > d.max_len) return CGLM_ERR_INVALID_ARG;
@@ -575,6 +584,10 @@ int cglm_attn_forward(cglm_kv_arena *a, const cglm_attn_seq *seqs, int n_seq, vo
         const int L = kv_before + appended;
         is_fast[i] = fast_ok && s.qlen == 1 && L >= 1 &&
                      decode_rows_aligned(s.q, s.k, s.v, s.q_head_stride, s.kv_head_stride, s.q_roped, s.k_roped);
+        if (dyn_past && !is_fast[i]) {
+            std::snprintf(g_err, sizeof(g_err), "CGLM_SEQ_N_PAST_DEVICE needs a shape and alignment the fused decode kernel takes");
+            return CGLM_ERR_UNSUPPORTED;
+        }
         if (is_fast[i]) {
             ++n_fast;
             decode_tiles += static_cast<long long>((L + kDecodeTile - 1) / kDecodeTile) * d.n_kv_head;
@@ -602,6 +615,7 @@ int cglm_attn_forward(cglm_kv_arena *a, const cglm_attn_seq *seqs, int n_seq, vo
         o.flags = s.flags;
         o.tok_begin = 0;
         o.pad = 0;
+        if (s.flags & CGLM_SEQ_N_PAST_DEVICE) o.n_past_dev = s.n_past_dev;   // shares the words of tok_begin / pad
     };
     uint8_t *ws = static_cast<uint8_t *>(workspace);
     LaunchCtx cx;
@@ -625,11 +639,13 @@ int cglm_attn_forward(cglm_kv_arena *a, const cglm_attn_seq *seqs, int n_seq, vo
     if (n_fast > 0) {
         static thread_local DecodeTable tab;
         int filled = 0;
+        bool dyn = false;
         tab.prefix[0] = 0;
         for (int i = 0; i <= n_seq; ++i) {
             if (i < n_seq && is_fast[i] == 1) {
                 SeqDev &o = tab.seqs[filled];
                 to_dev(seqs[i], o);
+                dyn = dyn || (o.flags & CGLM_SEQ_N_PAST_DEVICE);
                 const int L = o.kv_before + ((o.flags & CGLM_SEQ_NO_APPEND) ? 0 : 1);
                 tab.prefix[filled + 1] = tab.prefix[filled] + (L + kDecodeTile - 1) / kDecodeTile;
                 ++filled;
@@ -637,8 +653,9 @@ int cglm_attn_forward(cglm_kv_arena *a, const cglm_attn_seq *seqs, int n_seq, vo
             if (filled == kDecodeMaxSeqPerLaunch || (i == n_seq && filled > 0)) {
                 tab.n_seq = filled;
                 tab.pad = 0;
-                CGLM_CUDA(launch_decode(cx, tab));
+                CGLM_CUDA(launch_decode(cx, tab, dyn));
                 filled = 0;
+                dyn = false;
             }
         }
     }
@@ -851,6 +868,14 @@ int cglm_attn_splitkv_combine_arrived(void *xchg_local, int n_rank, int n_head, 
     if (!workspace) return CGLM_ERR_WORKSPACE;
     xchg_combine_kernel<<<1, 1024, 0, static_cast<cudaStream_t>(cuda_stream)>>>(
         static_cast<unsigned int *>(xchg_local), n_rank, n_head, head_dim, out, static_cast<WsHeader *>(workspace), timeout_us);
+    g_launch_count += 1;
+    CGLM_CUDA(cudaGetLastError());
+    return CGLM_OK;
+}
+
+int cglm_seq_advance(int *n_past_dev, int n, int delta, void *cuda_stream) {
+    if (!n_past_dev || n <= 0) return CGLM_ERR_INVALID_ARG;
+    seq_advance_kernel<<<(n + 127) / 128, 128, 0, static_cast<cudaStream_t>(cuda_stream)>>>(n_past_dev, n, delta);
     g_launch_count += 1;
     CGLM_CUDA(cudaGetLastError());
     return CGLM_OK;

@@ -38,9 +38,15 @@ struct SeqDev {
     int n_ctx;
     int kv_before;   // cached tokens attended besides the ones appended now (n_virtual + n_past, or kv_local)
     int flags;
-    int tok_begin;   // first row of this sequence in the staging buffers of the generic path
-    int pad;
+    union {
+        struct {
+            int tok_begin;   // generic path: first row of this sequence in the staging buffers
+            int pad;
+        };
+        const int *n_past_dev;   // fused decode with CGLM_SEQ_N_PAST_DEVICE: where the kernel reads n_past
+    };
 };
+static_assert(sizeof(SeqDev) == 128, "descriptors travel as 32 words");
 
 struct AttnShape {
     int H, G, D, R;       // heads, kv heads, head dim, H / G
@@ -253,7 +259,7 @@ struct DecodeTable {
     int prefix[kDecodeMaxSeqPerLaunch + 2];   // prefix[i] = 64-token tiles of sequences [0, i), per kv head
     SeqDev seqs[kDecodeMaxSeqPerLaunch];
 };
-cudaError_t launch_decode(const LaunchCtx &cx, const DecodeTable &tab);
+cudaError_t launch_decode(const LaunchCtx &cx, const DecodeTable &tab, bool n_past_on_device = false);
 // The decode kernel reads q/k/v head rows (and writes the optional roped copies) sixteen bytes at a time.
 inline bool decode_rows_aligned(const float *q, const float *k, const float *v, long long q_head_stride,
                                 long long kv_head_stride, const float *q_roped, const float *k_roped) {

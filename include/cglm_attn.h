@@ -109,12 +109,21 @@ typedef struct cglm_attn_seq {
     int kv_local;                     /* >0: tokens of this sequence present in this arena slot before the call */
     int flags;                        /* CGLM_SEQ_* */
     float *partial;                   /* with CGLM_SEQ_PARTIAL: f32 [n_head][head_dim+2] = acc | m | l instead of out */
+    /* step-graph use only (NULL otherwise) */
+    const int *n_past_dev;            /* with CGLM_SEQ_N_PAST_DEVICE: device word holding this sequence's n_past */
 } cglm_attn_seq;
 
 enum {
     CGLM_SEQ_NO_APPEND = 1,   /* this rank does not own position n_past: attend only */
     CGLM_SEQ_PARTIAL = 2,     /* emit un-normalised (acc, m, l) into .partial; .out is not written */
-    CGLM_SEQ_USE_KV_LOCAL = 4 /* attend over kv_local cached tokens (+ the appended one) instead of n_virtual + n_past */
+    CGLM_SEQ_USE_KV_LOCAL = 4,/* attend over kv_local cached tokens (+ the appended one) instead of n_virtual + n_past */
+    /* Decode step whose position is a device-side scalar, so that a CUDA graph holding the layer calls of one
+     * decode step can be replayed for the next token without being rebuilt (the reference rebuilds its ggml graph
+     * every token, chatglm.cpp:728-729): the kernel reads n_past from *n_past_dev when it runs; the host field
+     * n_past is only an upper bound (capacity check, launch sizing).  qlen 1, fused-decode shapes only
+     * (CGLM_ERR_UNSUPPORTED otherwise); a device value outside [0, capacity) is clamped and reported through the
+     * workspace status word as CGLM_ERR_INVALID_ARG.  cglm_seq_advance bumps the words between steps. */
+    CGLM_SEQ_N_PAST_DEVICE = 8
 };
 
 /* Scratch the kernels need for n_seq sequences per call with at most max_qlen tokens each. */
@@ -131,6 +140,8 @@ int cglm_attn_workspace_status(void *workspace, void *cuda_stream);
  */
 int cglm_attn_forward(cglm_kv_arena *arena, const cglm_attn_seq *seqs, int n_seq, void *workspace,
                       size_t workspace_bytes, void *cuda_stream);
+/* n_past_dev[i] += delta for i in [0, n): the last node of a captured decode step (see CGLM_SEQ_N_PAST_DEVICE). */
+int cglm_seq_advance(int *n_past_dev, int n, int delta, void *cuda_stream);
 
 /*
  * The same call for callers whose activations live in host memory, as ggml_backend_tensor_set /

@@ -30,7 +30,7 @@ def test_struct_layouts_match_header():
     from chatglm_cpp_b200 import _lib
     assert C.sizeof(_lib.AttnDesc) == 32
     # the same numbers are static_asserted against the C structs in csrc/cglm_attn_api.cu
-    assert C.sizeof(_lib.AttnSeq) == 120
+    assert C.sizeof(_lib.AttnSeq) == 128
     assert _lib.AttnSeq.position_ids.offset == 72 and _lib.AttnSeq.partial.offset == 112
 
 

@@ -399,6 +399,120 @@ def test_forward_host_pipeline_reuses_staging_buffers():
     assert torch.equal(arena.k_all()[:half], arena.k_all()[half:])
 
 
+def test_decode_with_4_byte_aligned_activation_takes_the_generic_path_and_agrees():
+    """The fused decode kernel reads q/k/v rows 16 bytes at a time; an activation that is only 4-byte aligned must be
+    routed to the generic CUDA path (same launch count as any generic call) and give the same output and cache."""
+    from chatglm_cpp_b200 import _lib
+    A = _A()
+    desc = make_desc(32, 2, 128, 512)
+    rng = np.random.default_rng(314)
+    arena, ws = A.KVArena(desc, 2), A.Workspace(desc, 1, 1)
+    k, v = random_cache(rng, desc, 300)
+    upload_cache(arena, 0, k, v)
+    upload_cache(arena, 1, k, v)
+    width = qkv_width(desc, False)
+    flat = torch.from_numpy(rng.standard_normal(width + 1).astype(np.float32)).cuda()
+    aligned = flat[:width].clone().view(1, width)          # 16-byte aligned copy of the same numbers
+    shifted = torch.empty(width + 1, device="cuda")
+    shifted[1:] = flat[:width]
+    shifted = shifted[1:].view(1, width)                    # starts 4 bytes into the allocation
+    assert aligned.data_ptr() % 16 == 0 and shifted.data_ptr() % 16 == 4
+    outs, counts = [], []
+    for slot, x in ((0, aligned), (1, shifted)):
+        out = torch.zeros(1, 4096, device="cuda")
+        before = _lib.lib().cglm_launch_count()
+        A.forward_batch(arena, ws, [A.SeqCall(qkv=x, slot=slot, n_past=300, out=out)])
+        torch.cuda.synchronize()
+        counts.append(_lib.lib().cglm_launch_count() - before)
+        outs.append(out)
+    assert ws.status() == 0
+    assert counts[0] == 1 and counts[1] == 2                # fused kernel; rope+append kernel and attend kernel
+    assert_out_close(outs[1].cpu().numpy(), outs[0].cpu().numpy(), "generic vs fused decode")
+    assert torch.equal(arena.k_cache(0), arena.k_cache(1))
+    assert torch.equal(arena.v_cache(0), arena.v_cache(1))
+    arena.close()
+
+
+def test_decode_step_graph_with_device_side_position_replays_for_new_tokens():
+    """The step loop of the reference (chatglm.cpp:726-755, 886-925) rebuilds its graph for every token.  Here the
+    layer calls of one decode step (two layers, three sequences of different lengths) are captured ONCE in a CUDA
+    graph with n_past read from device words, and replayed for four tokens; every replay must match the oracle run
+    token by token, caches included."""
+    from chatglm_cpp_b200 import _lib
+    A = _A()
+    H, G, D, M, n_layer = 32, 2, 128, 512, 2
+    desc = make_desc(H, G, D, M)
+    starts = [130, 63, 300]
+    n = len(starts)
+    rng = np.random.default_rng(99)
+    arena, ws = A.KVArena(desc, n_layer * n), A.Workspace(desc, n, 1)
+    cfg = oracle_cfg(desc, "f32")
+    host = {}
+    for layer in range(n_layer):
+        for i, P in enumerate(starts):
+            k, v = random_cache(rng, desc, P)
+            upload_cache(arena, layer * n + i, k, v)
+            host[(layer, i)] = (k, v)
+    width = qkv_width(desc, False)
+    qkv = torch.zeros(n_layer, n, width, device="cuda")                 # the graph's input buffers
+    outs = torch.zeros(n_layer, n, H * D, device="cuda")
+    n_past_dev = torch.tensor(starts, dtype=torch.int32, device="cuda")
+    bound = max(starts) + 8                                              # host-side upper bound of the positions
+    arrs = []
+    for layer in range(n_layer):
+        arr = (_lib.AttnSeq * n)()
+        for i in range(n):
+            A.fill_seq(arr[i], desc, A.SeqCall(qkv=qkv[layer, i:i + 1], slot=layer * n + i, n_past=bound,
+                                               out=outs[layer, i:i + 1], flags=A.SEQ_N_PAST_DEVICE,
+                                               n_past_dev=n_past_dev[i:i + 1]), False)
+        arrs.append(arr)
+    L = _lib.lib()
+
+    def step():
+        stream = torch.cuda.current_stream().cuda_stream
+        for layer in range(n_layer):
+            assert L.cglm_attn_forward(arena._h, arrs[layer], n, ws.ptr, ws.bytes, stream) == 0
+        assert L.cglm_seq_advance(n_past_dev.data_ptr(), n, 1, stream) == 0
+
+    side = torch.cuda.Stream()                  # one eager step first (token 0), as torch wants before a capture
+    side.wait_stream(torch.cuda.current_stream())
+    tokens = [rng.standard_normal((n_layer, n, width)).astype(np.float32) for _ in range(5)]
+    results = []
+    with torch.cuda.stream(side):
+        qkv.copy_(torch.from_numpy(tokens[0]))
+        step()
+        results.append(outs.clone())
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        step()                                   # captured, not executed
+    for t in range(1, 5):
+        qkv.copy_(torch.from_numpy(tokens[t]))
+        graph.replay()
+        results.append(outs.clone())
+    torch.cuda.synchronize()
+    assert ws.status() == 0
+    assert n_past_dev.cpu().tolist() == [p + 5 for p in starts]
+    for t in range(5):
+        for layer in range(n_layer):
+            for i, P in enumerate(starts):
+                k, v = host[(layer, i)]
+                want = O.attn_forward(cfg, tokens[t][layer, i:i + 1], False, k, v, P + t)   # appends into k, v
+                assert_out_close(results[t][layer, i:i + 1].cpu().numpy(), want, f"token {t} layer {layer} seq {i}")
+    for layer in range(n_layer):
+        for i in range(n):
+            gk, gv = download_cache(arena, layer * n + i)
+            np.testing.assert_array_equal(gk, host[(layer, i)][0])
+            np.testing.assert_array_equal(gv, host[(layer, i)][1])
+    # a position beyond the capacity is clamped and reported, never followed
+    n_past_dev.fill_(M + 5)
+    step()
+    torch.cuda.synchronize()
+    assert ws.status() == _lib.ERR_INVALID_ARG
+    arena.close()
+
+
 def test_argument_errors_return_codes():
     from chatglm_cpp_b200 import _lib
     A = _A()
