@@ -534,6 +534,48 @@ def run_ours(args, w):
     ms_e2e, _ = timed(step_host, max(3, args.steps // 2), max(3, args.warmup))
     e2e_steps = max(3, args.steps // 2)
 
+    # Optional: the same step issued as ONE CUDA graph whose layer calls read n_past from device words
+    # (CGLM_SEQ_N_PAST_DEVICE), the form a caller uses to replay a decode step for every new token without rebuilding
+    # anything.  The words are advanced by 0 here so that every replay is the step the other figures measure.
+    step_graph = None
+    if args.step_graph:
+        n_past_dev = torch.tensor([int(p) for p in n_past], dtype=torch.int32, device="cuda")
+        dyn_arrays = []
+        for l in range(layers):
+            arr = (_lib.AttnSeq * n)()
+            for i in range(n):
+                call = A.SeqCall(qkv=qkv_dev[l, i:i + 1], slot=l * n + i, n_past=int(n_past[i]), n_ctx=int(n_ctx[i]),
+                                 out=out_dev[l, i:i + 1], flags=_lib.SEQ_N_PAST_DEVICE, n_past_dev=n_past_dev[i:i + 1])
+                A.fill_seq(arr[i], desc, call, w["interleaved"])
+            dyn_arrays.append(arr)
+
+        def step_dyn():
+            st = torch.cuda.current_stream().cuda_stream
+            for l in range(layers):
+                rc = L.cglm_attn_forward(arena._h, dyn_arrays[l], n, ws.ptr, ws.bytes, st)
+                if rc != 0:
+                    raise _lib.CglmError(rc, "cglm_attn_forward")
+            rc = L.cglm_seq_advance(n_past_dev.data_ptr(), n, 0, st)
+            if rc != 0:
+                raise _lib.CglmError(rc, "cglm_seq_advance")
+
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            step_dyn()
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            step_dyn()
+        ms_graph, _ = timed(graph.replay, args.steps, args.warmup)
+        if ws.status() != 0:
+            raise SystemExit("device-side status is not clean after the step-graph region")
+        step_graph = {"value": tokens_per_step_of(n, world) * args.steps / (ms_graph * 1e-3), "unit": "tokens/s",
+                      "ms_per_step": ms_graph / args.steps, "launches_per_step": layers + 1,
+                      "note": "one CUDA graph per decode step, n_past read from device words, replayed"}
+        graph = None
+
     tokens_per_step = n * world
     value = tokens_per_step * args.steps / (ms * 1e-3)
     e2e_value = tokens_per_step * e2e_steps / (ms_e2e * 1e-3)
@@ -575,10 +617,16 @@ def run_ours(args, w):
             "gpu_launches": int(launches) * world,
             "clocks": clocks,
         }
+        if step_graph is not None:
+            line["step_graph"] = step_graph
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
+
+
+def tokens_per_step_of(n, world):
+    return n * world
 
 
 def main():
@@ -591,6 +639,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-graph", action="store_true", help="split-KV workload: issue every step eagerly")
     ap.add_argument("--exchange", choices=["p2p", "nccl"], default="p2p", help="split-KV workload: how partials travel")
+    ap.add_argument("--step-graph", action="store_true",
+                    help="batched decode workloads: also time the step as one replayed CUDA graph (device-side n_past)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     w = WORKLOADS[args.workload]
