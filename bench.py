@@ -571,7 +571,7 @@ def run_ours(args, w):
         ms_graph, _ = timed(graph.replay, args.steps, args.warmup)
         if ws.status() != 0:
             raise SystemExit("device-side status is not clean after the step-graph region")
-        step_graph = {"value": tokens_per_step_of(n, world) * args.steps / (ms_graph * 1e-3), "unit": "tokens/s",
+        step_graph = {"value": n * world * args.steps / (ms_graph * 1e-3), "unit": "tokens/s",
                       "ms_per_step": ms_graph / args.steps, "launches_per_step": layers + 1,
                       "note": "one CUDA graph per decode step, n_past read from device words, replayed"}
         graph = None
@@ -623,10 +623,6 @@ def run_ours(args, w):
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
-
-
-def tokens_per_step_of(n, world):
-    return n * world
 
 
 def main():
