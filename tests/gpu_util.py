@@ -61,23 +61,30 @@ def qkv_width(desc: AttnDesc, interleaved: bool) -> int:
     return 3 * desc.n_head * desc.head_dim if interleaved else (desc.n_head + 2 * desc.n_kv_head) * desc.head_dim
 
 
-def run_decode_batch(desc: AttnDesc, n_past_list, seed=0, interleaved=False, n_ctx_list=None, check_rope=True):
-    """One decode step for a batch through the CUDA path and the oracle; asserts the parity gates."""
+def run_decode_batch(desc: AttnDesc, n_past_list, seed=0, interleaved=False, n_ctx_list=None, check_rope=True,
+                     n_past_on_device=False):
+    """One decode step for a batch through the CUDA path and the oracle; asserts the parity gates.
+    n_past_on_device: the kernel reads every position from a device word (CGLM_SEQ_N_PAST_DEVICE); the host field
+    then only carries an upper bound."""
     rng = np.random.default_rng(seed)
     n = len(n_past_list)
     V = desc.n_virtual
     arena = A.KVArena(desc, n)
     ws = A.Workspace(desc, n, 1)
     calls, host = [], []
+    n_past_dev = torch.tensor([int(p) for p in n_past_list], dtype=torch.int32, device="cuda")
+    bound = desc.max_len - V - 1
     for i, P in enumerate(n_past_list):
         k, v = random_cache(rng, desc, V + P)
         upload_cache(arena, i, k, v)
         qkv = rng.standard_normal((1, qkv_width(desc, interleaved))).astype(np.float32)
         n_ctx = n_ctx_list[i] if n_ctx_list is not None else 0
-        call = A.SeqCall(qkv=torch.from_numpy(qkv).cuda(), slot=i, n_past=P, n_ctx=n_ctx,
+        call = A.SeqCall(qkv=torch.from_numpy(qkv).cuda(), slot=i, n_past=bound if n_past_on_device else P, n_ctx=n_ctx,
                          out=torch.zeros(1, desc.n_head * desc.head_dim, device="cuda"),
                          q_roped=torch.zeros(1, desc.n_head, desc.head_dim, device="cuda"),
-                         k_roped=torch.zeros(1, desc.n_kv_head, desc.head_dim, device="cuda"))
+                         k_roped=torch.zeros(1, desc.n_kv_head, desc.head_dim, device="cuda"),
+                         flags=A.SEQ_N_PAST_DEVICE if n_past_on_device else 0,
+                         n_past_dev=n_past_dev[i:i + 1] if n_past_on_device else None)
         calls.append(call)
         host.append((qkv, k, v, n_ctx))
     A.forward_batch(arena, ws, calls, interleaved)

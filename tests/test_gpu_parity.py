@@ -433,6 +433,17 @@ def test_decode_with_4_byte_aligned_activation_takes_the_generic_path_and_agrees
     arena.close()
 
 
+def test_decode_batch_with_device_side_positions_mixed_lengths():
+    """The instantiation of the decode kernel that reads n_past from device words, on a batch whose spans cross item
+    boundaries and whose grid (sized from the host's upper bounds) is larger than the real number of tiles needs."""
+    desc = make_desc(32, 2, 128, 2048)
+    rng = np.random.default_rng(4242)
+    n_past = [int(x) for x in rng.integers(1, 2000, size=48)]
+    run_decode_batch(desc, n_past, seed=17, n_past_on_device=True)
+    v1 = make_desc(8, 8, 128, 512, rope=O.ROPE_CHATGLM, mask=O.MASK_CHATGLM)
+    run_decode_batch(v1, [100, 257, 31], seed=18, interleaved=True, n_ctx_list=[40, 200, 10], n_past_on_device=True)
+
+
 def test_decode_step_graph_with_device_side_position_replays_for_new_tokens():
     """The step loop of the reference (chatglm.cpp:726-755, 886-925) rebuilds its graph for every token.  Here the
     layer calls of one decode step (two layers, three sequences of different lengths) are captured ONCE in a CUDA
