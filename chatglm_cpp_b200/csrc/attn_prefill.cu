@@ -122,8 +122,11 @@ rope_table_kernel(AttnShape sh, SeqDev sq, float2 *__restrict__ table) {
 __global__ void __launch_bounds__(kPrepThreads)
 prefill_prepare_kernel(AttnShape sh, SeqDev sq, uint16_t *__restrict__ k_base, uint16_t *__restrict__ v_base,
                        __half *__restrict__ q_half, int s_pad, const float2 *__restrict__ table, int table_by_position) {
-    // the attention kernel that follows is launched as a programmatic dependent: let its CTAs take their places
-    // (shared memory, tensor memory, barriers) while this grid runs; it waits for this grid before its first load
+    // Launched as a programmatic dependent itself (its launch latency hides behind the previous kernel of the
+    // stream): nothing is read or written before that kernel has completed.  The attention kernel that follows is a
+    // programmatic dependent of this grid: let its CTAs take their places (shared memory, tensor memory, barriers)
+    // while this grid runs; it waits for this grid before its first load.
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     __shared__ __half tile_mem[kD][kPrepTokens + 2];       // v CTAs: [dim][token] transpose tile
     const int S = sq.qlen, H = sh.H, G = sh.G, M = sh.M;
@@ -597,19 +600,23 @@ cudaError_t launch_prefill(const LaunchCtx &cx, const SeqDev &sq, const CUtensor
         table_by_position = 0;
         ++launched;
     }
-    dim3 prep_grid((S + kPrepTokens - 1) / kPrepTokens, (cx.shape.H + 1) / 2 + 2 * cx.shape.G);
-    prefill_prepare_kernel<<<prep_grid, kPrepThreads, 0, cx.stream>>>(cx.shape, sq, cx.k_base, cx.v_base, q_half, s_pad,
-                                                                     table, table_by_position);
-    cudaError_t e = cudaGetLastError();
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;   // see griddepcontrol.wait in both kernels
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchConfig_t pcfg = {};
+    pcfg.gridDim = dim3((S + kPrepTokens - 1) / kPrepTokens, (cx.shape.H + 1) / 2 + 2 * cx.shape.G);
+    pcfg.blockDim = dim3(kPrepThreads);
+    pcfg.stream = cx.stream;
+    pcfg.attrs = attr;
+    pcfg.numAttrs = 1;
+    cudaError_t e = cudaLaunchKernelEx(&pcfg, prefill_prepare_kernel, cx.shape, sq, cx.k_base, cx.v_base, q_half, s_pad, table,
+                                       table_by_position);
     if (e != cudaSuccess) return e;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((s_pad / kQTile + 1) / 2, cx.shape.H);   // each CTA takes q tiles (n_q - 1 - x) and x
     cfg.blockDim = dim3(kThreads);
     cfg.dynamicSmemBytes = smem_bytes;
     cfg.stream = cx.stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;   // see griddepcontrol.wait in the kernel
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     e = cudaLaunchKernelEx(&cfg, prefill_attn_kernel, q_map, k_map, v_map, cx.shape, S, sq.slot * cx.shape.G, sq.out, cx.hdr);
