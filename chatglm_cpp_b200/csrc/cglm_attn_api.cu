@@ -707,26 +707,62 @@ int cglm_attn_forward_host(cglm_kv_arena *a, const cglm_attn_seq *seqs, int n_se
     cudaStream_t st = static_cast<cudaStream_t>(cuda_stream);
     const long long H = d.n_head, G = d.n_kv_head, D = d.head_dim;
     const long long row = (H + 2 * G) * D, orow = H * D;
-    long long n_tok = 0;
-    std::vector<cglm_attn_seq> dev_seqs(seqs, seqs + n_seq);
     for (int i = 0; i < n_seq; ++i) {
         if (seqs[i].qlen <= 0) return CGLM_ERR_INVALID_ARG;
-        cglm_attn_seq &s = dev_seqs[i];
-        const float *base = dev_qkv + n_tok * row;
-        s.q = base;
-        if (interleaved_qkv) {   // chatglm.cpp:638-644
-            s.k = base + D; s.v = base + 2 * D;
-            s.q_head_stride = s.kv_head_stride = 3 * D;
-        } else {                 // chatglm.cpp:646-652
-            s.k = base + H * D; s.v = base + (H + G) * D;
-            s.q_head_stride = s.kv_head_stride = D;
-        }
-        s.q_tok_stride = s.kv_tok_stride = row;
-        s.out = dev_out + n_tok * orow;
-        s.position_ids = nullptr; s.q_roped = nullptr; s.k_roped = nullptr; s.partial = nullptr;
-        s.flags = 0; s.kv_local = 0;
-        n_tok += seqs[i].qlen;
     }
+    long long n_tok = 0;
+    std::vector<cglm_attn_seq> dev_seqs(seqs, seqs + n_seq);
+    // descriptors over a packed [tokens][row] activation at in_base and a packed [tokens][orow] output at out_base
+    auto point_at = [&](const float *in_base, float *out_base) {
+        n_tok = 0;
+        for (int i = 0; i < n_seq; ++i) {
+            cglm_attn_seq &s = dev_seqs[i];
+            const float *base = in_base + n_tok * row;
+            s.q = base;
+            if (interleaved_qkv) {   // chatglm.cpp:638-644
+                s.k = base + D; s.v = base + 2 * D;
+                s.q_head_stride = s.kv_head_stride = 3 * D;
+            } else {                 // chatglm.cpp:646-652
+                s.k = base + H * D; s.v = base + (H + G) * D;
+                s.q_head_stride = s.kv_head_stride = D;
+            }
+            s.q_tok_stride = s.kv_tok_stride = row;
+            s.out = out_base + n_tok * orow;
+            s.position_ids = nullptr; s.q_roped = nullptr; s.k_roped = nullptr; s.partial = nullptr;
+            s.n_past_dev = nullptr;
+            s.flags = 0; s.kv_local = 0;
+            n_tok += seqs[i].qlen;
+        }
+    };
+    // ---- small decode steps on pinned host buffers: no staging at all ------------------------------------------
+    // Pinned (page-locked) host memory is mapped into the device's address space.  For a decode call of a few
+    // sequences the kernel reads the activations across PCIe where it would have read the staging copy, and stores
+    // the outputs straight into the host buffer: the same bytes cross the bus, but no copy, no event and no stream
+    // wait stands between two launches (measured: 28 -> 15 us per call for one sequence).  Results are in host
+    // memory once the stream has been synchronised.  Beyond about 128 KiB of activations the bus latency of the
+    // many small reads and their repetition by every CTA that holds a part of a sequence cost more than the copies
+    // (64 sequences: half the throughput of the staged pipeline), so larger calls, pageable host memory and
+    // prompts keep the staged pipeline below.
+    {
+        constexpr long long kZeroCopyMaxBytes = 128 * 1024;
+        bool decode_only = fast_decode_shape(a) && static_cast<long long>(n_seq) * row * 4 <= kZeroCopyMaxBytes;
+        for (int i = 0; i < n_seq && decode_only; ++i) decode_only = seqs[i].qlen == 1;
+        auto mapped = [](const void *p) -> void * {
+            cudaPointerAttributes at;
+            if (cudaPointerGetAttributes(&at, p) != cudaSuccess) {
+                cudaGetLastError();
+                return nullptr;
+            }
+            return at.type == cudaMemoryTypeHost ? at.devicePointer : nullptr;
+        };
+        void *din = decode_only ? mapped(qkv_host) : nullptr;
+        void *dout = din ? mapped(out_host) : nullptr;
+        if (din && dout) {
+            point_at(static_cast<const float *>(din), static_cast<float *>(dout));
+            return cglm_attn_forward(a, dev_seqs.data(), n_seq, workspace, workspace_bytes, cuda_stream);
+        }
+    }
+    point_at(dev_qkv, dev_out);
     // ---- pipeline: H2D on copy_in, kernel on the caller's stream, D2H on copy_out ---------------------------------
     std::unique_lock<std::mutex> lock(a->mu);
     if (!a->host_ready) {

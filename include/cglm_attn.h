@@ -156,6 +156,10 @@ int cglm_seq_advance(int *n_past_dev, int n, int delta, void *cuda_stream);
  * neighbouring calls different staging buffers, two or three pairs are enough; reuse of a staging buffer is ordered
  * by the library).  out_host is valid once cglm_attn_host_drain has been enqueued on a stream and that stream has
  * been synchronised.  Use pinned host memory for truly asynchronous copies.
+ * Small decode calls (every qlen 1, fused-decode shape, at most 128 KiB of activations) whose two host buffers are
+ * pinned skip the staging altogether: the kernel reads the activations from, and stores the outputs to, the mapped
+ * host memory across PCIe, so nothing stands between two launches; the same drain-and-synchronise rule makes
+ * out_host valid.
  */
 int cglm_attn_forward_host(cglm_kv_arena *arena, const cglm_attn_seq *seqs, int n_seq, int interleaved_qkv,
                            const float *qkv_host, float *out_host, float *dev_qkv, float *dev_out,

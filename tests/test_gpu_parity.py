@@ -328,7 +328,10 @@ def test_splitkv_partials_combine_to_full_attention():
     np.testing.assert_array_equal(gv[:, :, P - r_own * chunk], vf[:, :, P])
 
 
-def test_forward_host_roundtrip_matches_device_call():
+@pytest.mark.parametrize("pinned", [True, False])
+def test_forward_host_roundtrip_matches_device_call(pinned):
+    """Host-buffer call against the plain device call.  Pinned host buffers are read and written by the decode kernel
+    directly (one launch, no copies); pageable ones go through the staged copy pipeline."""
     from chatglm_cpp_b200 import _lib
     A = _A()
     desc = make_desc(32, 2, 128, 1024)
@@ -344,8 +347,8 @@ def test_forward_host_roundtrip_matches_device_call():
     calls = [A.SeqCall(qkv=torch.from_numpy(qkv[i:i + 1]).cuda(), slot=i, n_past=P, out=torch.zeros(1, 4096, device="cuda"))
              for i, P in enumerate(n_past)]
     A.forward_batch(arena, ws, calls)
-    qkv_pinned = torch.from_numpy(qkv).pin_memory()
-    out_pinned = torch.zeros(n, 4096).pin_memory()
+    qkv_pinned = torch.from_numpy(qkv).pin_memory() if pinned else torch.from_numpy(qkv.copy())
+    out_pinned = torch.zeros(n, 4096).pin_memory() if pinned else torch.zeros(n, 4096)
     dev_qkv, dev_out = torch.empty(n, qkv.shape[1], device="cuda"), torch.empty(n, 4096, device="cuda")
     arr = (_lib.AttnSeq * n)()
     for i, P in enumerate(n_past):
@@ -368,8 +371,8 @@ def test_forward_host_pipeline_reuses_staging_buffers():
     A = _A()
     desc = make_desc(32, 2, 128, 2048)
     rng = np.random.default_rng(41)
-    n_layers, n = 6, 4
-    n_past = [1500, 20, 700, 2047]
+    n_layers, n = 6, 8          # 8 x 18 KiB of activations per call: above the zero-copy limit, so the staged path
+    n_past = [1500, 20, 700, 2047, 64, 1, 1023, 333]
     arena, ws = A.KVArena(desc, 2 * n_layers * n), A.Workspace(desc, n, 1)
     arena.k_all().normal_(); arena.v_all().normal_()
     half = n_layers * n
