@@ -76,6 +76,22 @@ __device__ __forceinline__ void umma_commit(uint64_t *bar) {
 }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+// packed f32x2 arithmetic and the three-input maximum of sm_100: half the instructions of the scalar forms
+__device__ __forceinline__ void fma2(float &d0, float &d1, float a0, float a1, float b, float c) {
+    asm("{\n\t.reg .b64 ra, rb, rc, rd;\n\tmov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %4};\n\tmov.b64 rc, {%5, %5};\n\t"
+        "fma.rn.f32x2 rd, ra, rb, rc;\n\tmov.b64 {%0, %1}, rd;\n\t}"
+        : "=f"(d0), "=f"(d1) : "f"(a0), "f"(a1), "f"(b), "f"(c));
+}
+__device__ __forceinline__ void add2(float &d0, float &d1, float a0, float a1) {   // (d0, d1) += (a0, a1)
+    asm("{\n\t.reg .b64 ra, rb, rd;\n\tmov.b64 ra, {%0, %1};\n\tmov.b64 rb, {%2, %3};\n\tadd.rn.f32x2 rd, ra, rb;\n\t"
+        "mov.b64 {%0, %1}, rd;\n\t}"
+        : "+f"(d0), "+f"(d1) : "f"(a0), "f"(a1));
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
 // 32 consecutive f32 columns of this thread's TMEM lane
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
     uint32_t r[32];
@@ -458,9 +474,9 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
             }
             float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-            for (int i = 0; i < kKvTile; i += 4) {
-                mx4[0] = fmaxf(mx4[0], sv[i]); mx4[1] = fmaxf(mx4[1], sv[i + 1]);
-                mx4[2] = fmaxf(mx4[2], sv[i + 2]); mx4[3] = fmaxf(mx4[3], sv[i + 3]);
+            for (int i = 0; i < kKvTile; i += 8) {
+                mx4[0] = max3(mx4[0], sv[i], sv[i + 1]); mx4[1] = max3(mx4[1], sv[i + 2], sv[i + 3]);
+                mx4[2] = max3(mx4[2], sv[i + 4], sv[i + 5]); mx4[3] = max3(mx4[3], sv[i + 6], sv[i + 7]);
             }
             const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * kLog2e;
             // keep the old reference unless the maximum outgrew it by more than the threshold
@@ -499,10 +515,10 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
                 uint32_t packed[16];
 #pragma unroll
                 for (int i = 0; i < 32; i += 2) {
-                    const float p0 = ex2_approx(fmaf(sv[ch * 32 + i], kLog2e, -m_base));       // masked scores are -inf: p = 0
-                    const float p1 = ex2_approx(fmaf(sv[ch * 32 + i + 1], kLog2e, -m_base));
-                    sum4[(i >> 1) & 1] += p0;
-                    sum4[2 + ((i >> 1) & 1)] += p1;
+                    float e0, e1;
+                    fma2(e0, e1, sv[ch * 32 + i], sv[ch * 32 + i + 1], kLog2e, -m_base);   // masked scores are -inf: p = 0
+                    const float p0 = ex2_approx(e0), p1 = ex2_approx(e1);
+                    add2(sum4[2 * ((i >> 1) & 1)], sum4[2 * ((i >> 1) & 1) + 1], p0, p1);
                     packed[i >> 1] = pack_half2(p0, p1);
                 }
                 // tokens [32ch, 32ch+32) of the tile: half = ch / 2, 16-byte chunks (ch % 2) * 4 .. +3 of the 128-byte row
