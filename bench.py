@@ -54,7 +54,7 @@ WORKLOADS = {
     "glm1_6b_mha_decode": dict(H=32, G=32, D=128, M=4096, layers=28, seqs=4, n_past=(2048, 2048), rope=4,
                                theta=10000.0, interleaved=True, mask=1, seed=1005),
 }
-HBM_FALLBACK_GBS = 6650.0   # earlier measurement on this pool, used only without MEASURED_PEAKS.json
+HBM_FALLBACK_GBS = 6650.0   # B200 copy bandwidth from an earlier measurement, used only without MEASURED_PEAKS.json
 # (dram__bytes_read.sum + dram__bytes_write.sum) / algorithmic KV bytes of one decode launch, from the ncu capture of
 # the _small workload, whose launches are identical to the default workload's (see profiles/): 316.5 MB / 303.5 MB.
 NCU_TRAFFIC_PER_KV_BYTE = 1.043

@@ -76,26 +76,6 @@ def build(force: bool = False, verbose: bool = False) -> str:
     return LIB_PATH
 
 
-def build_cpp_test() -> str:
-    """Compiles tests/cpp/test_basic_attention.cpp against the library and the CPU oracle (test binary, in-tree)."""
-    root = os.path.dirname(PKG)
-    src = os.path.join(root, "tests", "cpp", "test_basic_attention.cpp")
-    out_dir = os.path.join(root, "tests", "cpp", "bin")
-    out = os.path.join(out_dir, "test_basic_attention")
-    os.makedirs(out_dir, exist_ok=True)
-    deps = [src, LIB_PATH, os.path.join(root, "oracle", "liboracle_attn.so"), os.path.join(root, "include", "chatglm_b200.h")]
-    if os.path.exists(out) and all(os.path.getmtime(out) >= os.path.getmtime(d) for d in deps):
-        return out
-    cmd = [_nvcc(), "-std=c++17", "-O2", "-x", "cu", src, "-o", out, "-L" + LIB_DIR, "-lcglm_attn",
-           "-L" + os.path.join(root, "oracle"), "-loracle_attn", "-Xlinker", "-rpath", "-Xlinker", "$ORIGIN/../../../chatglm_cpp_b200/lib",
-           "-Xlinker", "-rpath", "-Xlinker", "$ORIGIN/../../../oracle", "-cudart", "static"]
-    r = subprocess.run(cmd, capture_output=True, text=True)
-    if r.returncode != 0:
-        sys.stderr.write(r.stdout + r.stderr)
-        raise RuntimeError("building the C++ boundary test failed")
-    return out
-
-
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
     ap.add_argument("--force", action="store_true")

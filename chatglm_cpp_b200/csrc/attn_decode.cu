@@ -33,7 +33,7 @@
 
 namespace cglm {
 
-unsigned long long g_launch_count = 0;
+std::atomic<unsigned long long> g_launch_count{0};
 
 namespace {
 
@@ -939,13 +939,14 @@ cudaError_t launch_decode(const LaunchCtx &cx, const DecodeTable &tab, bool n_pa
     if (tab.n_seq == 0 || total_tiles == 0) {
         return cudaSuccess;
     }
-    static bool configured = false;
+    static PerDeviceOnce configured;
     const int smem_bytes = static_cast<int>(sizeof(DecodeSmem)) + 1024;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(decode_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
+    if (configured.needed(cx.device)) {
+        cudaError_t e = require_current_device(cx.device);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(decode_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
         if (e == cudaSuccess) e = cudaFuncSetAttribute(decode_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
         if (e != cudaSuccess) return e;
-        configured = true;
+        configured.mark(cx.device);
     }
     // Grid: about 36 tiles (1.1 MiB of cache) per CTA, at least one CTA per SM and at most 1.75 per SM.  Measured
     // on B200 for 4 k to 19 k tiles per launch: fewer, longer spans mean fewer partials and merges, and an SM that

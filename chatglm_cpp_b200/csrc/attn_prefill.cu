@@ -596,12 +596,13 @@ cudaError_t launch_prefill(const LaunchCtx &cx, const SeqDev &sq, const CUtensor
                            const CUtensorMap &v_map, __half *q_half) {
     const int S = sq.qlen;
     const int s_pad = (S + kQTile - 1) / kQTile * kQTile;
-    static bool configured = false;
+    static PerDeviceOnce configured;
     const int smem_bytes = static_cast<int>(sizeof(PrefillSmem)) + 1024;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(prefill_attn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
+    if (configured.needed(cx.device)) {
+        cudaError_t e = require_current_device(cx.device);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(prefill_attn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
         if (e != cudaSuccess) return e;
-        configured = true;
+        configured.mark(cx.device);
     }
     // Angles: positions derived from the token index lie inside the arena's table (one row per cache position);
     // explicit position ids may not, so a call that brings them gets a table of its own first.

@@ -522,8 +522,7 @@ int cglm_attn_workspace_init(void *workspace, size_t workspace_bytes, void *cuda
     if (!workspace || workspace_bytes < sizeof(WsHeader)) return CGLM_ERR_WORKSPACE;
     cudaStream_t st = static_cast<cudaStream_t>(cuda_stream);
     CGLM_CUDA(cudaMemsetAsync(workspace, 0, workspace_bytes, st));
-    const unsigned int magic = kWsMagic;
-    CGLM_CUDA(cudaMemcpyAsync(workspace, &magic, sizeof(magic), cudaMemcpyHostToDevice, st));
+    CGLM_CUDA(cudaMemsetAsync(workspace, static_cast<int>(kWsMagic & 0xffu), sizeof(unsigned int), st));   // the magic is one byte, four times
     return CGLM_OK;
 }
 
@@ -563,7 +562,8 @@ int cglm_attn_forward(cglm_kv_arena *a, const cglm_attn_seq *seqs, int n_seq, vo
         const cglm_attn_seq &s = seqs[i];
         if (!s.q || !s.k || !s.v || s.qlen <= 0 || s.n_past < 0 || s.slot < 0 || s.slot >= a->n_slots)
             return CGLM_ERR_INVALID_ARG;
-        if (s.qlen > 1 && s.n_past != 0) return CGLM_ERR_INVALID_ARG;   // chatglm.cpp:689 masks only at n_past == 0
+        // qlen > 1 with n_past != 0 (a prompt fed in chunks) is served like the reference serves it: no mask at all
+        // (chatglm.cpp:689 masks only at n_past == 0), on the generic path
         const bool partial = (s.flags & CGLM_SEQ_PARTIAL) != 0;
         if (partial ? !s.partial : !s.out) return CGLM_ERR_INVALID_ARG;
         // vector stores: out rows are written 16 bytes at a time, partial rows 8 bytes at a time
@@ -634,6 +634,7 @@ int cglm_attn_forward(cglm_kv_arena *a, const cglm_attn_seq *seqs, int n_seq, vo
     cx.rope_tab_len = a->rope_tab_len;
     cx.stream = st;
     cx.n_sm = a->n_sm;
+    cx.device = a->device;
 
     // fused decode: descriptors and tile prefix travel as kernel parameters, kDecodeMaxSeqPerLaunch per launch
     if (n_fast > 0) {
@@ -946,6 +947,6 @@ const char *cglm_status_string(int status) {
 
 const char *cglm_last_error_string(void) { return g_err; }
 
-unsigned long long cglm_launch_count(void) { return g_launch_count; }
+unsigned long long cglm_launch_count(void) { return g_launch_count.load(); }
 
 }  // extern "C"

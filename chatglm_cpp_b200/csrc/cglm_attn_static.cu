@@ -47,7 +47,6 @@ static_assert(kStaticCountersOff % 256 == 0 && kStaticPartialsOff % 256 == 0, "r
 // The scratch itself.  In host code this name is only a handle for cudaGetSymbolAddress, never an address.
 static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
 
-constexpr int kMaxDevices = 64;
 unsigned char *g_scratch_ptr[kMaxDevices] = {};   // device address of the array, per device ordinal
 std::mutex g_setup_mu;
 
@@ -94,6 +93,7 @@ extern "C" int cglm_attn_decode_static(cglm_kv_arena *arena, const cglm_attn_seq
     if (rc != CGLM_OK) return rc;
     cudaStream_t st = static_cast<cudaStream_t>(cuda_stream);
 
+    const int n_slots = cglm_kv_arena_n_slots(arena);
     static thread_local DecodeTable tab;
     tab.n_seq = n_seq;
     tab.pad = 0;
@@ -101,6 +101,8 @@ extern "C" int cglm_attn_decode_static(cglm_kv_arena *arena, const cglm_attn_seq
     for (int i = 0; i < n_seq; ++i) {
         const cglm_attn_seq &s = seqs[i];
         if (!s.q || !s.k || !s.v || !s.out || s.qlen != 1 || s.n_past < 0 || s.flags != 0) return CGLM_ERR_INVALID_ARG;
+        // the slot selects where the helper warp appends and which rows TMA reads: never outside the arena
+        if (s.slot < 0 || s.slot >= n_slots) return CGLM_ERR_INVALID_ARG;
         if ((reinterpret_cast<uintptr_t>(s.out) & 15) || (reinterpret_cast<uintptr_t>(s.q) & 3) ||
             (reinterpret_cast<uintptr_t>(s.k) & 3) || (reinterpret_cast<uintptr_t>(s.v) & 3))
             return CGLM_ERR_INVALID_ARG;
@@ -108,7 +110,7 @@ extern "C" int cglm_attn_decode_static(cglm_kv_arena *arena, const cglm_attn_seq
             set_last_error("q, k, v rows must be 16-byte aligned (pointers and head strides)");
             return CGLM_ERR_UNSUPPORTED;
         }
-        if (shape.V + s.n_past + 1 > shape.M) return CGLM_ERR_INVALID_ARG;
+        if (static_cast<long long>(shape.V) + s.n_past + 1 > shape.M) return CGLM_ERR_INVALID_ARG;
         if (shape.rope_type == CGLM_ROPE_CHATGLM && !s.position_ids && s.n_ctx < 2) return CGLM_ERR_INVALID_ARG;
         SeqDev &o = tab.seqs[i];
         o.q = s.q; o.k = s.k; o.v = s.v;
@@ -125,6 +127,7 @@ extern "C" int cglm_attn_decode_static(cglm_kv_arena *arena, const cglm_attn_seq
     // start at zero (a call that ran into a timeout can leave counters behind); the partial slots need no
     // clearing, every slot that is read was written by the same launch.
     cudaError_t e = cudaMemsetAsync(scratch, 0, kStaticPartialsOff, st);
+    if (e == cudaSuccess) e = cudaMemsetAsync(scratch, static_cast<int>(kWsMagic & 0xffu), sizeof(unsigned int), st);   // header magic
     if (e != cudaSuccess) {
         { char msg__[200]; std::snprintf(msg__, sizeof(msg__), "cudaMemsetAsync: %s", cudaGetErrorString(e)); set_last_error(msg__); }
         return CGLM_ERR_CUDA;
@@ -144,6 +147,7 @@ extern "C" int cglm_attn_decode_static(cglm_kv_arena *arena, const cglm_attn_seq
     cx.rope_tab = arena_rope_tab(arena, &cx.rope_tab_len);
     cx.stream = st;
     cx.n_sm = arena_sm_count(arena);
+    cx.device = dev;
     e = launch_decode(cx, tab);
     if (e != cudaSuccess) {
         { char msg__[200]; std::snprintf(msg__, sizeof(msg__), "decode launch: %s", cudaGetErrorString(e)); set_last_error(msg__); }

@@ -1,6 +1,7 @@
 // Shared device-side declarations of the attention KV-cache kernels (sm_100a).
 #pragma once
 
+#include <atomic>
 #include <cuda.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
@@ -20,7 +21,7 @@ struct WsHeader {
     int reserved[62];
 };
 static_assert(sizeof(WsHeader) == 256, "control block is 256 bytes");
-constexpr unsigned int kWsMagic = 0x43474c4du;  // "CGLM"
+constexpr unsigned int kWsMagic = 0x5a5a5a5au;  // one byte repeated, so that a memset can write it
 
 // Device-side copy of one cglm_attn_seq with everything resolved that the kernels would otherwise
 // re-derive: cache row of the first kv head, attended length, rope positions.
@@ -243,7 +244,25 @@ struct LaunchCtx {
     int rope_tab_len;
     cudaStream_t stream;
     int n_sm;
+    int device;                  // ordinal of the arena's device, which must be the current one
 };
+
+// Per-function attributes (the opt-in to more than 48 KiB of dynamic shared memory) are per device: a process that
+// drives several GPUs sets them once on each.  Returns true when `device` still needs its set-up; the caller then
+// sets the attributes with that device current and calls device_setup_done.
+constexpr int kMaxDevices = 64;
+struct PerDeviceOnce {
+    std::atomic<bool> done[kMaxDevices];
+    bool needed(int device) const { return device < 0 || device >= kMaxDevices || !done[device].load(std::memory_order_acquire); }
+    void mark(int device) { if (device >= 0 && device < kMaxDevices) done[device].store(true, std::memory_order_release); }
+};
+// cudaErrorInvalidDevice unless `device` is the calling thread's current device
+inline cudaError_t require_current_device(int device) {
+    int cur = -1;
+    cudaError_t e = cudaGetDevice(&cur);
+    if (e != cudaSuccess) return e;
+    return cur == device ? cudaSuccess : cudaErrorInvalidDevice;
+}
 
 // generic path (any head_dim <= 256, any cache capacity, prefill and decode, every rope and mask mode);
 // seqs_dev[i].tok_begin indexes q_stage, total_tokens = sum of qlen
@@ -277,6 +296,6 @@ int decode_max_ctas(int n_sm);
 constexpr int kDecodeMergeFan = 16;   // CTAs per group of the two-level merge
 constexpr int kDecodePartialFloats = 16 * 128 + 32;   // acc[16][128] | m[16] | l[16]
 
-extern unsigned long long g_launch_count;
+extern std::atomic<unsigned long long> g_launch_count;   // bumped from any host thread
 
 }  // namespace cglm

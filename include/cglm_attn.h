@@ -98,7 +98,7 @@ typedef struct cglm_attn_seq {
     long long q_tok_stride, q_head_stride;
     long long kv_tok_stride, kv_head_stride;
     int slot;                         /* which cache pair of the arena */
-    int qlen;                         /* tokens in this call; > 1 only with n_past == 0 (chatglm.cpp:689) */
+    int qlen;                         /* tokens in this call; masks apply only at n_past == 0 (chatglm.cpp:689) */
     int n_past;
     int n_ctx;                        /* prompt length; only CGLM_ROPE_CHATGLM derives ids from it (chatglm.cpp:1147-1151) */
     const int *position_ids;          /* optional [qlen] (or [2*qlen] for CGLM_ROPE_CHATGLM); NULL: derived from n_past, n_ctx */

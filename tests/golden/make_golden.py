@@ -184,7 +184,8 @@ def make_rope_hf():
 
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", default=os.environ.get("CHATGLM_CPP_REFERENCE"), required="CHATGLM_CPP_REFERENCE" not in os.environ,
+                    help="checkout of li-plus/chatglm.cpp (or set CHATGLM_CPP_REFERENCE)")
     ap.add_argument("--skip-hf", action="store_true")
     a = ap.parse_args()
     for n in FIXTURES:

@@ -13,7 +13,8 @@ def test_cpp_basic_attention_mirror():
     from oracle import attn_oracle
     build.build()
     attn_oracle.build()
-    exe = build.build_cpp_test()
+    from cpp.build_cpp import build_cpp_test
+    exe = build_cpp_test()
     r = subprocess.run([exe], capture_output=True, text=True, timeout=600)
     print(r.stdout, r.stderr)
     assert r.returncode == 0, r.stdout + r.stderr
@@ -26,4 +27,5 @@ def test_cpp_boundary_test_builds():
     from oracle import attn_oracle
     build.build()
     attn_oracle.build()
-    assert os.path.exists(build.build_cpp_test())
+    from cpp.build_cpp import build_cpp_test
+    assert os.path.exists(build_cpp_test())

@@ -527,6 +527,38 @@ def test_decode_step_graph_with_device_side_position_replays_for_new_tokens():
     arena.close()
 
 
+@pytest.mark.parametrize("H,G,D,M,V,rope,mask", [
+    (32, 2, 128, 512, 0, O.ROPE_CHATGLM2, O.MASK_CAUSAL),
+    (8, 8, 64, 200, 5, O.ROPE_CHATGLM, O.MASK_CHATGLM),
+])
+def test_chunked_prompt_second_chunk_attends_everything(H, G, D, M, V, rope, mask):
+    """qlen > 1 with n_past > 0 (a prompt fed in two chunks): the reference builds no mask then (chatglm.cpp:689),
+    so every row of the second chunk sees the whole cache including the chunk's later tokens.  Same here."""
+    A = _A()
+    desc = make_desc(H, G, D, M, V, rope, 10000.0, mask)
+    inter = rope == O.ROPE_CHATGLM
+    rng = np.random.default_rng(H + D)
+    arena, ws = A.KVArena(desc, 1), A.Workspace(desc, 1, 64)
+    attn = A.BasicAttention(arena, 0, ws, inter)
+    cfg = oracle_cfg(desc, "f32")
+    k, v = random_cache(rng, desc, V)
+    upload_cache(arena, 0, k, v)
+    n_past = 0
+    for qlen in (40, 23, 1):
+        qkv = rng.standard_normal((qlen, qkv_width(desc, inter))).astype(np.float32)
+        out, qr, kr = attn.forward(torch.from_numpy(qkv).cuda(), n_past, n_ctx=63, want_roped=True)
+        torch.cuda.synchronize()
+        want, oqr, okr = O.attn_forward(cfg, qkv, inter, k, v, n_past, n_ctx=63, want_roped=True)
+        assert_out_close(out.cpu().numpy(), want, f"qlen {qlen} n_past {n_past}")
+        assert ulp_distance(qr.cpu().numpy(), oqr).max() <= ROPE_MAX_ULP
+        assert ulp_distance(kr.cpu().numpy(), okr).max() <= ROPE_MAX_ULP
+        n_past += qlen
+    gk, gv = download_cache(arena, 0)
+    np.testing.assert_array_equal(gk, k)
+    np.testing.assert_array_equal(gv, v)
+    assert ws.status() == 0
+
+
 def test_argument_errors_return_codes():
     from chatglm_cpp_b200 import _lib
     A = _A()
@@ -540,9 +572,6 @@ def test_argument_errors_return_codes():
     assert e.value.status == _lib.ERR_INVALID_ARG
     with pytest.raises(_lib.CglmError):        # slot out of range
         A.forward_batch(arena, ws, [A.SeqCall(qkv=qkv, slot=1, n_past=0, out=out)])
-    with pytest.raises(_lib.CglmError):        # qlen > 1 with n_past > 0
-        A.forward_batch(arena, ws, [A.SeqCall(qkv=torch.zeros(2, qkv.shape[1], device="cuda"), slot=0, n_past=3,
-                                              out=torch.zeros(2, 4096, device="cuda"))])
     arr = (_lib.AttnSeq * 1)()
     A.fill_seq(arr[0], desc, A.SeqCall(qkv=qkv, slot=0, n_past=0, out=out), False)
     assert L.cglm_attn_forward(arena._h, arr, 1, ws.ptr, 1024, None) == _lib.ERR_WORKSPACE

@@ -40,12 +40,16 @@ def test_oracle_reproduces_reference_fixture(name, numerics):
     np.testing.assert_array_equal(vc, z["v_cache_final"].view(np.uint16))
 
 
-@pytest.mark.skipif(not os.path.isdir("/root/reference/tests/data"), reason="reference checkout absent")
+# where a checkout of li-plus/chatglm.cpp is mounted, if anywhere (CHATGLM_CPP_REFERENCE=/path/to/checkout)
+REFERENCE_DATA = os.path.join(os.environ.get("CHATGLM_CPP_REFERENCE", ""), "tests", "data")
+
+
+@pytest.mark.skipif(not os.path.isdir(REFERENCE_DATA), reason="CHATGLM_CPP_REFERENCE does not point at a reference checkout")
 @pytest.mark.parametrize("name", MODEL_FIXTURES)
 def test_committed_fixture_matches_reference_file(name):
     """The committed .npz carries exactly the golden bytes of the reference's .data file."""
     z, meta, w = load_fixture(name)
-    raw = np.fromfile(os.path.join("/root/reference/tests/data", name + ".data"), np.uint8)
+    raw = np.fromfile(os.path.join(REFERENCE_DATA, name + ".data"), np.uint8)
     tail = np.concatenate([np.concatenate([z[f"x{i}"].view(np.uint8), z[f"y{i}"].reshape(-1).view(np.uint8)])
                            for i in (1, 2, 3)])
     np.testing.assert_array_equal(raw[-tail.size:], tail)

@@ -66,6 +66,14 @@ def test_static_scratch_limits_are_refused():
         A.fill_seq(arr[i], desc, A.SeqCall(qkv=qkv, slot=0, n_past=1, out=out), False)
     assert L.cglm_attn_decode_static(arena._h, arr, n, 0, None) == _lib.ERR_WORKSPACE
     assert b"128 sequences" in L.cglm_last_error_string()
+    # a slot outside the arena or a position beyond the cache capacity is refused by return code: nothing is launched
+    before = L.cglm_launch_count()
+    one = (_lib.AttnSeq * 1)()
+    for slot, n_past in ((-1, 1), (1, 1), (0, 255), (0, 256), (0, 2**31 - 1)):
+        A.fill_seq(one[0], desc, A.SeqCall(qkv=qkv, slot=slot, n_past=n_past, out=out), False)
+        want = _lib.OK if (slot, n_past) == (0, 255) else _lib.ERR_INVALID_ARG
+        assert L.cglm_attn_decode_static(arena._h, one, 1, 1, None) == want, (slot, n_past)
+    assert L.cglm_launch_count() == before + 1
     # shapes outside the fused decode kernel are refused, not served by another path
     small = A.KVArena(make_desc(8, 2, 64, 256), 1)
     arr1 = (_lib.AttnSeq * 1)()
