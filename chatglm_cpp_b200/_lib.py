@@ -31,7 +31,25 @@ class AttnSeq(C.Structure):
                 ("n_past_dev", C.c_void_p)]
 
 
-# every symbol include/cglm_attn.h declares: name -> (restype, argtypes)
+class ModelConfig(C.Structure):
+    """cglm_model_config of include/cglm_model_file.h."""
+    _fields_ = [("model_type", C.c_int), ("version", C.c_int), ("dtype", C.c_int), ("vocab_size", C.c_int),
+                ("hidden_size", C.c_int), ("num_attention_heads", C.c_int), ("num_key_value_heads", C.c_int),
+                ("num_hidden_layers", C.c_int), ("intermediate_size", C.c_int), ("norm_eps", C.c_float),
+                ("num_virtual_tokens", C.c_int), ("rope_theta", C.c_float), ("max_length", C.c_int),
+                ("bos_token_id", C.c_int), ("eos_token_id", C.c_int), ("pad_token_id", C.c_int), ("sep_token_id", C.c_int),
+                ("hidden_act", C.c_int), ("use_qkv_bias", C.c_int), ("use_dense_bias", C.c_int),
+                ("interleaved_qkv", C.c_int), ("tie_word_embeddings", C.c_int), ("rope_type", C.c_int),
+                ("attn_mask_type", C.c_int)]
+
+
+class TensorInfo(C.Structure):
+    """cglm_tensor_info of include/cglm_model_file.h."""
+    _fields_ = [("name", C.c_char_p), ("ndim", C.c_int), ("ne", C.c_longlong * 4), ("dtype", C.c_int),
+                ("data", C.c_void_p), ("nbytes", C.c_size_t), ("offset", C.c_size_t)]
+
+
+# every symbol include/cglm_attn.h and include/cglm_model_file.h declare: name -> (restype, argtypes)
 SYMBOLS = {
     "cglm_kv_arena_create": (C.c_int, [C.POINTER(AttnDesc), C.c_int, C.POINTER(C.c_void_p)]),
     "cglm_kv_arena_destroy": (C.c_int, [C.c_void_p]),
@@ -63,6 +81,18 @@ SYMBOLS = {
     "cglm_status_string": (C.c_char_p, [C.c_int]),
     "cglm_last_error_string": (C.c_char_p, []),
     "cglm_launch_count": (C.c_ulonglong, []),
+    # include/cglm_model_file.h
+    "cglm_model_file_open": (C.c_int, [C.c_char_p, C.POINTER(C.c_void_p)]),
+    "cglm_model_file_open_memory": (C.c_int, [C.c_void_p, C.c_size_t, C.POINTER(C.c_void_p)]),
+    "cglm_model_file_close": (C.c_int, [C.c_void_p]),
+    "cglm_model_file_config": (C.c_int, [C.c_void_p, C.POINTER(ModelConfig)]),
+    "cglm_model_file_tokenizer": (C.c_int, [C.c_void_p, C.POINTER(C.c_void_p), C.POINTER(C.c_size_t)]),
+    "cglm_model_file_n_tensors": (C.c_int, [C.c_void_p]),
+    "cglm_model_file_tensor": (C.c_int, [C.c_void_p, C.c_int, C.POINTER(TensorInfo)]),
+    "cglm_model_file_find": (C.c_int, [C.c_void_p, C.c_char_p, C.POINTER(TensorInfo)]),
+    "cglm_model_file_attn_desc": (C.c_int, [C.c_void_p, C.c_int, C.POINTER(AttnDesc)]),
+    "cglm_model_file_attn_weight_name": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_char_p, C.c_size_t]),
+    "cglm_model_file_load_prefix": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_void_p]),
 }
 
 _lib = None

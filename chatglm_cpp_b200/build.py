@@ -37,7 +37,8 @@ def _sources():
 
 def _deps_mtime() -> float:
     hdrs = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".cuh", ".h"))]
-    hdrs.append(os.path.join(os.path.dirname(PKG), "include", "cglm_attn.h"))
+    inc = os.path.join(os.path.dirname(PKG), "include")
+    hdrs += [os.path.join(inc, f) for f in os.listdir(inc) if f.endswith(".h")]
     return max(os.path.getmtime(h) for h in hdrs)
 
 

@@ -15,6 +15,8 @@
 #pragma once
 
 #include <cstdint>
+#include <cstring>
+#include <map>
 #include <memory>
 #include <sstream>
 #include <stdexcept>
@@ -169,6 +171,138 @@ class BasicAttention {
     int slot_ = -1;
     int head_size_ = 0;
     int n_ctx_ = 0;
+};
+
+// ---- model file (chatglm.h:40-86, 107-203; chatglm.cpp:295-391, 1754-1848) ---------------------------------------
+// The container the reference's converter writes: header, config record, tokenizer blob, tensors.  Host code only.
+enum class ModelType { CHATGLM = 1, CHATGLM2 = 2, CHATGLM3 = 3, CHATGLM4 = 4 };
+enum class ActivationType { GELU, SILU };
+
+// The three config records as they sit in the file (all members 4 bytes wide; dtype is a ggml_type value).
+struct ConfigRecordV1 {
+    int dtype, vocab_size, hidden_size, num_attention_heads, num_hidden_layers, intermediate_size;
+    int max_length;                                        // sequence generation
+    int bos_token_id, eos_token_id, pad_token_id, sep_token_id;   // tokenizer
+};
+struct ConfigRecordV1GQA : public ConfigRecordV1 {
+    int num_key_value_heads;
+};
+struct ConfigRecordV2 {
+    int dtype, vocab_size, hidden_size, num_attention_heads, num_key_value_heads, num_hidden_layers, intermediate_size;
+    float norm_eps;
+    int num_virtual_tokens;
+    float rope_theta;
+    int max_length, eos_token_id, pad_token_id;
+};
+static_assert(sizeof(ConfigRecordV1) == 44 && sizeof(ConfigRecordV1GQA) == 48 && sizeof(ConfigRecordV2) == 52,
+              "config records are packed 4-byte fields");
+
+class ModelConfig {
+  public:
+    ModelConfig() = default;
+    ModelConfig(ModelType model_type, int dtype, int vocab_size, int hidden_size, int num_attention_heads,
+                int num_key_value_heads, int num_hidden_layers, int intermediate_size, float norm_eps, float rope_theta,
+                int num_virtual_tokens, int max_length, int bos_token_id, int eos_token_id, int pad_token_id,
+                int sep_token_id);
+    ModelConfig(ModelType model_type, const ConfigRecordV1 &rec, float norm_eps, float rope_theta, int num_virtual_tokens);
+    ModelConfig(ModelType model_type, const ConfigRecordV1GQA &rec, float norm_eps, float rope_theta, int num_virtual_tokens);
+    ModelConfig(ModelType model_type, const ConfigRecordV2 &rec);
+
+    // what every BasicAttention of this model is constructed with (chatglm.h:443-455)
+    cglm_attn_desc attn_desc() const;
+
+    ModelType model_type = ModelType::CHATGLM2;
+    int dtype = 0;
+    int vocab_size = 0, hidden_size = 0, num_attention_heads = 0, num_key_value_heads = 0, num_hidden_layers = 0;
+    int intermediate_size = 0;
+    float norm_eps = 0.f;
+    ActivationType hidden_act = ActivationType::SILU;
+    bool use_qkv_bias = false, use_dense_bias = false, interleaved_qkv = false, tie_word_embeddings = false;
+    RopeType rope_type = RopeType::CHATGLM2;
+    float rope_theta = 10000.f;
+    AttentionMaskType attn_mask_type = AttentionMaskType::CAUSAL;
+    int num_virtual_tokens = 0;
+    int max_length = 0;
+    int bos_token_id = -1, eos_token_id = -1, pad_token_id = -1, sep_token_id = -1;
+};
+
+// read-only mapping of a file
+class MappedFile {
+  public:
+    explicit MappedFile(const std::string &path);
+    ~MappedFile();
+    MappedFile(const MappedFile &) = delete;
+    MappedFile &operator=(const MappedFile &) = delete;
+
+    char *data = nullptr;
+    size_t size = 0;
+};
+
+// a tensor of the state dict: a view into the mapped file
+struct HostTensor {
+    int ndim = 0;
+    int64_t ne[4] = {1, 1, 1, 1};   // ne[0] innermost
+    int dtype = 0;                  // ggml_type
+    const void *data = nullptr;
+    size_t nbytes = 0;
+    size_t offset = 0;              // of data from the start of the file (a multiple of 16)
+};
+
+struct StateDict {
+    std::vector<std::string> names;           // file order
+    std::map<std::string, HostTensor> kv;
+};
+
+// elements and bytes per block of a ggml type the converter emits; false for any other type
+bool ggml_type_block(int dtype, int *block_elems, int *block_bytes);
+
+// cursor over the mapped bytes; every read is checked against the end of the file
+class ModelLoader {
+  public:
+    ModelLoader(const char *data, size_t size) : data(data), size(size), ptr(data) {}
+
+    int64_t tell() const { return ptr - data; }
+    void seek(int64_t offset, int whence);
+
+    template <typename T>
+    T read_basic() {
+        need(sizeof(T));
+        T obj;
+        std::memcpy(&obj, ptr, sizeof(T));
+        ptr += sizeof(T);
+        return obj;
+    }
+    std::string read_string(size_t length);
+    // name, ndim, shape, dtype, data at the next 16-byte boundary, until the end of the file
+    StateDict read_state_dict();
+
+    const char *const data;
+    const size_t size;
+    const char *ptr;
+
+  private:
+    void need(size_t n) const;
+};
+
+// What the Pipeline constructor learns from a file before it builds the model: config (max_length optionally
+// lowered, never raised), the tokenizer blob, the state dict.
+class ModelFile {
+  public:
+    explicit ModelFile(const std::string &path, int max_length = 0);
+    ModelFile(const void *data, size_t size, int max_length = 0);   // caller-owned memory
+
+    // "query_key_value.weight" (0), "query_key_value.bias" (1), "dense.weight" (2), "dense.bias" (3) of a layer
+    std::string attn_weight_name(int layer, int which) const;
+
+    ModelConfig config;
+    int version = 0;
+    const char *tokenizer_data = nullptr;
+    size_t tokenizer_size = 0;
+    StateDict state_dict;
+
+  private:
+    void parse(const char *data, size_t size, int max_length);
+    std::unique_ptr<MappedFile> mapped_;
 };
 
 }  // namespace chatglm

@@ -1,4 +1,5 @@
-"""CPU-only checks of the drop-in boundary: the built library loads and exports what include/cglm_attn.h declares."""
+"""CPU-only checks of the drop-in boundary: the built library loads and exports what the C headers under include/
+declare."""
 import ctypes as C
 import os
 import re
@@ -9,9 +10,12 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
 def _declared_symbols():
-    text = open(os.path.join(ROOT, "include", "cglm_attn.h")).read()
-    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
-    return sorted(set(re.findall(r"\b(cglm_[a-z0-9_]+)\s*\(", text)))
+    names = set()
+    for header in ("cglm_attn.h", "cglm_model_file.h"):
+        text = open(os.path.join(ROOT, "include", header)).read()
+        text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+        names |= set(re.findall(r"\b(cglm_[a-z0-9_]+)\s*\(", text))
+    return sorted(names)
 
 
 def test_header_symbols_are_exported_and_bound():
@@ -21,7 +25,7 @@ def test_header_symbols_are_exported_and_bound():
     declared = _declared_symbols()
     assert len(declared) >= 15
     for name in declared:
-        assert hasattr(handle, name), f"{name} declared in cglm_attn.h but not exported"
+        assert hasattr(handle, name), f"{name} declared under include/ but not exported"
         assert name in _lib.SYMBOLS, f"{name} has no ctypes binding"
     assert set(_lib.SYMBOLS) == set(declared)
 
