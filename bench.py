@@ -474,13 +474,16 @@ def run_ours(args, w):
     stage_qkv = [torch.empty(n, row, device="cuda") for _ in range(n_stage)]
     stage_out = [torch.empty(n, orow, device="cuda") for _ in range(n_stage)]
 
-    # one descriptor array per layer, built once: slot of (layer l, sequence i) is l*n + i
+    # one descriptor array per layer, built once: slot of (layer l, sequence i) is l*n + i.  Every layer call reads
+    # cache rows that no kernel of the step writes (a call appends at n_past of its own layer's slots only), which is
+    # what CGLM_SEQ_CACHE_SETTLED promises: a launch may stream cache tiles while the previous layer's launch drains.
+    seq_flags = 0 if args.no_settled else _lib.SEQ_CACHE_SETTLED
     seq_arrays = []
     for l in range(layers):
         arr = (_lib.AttnSeq * n)()
         for i in range(n):
             call = A.SeqCall(qkv=qkv_dev[l, i:i + 1], slot=l * n + i, n_past=int(n_past[i]), n_ctx=int(n_ctx[i]),
-                             out=out_dev[l, i:i + 1])
+                             out=out_dev[l, i:i + 1], flags=seq_flags)
             A.fill_seq(arr[i], desc, call, w["interleaved"])
         seq_arrays.append(arr)
     stream = torch.cuda.current_stream().cuda_stream
@@ -633,6 +636,8 @@ def main():
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--workload", choices=sorted(WORKLOADS), default="glm4_9b_batched_decode")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-settled", action="store_true",
+                    help="decode workloads: do not pass CGLM_SEQ_CACHE_SETTLED (every launch waits for the previous one to drain)")
     ap.add_argument("--no-graph", action="store_true", help="split-KV workload: issue every step eagerly")
     ap.add_argument("--exchange", choices=["p2p", "nccl"], default="p2p", help="split-KV workload: how partials travel")
     ap.add_argument("--step-graph", action="store_true",

@@ -13,7 +13,7 @@ LIB_PATH = os.path.join(_PKG, "lib", "libcglm_attn.so")
 OK, ERR_INVALID_ARG, ERR_CUDA, ERR_WORKSPACE, ERR_UNSUPPORTED, ERR_TIMEOUT, ERR_NO_DEVICE = 0, -1, -2, -3, -4, -5, -6
 ROPE_GPTJ, ROPE_NEOX, ROPE_CHATGLM, ROPE_CHATGLM2, ROPE_DISABLED = 0, 2, 4, 8, 10000
 MASK_CAUSAL, MASK_CHATGLM = 0, 1
-SEQ_NO_APPEND, SEQ_PARTIAL, SEQ_USE_KV_LOCAL, SEQ_N_PAST_DEVICE = 1, 2, 4, 8
+SEQ_NO_APPEND, SEQ_PARTIAL, SEQ_USE_KV_LOCAL, SEQ_N_PAST_DEVICE, SEQ_CACHE_SETTLED = 1, 2, 4, 8, 16
 
 
 class AttnDesc(C.Structure):

@@ -16,7 +16,7 @@ import torch
 
 from . import _lib
 from ._lib import (AttnDesc, AttnSeq, MASK_CAUSAL, MASK_CHATGLM, ROPE_CHATGLM, ROPE_CHATGLM2, ROPE_DISABLED,  # noqa: F401
-                   ROPE_GPTJ, ROPE_NEOX, SEQ_NO_APPEND, SEQ_N_PAST_DEVICE, SEQ_PARTIAL, SEQ_USE_KV_LOCAL, check)
+                   ROPE_GPTJ, ROPE_NEOX, SEQ_CACHE_SETTLED, SEQ_NO_APPEND, SEQ_N_PAST_DEVICE, SEQ_PARTIAL, SEQ_USE_KV_LOCAL, check)
 
 
 def _stream_ptr() -> int:

@@ -567,6 +567,15 @@ __device__ __noinline__ void deliver_part(const DeliverArgs *da, long long b, in
     merge(base, k_first, first_slot, k0, k1, final_dst, final_kind);
 }
 
+// Tiles [pos, pos_end) of the line into L2 only (no shared memory, no barrier): issued by the producer of a launch
+// whose caches are settled while the previous kernel of the stream is still draining.
+__device__ __forceinline__ void tma_prefetch_l2_3d(const CUtensorMap *map, int c0, int c1, int c2) {
+    asm volatile("cp.async.bulk.prefetch.tensor.3d.L2.global.tile [%0, {%1, %2, %3}];" ::"l"(map), "r"(c0), "r"(c1), "r"(c2) : "memory");
+}
+__device__ __forceinline__ void tma_prefetch_l2_2d(const CUtensorMap *map, int c0, int c1) {
+    asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(map), "r"(c0), "r"(c1) : "memory");
+}
+
 // kDynPast: sequences may carry CGLM_SEQ_N_PAST_DEVICE.  Their position is read from device memory once the previous
 // kernel of the stream has completed, the tile prefix is rebuilt from it, and nothing runs ahead of the dependency
 // wait (the spans are not known before).  A second instantiation, so that the common case pays nothing for it.
@@ -600,6 +609,10 @@ decode_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__
     // precedes the launch.  The prefix sums are searched by every role, so they are copied to shared memory once
     // (dependent reads of parameter space miss the small constant cache one after another).
     const int n_seq = tab.n_seq;
+    // Settled caches (every sequence carries CGLM_SEQ_CACHE_SETTLED): no kernel that can still be running writes the
+    // cache rows this launch reads, so the producer streams tiles without waiting for the previous kernel of the
+    // stream; tab.settled - 1 further tiles per CTA are pulled into L2 behind the ring.
+    const bool settled = !kDynPast && tab.settled != 0;
     if (kDynPast) {
         asm volatile("griddepcontrol.wait;" ::: "memory");
         asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
@@ -653,7 +666,7 @@ decode_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__
     // From here on this grid touches global memory, so it waits until the previous kernel has completed and its
     // writes are visible.  Stream order is preserved.
     // (The helper warp of a CTA with work waits inside its loop, after a dry pass over its first segment.)
-    if (!kDynPast && (warp != kHelperWarp || span_lo >= span_hi)) {
+    if (!kDynPast && (warp != kHelperWarp || span_lo >= span_hi) && !(settled && warp == kProducerWarp && span_lo < span_hi)) {
         asm volatile("griddepcontrol.wait;" ::: "memory");
         asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     }
@@ -666,16 +679,32 @@ decode_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__
         if (lane == 0) {
             long long pos = span_lo;
             unsigned int n = 0;
+            bool ahead = settled;   // this thread has not waited for the previous kernel yet
             while (pos < span_hi && !sm.abort_flag) {
                 const ItemPos ip = locate(sm.prefix, n_seq, G, pos);
                 const int row = sm.slot[ip.seq] * G + ip.g;
                 const long long seg_end = min(span_hi, ip.item_begin + ip.n_tiles);
                 for (int t = ip.tile; pos < seg_end; ++t, ++pos, ++n) {
                     const int st = n % kStages;
-                    if (n == 1) {
+                    if (n == 1 && !settled) {
                         // The first tile goes out at once; the rest of the ring's initial burst waits until the helper
                         // warp has issued the first segment's few small loads, so that they do not queue behind it.
                         mbar_wait_bounded(&sm.hstart, 0, &sm.abort_flag);
+                    }
+                    if (ahead && n == kStages) {
+                        // The ring is full and nothing can be consumed before the previous kernel has completed (the
+                        // consumers need q): pull the next tiles of the span into L2 meanwhile, then wait like every
+                        // other thread, so that the bounded waits below only count time this grid could make progress.
+                        const long long pf_end = min(span_hi, pos + (tab.settled - 1));
+                        for (long long pp = pos; pp < pf_end; ++pp) {
+                            const ItemPos pi = locate(sm.prefix, n_seq, G, pp);
+                            const int prow = sm.slot[pi.seq] * G + pi.g;
+                            tma_prefetch_l2_3d(&k_map, 0, pi.tile * kTile, prow);
+                            tma_prefetch_l2_3d(&k_map, 64, pi.tile * kTile, prow);
+                            tma_prefetch_l2_2d(&v_map, pi.tile * kTile, prow * kD);
+                        }
+                        asm volatile("griddepcontrol.wait;" ::: "memory");
+                        ahead = false;
                     }
                     if (!mbar_wait_bounded(&sm.empty[st], ((n / kStages) & 1u) ^ 1u, &sm.abort_flag)) break;
                     uint8_t *dst = sm.stage[st];

@@ -4,6 +4,7 @@
 #include <cmath>
 #include <cstddef>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 #include <new>
@@ -95,6 +96,17 @@ AttnShape make_shape(const cglm_attn_desc &d) {
 }
 
 size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+
+// Tiles per CTA that a settled decode launch pulls into L2 behind its shared-memory ring while the previous kernel
+// drains.  CGLM_DECODE_L2_AHEAD overrides the default (tuning knob, read once).
+int decode_l2_ahead() {
+    static const int v = [] {
+        const char *e = std::getenv("CGLM_DECODE_L2_AHEAD");
+        const int x = e ? std::atoi(e) : 4;
+        return x < 0 ? 0 : (x > 64 ? 64 : x);
+    }();
+    return v;
+}
 
 // ---- workspace layout (fixed regions first, so that self-resetting counters stay where they are) ------
 struct WsLayout {
@@ -591,7 +603,7 @@ int cglm_attn_forward(cglm_kv_arena *a, const cglm_attn_seq *seqs, int n_seq, vo
         if (is_fast[i]) {
             ++n_fast;
             decode_tiles += static_cast<long long>((L + kDecodeTile - 1) / kDecodeTile) * d.n_kv_head;
-        } else if (prefill_ok && s.qlen >= kPrefillMinTokens && s.n_past == 0 && s.flags == 0) {
+        } else if (prefill_ok && s.qlen >= kPrefillMinTokens && s.n_past == 0 && (s.flags & ~CGLM_SEQ_CACHE_SETTLED) == 0) {
             is_fast[i] = 2;
             ++n_prefill;
             const size_t need = prefill_q_half_bytes(d.n_head, s.qlen);
@@ -640,23 +652,25 @@ int cglm_attn_forward(cglm_kv_arena *a, const cglm_attn_seq *seqs, int n_seq, vo
     if (n_fast > 0) {
         static thread_local DecodeTable tab;
         int filled = 0;
-        bool dyn = false;
+        bool dyn = false, settled = true;
         tab.prefix[0] = 0;
         for (int i = 0; i <= n_seq; ++i) {
             if (i < n_seq && is_fast[i] == 1) {
                 SeqDev &o = tab.seqs[filled];
                 to_dev(seqs[i], o);
                 dyn = dyn || (o.flags & CGLM_SEQ_N_PAST_DEVICE);
+                settled = settled && (o.flags & CGLM_SEQ_CACHE_SETTLED);
                 const int L = o.kv_before + ((o.flags & CGLM_SEQ_NO_APPEND) ? 0 : 1);
                 tab.prefix[filled + 1] = tab.prefix[filled] + (L + kDecodeTile - 1) / kDecodeTile;
                 ++filled;
             }
             if (filled == kDecodeMaxSeqPerLaunch || (i == n_seq && filled > 0)) {
                 tab.n_seq = filled;
-                tab.pad = 0;
+                tab.settled = settled && !dyn ? 1 + decode_l2_ahead() : 0;
                 CGLM_CUDA(launch_decode(cx, tab, dyn));
                 filled = 0;
                 dyn = false;
+                settled = true;
             }
         }
     }
@@ -731,7 +745,7 @@ int cglm_attn_forward_host(cglm_kv_arena *a, const cglm_attn_seq *seqs, int n_se
             s.out = out_base + n_tok * orow;
             s.position_ids = nullptr; s.q_roped = nullptr; s.k_roped = nullptr; s.partial = nullptr;
             s.n_past_dev = nullptr;
-            s.flags = 0; s.kv_local = 0;
+            s.flags = seqs[i].flags & CGLM_SEQ_CACHE_SETTLED; s.kv_local = 0;
             n_tok += seqs[i].qlen;
         }
     };

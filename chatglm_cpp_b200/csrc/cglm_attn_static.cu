@@ -96,7 +96,7 @@ extern "C" int cglm_attn_decode_static(cglm_kv_arena *arena, const cglm_attn_seq
     const int n_slots = cglm_kv_arena_n_slots(arena);
     static thread_local DecodeTable tab;
     tab.n_seq = n_seq;
-    tab.pad = 0;
+    tab.settled = 0;
     tab.prefix[0] = 0;
     for (int i = 0; i < n_seq; ++i) {
         const cglm_attn_seq &s = seqs[i];

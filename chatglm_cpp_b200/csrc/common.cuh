@@ -274,7 +274,7 @@ constexpr int kDecodeMaxSeqPerLaunch = 128;
 // that no upload or load stands between the launch and its first memory request.
 struct DecodeTable {
     int n_seq;
-    int pad;
+    int settled;   // 0, or 1 + tiles per CTA to pull into L2 ahead of the ring: every sequence carries CGLM_SEQ_CACHE_SETTLED
     int prefix[kDecodeMaxSeqPerLaunch + 2];   // prefix[i] = 64-token tiles of sequences [0, i), per kv head
     SeqDev seqs[kDecodeMaxSeqPerLaunch];
 };

@@ -123,7 +123,17 @@ enum {
      * n_past is only an upper bound (capacity check, launch sizing).  qlen 1, fused-decode shapes only
      * (CGLM_ERR_UNSUPPORTED otherwise); a device value outside [0, capacity) is clamped and reported through the
      * workspace status word as CGLM_ERR_INVALID_ARG.  cglm_seq_advance bumps the words between steps. */
-    CGLM_SEQ_N_PAST_DEVICE = 8
+    CGLM_SEQ_N_PAST_DEVICE = 8,
+    /* A promise by the caller: no kernel that precedes this call on its stream and can still be running when this
+     * call's kernel starts writes cache positions [0, n_virtual + n_past) of this sequence's slot.  The library launches its kernels as programmatic
+     * dependents, so "can still be running" means the kernel enqueued immediately before (and, behind a kernel that
+     * releases its dependents before it has waited for its own predecessor, that predecessor too).  The promise holds
+     * for the layer calls of a decode step: what precedes is the qkv projection or another layer's attention.  It does
+     * not hold for a call that directly follows a prefill, a cglm_kv_load_prefix or any other kernel that writes the
+     * same slot.  When every one-token sequence of a call carries the flag, the fused decode kernel starts streaming
+     * cache tiles (and pulls a few more into L2) while the previous kernel is still draining; q, k, v and the appended
+     * row are still read and written only after that kernel has completed.  Without the flag nothing is read early. */
+    CGLM_SEQ_CACHE_SETTLED = 16
 };
 
 /* Scratch the kernels need for n_seq sequences per call with at most max_qlen tokens each. */
@@ -150,7 +160,7 @@ int cglm_seq_advance(int *n_past_dev, int n, int delta, void *cuda_stream);
  *   qkv_host  f32 [n_tokens][(H+2G)*D], the rows of all sequences back to back (sequence i owns rows
  *             [tok_begin_i, tok_begin_i + qlen_i)); out_host f32 [n_tokens][H*D].
  * interleaved_qkv selects the v1 layout.  dev_qkv / dev_out are device staging buffers of at least those sizes.
- * Only n_past / qlen / n_ctx / slot of each descriptor are read.
+ * Only n_past / qlen / n_ctx / slot (and CGLM_SEQ_CACHE_SETTLED of flags) of each descriptor are read.
  * The two copies run on streams of the arena's own and the kernels on cuda_stream, chained by events, so that the
  * upload of one call and the download of another overlap the kernels between them (one call per layer: give
  * neighbouring calls different staging buffers, two or three pairs are enough; reuse of a staging buffer is ordered

@@ -182,6 +182,45 @@ def make_rope_hf():
     print("rope_d128_hf.npz written")
 
 
+def make_rope_modes_hf():
+    """Full-head GPTJ and NEOX rotary and the ChatGLM-6B 2-D rotary at head_dim 128, through the rotary helpers of
+    Hugging Face transformers (GPT-J: rotate_every_two; LLaMA / GPT-NeoX: rotate_half) with float64 angles.  The
+    ladder inv_freq = theta^(-2i/n_dims) is the one both HF models build.  The 2-D form follows ChatGLM-6B's published
+    formulation: the head is cut in two halves of D/2, each half is rotated NeoX-style (pairs (i, i + D/4)) over
+    n_dims = D/2 with base 10000, the first by the position id and the second by the block position id."""
+    import torch
+    from transformers.models.gptj.modeling_gptj import apply_rotary_pos_emb as gptj_apply
+    from transformers.models.llama.modeling_llama import apply_rotary_pos_emb as neox_apply
+
+    rng = np.random.default_rng(20241125)
+    D = 128
+    pos = np.array([0, 1, 2, 7, 513, 2047, 8191, 40000], np.int64)
+    blk = np.array([0, 0, 3, 1, 77, 1, 300, 2], np.int64)
+    x = rng.standard_normal((len(pos), 3, D)).astype(np.float32)      # [s, heads, d]
+    tx = torch.from_numpy(x).double()[None]                            # [1, s, h, d]
+    out = {"pos": pos.astype(np.int32), "block": blk.astype(np.int32), "x": x}
+    for theta in (10000.0, 50000.0):
+        inv = 1.0 / (theta ** (torch.arange(0, D, 2, dtype=torch.float64) / D))          # [D/2]
+        ang = torch.from_numpy(pos).double()[:, None] * inv[None, :]                      # [s, D/2]
+        y_gptj = gptj_apply(tx, ang.sin()[None], ang.cos()[None])                         # pairs (2i, 2i+1)
+        emb = torch.cat((ang, ang), dim=-1)[None]
+        y_neox, _ = neox_apply(tx, tx, emb.cos(), emb.sin(), unsqueeze_dim=2)             # pairs (i, i + D/2)
+        tag = f"t{int(theta)}"
+        out[f"gptj_{tag}"] = y_gptj[0].numpy()
+        out[f"neox_{tag}"] = y_neox[0].numpy()
+    half = D // 2
+    inv = 1.0 / (10000.0 ** (torch.arange(0, half, 2, dtype=torch.float64) / half))      # [D/4]
+    halves = []
+    for ids, sl in ((pos, slice(0, half)), (blk, slice(half, D))):
+        ang = torch.from_numpy(ids).double()[:, None] * inv[None, :]
+        emb = torch.cat((ang, ang), dim=-1)[None]
+        y, _ = neox_apply(tx[..., sl], tx[..., sl], emb.cos(), emb.sin(), unsqueeze_dim=2)
+        halves.append(y)
+    out["glm2d"] = torch.cat(halves, dim=-1)[0].numpy()
+    np.savez_compressed(os.path.join(HERE, "rope_modes_d128_hf.npz"), **out)
+    print("rope_modes_d128_hf.npz written")
+
+
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", default=os.environ.get("CHATGLM_CPP_REFERENCE"), required="CHATGLM_CPP_REFERENCE" not in os.environ,
@@ -192,3 +231,4 @@ if __name__ == "__main__":
         convert(a.reference, n)
     if not a.skip_hf:
         make_rope_hf()
+        make_rope_modes_hf()

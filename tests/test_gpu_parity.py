@@ -436,6 +436,51 @@ def test_decode_with_4_byte_aligned_activation_takes_the_generic_path_and_agrees
     arena.close()
 
 
+def test_decode_with_settled_caches_streams_early_and_gives_the_same_bits():
+    """CGLM_SEQ_CACHE_SETTLED lets a launch read cache tiles while the previous launch of the stream drains.  Eight
+    layer calls back to back, each on its own slots, with and without the flag: same output bits, same caches, and
+    parity with the oracle for the flagged run."""
+    from chatglm_cpp_b200 import _lib
+    A = _A()
+    desc = make_desc(32, 2, 128, 4096)
+    rng = np.random.default_rng(515)
+    n_layer, n_past = 8, [4000, 130, 2500, 64, 3333, 1, 700, 2047, 1999, 3071]
+    n = len(n_past)
+    arena, ws = A.KVArena(desc, 2 * n_layer * n), A.Workspace(desc, n, 1)
+    host = []
+    for s in range(n_layer * n):
+        k, v = random_cache(rng, desc, n_past[s % n])
+        upload_cache(arena, s, k, v)
+        upload_cache(arena, n_layer * n + s, k, v)
+        host.append((k, v))
+    width = qkv_width(desc, False)
+    qkv_h = rng.standard_normal((n_layer, n, width)).astype(np.float32)
+    qkv = torch.from_numpy(qkv_h).cuda()
+    outs = [torch.zeros(n_layer, n, 4096, device="cuda") for _ in range(2)]
+    torch.cuda.synchronize()
+    for run, flags in enumerate((0, A.SEQ_CACHE_SETTLED)):
+        for layer in range(n_layer):
+            A.forward_batch(arena, ws, [A.SeqCall(qkv=qkv[layer, i:i + 1], slot=run * n_layer * n + layer * n + i,
+                                                  n_past=n_past[i], out=outs[run][layer, i:i + 1], flags=flags)
+                                        for i in range(n)])
+        torch.cuda.synchronize()
+        assert ws.status() == 0
+    assert torch.equal(outs[0], outs[1])
+    half = n_layer * n
+    assert torch.equal(arena.k_all()[:half], arena.k_all()[half:])
+    assert torch.equal(arena.v_all()[:half], arena.v_all()[half:])
+    cfg = oracle_cfg(desc, "f32")
+    for layer in (0, n_layer - 1):
+        for i in range(n):
+            k, v = host[layer * n + i]
+            want = O.attn_forward(cfg, qkv_h[layer, i:i + 1], False, k, v, n_past[i])
+            assert_out_close(outs[1][layer, i:i + 1].cpu().numpy(), want, f"layer {layer} seq {i}")
+            gk, gv = download_cache(arena, half + layer * n + i)
+            np.testing.assert_array_equal(gk, k)
+            np.testing.assert_array_equal(gv, v)
+    arena.close()
+
+
 def test_decode_batch_with_device_side_positions_mixed_lengths():
     """The instantiation of the decode kernel that reads n_past from device words, on a batch whose spans cross item
     boundaries and whose grid (sized from the host's upper bounds) is larger than the real number of tiles needs."""

@@ -87,6 +87,31 @@ def test_oracle_rope_d128_matches_hf_glm(tag):
         assert (err <= 2e-6 + 2e-7 * pos).all(), err
 
 
+@pytest.mark.parametrize("mode", ["gptj_t10000", "gptj_t50000", "neox_t10000", "neox_t50000", "glm2d"])
+def test_oracle_rope_modes_d128_match_hf_helpers(mode):
+    """The full-head GPTJ / NEOX branches (apply_rotary_emb_basic, chatglm.cpp:523-537) and the ChatGLM-6B 2-D rotary
+    (apply_rotary_emb_glm, chatglm.cpp:539-574) at head_dim 128 against vectors made with the rotary helpers of Hugging
+    Face transformers (tests/golden/make_golden.py:make_rope_modes_hf): pair pattern, ladder, which half takes which id."""
+    z = np.load(os.path.join(os.path.dirname(__file__), "golden", "rope_modes_d128_hf.npz"))
+    x, pos, blk = z["x"], z["pos"], z["block"]
+    if mode == "glm2d":
+        cfg = O.make_cfg(3, 3, 128, 8, 0, O.ROPE_CHATGLM, 10000.0, O.MASK_CHATGLM)
+        ids = np.concatenate([pos, blk]).astype(np.int32)      # [2S]: position ids, then block position ids
+        scale = np.maximum(pos, blk)
+    else:
+        kind, tag = mode.split("_t")
+        cfg = O.make_cfg(3, 3, 128, 8, 0, O.ROPE_GPTJ if kind == "gptj" else O.ROPE_NEOX, float(tag))
+        ids, scale = pos.astype(np.int32), pos
+    got = O.apply_rotary_emb(cfg, x, ids)
+    want = z[mode]
+    # f32 iterated-ladder angles (theta_scale rounded to f32, one more rounding per ladder step: a relative angle
+    # error of about i * 6e-8 at step i) against float64 angles: the gap grows with the position and nothing else
+    err = np.abs(got - want).max(axis=(1, 2))
+    assert (err <= 2e-6 + 5e-7 * scale).all(), err
+    # and a wrong pair pattern or ladder would be off by O(1)
+    assert np.abs(want - x).max() > 0.5
+
+
 def test_rope_modes_small_cases():
     """The four rope modes on hand-checkable inputs (chatglm.cpp:523-618)."""
     x = np.arange(1, 9, dtype=np.float32).reshape(1, 1, 8)
