@@ -14,6 +14,8 @@ OK, ERR_INVALID_ARG, ERR_CUDA, ERR_WORKSPACE, ERR_UNSUPPORTED, ERR_TIMEOUT, ERR_
 ROPE_GPTJ, ROPE_NEOX, ROPE_CHATGLM, ROPE_CHATGLM2, ROPE_DISABLED = 0, 2, 4, 8, 10000
 MASK_CAUSAL, MASK_CHATGLM = 0, 1
 SEQ_NO_APPEND, SEQ_PARTIAL, SEQ_USE_KV_LOCAL, SEQ_N_PAST_DEVICE, SEQ_CACHE_SETTLED = 1, 2, 4, 8, 16
+SEQ_QKV_F16, SEQ_OUT_F16 = 32, 64
+HOST_INTERLEAVED_QKV, HOST_F16 = 1, 2
 
 
 class AttnDesc(C.Structure):
@@ -52,6 +54,8 @@ class TensorInfo(C.Structure):
 # every symbol include/cglm_attn.h and include/cglm_model_file.h declare: name -> (restype, argtypes)
 SYMBOLS = {
     "cglm_kv_arena_create": (C.c_int, [C.POINTER(AttnDesc), C.c_int, C.POINTER(C.c_void_p)]),
+    "cglm_kv_arena_adopt": (C.c_int, [C.POINTER(AttnDesc), C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.POINTER(C.c_void_p)]),
+    "cglm_kv_angle_table_bytes": (C.c_size_t, [C.POINTER(AttnDesc)]),
     "cglm_kv_arena_destroy": (C.c_int, [C.c_void_p]),
     "cglm_kv_arena_k_cache": (C.c_void_p, [C.c_void_p, C.c_int]),
     "cglm_kv_arena_v_cache": (C.c_void_p, [C.c_void_p, C.c_int]),
@@ -74,9 +78,8 @@ SYMBOLS = {
     "cglm_xchg_free": (C.c_int, [C.c_void_p]),
     "cglm_xchg_export": (C.c_int, [C.c_void_p, C.c_char_p]),
     "cglm_xchg_import": (C.c_int, [C.c_char_p, C.c_int, C.POINTER(C.c_void_p)]),
-    "cglm_attn_splitkv_push": (C.c_int, [C.c_void_p, C.POINTER(C.c_void_p), C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p]),
-    "cglm_attn_splitkv_combine_arrived": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_uint,
-                                                    C.c_void_p]),
+    "cglm_attn_splitkv_step": (C.c_int, [C.c_void_p, C.POINTER(AttnSeq), C.POINTER(C.c_void_p), C.c_int, C.c_int, C.c_void_p,
+                                         C.c_int, C.c_uint, C.c_void_p, C.c_size_t, C.c_void_p]),
     "cglm_kv_load_prefix": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_void_p]),
     "cglm_status_string": (C.c_char_p, [C.c_int]),
     "cglm_last_error_string": (C.c_char_p, []),

@@ -33,13 +33,21 @@ class _DevView:
 class KVArena:
     """All k_cache / v_cache pairs of a model (layers x sequences) in one device allocation."""
 
-    def __init__(self, desc: AttnDesc, n_slots: int):
+    def __init__(self, desc: AttnDesc, n_slots: int, adopt=None):
+        """adopt: (k_all, v_all[, angle_table]) caller-owned device tensors in the arena's layout (cglm_kv_arena_adopt);
+        the arena then allocates nothing and the tensors must outlive it."""
         if not torch.cuda.is_available():
             raise RuntimeError("KVArena needs a CUDA device: this package has no CPU fallback")
         self.desc = desc
         self.n_slots = n_slots
         handle = C.c_void_p()
-        check(_lib.lib().cglm_kv_arena_create(C.byref(desc), n_slots, C.byref(handle)), "cglm_kv_arena_create")
+        if adopt is None:
+            check(_lib.lib().cglm_kv_arena_create(C.byref(desc), n_slots, C.byref(handle)), "cglm_kv_arena_create")
+        else:
+            self._adopted = adopt
+            table = adopt[2].data_ptr() if len(adopt) > 2 and adopt[2] is not None else None
+            check(_lib.lib().cglm_kv_arena_adopt(C.byref(desc), n_slots, adopt[0].data_ptr(), adopt[1].data_ptr(), table,
+                                                 C.byref(handle)), "cglm_kv_arena_adopt")
         self._h = handle
 
     def close(self):
@@ -103,11 +111,11 @@ class Workspace:
 @dataclass
 class SeqCall:
     """One sequence of a batched forward: a fused qkv activation on the device plus its cache slot."""
-    qkv: torch.Tensor                 # f32 [qlen, (H+2G)*D] (blocked) or [qlen, 3*H*D] (interleaved)
+    qkv: torch.Tensor                 # f32 or f16 [qlen, (H+2G)*D] (blocked) or [qlen, 3*H*D] (interleaved)
     slot: int
     n_past: int
     n_ctx: int = 0
-    out: Optional[torch.Tensor] = None        # f32 [qlen, H*D]
+    out: Optional[torch.Tensor] = None        # f32 or f16 [qlen, H*D]
     position_ids: Optional[torch.Tensor] = None
     q_roped: Optional[torch.Tensor] = None
     k_roped: Optional[torch.Tensor] = None
@@ -120,8 +128,8 @@ class SeqCall:
 def fill_seq(dst: AttnSeq, desc: AttnDesc, call: SeqCall, interleaved: bool) -> None:
     H, G, D = desc.n_head, desc.n_kv_head, desc.head_dim
     qkv = call.qkv
-    assert qkv.is_cuda and qkv.dtype == torch.float32 and qkv.is_contiguous() and qkv.dim() == 2
-    base, esz = qkv.data_ptr(), 4
+    assert qkv.is_cuda and qkv.dtype in (torch.float32, torch.float16) and qkv.is_contiguous() and qkv.dim() == 2
+    base, esz = qkv.data_ptr(), qkv.element_size()
     row = qkv.shape[1]
     if interleaved:   # chatglm.cpp:638-644
         assert row == 3 * H * D and H == G
@@ -139,6 +147,10 @@ def fill_seq(dst: AttnSeq, desc: AttnDesc, call: SeqCall, interleaved: bool) -> 
     dst.k_roped = call.k_roped.data_ptr() if call.k_roped is not None else None
     dst.partial = call.partial.data_ptr() if call.partial is not None else None
     dst.kv_local, dst.flags = call.kv_local, call.flags
+    if qkv.dtype == torch.float16:
+        dst.flags |= _lib.SEQ_QKV_F16
+    if call.out is not None and call.out.dtype == torch.float16:
+        dst.flags |= _lib.SEQ_OUT_F16
     dst.n_past_dev = call.n_past_dev.data_ptr() if call.n_past_dev is not None else None
 
 
@@ -173,10 +185,10 @@ class BasicAttention:
         self.v_cache = arena.v_cache(slot)   # [#kvh, d, s]
 
     def forward(self, qkv: torch.Tensor, n_past: int, n_ctx: int = 0, position_ids: Optional[torch.Tensor] = None,
-                want_roped: bool = False):
+                want_roped: bool = False, out_dtype: torch.dtype = torch.float32):
         d = self.arena.desc
         qlen = qkv.shape[0]
-        out = torch.empty(qlen, d.n_head * d.head_dim, dtype=torch.float32, device="cuda")
+        out = torch.empty(qlen, d.n_head * d.head_dim, dtype=out_dtype, device="cuda")
         qr = kr = None
         if want_roped:
             qr = torch.empty(qlen, d.n_head, d.head_dim, dtype=torch.float32, device="cuda")
@@ -188,10 +200,9 @@ class BasicAttention:
 
 
 class SplitKVExchange:
-    """One rank's side of the peer-memory exchange of split-KV partials (cglm_attn_splitkv_push /
-    cglm_attn_splitkv_combine_arrived).  ``buffers`` holds every rank's exchange buffer as a tensor valid on this
-    device (entry ``rank`` is the local one); how the peers' buffers were mapped (CUDA IPC between processes, plain
-    tensors inside one process) is the caller's business."""
+    """One rank's side of the fused split-KV step (cglm_attn_splitkv_step).  ``buffers`` holds every rank's exchange
+    buffer as a tensor valid on this device (entry ``rank`` is the local one); how the peers' buffers were mapped
+    (CUDA IPC between processes, plain tensors inside one process) is the caller's business."""
 
     def __init__(self, buffers: Sequence, rank: int, n_head: int, head_dim: int):
         """buffers: per rank a tensor on this device, or a raw device pointer (int) valid on this device."""
@@ -232,15 +243,12 @@ class SplitKVExchange:
     def new_buffer(n_rank: int, n_head: int, head_dim: int) -> torch.Tensor:
         return torch.zeros((SplitKVExchange.bytes(n_rank, n_head, head_dim) + 3) // 4, dtype=torch.int32, device="cuda")
 
-    def push(self, partial: torch.Tensor) -> None:
-        assert partial.is_cuda and partial.dtype == torch.float32 and partial.is_contiguous()
-        check(_lib.lib().cglm_attn_splitkv_push(partial.data_ptr(), self._ptrs, self.n_rank, self.rank, self.n_head,
-                                                self.head_dim, _stream_ptr()), "cglm_attn_splitkv_push")
-
-    def combine_arrived(self, out: torch.Tensor, ws: "Workspace", timeout_us: int = 0) -> None:
-        check(_lib.lib().cglm_attn_splitkv_combine_arrived(self._local, self.n_rank, self.n_head,
-                                                           self.head_dim, out.data_ptr(), ws.ptr, timeout_us, _stream_ptr()),
-              "cglm_attn_splitkv_combine_arrived")
+    def step(self, arena: "KVArena", ws: "Workspace", seq_array, out: Optional[torch.Tensor], combine: bool = True,
+             timeout_us: int = 0) -> None:
+        """One fused launch: attention over this rank's slice, rows published to every rank, merged into ``out``."""
+        check(_lib.lib().cglm_attn_splitkv_step(arena._h, seq_array, self._ptrs, self.n_rank, self.rank,
+                                                out.data_ptr() if out is not None else None, int(combine), timeout_us,
+                                                ws.ptr, ws.bytes, _stream_ptr()), "cglm_attn_splitkv_step")
 
 
 def splitkv_combine(partials: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:

@@ -86,11 +86,22 @@ struct MergeCtx {
 // What a team hands to deliver_part, parked in shared memory: the function is kept out of line (one copy of the
 // merge code for its three callers), and a stack frame in local memory would put loads from a saturated memory
 // system on the critical path of the launch's last microseconds.
+// Exchange state of a fused split-KV step, in shared memory: the kernel parameter plus what the helper warp reads
+// after the dependency wait.
+struct XchgShared {
+    XchgDev xd;
+    WsHeader *hdr;
+    unsigned int epoch;    // this step's number = the local buffer's counter + 1
+    int slot_words;        // n_head * (head_dim + 2)
+    int H, G, R;
+};
+
 struct DeliverArgs {
     ItemPos ip;
     ItemOut io;
     MergeCtx mc;
     int G, R;
+    const XchgShared *xs;   // non-null: the item's (acc, m, l) rows go to every rank's exchange buffer
 };
 
 struct __align__(1024) DecodeSmem {
@@ -102,6 +113,7 @@ struct __align__(1024) DecodeSmem {
     SeqDev sq;                                     // the helper warp's copy of the descriptor it is preparing
     int npast[kDecodeMaxSeqPerLaunch];             // kDynPast: every sequence's n_past as read from the device
     DeliverArgs dargs[kConsumerWarps + 1];         // per calling warp: arguments of deliver_part
+    XchgShared xs;                                 // exchange instantiation only
     uint64_t full[kStages];
     uint64_t empty[kStages];
     uint64_t qfull[2];
@@ -293,6 +305,24 @@ __device__ __forceinline__ void load_seq_desc(SeqDev &dst, const SeqDev &src, in
 //   CHATGLM:  each 64-dim half rotates as pairs (i, i+32) by ladder angle i, the first half by the position id and
 //             the second by the block position id: the partner of lane l sits in lane l ^ 8.
 __device__ __forceinline__ float4 ldg4(const float *p) { return __ldg(reinterpret_cast<const float4 *>(p)); }
+// four consecutive activations starting at element index e of a row that is f32, or f16 with CGLM_SEQ_QKV_F16
+__device__ __forceinline__ float4 ld_act4(const float *row, long long e, bool f16) {
+    if (f16) {
+        const uint2 u = __ldg(reinterpret_cast<const uint2 *>(reinterpret_cast<const __half *>(row) + e));
+        const float2 a = __half22float2(*reinterpret_cast<const __half2 *>(&u.x));
+        const float2 b = __half22float2(*reinterpret_cast<const __half2 *>(&u.y));
+        return make_float4(a.x, a.y, b.x, b.y);
+    }
+    return ldg4(row + e);
+}
+// four consecutive outputs at element index e of an f32 row, or of an f16 row with CGLM_SEQ_OUT_F16
+__device__ __forceinline__ void st_out4(float *row, long long e, bool f16, float a, float b, float c, float d) {
+    if (f16) {
+        *reinterpret_cast<uint2 *>(reinterpret_cast<__half *>(row) + e) = make_uint2(pack_half2(a, b), pack_half2(c, d));
+    } else {
+        *reinterpret_cast<float4 *>(row + e) = make_float4(a, b, c, d);
+    }
+}
 __device__ __forceinline__ uint2 pack_half4(float a, float b, float c, float d) {
     return make_uint2(pack_half2(a, b), pack_half2(c, d));
 }
@@ -316,16 +346,17 @@ __device__ __forceinline__ void prepare_segment(QBuf &qb, const AttnShape &sh, c
     const bool k_needed = appender || (has_last_tile && sq.k_roped);
     const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
     float4 x[kRows + 1], xv = zero4;   // x[kRows]: the new k row
+    const bool in_f16 = (sq.flags & CGLM_SEQ_QKV_F16) != 0;   // element strides either way
     {
-        const float *src = sq.q + static_cast<long long>(g) * R * sq.q_head_stride + 4 * lane;
+        long long e = static_cast<long long>(g) * R * sq.q_head_stride + 4 * lane;
 #pragma unroll
         for (int r = 0; r < kRows; ++r) {
-            x[r] = (r < R && !dry) ? ldg4(src) : zero4;
-            src += sq.q_head_stride;
+            x[r] = (r < R && !dry) ? ld_act4(sq.q, e, in_f16) : zero4;
+            e += sq.q_head_stride;
         }
     }
-    x[kRows] = (k_needed && !dry) ? ldg4(sq.k + g * sq.kv_head_stride + 4 * lane) : zero4;
-    if (appender && !dry) xv = ldg4(sq.v + g * sq.kv_head_stride + 4 * lane);
+    x[kRows] = (k_needed && !dry) ? ld_act4(sq.k, g * sq.kv_head_stride + 4 * lane, in_f16) : zero4;
+    if (appender && !dry) xv = ld_act4(sq.v, g * sq.kv_head_stride + 4 * lane, in_f16);
     // Lane l fetches ladder angle l of the position stream (and of the block-position stream in CHATGLM mode) from
     // the arena's table in the same round trip.
     int pos_id = 0, block_id = 0;
@@ -432,7 +463,8 @@ __device__ __forceinline__ int group_slot(long long grp, long long b0) { return 
 // that source k_first uses its second slot when first_slot is 1 (the CTA or group in which the item begins holds
 // the end of the previous item in its first slot).  Every caller goes through this routine with the same source
 // order, so the result does not depend on which CTA or warp happens to complete the item.
-// dst_kind 0: the result is a group partial (un-normalised) at dst; 1: the sequence's (acc, m, l) row; 2: its output.
+// dst_kind 0: the result is a group partial (un-normalised) at dst; 1: the sequence's (acc, m, l) row; 2: its f32
+// output; 3: its f16 output.
 __device__ __forceinline__ void merge_row_chunk(const float *base, long long k_first, int first_slot, long long k0,
                                                 long long k1, float *dst, int dst_kind, int r, int d0) {
     float m_run = -INFINITY, den = 0.f;
@@ -484,12 +516,12 @@ __device__ __forceinline__ void merge_row_chunk(const float *base, long long k_f
 #pragma unroll
         for (int e = 0; e < 8; ++e) *reinterpret_cast<float2 *>(po + d0 + 2 * e) = make_float2(acc[2 * e], acc[2 * e + 1]);
         if (d0 == 0) { po[kD] = m_run * kLn2; po[kD + 1] = den; }
-    } else {
+    } else {   // 2: f32 output row, 3: f16 output row (dst addresses row 0 of the kv head in the output's own type)
         const float inv = 1.f / den;
-        float4 *op = reinterpret_cast<float4 *>(dst + static_cast<long long>(r) * kD + d0);
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-            op[e] = make_float4(acc[4 * e] * inv, acc[4 * e + 1] * inv, acc[4 * e + 2] * inv, acc[4 * e + 3] * inv);
+            st_out4(dst, static_cast<long long>(r) * kD + d0 + 4 * e, dst_kind == 3, acc[4 * e] * inv, acc[4 * e + 1] * inv,
+                    acc[4 * e + 2] * inv, acc[4 * e + 3] * inv);
         }
     }
 }
@@ -502,6 +534,105 @@ __device__ __forceinline__ int count_part(int *ctr, int expected) {
     return last;
 }
 
+
+// ---- fused split-KV step: publish an item's rows to the peers, combine when everything has arrived --------------------
+// Called by the team (n_thr threads, index t) that has just written the (acc, m, l) rows of kv head g into this rank's
+// slot of the LOCAL exchange buffer.  The team copies the rows into the same slot of every peer's buffer with plain
+// peer stores, fences at system scope and publishes the step number in the arrival word [rank][g] of every buffer
+// (release).  The team that publishes this rank's last kv head then waits, with a bound, until the arrival words of
+// every rank and kv head in the local buffer hold the step number, merges the n_rank partials (log-sum-exp) into
+// xd.out and advances the local step counter.  Nothing here waits for another CTA of this grid, only for other GPUs.
+__device__ __noinline__ void xchg_finish(const XchgShared *xs, int g, int t, int n_thr, int *cta_flag) {
+    const XchgDev &xd = xs->xd;
+    const unsigned int e = xs->epoch;
+    const int set = static_cast<int>(e & 1u), n_rank = xd.n_rank, rank = xd.rank, G = xs->G, R = xs->R;
+    auto team_sync = [&]() {
+        if (cta_flag) named_bar_sync(1, n_thr); else __syncwarp();
+    };
+    auto team_and = [&](int v) -> int {   // logical AND over the team; every member calls it
+        if (cta_flag) {
+            named_bar_sync(1, n_thr);
+            if (t == 0) *cta_flag = 1;
+            named_bar_sync(1, n_thr);
+            if (!v) *cta_flag = 0;
+            named_bar_sync(1, n_thr);
+            return *cta_flag;
+        }
+        return __all_sync(0xffffffffu, v != 0);
+    };
+    team_sync();   // the rows written by the other members are visible
+    unsigned int *local = xd.peer[rank];
+    const size_t row0 = static_cast<size_t>(g) * R * (kD + 2);   // first float of the item's rows inside a slot
+    const int n2 = R * (kD + 2) / 2;                              // the item's rows as float2 units
+    const float2 *src = reinterpret_cast<const float2 *>(reinterpret_cast<const float *>(local + xchg_slot_word(set, rank, n_rank, xs->slot_words)) + row0);
+    for (int p = 0; p < n_rank; ++p) {
+        if (p == rank) continue;
+        float2 *dst = reinterpret_cast<float2 *>(reinterpret_cast<float *>(xd.peer[p] + xchg_slot_word(set, rank, n_rank, xs->slot_words)) + row0);
+        for (int i = t; i < n2; i += n_thr) dst[i] = __ldcg(src + i);
+    }
+    __threadfence_system();
+    team_sync();
+    int last = 0;
+    if (t == 0) {
+        for (int p = 0; p < n_rank; ++p) {
+            asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(xd.peer[p] + xchg_flag_word(set, rank, g)), "r"(e) : "memory");
+        }
+        last = atomicAdd(&xs->hdr->xchg_items, 1) == G - 1;
+        if (last) atomicExch(&xs->hdr->xchg_items, 0);   // ready for the next step
+    }
+    if (cta_flag) {
+        if (t == 0) *cta_flag = last;
+        named_bar_sync(1, n_thr);
+        last = *cta_flag;
+    } else {
+        last = __shfl_sync(0xffffffffu, last, 0);
+    }
+    if (!last) return;
+    int ok = 1;
+    if (xd.combine) {
+        long long t0, now;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+        const long long limit = static_cast<long long>(xd.timeout_us) * 1000;
+        for (int w = t; w < n_rank * G; w += n_thr) {
+            const unsigned int *flag = local + xchg_flag_word(set, w / G, w % G);
+            bool seen = false;
+            for (unsigned int spin = 0; spin < (1u << 26); ++spin) {   // the timer bounds the wait, the count bounds the loop
+                unsigned int v;
+                asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+                if (v == e) { seen = true; break; }
+                asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+                if (now - t0 > limit) break;
+                __nanosleep(100);
+            }
+            if (!seen) ok = 0;
+        }
+        ok = team_and(ok);
+        if (ok) {
+            const int H = xs->H, sw = xs->slot_words;
+            const float *slots = reinterpret_cast<const float *>(local + xchg_slot_word(set, 0, n_rank, sw));
+            for (int u = t; u < H * (kD / 4); u += n_thr) {   // one q head's four dims per unit
+                const int h = u / (kD / 4), d0 = 4 * (u % (kD / 4));
+                float m_star = -INFINITY;
+                for (int p = 0; p < n_rank; ++p) m_star = fmaxf(m_star, __ldcg(slots + static_cast<size_t>(p) * sw + h * (kD + 2) + kD));
+                float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f, den = 0.f;
+                for (int p = 0; p < n_rank; ++p) {
+                    const float *pp = slots + static_cast<size_t>(p) * sw + h * (kD + 2);
+                    const float m = __ldcg(pp + kD);
+                    const float w = m == -INFINITY ? 0.f : __expf(m - m_star);
+                    const float2 x01 = __ldcg(reinterpret_cast<const float2 *>(pp + d0));
+                    const float2 x23 = __ldcg(reinterpret_cast<const float2 *>(pp + d0 + 2));
+                    a0 += w * x01.x; a1 += w * x01.y; a2 += w * x23.x; a3 += w * x23.y;
+                    den += w * __ldcg(pp + kD + 1);
+                }
+                const float inv = 1.f / den;
+                *reinterpret_cast<float4 *>(xd.out + static_cast<size_t>(h) * kD + d0) = make_float4(a0 * inv, a1 * inv, a2 * inv, a3 * inv);
+            }
+        } else if (t == 0) {
+            atomicExch(&xs->hdr->status, static_cast<int>(CGLM_ERR_TIMEOUT));
+        }
+    }
+    if (t == 0) *reinterpret_cast<volatile unsigned int *>(local) = e;   // the step is over for this rank, merged or not
+}
 
 // Called by a team of n_thr threads (the four consumer warps at the end of a span, or the helper warp in the
 // middle of one) after CTA `b` stored its part of item da->ip.  t: index inside the team.  cta_flag: shared-memory
@@ -536,9 +667,11 @@ __device__ __noinline__ void deliver_part(const DeliverArgs *da, long long b, in
     const int first_cta_slot = span_start(b0, mc.total, mc.nb) >= ip.item_begin ? 0 : 1;
     const long long g0 = b0 / kMergeFan, g1 = b1 / kMergeFan;
     const int first_grp_slot = group_slot(g0, b0);
+    const bool out_f16 = (sq.flags & CGLM_SEQ_OUT_F16) != 0;
     float *final_dst = (sq.flags & CGLM_SEQ_PARTIAL) ? sq.partial + static_cast<long long>(ip.g) * sh.R * (kD + 2)
-                                                      : sq.out + static_cast<long long>(ip.g) * sh.R * kD;
-    const int final_kind = (sq.flags & CGLM_SEQ_PARTIAL) ? 1 : 2;
+                       : out_f16 ? reinterpret_cast<float *>(reinterpret_cast<__half *>(sq.out) + static_cast<long long>(ip.g) * sh.R * kD)
+                                 : sq.out + static_cast<long long>(ip.g) * sh.R * kD;
+    const int final_kind = (sq.flags & CGLM_SEQ_PARTIAL) ? 1 : (out_f16 ? 3 : 2);
     // one merge loop for the three uses below (the arguments vary, the code does not)
     auto merge = [&](const float *base, long long k_first, int first_slot, long long k0, long long k1, float *dst, int kind) {
 #pragma unroll 1
@@ -565,6 +698,7 @@ __device__ __noinline__ void deliver_part(const DeliverArgs *da, long long b, in
     }
     __threadfence();
     merge(base, k_first, first_slot, k0, k1, final_dst, final_kind);
+    if (da->xs) xchg_finish(da->xs, ip.g, t, n_thr, cta_flag);
 }
 
 // Tiles [pos, pos_end) of the line into L2 only (no shared memory, no barrier): issued by the producer of a launch
@@ -579,12 +713,16 @@ __device__ __forceinline__ void tma_prefetch_l2_2d(const CUtensorMap *map, int c
 // kDynPast: sequences may carry CGLM_SEQ_N_PAST_DEVICE.  Their position is read from device memory once the previous
 // kernel of the stream has completed, the tile prefix is rebuilt from it, and nothing runs ahead of the dependency
 // wait (the spans are not known before).  A second instantiation, so that the common case pays nothing for it.
-template <bool kDynPast>
+// kXchg: fused split-KV step.  The launch holds one sequence (this rank's slice of the KV length, CGLM_SEQ_PARTIAL
+// semantics); its partial rows are written into the local exchange buffer and published to every rank by the CTA
+// that completes them (xchg_finish).  A third instantiation: the other two carry none of it.
+template <bool kDynPast, bool kXchg>
 __global__ void __launch_bounds__(kThreads, 2)
 decode_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map,
               const __grid_constant__ DecodeTable tab, AttnShape sh, uint16_t *__restrict__ k_base,
               uint16_t *__restrict__ v_base, WsHeader *hdr, int *counters, int *gcounters, float *partials,
-              float *gpartials, const float2 *__restrict__ rope_tab, int rope_tab_len) {
+              float *gpartials, const float2 *__restrict__ rope_tab, int rope_tab_len,
+              const __grid_constant__ XchgDev xchg) {
     extern __shared__ uint8_t smem_raw[];
     DecodeSmem &sm = *reinterpret_cast<DecodeSmem *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -604,6 +742,12 @@ decode_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__
         mbar_init(&sm.pdone[0], kConsumerWarps);
         mbar_init(&sm.pdone[1], kConsumerWarps);
         fence_mbar_init();
+        if (kXchg) {
+            sm.xs.xd = xchg;
+            sm.xs.hdr = hdr;
+            sm.xs.slot_words = sh.H * (kD + 2);
+            sm.xs.H = sh.H; sm.xs.G = sh.G; sm.xs.R = sh.R;
+        }
     }
     // The sequence descriptors and the prefix sums of their tile counts arrive as kernel parameters: no upload
     // precedes the launch.  The prefix sums are searched by every role, so they are copied to shared memory once
@@ -613,9 +757,10 @@ decode_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__
     // cache rows this launch reads, so the producer streams tiles without waiting for the previous kernel of the
     // stream; tab.settled - 1 further tiles per CTA are pulled into L2 behind the ring.
     const bool settled = !kDynPast && tab.settled != 0;
+    const int trigger = tab.trigger;
     if (kDynPast) {
         asm volatile("griddepcontrol.wait;" ::: "memory");
-        asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+        if (trigger == 0) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
         for (int i = tid; i < n_seq; i += kThreads) {
             int np = tab.seqs[i].n_past;
             if (tab.seqs[i].flags & CGLM_SEQ_N_PAST_DEVICE) {
@@ -668,7 +813,7 @@ decode_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__
     // (The helper warp of a CTA with work waits inside its loop, after a dry pass over its first segment.)
     if (!kDynPast && (warp != kHelperWarp || span_lo >= span_hi) && !(settled && warp == kProducerWarp && span_lo < span_hi)) {
         asm volatile("griddepcontrol.wait;" ::: "memory");
-        asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+        if (trigger == 0) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     }
     if (span_lo >= span_hi) {
         return;
@@ -715,6 +860,7 @@ decode_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__
                 }
                 if (pos < seg_end) break;   // a wait ran out
             }
+            if (trigger == 1) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
         }
     } else if (warp == kHelperWarp) {
         // ================================ helper warp ==================================================
@@ -749,6 +895,20 @@ decode_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__
                 if (sidx == 0 && !dry && !kDynPast) {
                     asm volatile("griddepcontrol.wait;" ::: "memory");
                 }
+                if (kXchg && !dry) {
+                    // this step's number, and where this rank's rows go inside the local exchange buffer
+                    if (sidx == 0) {
+                        unsigned int ep = 0;
+                        if (lane == 0) {
+                            ep = *reinterpret_cast<volatile unsigned int *>(sm.xs.xd.peer[sm.xs.xd.rank]) + 1u;
+                            sm.xs.epoch = ep;
+                        }
+                        __syncwarp();
+                    }
+                    sq.partial = reinterpret_cast<float *>(sm.xs.xd.peer[sm.xs.xd.rank] +
+                                                           xchg_slot_word(static_cast<int>(sm.xs.epoch & 1u), sm.xs.xd.rank,
+                                                                          sm.xs.xd.n_rank, sm.xs.slot_words));
+                }
                 prepare_segment(sm.qb[b], sh, sq, ip.g, sq.slot * G + ip.g, has_last_tile, appender, lane, k_base, v_base,
                                 rope_tab, rope_tab_len, (sidx == 0 && !dry) ? &sm.hstart : nullptr, dry);
             }
@@ -758,7 +918,7 @@ decode_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__
                 mbar_wait_bounded(&sm.pdone[prev_slot], 0, &sm.abort_flag);   // each used once: a CTA has <= 2 partials
                 {
                     DeliverArgs &da = sm.dargs[kConsumerWarps];
-                    if (lane == 0) { da.ip = prev_ip; da.io = prev_sq; da.mc = mc; da.G = G; da.R = R; }
+                    if (lane == 0) { da.ip = prev_ip; da.io = prev_sq; da.mc = mc; da.G = G; da.R = R; da.xs = kXchg ? &sm.xs : nullptr; }
                     __syncwarp();
                     deliver_part(&da, blockIdx.x, lane, 32, nullptr);
                     __syncwarp();
@@ -776,7 +936,7 @@ decode_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__
             mbar_wait_bounded(&sm.pdone[prev_slot], 0, &sm.abort_flag);
             {
                     DeliverArgs &da = sm.dargs[kConsumerWarps];
-                    if (lane == 0) { da.ip = prev_ip; da.io = prev_sq; da.mc = mc; da.G = G; da.R = R; }
+                    if (lane == 0) { da.ip = prev_ip; da.io = prev_sq; da.mc = mc; da.G = G; da.R = R; da.xs = kXchg ? &sm.xs : nullptr; }
                     __syncwarp();
                     deliver_part(&da, blockIdx.x, lane, 32, nullptr);
                     __syncwarp();
@@ -846,6 +1006,9 @@ decode_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__
             // the q tile, newk and newv of this segment are no longer needed
             __syncwarp();
             if (lane == 0) mbar_arrive(&sm.qempty[sidx & 1]);
+            // Every tile of the span has been consumed: from here on this CTA only folds and merges, so the next kernel
+            // of the stream may take its place (it starts once every CTA of this grid has said so or has exited).
+            if (trigger == 2 && seg_end == span_hi && warp == 0) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
             // ---- fold the four warps' states -----------------------------------------------------------------
             // Each warp attended its own 16 tokens of every tile and holds (m, l, O[16][128]) for them.  The stage
@@ -916,8 +1079,8 @@ decode_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__
                             *reinterpret_cast<float2 *>(pp) = make_float2(acc.x, acc.y);
                             *reinterpret_cast<float2 *>(pp + 2) = make_float2(acc.z, acc.w);
                         } else {
-                            *reinterpret_cast<float4 *>(out_ptr + static_cast<long long>(head) * kD + 4 * q) =
-                                make_float4(acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv);
+                            st_out4(out_ptr, static_cast<long long>(head) * kD + 4 * q, (flags & CGLM_SEQ_OUT_F16) != 0,
+                                    acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv);
                         }
                     }
                 }
@@ -945,9 +1108,12 @@ decode_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__
                 // complete.  The team barrier inside deliver_part also orders every warp's partial stores before the count.
                 const MergeCtx mc{total, nb, counters, gcounters, partials, gpartials};
                 DeliverArgs &da = sm.dargs[warp];   // every warp parks its own copy: no barrier needed before the call
-                if (lane == 0) { da.ip = ip; da.io = ItemOut{out_ptr, partial_ptr, flags}; da.mc = mc; da.G = G; da.R = R; }
+                if (lane == 0) { da.ip = ip; da.io = ItemOut{out_ptr, partial_ptr, flags}; da.mc = mc; da.G = G; da.R = R; da.xs = kXchg ? &sm.xs : nullptr; }
                 __syncwarp();
                 deliver_part(&da, blockIdx.x, tid, kConsumerThreads, &sm.last_flag);
+            } else if (kXchg && whole_item) {
+                // the whole kv head was this CTA's: its rows are in the local buffer, publish them
+                xchg_finish(&sm.xs, g, tid, kConsumerThreads, &sm.last_flag);
             }
             first_segment = false;
             ++sidx;
@@ -962,7 +1128,7 @@ decode_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__
 
 int decode_max_ctas(int n_sm) { return 2 * n_sm; }   // bound used to size scratch; launch_decode picks the grid
 
-cudaError_t launch_decode(const LaunchCtx &cx, const DecodeTable &tab, bool n_past_on_device) {
+cudaError_t launch_decode(const LaunchCtx &cx, const DecodeTable &tab, bool n_past_on_device, const XchgDev *xchg) {
     // with device-side positions tab.prefix holds the tile counts of the host's upper bounds: good for sizing only
     const long long total_tiles = static_cast<long long>(tab.prefix[tab.n_seq]) * cx.shape.G;
     if (tab.n_seq == 0 || total_tiles == 0) {
@@ -972,8 +1138,9 @@ cudaError_t launch_decode(const LaunchCtx &cx, const DecodeTable &tab, bool n_pa
     const int smem_bytes = static_cast<int>(sizeof(DecodeSmem)) + 1024;
     if (configured.needed(cx.device)) {
         cudaError_t e = require_current_device(cx.device);
-        if (e == cudaSuccess) e = cudaFuncSetAttribute(decode_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
-        if (e == cudaSuccess) e = cudaFuncSetAttribute(decode_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(decode_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(decode_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(decode_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
         if (e != cudaSuccess) return e;
         configured.mark(cx.device);
     }
@@ -995,12 +1162,12 @@ cudaError_t launch_decode(const LaunchCtx &cx, const DecodeTable &tab, bool n_pa
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    cudaError_t e =
-        n_past_on_device
-            ? cudaLaunchKernelEx(&cfg, decode_kernel<true>, *cx.k_map, *cx.v_map, tab, cx.shape, cx.k_base, cx.v_base, cx.hdr,
-                                 cx.counters, cx.gcounters, cx.partials, cx.gpartials, cx.rope_tab, cx.rope_tab_len)
-            : cudaLaunchKernelEx(&cfg, decode_kernel<false>, *cx.k_map, *cx.v_map, tab, cx.shape, cx.k_base, cx.v_base, cx.hdr,
-                                 cx.counters, cx.gcounters, cx.partials, cx.gpartials, cx.rope_tab, cx.rope_tab_len);
+    if (xchg && (n_past_on_device || tab.n_seq != 1)) return cudaErrorInvalidValue;
+    static const XchgDev no_xchg = {};
+    const XchgDev &xd = xchg ? *xchg : no_xchg;
+    auto kernel = xchg ? decode_kernel<false, true> : (n_past_on_device ? decode_kernel<true, false> : decode_kernel<false, false>);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, *cx.k_map, *cx.v_map, tab, cx.shape, cx.k_base, cx.v_base, cx.hdr, cx.counters,
+                                       cx.gcounters, cx.partials, cx.gpartials, cx.rope_tab, cx.rope_tab_len, xd);
     g_launch_count += 1;
     return e != cudaSuccess ? e : cudaGetLastError();
 }

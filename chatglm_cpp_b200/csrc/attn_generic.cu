@@ -53,25 +53,27 @@ rope_append_kernel(AttnShape sh, const SeqDev *__restrict__ seqs, int n_seq, uin
 
     const int cache_pos = sq.kv_before + s;
     const bool do_append = !(sq.flags & CGLM_SEQ_NO_APPEND);
+    const bool in_f16 = (sq.flags & CGLM_SEQ_QKV_F16) != 0;
     const int half_pairs = D / 2;   // every head is walked as D/2 (i0, i1) pairs, rotated or not
     // q heads then k heads
     for (int idx = threadIdx.x; idx < (H + G) * half_pairs; idx += blockDim.x) {
         const int head = idx / half_pairs, p = idx % half_pairs;
         const bool is_q = head < H;
         const int hh = is_q ? head : head - H;
-        const float *src = is_q ? sq.q + s * sq.q_tok_stride + hh * sq.q_head_stride
-                                : sq.k + s * sq.kv_tok_stride + hh * sq.kv_head_stride;
+        const float *base = is_q ? sq.q : sq.k;
+        const long long row = is_q ? s * sq.q_tok_stride + hh * sq.q_head_stride : s * sq.kv_tok_stride + hh * sq.kv_head_stride;
         int i0, i1;
         float y0, y1;
         if (p < n_pairs) {
             const RopePair rp = rope_pair(sh.rope_type, D, p);
             i0 = rp.i0; i1 = rp.i1;
-            rope_rotate(src[i0], src[i1], cs[rp.stream][rp.ladder][0], cs[rp.stream][rp.ladder][1], y0, y1);
+            rope_rotate(ld_act(base, row + i0, in_f16), ld_act(base, row + i1, in_f16), cs[rp.stream][rp.ladder][0],
+                        cs[rp.stream][rp.ladder][1], y0, y1);
         } else {
             // elements no pair rotates: for CHATGLM2 the second half of the head, for DISABLED all of it
             const int first_free = sh.rope_type == CGLM_ROPE_CHATGLM2 ? D / 2 : 0;
             i0 = first_free + 2 * (p - n_pairs); i1 = i0 + 1;
-            y0 = src[i0]; y1 = src[i1];
+            y0 = ld_act(base, row + i0, in_f16); y1 = ld_act(base, row + i1, in_f16);
         }
         if (is_q) {
             float *dst = q_stage + (static_cast<long long>(sq.tok_begin + s) * H + hh) * D;
@@ -96,7 +98,7 @@ rope_append_kernel(AttnShape sh, const SeqDev *__restrict__ seqs, int n_seq, uin
     if (do_append) {
         for (int idx = threadIdx.x; idx < G * D; idx += blockDim.x) {
             const int g = idx / D, d = idx % D;
-            const float x = sq.v[s * sq.kv_tok_stride + g * sq.kv_head_stride + d];
+            const float x = ld_act(sq.v, s * sq.kv_tok_stride + g * sq.kv_head_stride + d, in_f16);
             v_base[(static_cast<long long>(sq.slot * G + g) * D + d) * M + cache_pos] =
                 __half_as_ushort(__float2half_rn(x));
         }
@@ -201,11 +203,12 @@ attend_kernel(AttnShape sh, const SeqDev *__restrict__ seqs, int n_seq, int tota
         if (lane == 0) { pp[D] = m_run; pp[D + 1] = l_run; }
     } else {
         const float inv = 1.f / l_run;
-        float *o = sq.out + (static_cast<long long>(s) * H + h) * D;
+        const long long o = (static_cast<long long>(s) * H + h) * D;
+        const bool out_f16 = (sq.flags & CGLM_SEQ_OUT_F16) != 0;
 #pragma unroll
         for (int i = 0; i < kMaxHeadDim / 32; ++i) {
             const int d = lane + 32 * i;
-            if (d < D) o[d] = acc[i] * inv;
+            if (d < D) st_out(sq.out, o + d, out_f16, acc[i] * inv);
         }
     }
 }

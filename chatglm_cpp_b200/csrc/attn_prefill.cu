@@ -146,6 +146,7 @@ prefill_prepare_kernel(AttnShape sh, SeqDev sq, uint16_t *__restrict__ k_base, u
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     __shared__ __half tile_mem[kD][kPrepTokens + 2];       // v CTAs: [dim][token] transpose tile
     const int S = sq.qlen, H = sh.H, G = sh.G, M = sh.M;
+    const bool in_f16 = (sq.flags & CGLM_SEQ_QKV_F16) != 0;
     const int t_begin = blockIdx.x * kPrepTokens;
     const int n_tok = min(kPrepTokens, S - t_begin);
     const int n_qpair = (H + 1) / 2;
@@ -162,7 +163,7 @@ prefill_prepare_kernel(AttnShape sh, SeqDev sq, uint16_t *__restrict__ k_base, u
 #pragma unroll
             for (int u = 0; u < 8; ++u) {
                 const int t = t0 + 2 * u;
-                x[u] = t < n_tok ? __ldg(sq.v + (t_begin + t) * sq.kv_tok_stride + g * sq.kv_head_stride + d) : 0.f;
+                x[u] = t < n_tok ? ld_act(sq.v, (t_begin + t) * sq.kv_tok_stride + g * sq.kv_head_stride + d, in_f16) : 0.f;
             }
 #pragma unroll
             for (int u = 0; u < 8; ++u) {
@@ -204,7 +205,8 @@ prefill_prepare_kernel(AttnShape sh, SeqDev sq, uint16_t *__restrict__ k_base, u
     const float2 *tab = table_by_position ? table + cs_ladder : table + (static_cast<long long>(cs_stream) * S + t_begin) * 32 + cs_ladder;
     for (int hi = 0; hi < n_heads; ++hi) {
         const int hh = head0 + hi;
-        const float *src_head = is_q ? sq.q + hh * sq.q_head_stride : sq.k + hh * sq.kv_head_stride;
+        const float *src_base = is_q ? sq.q : sq.k;
+        const long long head_off = is_q ? hh * sq.q_head_stride : hh * sq.kv_head_stride;
         const long long tok_stride = is_q ? sq.q_tok_stride : sq.kv_tok_stride;
         for (int t0 = tid >> 6; t0 < n_tok; t0 += 4 * kBatch) {
             float x0[kBatch], x1[kBatch];
@@ -215,9 +217,9 @@ prefill_prepare_kernel(AttnShape sh, SeqDev sq, uint16_t *__restrict__ k_base, u
                 x0[u] = x1[u] = 0.f;
                 cs[u] = make_float2(1.f, 0.f);
                 if (t < n_tok) {
-                    const float *src = src_head + (t_begin + t) * tok_stride;
-                    x0[u] = __ldg(src + i0);
-                    x1[u] = __ldg(src + i1);
+                    const long long src = head_off + (t_begin + t) * tok_stride;
+                    x0[u] = ld_act(src_base, src + i0, in_f16);
+                    x1[u] = ld_act(src_base, src + i1, in_f16);
                     if (rotated) {
                         // derived ids (chatglm.cpp:1142-1153, 1319-1327 with n_past = 0), as selects: a branch here
                         // would split the batch of loads into one round trip per token
@@ -279,7 +281,7 @@ prefill_prepare_kernel(AttnShape sh, SeqDev sq, uint16_t *__restrict__ k_base, u
 __global__ void __launch_bounds__(kThreads, 1)
 prefill_attn_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap k_map,
                     const __grid_constant__ CUtensorMap v_map, AttnShape sh, int S, int kv_row0, float *__restrict__ out,
-                    WsHeader *hdr) {
+                    int out_f16, WsHeader *hdr) {
     extern __shared__ uint8_t smem_raw[];
     PrefillSmem &sm = *reinterpret_cast<PrefillSmem *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -562,7 +564,12 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
         for (int r = warp; r < kQTile; r += kSoftmaxThreads / 32) {
             if (s0 + r < S) {
                 const float4 val = *reinterpret_cast<const float4 *>(&stage[r * kOutStride + 4 * lane]);
-                *reinterpret_cast<float4 *>(out + (static_cast<long long>(s0 + r) * sh.H + h) * kD + 4 * lane) = val;
+                const long long o = (static_cast<long long>(s0 + r) * sh.H + h) * kD + 4 * lane;
+                if (out_f16) {
+                    *reinterpret_cast<uint2 *>(reinterpret_cast<__half *>(out) + o) = make_uint2(pack_half2(val.x, val.y), pack_half2(val.z, val.w));
+                } else {
+                    *reinterpret_cast<float4 *>(out + o) = val;
+                }
             }
         }
         jt0 += n_kv;
@@ -636,7 +643,8 @@ cudaError_t launch_prefill(const LaunchCtx &cx, const SeqDev &sq, const CUtensor
     cfg.stream = cx.stream;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    e = cudaLaunchKernelEx(&cfg, prefill_attn_kernel, q_map, k_map, v_map, cx.shape, S, sq.slot * cx.shape.G, sq.out, cx.hdr);
+    e = cudaLaunchKernelEx(&cfg, prefill_attn_kernel, q_map, k_map, v_map, cx.shape, S, sq.slot * cx.shape.G, sq.out,
+                           (sq.flags & CGLM_SEQ_OUT_F16) ? 1 : 0, cx.hdr);
     g_launch_count += launched;
     return e != cudaSuccess ? e : cudaGetLastError();
 }

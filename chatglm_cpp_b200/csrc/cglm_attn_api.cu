@@ -25,7 +25,7 @@ struct cglm_kv_arena {
     int n_slots;
     int device;
     int n_sm;
-    uint8_t *base;        // one allocation: K slabs, then V slabs
+    uint8_t *base;        // one allocation: K slabs, then V slabs; null when the caches are caller-owned (adopted)
     uint16_t *k_base;
     uint16_t *v_base;
     float2 *rope_tab;     // GLM rope modes at head_dim 128: (cos, sin) of ladder step i at position p, [max_len][32]
@@ -104,6 +104,15 @@ int decode_l2_ahead() {
         const char *e = std::getenv("CGLM_DECODE_L2_AHEAD");
         const int x = e ? std::atoi(e) : 4;
         return x < 0 ? 0 : (x > 64 ? 64 : x);
+    }();
+    return v;
+}
+// When a decode CTA releases the next kernel of the stream (see DecodeTable::trigger).  CGLM_DECODE_TRIGGER overrides.
+int decode_trigger() {
+    static const int v = [] {
+        const char *e = std::getenv("CGLM_DECODE_TRIGGER");
+        const int x = e ? std::atoi(e) : 2;
+        return x < 0 || x > 2 ? 2 : x;
     }();
     return v;
 }
@@ -276,81 +285,6 @@ __global__ void combine_kernel(const float *__restrict__ partials, int n_part, i
     }
 }
 
-// ---- split-KV exchange over peer memory ----------------------------------------------------------------------
-// Exchange buffer: [0] step counter, [1..15] unused, then 2 sets of n_rank arrival words (padded to 16 words per
-// set), then 2 sets of n_rank partial slots of n_head * (head_dim + 2) floats.
-constexpr int kXchgMaxRanks = 16;
-struct XchgPeers {
-    void *buf[kXchgMaxRanks];
-};
-__host__ __device__ inline size_t xchg_flag_word(int set, int rank) { return 16 + static_cast<size_t>(set) * kXchgMaxRanks + rank; }
-__host__ __device__ inline size_t xchg_slot_word(int set, int rank, int n_rank, int slot_words) {
-    return 16 + 2 * kXchgMaxRanks + (static_cast<size_t>(set) * n_rank + rank) * slot_words;
-}
-
-// one CTA per destination rank: plain (peer) stores of the partial, then the arrival word with release semantics
-__global__ void xchg_push_kernel(const float *__restrict__ partial, XchgPeers peers, int n_rank, int rank, int slot_words) {
-    const unsigned int e = *reinterpret_cast<volatile unsigned int *>(peers.buf[rank]) + 1u;   // local counter
-    unsigned int *dst = static_cast<unsigned int *>(peers.buf[blockIdx.x]);
-    float2 *slot = reinterpret_cast<float2 *>(dst + xchg_slot_word(e & 1u, rank, n_rank, slot_words));
-    const float2 *src = reinterpret_cast<const float2 *>(partial);
-    for (int i = threadIdx.x; i < slot_words / 2; i += blockDim.x) slot[i] = src[i];
-    __threadfence_system();
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(dst + xchg_flag_word(e & 1u, rank)), "r"(e) : "memory");
-    }
-}
-
-// one CTA: bounded wait for the n_rank arrival words, log-sum-exp merge of the slots, counter advance
-__global__ void __launch_bounds__(1024)
-xchg_combine_kernel(unsigned int *__restrict__ local, int n_rank, int H, int D, float *__restrict__ out, WsHeader *hdr,
-                    unsigned int timeout_us) {
-    __shared__ int ok;
-    const unsigned int e = local[0] + 1u;
-    const int slot_words = H * (D + 2);
-    if (threadIdx.x == 0) ok = 1;
-    __syncthreads();
-    if (threadIdx.x < n_rank) {
-        const unsigned int *flag = local + xchg_flag_word(e & 1u, threadIdx.x);
-        long long t0, t;
-        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
-        const long long limit = static_cast<long long>(timeout_us ? timeout_us : 1000000u) * 1000;
-        bool seen = false;
-        for (unsigned int spin = 0; spin < (1u << 28); ++spin) {   // the timer bounds the wait; the count bounds the loop
-            unsigned int v;
-            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
-            if (v == e) { seen = true; break; }
-            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-            if (t - t0 > limit) break;
-            __nanosleep(200);
-        }
-        if (!seen) ok = 0;
-    }
-    __syncthreads();
-    if (ok) {
-        const float *slots = reinterpret_cast<const float *>(local + xchg_slot_word(e & 1u, 0, n_rank, slot_words));
-        for (int i = threadIdx.x; i < H * D; i += blockDim.x) {
-            const int h = i / D, d = i - h * D;
-            float m_star = -INFINITY;
-            for (int p = 0; p < n_rank; ++p) m_star = fmaxf(m_star, __ldcg(slots + static_cast<size_t>(p) * slot_words + h * (D + 2) + D));
-            float acc = 0.f, den = 0.f;
-            for (int p = 0; p < n_rank; ++p) {
-                const float *pp = slots + static_cast<size_t>(p) * slot_words + h * (D + 2);
-                const float m = __ldcg(pp + D);
-                const float w = m == -INFINITY ? 0.f : __expf(m - m_star);
-                acc += w * __ldcg(pp + d);
-                den += w * __ldcg(pp + D + 1);
-            }
-            out[i] = acc / den;
-        }
-    } else if (threadIdx.x == 0) {
-        atomicExch(&hdr->status, static_cast<int>(CGLM_ERR_TIMEOUT));
-    }
-    __syncthreads();
-    if (threadIdx.x == 0) local[0] = e;
-}
-
 __global__ void seq_advance_kernel(int *__restrict__ n_past, int n, int delta) {
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) n_past[i] += delta;
@@ -367,6 +301,27 @@ __global__ void load_prefix_kernel(const uint16_t *__restrict__ past_kv, uint16_
         k_slot[(static_cast<long long>(g) * M + t) * D + d] = past_kv[i];
         v_slot[(static_cast<long long>(g) * D + d) * M + t] = past_kv[n + i];
     }
+}
+
+LaunchCtx make_launch_ctx(const cglm_kv_arena *a, uint8_t *ws, const WsLayout &lay, cudaStream_t st) {
+    LaunchCtx cx;
+    cx.shape = make_shape(a->desc);
+    cx.k_base = a->k_base;
+    cx.v_base = a->v_base;
+    cx.hdr = reinterpret_cast<WsHeader *>(ws);
+    cx.counters = reinterpret_cast<int *>(ws + lay.counters);
+    cx.gcounters = reinterpret_cast<int *>(ws + lay.gcounters);
+    cx.partials = reinterpret_cast<float *>(ws + lay.partials);
+    cx.gpartials = reinterpret_cast<float *>(ws + lay.gpartials);
+    cx.q_stage = reinterpret_cast<float *>(ws + lay.q_stage);
+    cx.k_map = &a->k_map;
+    cx.v_map = &a->v_map;
+    cx.rope_tab = a->rope_tab;
+    cx.rope_tab_len = a->rope_tab_len;
+    cx.stream = st;
+    cx.n_sm = a->n_sm;
+    cx.device = a->device;
+    return cx;
 }
 
 int ring_reserve(cglm_kv_arena *a, int n_seq, SeqDev **slot, cudaEvent_t *ev) {
@@ -476,6 +431,76 @@ int cglm_kv_arena_create(const cglm_attn_desc *desc, int n_slots, cglm_kv_arena 
     return CGLM_OK;
 }
 
+size_t cglm_kv_angle_table_bytes(const cglm_attn_desc *desc) {
+    if (!desc_ok(desc)) return 0;
+    const bool glm_rope = desc->rope_type == CGLM_ROPE_CHATGLM2 || desc->rope_type == CGLM_ROPE_CHATGLM;
+    return desc->head_dim == 128 && glm_rope ? static_cast<size_t>(desc->max_len) * 32 * sizeof(float2) : 0;
+}
+
+int cglm_kv_arena_adopt(const cglm_attn_desc *desc, int n_slots, void *k_base, void *v_base, void *angle_table,
+                        cglm_kv_arena **out) {
+    if (!desc_ok(desc) || n_slots <= 0 || !out || !k_base || !v_base) return CGLM_ERR_INVALID_ARG;
+    if (desc->head_dim > 256) return CGLM_ERR_UNSUPPORTED;
+    // TMA wants 16-byte aligned bases; ask for the 128 bytes a swizzled row spans
+    if ((reinterpret_cast<uintptr_t>(k_base) | reinterpret_cast<uintptr_t>(v_base) | reinterpret_cast<uintptr_t>(angle_table)) & 127)
+        return CGLM_ERR_INVALID_ARG;
+    int n_sm = 0, major = 0;
+    int rc = device_sm_count(&n_sm, &major);
+    if (rc != CGLM_OK) return rc;
+    if (major < 10) {
+        std::snprintf(g_err, sizeof(g_err), "compute capability %d.x device: this library carries sm_100a code only", major);
+        return CGLM_ERR_NO_DEVICE;
+    }
+    cudaPointerAttributes at;
+    for (void *p : {k_base, v_base}) {   // device memory of the current device, not a host pointer
+        int dev = -1;
+        cudaGetDevice(&dev);
+        if (cudaPointerGetAttributes(&at, p) != cudaSuccess || at.type != cudaMemoryTypeDevice || at.device != dev) {
+            cudaGetLastError();
+            std::snprintf(g_err, sizeof(g_err), "adopted caches must be device memory of the current device");
+            return CGLM_ERR_INVALID_ARG;
+        }
+    }
+    cglm_kv_arena *a = new (std::nothrow) cglm_kv_arena();
+    if (!a) return CGLM_ERR_INVALID_ARG;
+    a->desc = *desc;
+    a->n_slots = n_slots;
+    a->n_sm = n_sm;
+    cudaGetDevice(&a->device);
+    a->k_slot_elems = static_cast<size_t>(desc->n_kv_head) * desc->max_len * desc->head_dim;
+    a->base = nullptr;
+    a->k_base = static_cast<uint16_t *>(k_base);
+    a->v_base = static_cast<uint16_t *>(v_base);
+    a->rope_tab = nullptr;
+    a->rope_tab_len = 0;
+    if (angle_table && cglm_kv_angle_table_bytes(desc) > 0) {
+        a->rope_tab = static_cast<float2 *>(angle_table);
+        a->rope_tab_len = desc->max_len;
+        const long long n = static_cast<long long>(a->rope_tab_len) * 32;
+        rope_arena_table_kernel<<<static_cast<unsigned>((n + 255) / 256), 256>>>(make_shape(*desc).theta_scale, a->rope_tab_len,
+                                                                               a->rope_tab);
+        cudaError_t e = cudaGetLastError();
+        if (e == cudaSuccess) e = cudaDeviceSynchronize();
+        if (e != cudaSuccess) {
+            delete a;
+            return fail_cuda(e, "rope table");
+        }
+    }
+    a->has_tmaps = desc->head_dim == 128 && desc->max_len % 8 == 0 && build_tensor_maps(a);
+    a->ring = nullptr;
+    a->ring_slots = 64;
+    a->ring_cap = 0;
+    a->ring_next = 0;
+    a->ring_events = new cudaEvent_t[a->ring_slots];
+    for (int i = 0; i < a->ring_slots; ++i) {
+        cudaEventCreateWithFlags(&a->ring_events[i], cudaEventDisableTiming);
+    }
+    a->host_ready = false;
+    a->host_next = 0;
+    *out = a;
+    return CGLM_OK;
+}
+
 int cglm_kv_arena_destroy(cglm_kv_arena *a) {
     if (!a) return CGLM_ERR_INVALID_ARG;
     cudaDeviceSynchronize();
@@ -489,7 +514,7 @@ int cglm_kv_arena_destroy(cglm_kv_arena *a) {
     for (int i = 0; i < a->ring_slots; ++i) cudaEventDestroy(a->ring_events[i]);
     delete[] a->ring_events;
     if (a->ring) cudaFreeHost(a->ring);
-    cudaFree(a->base);
+    if (a->base) cudaFree(a->base);   // adopted caches stay with their owner
     delete a;
     return CGLM_OK;
 }
@@ -578,10 +603,13 @@ int cglm_attn_forward(cglm_kv_arena *a, const cglm_attn_seq *seqs, int n_seq, vo
         // (chatglm.cpp:689 masks only at n_past == 0), on the generic path
         const bool partial = (s.flags & CGLM_SEQ_PARTIAL) != 0;
         if (partial ? !s.partial : !s.out) return CGLM_ERR_INVALID_ARG;
-        // vector stores: out rows are written 16 bytes at a time, partial rows 8 bytes at a time
-        if ((reinterpret_cast<uintptr_t>(s.out) & 15) || (reinterpret_cast<uintptr_t>(s.partial) & 7) ||
-            (reinterpret_cast<uintptr_t>(s.q) & 3) || (reinterpret_cast<uintptr_t>(s.k) & 3) ||
-            (reinterpret_cast<uintptr_t>(s.v) & 3))
+        // vector stores: out rows are written four elements at a time (16 bytes of f32, 8 of f16), partial rows 8 bytes
+        // at a time; activations are at least element-aligned
+        const bool qkv_f16 = (s.flags & CGLM_SEQ_QKV_F16) != 0, out_f16 = (s.flags & CGLM_SEQ_OUT_F16) != 0;
+        const uintptr_t in_mask = qkv_f16 ? 1 : 3;
+        if ((reinterpret_cast<uintptr_t>(s.out) & (out_f16 ? 7 : 15)) || (reinterpret_cast<uintptr_t>(s.partial) & 7) ||
+            (reinterpret_cast<uintptr_t>(s.q) & in_mask) || (reinterpret_cast<uintptr_t>(s.k) & in_mask) ||
+            (reinterpret_cast<uintptr_t>(s.v) & in_mask))
             return CGLM_ERR_INVALID_ARG;
         if ((s.flags & CGLM_SEQ_NO_APPEND) && (!partial || s.qlen != 1)) return CGLM_ERR_INVALID_ARG;
         if ((s.flags & CGLM_SEQ_USE_KV_LOCAL) && (s.kv_local < 0 || s.qlen != 1)) return CGLM_ERR_INVALID_ARG;
@@ -595,7 +623,7 @@ int cglm_attn_forward(cglm_kv_arena *a, const cglm_attn_seq *seqs, int n_seq, vo
         if (d.rope_type == CGLM_ROPE_CHATGLM && !s.position_ids && s.n_ctx < 2) return CGLM_ERR_INVALID_ARG;
         const int L = kv_before + appended;
         is_fast[i] = fast_ok && s.qlen == 1 && L >= 1 &&
-                     decode_rows_aligned(s.q, s.k, s.v, s.q_head_stride, s.kv_head_stride, s.q_roped, s.k_roped);
+                     decode_rows_aligned(s.q, s.k, s.v, s.q_head_stride, s.kv_head_stride, s.q_roped, s.k_roped, qkv_f16);
         if (dyn_past && !is_fast[i]) {
             std::snprintf(g_err, sizeof(g_err), "CGLM_SEQ_N_PAST_DEVICE needs a shape and alignment the fused decode kernel takes");
             return CGLM_ERR_UNSUPPORTED;
@@ -603,7 +631,7 @@ int cglm_attn_forward(cglm_kv_arena *a, const cglm_attn_seq *seqs, int n_seq, vo
         if (is_fast[i]) {
             ++n_fast;
             decode_tiles += static_cast<long long>((L + kDecodeTile - 1) / kDecodeTile) * d.n_kv_head;
-        } else if (prefill_ok && s.qlen >= kPrefillMinTokens && s.n_past == 0 && (s.flags & ~CGLM_SEQ_CACHE_SETTLED) == 0) {
+        } else if (prefill_ok && s.qlen >= kPrefillMinTokens && s.n_past == 0 && (s.flags & ~(CGLM_SEQ_CACHE_SETTLED | CGLM_SEQ_QKV_F16 | CGLM_SEQ_OUT_F16)) == 0) {
             is_fast[i] = 2;
             ++n_prefill;
             const size_t need = prefill_q_half_bytes(d.n_head, s.qlen);
@@ -630,23 +658,7 @@ int cglm_attn_forward(cglm_kv_arena *a, const cglm_attn_seq *seqs, int n_seq, vo
         if (s.flags & CGLM_SEQ_N_PAST_DEVICE) o.n_past_dev = s.n_past_dev;   // shares the words of tok_begin / pad
     };
     uint8_t *ws = static_cast<uint8_t *>(workspace);
-    LaunchCtx cx;
-    cx.shape = make_shape(d);
-    cx.k_base = a->k_base;
-    cx.v_base = a->v_base;
-    cx.hdr = reinterpret_cast<WsHeader *>(ws);
-    cx.counters = reinterpret_cast<int *>(ws + lay.counters);
-    cx.gcounters = reinterpret_cast<int *>(ws + lay.gcounters);
-    cx.partials = reinterpret_cast<float *>(ws + lay.partials);
-    cx.gpartials = reinterpret_cast<float *>(ws + lay.gpartials);
-    cx.q_stage = reinterpret_cast<float *>(ws + lay.q_stage);
-    cx.k_map = &a->k_map;
-    cx.v_map = &a->v_map;
-    cx.rope_tab = a->rope_tab;
-    cx.rope_tab_len = a->rope_tab_len;
-    cx.stream = st;
-    cx.n_sm = a->n_sm;
-    cx.device = a->device;
+    LaunchCtx cx = make_launch_ctx(a, ws, lay, st);
 
     // fused decode: descriptors and tile prefix travel as kernel parameters, kDecodeMaxSeqPerLaunch per launch
     if (n_fast > 0) {
@@ -667,6 +679,8 @@ int cglm_attn_forward(cglm_kv_arena *a, const cglm_attn_seq *seqs, int n_seq, vo
             if (filled == kDecodeMaxSeqPerLaunch || (i == n_seq && filled > 0)) {
                 tab.n_seq = filled;
                 tab.settled = settled && !dyn ? 1 + decode_l2_ahead() : 0;
+                tab.trigger = decode_trigger();
+                tab.pad = 0;
                 CGLM_CUDA(launch_decode(cx, tab, dyn));
                 filled = 0;
                 dyn = false;
@@ -713,11 +727,14 @@ int cglm_attn_forward(cglm_kv_arena *a, const cglm_attn_seq *seqs, int n_seq, vo
     return CGLM_OK;
 }
 
-int cglm_attn_forward_host(cglm_kv_arena *a, const cglm_attn_seq *seqs, int n_seq, int interleaved_qkv,
-                           const float *qkv_host, float *out_host, float *dev_qkv, float *dev_out, void *workspace,
+int cglm_attn_forward_host(cglm_kv_arena *a, const cglm_attn_seq *seqs, int n_seq, int layout,
+                           const void *qkv_host, void *out_host, void *dev_qkv, void *dev_out, void *workspace,
                            size_t workspace_bytes, void *cuda_stream) {
     if (!a || !seqs || n_seq <= 0 || !qkv_host || !out_host || !dev_qkv || !dev_out) return CGLM_ERR_INVALID_ARG;
+    if (layout & ~(CGLM_HOST_INTERLEAVED_QKV | CGLM_HOST_F16)) return CGLM_ERR_INVALID_ARG;
     const cglm_attn_desc &d = a->desc;
+    const bool interleaved_qkv = (layout & CGLM_HOST_INTERLEAVED_QKV) != 0, act_f16 = (layout & CGLM_HOST_F16) != 0;
+    const size_t esz = act_f16 ? 2 : 4;
     if (interleaved_qkv && d.n_head != d.n_kv_head) return CGLM_ERR_INVALID_ARG;   // chatglm.cpp:637
     cudaStream_t st = static_cast<cudaStream_t>(cuda_stream);
     const long long H = d.n_head, G = d.n_kv_head, D = d.head_dim;
@@ -728,24 +745,26 @@ int cglm_attn_forward_host(cglm_kv_arena *a, const cglm_attn_seq *seqs, int n_se
     long long n_tok = 0;
     std::vector<cglm_attn_seq> dev_seqs(seqs, seqs + n_seq);
     // descriptors over a packed [tokens][row] activation at in_base and a packed [tokens][orow] output at out_base
-    auto point_at = [&](const float *in_base, float *out_base) {
+    auto point_at = [&](const void *in_base, void *out_base) {
         n_tok = 0;
         for (int i = 0; i < n_seq; ++i) {
             cglm_attn_seq &s = dev_seqs[i];
-            const float *base = in_base + n_tok * row;
-            s.q = base;
+            const char *base = static_cast<const char *>(in_base) + n_tok * row * esz;
+            auto at = [&](long long elems) { return reinterpret_cast<const float *>(base + elems * esz); };
+            s.q = at(0);
             if (interleaved_qkv) {   // chatglm.cpp:638-644
-                s.k = base + D; s.v = base + 2 * D;
+                s.k = at(D); s.v = at(2 * D);
                 s.q_head_stride = s.kv_head_stride = 3 * D;
             } else {                 // chatglm.cpp:646-652
-                s.k = base + H * D; s.v = base + (H + G) * D;
+                s.k = at(H * D); s.v = at((H + G) * D);
                 s.q_head_stride = s.kv_head_stride = D;
             }
             s.q_tok_stride = s.kv_tok_stride = row;
-            s.out = out_base + n_tok * orow;
+            s.out = reinterpret_cast<float *>(static_cast<char *>(out_base) + n_tok * orow * esz);
             s.position_ids = nullptr; s.q_roped = nullptr; s.k_roped = nullptr; s.partial = nullptr;
             s.n_past_dev = nullptr;
-            s.flags = seqs[i].flags & CGLM_SEQ_CACHE_SETTLED; s.kv_local = 0;
+            s.flags = (seqs[i].flags & CGLM_SEQ_CACHE_SETTLED) | (act_f16 ? (CGLM_SEQ_QKV_F16 | CGLM_SEQ_OUT_F16) : 0);
+            s.kv_local = 0;
             n_tok += seqs[i].qlen;
         }
     };
@@ -760,7 +779,7 @@ int cglm_attn_forward_host(cglm_kv_arena *a, const cglm_attn_seq *seqs, int n_se
     // prompts keep the staged pipeline below.
     {
         constexpr long long kZeroCopyMaxBytes = 128 * 1024;
-        bool decode_only = fast_decode_shape(a) && static_cast<long long>(n_seq) * row * 4 <= kZeroCopyMaxBytes;
+        bool decode_only = fast_decode_shape(a) && static_cast<long long>(n_seq) * row * static_cast<long long>(esz) <= kZeroCopyMaxBytes;
         for (int i = 0; i < n_seq && decode_only; ++i) decode_only = seqs[i].qlen == 1;
         auto mapped = [](const void *p) -> void * {
             cudaPointerAttributes at;
@@ -773,7 +792,7 @@ int cglm_attn_forward_host(cglm_kv_arena *a, const cglm_attn_seq *seqs, int n_se
         void *din = decode_only ? mapped(qkv_host) : nullptr;
         void *dout = din ? mapped(out_host) : nullptr;
         if (din && dout) {
-            point_at(static_cast<const float *>(din), static_cast<float *>(dout));
+            point_at(din, dout);
             return cglm_attn_forward(a, dev_seqs.data(), n_seq, workspace, workspace_bytes, cuda_stream);
         }
     }
@@ -807,7 +826,7 @@ int cglm_attn_forward_host(cglm_kv_arena *a, const cglm_attn_seq *seqs, int n_se
     a->host_next = (a->host_next + 1) % cglm_kv_arena::kHostCalls;
     lock.unlock();
     if (last_in) CGLM_CUDA(cudaStreamWaitEvent(a->copy_in, last_in->kernel, 0));
-    CGLM_CUDA(cudaMemcpyAsync(dev_qkv, qkv_host, sizeof(float) * n_tok * row, cudaMemcpyHostToDevice, a->copy_in));
+    CGLM_CUDA(cudaMemcpyAsync(dev_qkv, qkv_host, esz * n_tok * row, cudaMemcpyHostToDevice, a->copy_in));
     CGLM_CUDA(cudaEventRecord(me.h2d, a->copy_in));
     CGLM_CUDA(cudaStreamWaitEvent(st, me.h2d, 0));
     if (last_out) CGLM_CUDA(cudaStreamWaitEvent(st, last_out->d2h, 0));
@@ -815,7 +834,7 @@ int cglm_attn_forward_host(cglm_kv_arena *a, const cglm_attn_seq *seqs, int n_se
     if (rc != CGLM_OK) return rc;
     CGLM_CUDA(cudaEventRecord(me.kernel, st));
     CGLM_CUDA(cudaStreamWaitEvent(a->copy_out, me.kernel, 0));
-    CGLM_CUDA(cudaMemcpyAsync(out_host, dev_out, sizeof(float) * n_tok * orow, cudaMemcpyDeviceToHost, a->copy_out));
+    CGLM_CUDA(cudaMemcpyAsync(out_host, dev_out, esz * n_tok * orow, cudaMemcpyDeviceToHost, a->copy_out));
     CGLM_CUDA(cudaEventRecord(me.d2h, a->copy_out));
     me.dev_in = dev_qkv;
     me.dev_out = dev_out;
@@ -844,7 +863,7 @@ int cglm_attn_splitkv_combine(const float *partials, int n_part, int n_head, int
 }
 
 size_t cglm_attn_splitkv_xchg_bytes(int n_rank, int n_head, int head_dim) {
-    if (n_rank <= 0 || n_rank > kXchgMaxRanks || n_head <= 0 || head_dim <= 0) return 0;
+    if (n_rank <= 0 || n_rank > kXchgMaxRanks || n_head <= 0 || head_dim <= 0 || (head_dim & 1)) return 0;
     return sizeof(unsigned int) * xchg_slot_word(2, 0, n_rank, n_head * (head_dim + 2));
 }
 
@@ -895,32 +914,65 @@ int cglm_xchg_import(const unsigned char handle[64], int owner_device, void **pt
     return CGLM_OK;
 }
 
-int cglm_attn_splitkv_push(const float *partial, void *const *xchg, int n_rank, int rank, int n_head, int head_dim,
-                           void *cuda_stream) {
-    if (!partial || !xchg || n_rank <= 0 || n_rank > kXchgMaxRanks || rank < 0 || rank >= n_rank || n_head <= 0 ||
-        head_dim <= 0 || (head_dim & 1) || (reinterpret_cast<uintptr_t>(partial) & 7))
-        return CGLM_ERR_INVALID_ARG;
-    XchgPeers peers = {};
+int cglm_attn_splitkv_step(cglm_kv_arena *a, const cglm_attn_seq *seq, void *const *xchg, int n_rank, int rank, float *out,
+                           int combine, unsigned int timeout_us, void *workspace, size_t workspace_bytes, void *cuda_stream) {
+    if (!a || !seq || !xchg || n_rank <= 0 || n_rank > kXchgMaxRanks || rank < 0 || rank >= n_rank) return CGLM_ERR_INVALID_ARG;
+    if (combine && (!out || (reinterpret_cast<uintptr_t>(out) & 15))) return CGLM_ERR_INVALID_ARG;
+    if (!workspace) return CGLM_ERR_WORKSPACE;
+    const cglm_attn_desc &d = a->desc;
+    if (!fast_decode_shape(a) || d.n_kv_head > kXchgMaxKvHeads) {
+        std::snprintf(g_err, sizeof(g_err), "the fused split-KV step needs head_dim 128, <= 16 q heads per kv head, <= %d kv heads and a capacity that is a multiple of 8",
+                      kXchgMaxKvHeads);
+        return CGLM_ERR_UNSUPPORTED;
+    }
+    const cglm_attn_seq &s = *seq;
+    if (!s.q || !s.k || !s.v || s.qlen != 1 || s.n_past < 0 || s.slot < 0 || s.slot >= a->n_slots) return CGLM_ERR_INVALID_ARG;
+    if (s.flags & ~(CGLM_SEQ_NO_APPEND | CGLM_SEQ_USE_KV_LOCAL | CGLM_SEQ_PARTIAL | CGLM_SEQ_CACHE_SETTLED)) return CGLM_ERR_INVALID_ARG;
+    if ((s.flags & CGLM_SEQ_USE_KV_LOCAL) && s.kv_local < 0) return CGLM_ERR_INVALID_ARG;
+    const int kv_before = (s.flags & CGLM_SEQ_USE_KV_LOCAL) ? s.kv_local : d.n_virtual + s.n_past;
+    const int appended = (s.flags & CGLM_SEQ_NO_APPEND) ? 0 : 1;
+    if (static_cast<long long>(kv_before) + appended > d.max_len) return CGLM_ERR_INVALID_ARG;
+    if (kv_before + appended < 1) {
+        std::snprintf(g_err, sizeof(g_err), "a rank of a fused split-KV step must hold at least one attended position");
+        return CGLM_ERR_UNSUPPORTED;
+    }
+    if (d.rope_type == CGLM_ROPE_CHATGLM && !s.position_ids && s.n_ctx < 2) return CGLM_ERR_INVALID_ARG;
+    if (!decode_rows_aligned(s.q, s.k, s.v, s.q_head_stride, s.kv_head_stride, s.q_roped, s.k_roped)) {
+        std::snprintf(g_err, sizeof(g_err), "q, k, v rows must be 16-byte aligned (pointers and head strides)");
+        return CGLM_ERR_UNSUPPORTED;
+    }
+    const WsLayout lay = ws_layout(d, a->n_sm, 1, 0, 0);
+    if (workspace_bytes < lay.total) return CGLM_ERR_WORKSPACE;
+    XchgDev xd = {};
     for (int r = 0; r < n_rank; ++r) {
         if (!xchg[r] || (reinterpret_cast<uintptr_t>(xchg[r]) & 15)) return CGLM_ERR_INVALID_ARG;
-        peers.buf[r] = xchg[r];
+        xd.peer[r] = static_cast<unsigned int *>(xchg[r]);
     }
-    xchg_push_kernel<<<n_rank, 256, 0, static_cast<cudaStream_t>(cuda_stream)>>>(partial, peers, n_rank, rank,
-                                                                              n_head * (head_dim + 2));
-    g_launch_count += 1;
-    CGLM_CUDA(cudaGetLastError());
-    return CGLM_OK;
-}
-
-int cglm_attn_splitkv_combine_arrived(void *xchg_local, int n_rank, int n_head, int head_dim, float *out,
-                                      void *workspace, unsigned int timeout_us, void *cuda_stream) {
-    if (!xchg_local || !out || n_rank <= 0 || n_rank > kXchgMaxRanks || n_head <= 0 || head_dim <= 0)
-        return CGLM_ERR_INVALID_ARG;
-    if (!workspace) return CGLM_ERR_WORKSPACE;
-    xchg_combine_kernel<<<1, 1024, 0, static_cast<cudaStream_t>(cuda_stream)>>>(
-        static_cast<unsigned int *>(xchg_local), n_rank, n_head, head_dim, out, static_cast<WsHeader *>(workspace), timeout_us);
-    g_launch_count += 1;
-    CGLM_CUDA(cudaGetLastError());
+    xd.out = out;
+    xd.n_rank = n_rank;
+    xd.rank = rank;
+    xd.combine = combine != 0;
+    xd.timeout_us = timeout_us ? timeout_us : 20000u;
+    LaunchCtx cx = make_launch_ctx(a, static_cast<uint8_t *>(workspace), lay, static_cast<cudaStream_t>(cuda_stream));
+    static thread_local DecodeTable tab;
+    SeqDev &o = tab.seqs[0];
+    o = SeqDev{};
+    o.q = s.q; o.k = s.k; o.v = s.v;
+    o.q_tok_stride = s.q_tok_stride; o.q_head_stride = s.q_head_stride;
+    o.kv_tok_stride = s.kv_tok_stride; o.kv_head_stride = s.kv_head_stride;
+    o.position_ids = s.position_ids;
+    o.out = nullptr; o.q_roped = s.q_roped; o.k_roped = s.k_roped;
+    o.partial = nullptr;   // the kernel points it into the local exchange buffer once it knows the step number
+    o.slot = s.slot; o.qlen = 1; o.n_past = s.n_past; o.n_ctx = s.n_ctx;
+    o.kv_before = kv_before;
+    o.flags = s.flags | CGLM_SEQ_PARTIAL;
+    tab.n_seq = 1;
+    tab.settled = (s.flags & CGLM_SEQ_CACHE_SETTLED) ? 1 + decode_l2_ahead() : 0;
+    tab.trigger = decode_trigger();
+    tab.pad = 0;
+    tab.prefix[0] = 0;
+    tab.prefix[1] = (kv_before + appended + kDecodeTile - 1) / kDecodeTile;
+    CGLM_CUDA(launch_decode(cx, tab, false, &xd));
     return CGLM_OK;
 }
 

@@ -97,6 +97,8 @@ extern "C" int cglm_attn_decode_static(cglm_kv_arena *arena, const cglm_attn_seq
     static thread_local DecodeTable tab;
     tab.n_seq = n_seq;
     tab.settled = 0;
+    tab.trigger = 2;
+    tab.pad = 0;
     tab.prefix[0] = 0;
     for (int i = 0; i < n_seq; ++i) {
         const cglm_attn_seq &s = seqs[i];

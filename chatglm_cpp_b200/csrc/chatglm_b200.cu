@@ -217,4 +217,124 @@ void BasicAttention::load_prefix_cache(ModelContext *mctx, const Tensor *past_kv
     CHATGLM_CHECK_CGLM(cglm_kv_load_prefix(mctx->arena_, slot_, past_kv->data, mctx->stream_));
 }
 
+// ---- DecodeStep ----------------------------------------------------------------------------------------------------
+DecodeStep::DecodeStep(ModelContext *mctx, const std::vector<const BasicAttention *> &layers) : mctx_(mctx), layers_(layers) {
+    CHATGLM_CHECK(mctx && mctx->kv_allocated()) << "kv buffer not allocated";
+    CHATGLM_CHECK(!layers.empty()) << "no layers";
+    cudaStream_t st;
+    CHATGLM_CHECK_CUDA(cudaStreamCreateWithFlags(&st, cudaStreamNonBlocking));
+    stream_ = st;
+    // a workspace of its own: the captured graph holds its address, the context's may move when a longer prompt comes
+    workspace_bytes_ = cglm_attn_workspace_bytes(&mctx->desc_, 1, 1);
+    CHATGLM_CHECK(workspace_bytes_ > 0) << "invalid attention configuration";
+    CHATGLM_CHECK_CUDA(cudaMalloc(&workspace_, workspace_bytes_));
+    CHATGLM_CHECK_CGLM(cglm_attn_workspace_init(workspace_, workspace_bytes_, stream_));
+    cudaEvent_t e0, e1;
+    CHATGLM_CHECK_CUDA(cudaEventCreateWithFlags(&e0, cudaEventDisableTiming));
+    CHATGLM_CHECK_CUDA(cudaEventCreateWithFlags(&e1, cudaEventDisableTiming));
+    ev_in_ = e0;
+    ev_out_ = e1;
+    CHATGLM_CHECK_CUDA(cudaMalloc(reinterpret_cast<void **>(&n_past_dev_), sizeof(int)));
+    CHATGLM_CHECK_CUDA(cudaMemset(n_past_dev_, 0, sizeof(int)));
+    const cglm_attn_desc &d = mctx->desc_;
+    const int64_t hidden = static_cast<int64_t>(d.n_head) * d.head_dim;
+    const int64_t width = hidden + 2LL * d.head_dim * d.n_kv_head;
+    for (const BasicAttention *attn : layers_) {
+        CHATGLM_CHECK(attn && attn->slot_ >= 0) << "layer was not built against a context";
+        auto in = std::make_unique<Tensor>(), out = std::make_unique<Tensor>();
+        set_contiguous(in.get(), TYPE_F32, width, 1, 1);
+        set_contiguous(out.get(), TYPE_F32, hidden, 1, 1);
+        CHATGLM_CHECK_CUDA(cudaMalloc(&in->data, nbytes(in.get())));
+        CHATGLM_CHECK_CUDA(cudaMalloc(&out->data, nbytes(out.get())));
+        in->owned = out->owned = true;
+        cglm_attn_seq seq{};
+        const float *base = static_cast<const float *>(in->data);
+        if (attn->interleaved_qkv) {   // chatglm.cpp:636-644
+            seq.q = base; seq.k = base + d.head_dim; seq.v = base + 2 * d.head_dim;
+            seq.q_head_stride = seq.kv_head_stride = 3 * d.head_dim;
+        } else {                       // chatglm.cpp:646-652
+            seq.q = base; seq.k = base + hidden; seq.v = base + hidden + static_cast<long long>(d.head_dim) * d.n_kv_head;
+            seq.q_head_stride = seq.kv_head_stride = d.head_dim;
+        }
+        seq.q_tok_stride = seq.kv_tok_stride = width;
+        seq.slot = attn->slot_;
+        seq.qlen = 1;
+        seq.n_past = d.max_len - d.n_virtual - 1;   // upper bound: sizes the launch, the kernel reads the device word
+        seq.n_ctx = attn->n_ctx_;
+        seq.out = static_cast<float *>(out->data);
+        seq.flags = CGLM_SEQ_N_PAST_DEVICE;
+        seq.n_past_dev = n_past_dev_;
+        seqs_.push_back(seq);
+        qkv_.push_back(std::move(in));
+        context_.push_back(std::move(out));
+    }
+}
+
+DecodeStep::~DecodeStep() {
+    cudaStreamSynchronize(static_cast<cudaStream_t>(stream_));
+    if (graph_exec_) cudaGraphExecDestroy(static_cast<cudaGraphExec_t>(graph_exec_));
+    for (auto &t : qkv_) cudaFree(t->data);
+    for (auto &t : context_) cudaFree(t->data);
+    cudaFree(n_past_dev_);
+    cudaFree(workspace_);
+    cudaEventDestroy(static_cast<cudaEvent_t>(ev_in_));
+    cudaEventDestroy(static_cast<cudaEvent_t>(ev_out_));
+    cudaStreamDestroy(static_cast<cudaStream_t>(stream_));
+}
+
+void DecodeStep::set_n_past(int n_past) {
+    CHATGLM_CHECK(n_past >= 0 && n_past < mctx_->desc_.max_len - mctx_->desc_.n_virtual) << "n_past " << n_past << " beyond the cache";
+    cudaStream_t st = static_cast<cudaStream_t>(stream_);
+    CHATGLM_CHECK_CUDA(cudaStreamSynchronize(st));
+    CHATGLM_CHECK_CUDA(cudaMemcpyAsync(n_past_dev_, &n_past, sizeof(int), cudaMemcpyHostToDevice, st));
+    CHATGLM_CHECK_CUDA(cudaStreamSynchronize(st));
+    n_past_ = n_past;
+}
+
+void DecodeStep::record(int layer, void *stream) {
+    CHATGLM_CHECK(layer >= 0 && layer < static_cast<int>(seqs_.size())) << "no such layer";
+    CHATGLM_CHECK_CGLM(cglm_attn_forward(mctx_->arena_, &seqs_[layer], 1, workspace_, workspace_bytes_, stream ? stream : stream_));
+}
+
+void DecodeStep::record_advance(void *stream) {
+    CHATGLM_CHECK_CGLM(cglm_seq_advance(n_past_dev_, 1, 1, stream ? stream : stream_));
+}
+
+void DecodeStep::run() {
+    CHATGLM_CHECK(n_past_ + 1 <= mctx_->desc_.max_len - mctx_->desc_.n_virtual) << "the cache is full";
+    cudaStream_t st = static_cast<cudaStream_t>(stream_), outer = static_cast<cudaStream_t>(mctx_->stream_);
+    CHATGLM_CHECK_CUDA(cudaEventRecord(static_cast<cudaEvent_t>(ev_in_), outer));
+    CHATGLM_CHECK_CUDA(cudaStreamWaitEvent(st, static_cast<cudaEvent_t>(ev_in_), 0));
+    if (steps_ == 0) {
+        // the first step runs eagerly: whatever the library sets up on a first launch happens outside a capture
+        for (int l = 0; l < static_cast<int>(seqs_.size()); l++) record(l);
+        record_advance();
+    } else if (!graph_exec_) {
+        cudaGraph_t graph = nullptr;
+        CHATGLM_CHECK_CUDA(cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal));
+        try {
+            for (int l = 0; l < static_cast<int>(seqs_.size()); l++) record(l);
+            record_advance();
+        } catch (...) {
+            cudaStreamEndCapture(st, &graph);
+            if (graph) cudaGraphDestroy(graph);
+            throw;
+        }
+        CHATGLM_CHECK_CUDA(cudaStreamEndCapture(st, &graph));
+        cudaGraphExec_t exec = nullptr;
+        cudaError_t e = cudaGraphInstantiate(&exec, graph, 0);
+        cudaGraphDestroy(graph);
+        CHATGLM_CHECK(e == cudaSuccess) << "CUDA error: " << cudaGetErrorString(e);
+        graph_exec_ = exec;
+    }
+    if (steps_ > 0) {
+        CHATGLM_CHECK_CUDA(cudaGraphLaunch(static_cast<cudaGraphExec_t>(graph_exec_), st));
+        replays_ += 1;
+    }
+    CHATGLM_CHECK_CUDA(cudaEventRecord(static_cast<cudaEvent_t>(ev_out_), st));
+    CHATGLM_CHECK_CUDA(cudaStreamWaitEvent(outer, static_cast<cudaEvent_t>(ev_out_), 0));
+    n_past_ += 1;
+    steps_ += 1;
+}
+
 }  // namespace chatglm

@@ -18,7 +18,8 @@ namespace cglm {
 struct WsHeader {
     unsigned int magic;   // kWsMagic once cglm_attn_workspace_init ran
     int status;           // sticky device-side status (0 or CGLM_ERR_*)
-    int reserved[62];
+    int xchg_items;       // split-KV step: kv heads of this rank whose partial rows have been published (self-resetting)
+    int reserved[61];
 };
 static_assert(sizeof(WsHeader) == 256, "control block is 256 bytes");
 constexpr unsigned int kWsMagic = 0x5a5a5a5au;  // one byte repeated, so that a memset can write it
@@ -156,6 +157,14 @@ __device__ __forceinline__ void named_bar_sync(int id, int n_threads) {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(n_threads) : "memory");
 }
 
+// ---- activations: f32, or f16 with CGLM_SEQ_QKV_F16 / CGLM_SEQ_OUT_F16 (element indices either way) -----------------
+__device__ __forceinline__ float ld_act(const float *base, long long e, bool f16) {
+    return f16 ? __half2float(__ldg(reinterpret_cast<const __half *>(base) + e)) : __ldg(base + e);
+}
+__device__ __forceinline__ void st_out(float *base, long long e, bool f16, float x) {
+    if (f16) reinterpret_cast<__half *>(base)[e] = __float2half_rn(x); else base[e] = x;
+}
+
 // ---- RoPE pieces shared by every kernel --------------------------------------------------------------
 // Angle i of a position: theta_0 = pos, theta_{j+1} = theta_j * theta_scale, each product rounded to f32
 // (the iterated ladder of ggml's rope cache).  cos/sin are taken in double and rounded once, which
@@ -227,6 +236,28 @@ __device__ __forceinline__ void derive_positions(const SeqDev &sq, int rope_type
     }
 }
 
+// ---- split-KV exchange buffer (one per rank, in that rank's memory, mapped into every peer) ----------------------
+// words: [0] step counter (the last step this rank combined), [1, 32) unused,
+//        then 2 sets (alternating by step) of kXchgMaxRanks * kXchgMaxKvHeads arrival words [rank][kv head],
+//        then 2 sets of n_rank partial slots of n_head * (head_dim + 2) floats (acc | m | l per q head).
+constexpr int kXchgMaxRanks = 16;
+constexpr int kXchgMaxKvHeads = 32;
+constexpr int kXchgHeaderWords = 32;
+__host__ __device__ inline size_t xchg_flag_word(int set, int rank, int g) {
+    return kXchgHeaderWords + (static_cast<size_t>(set) * kXchgMaxRanks + rank) * kXchgMaxKvHeads + g;
+}
+__host__ __device__ inline size_t xchg_slot_word(int set, int rank, int n_rank, int slot_words) {
+    return kXchgHeaderWords + 2 * kXchgMaxRanks * kXchgMaxKvHeads + (static_cast<size_t>(set) * n_rank + rank) * slot_words;
+}
+// What a fused split-KV step knows about the exchange (kernel parameter of the decode kernel's exchange instantiation).
+struct XchgDev {
+    unsigned int *peer[kXchgMaxRanks];   // every rank's buffer as mapped on this GPU; peer[rank] is the local one
+    float *out;                          // combined context f32 [n_head * head_dim] (ranks that combine)
+    int n_rank, rank;
+    int combine;                         // 0: publish only (gather to the ranks that combine)
+    unsigned int timeout_us;             // bound of the wait for the peers' arrival words
+};
+
 // ---- launchers implemented in the kernel translation units ------------------------------------------
 struct LaunchCtx {
     AttnShape shape;
@@ -275,16 +306,22 @@ constexpr int kDecodeMaxSeqPerLaunch = 128;
 struct DecodeTable {
     int n_seq;
     int settled;   // 0, or 1 + tiles per CTA to pull into L2 ahead of the ring: every sequence carries CGLM_SEQ_CACHE_SETTLED
+    int trigger;   // when a CTA releases the next kernel of the stream: 0 at its start, 1 last tile requested, 2 last tile consumed
+    int pad;
     int prefix[kDecodeMaxSeqPerLaunch + 2];   // prefix[i] = 64-token tiles of sequences [0, i), per kv head
     SeqDev seqs[kDecodeMaxSeqPerLaunch];
 };
-cudaError_t launch_decode(const LaunchCtx &cx, const DecodeTable &tab, bool n_past_on_device = false);
-// The decode kernel reads q/k/v head rows (and writes the optional roped copies) sixteen bytes at a time.
+// xchg != null: the single sequence of tab is one rank's slice of a split-KV step (CGLM_SEQ_PARTIAL semantics); the
+// kernel publishes its (acc, m, l) rows into every rank's exchange buffer and, on ranks that combine, merges them.
+cudaError_t launch_decode(const LaunchCtx &cx, const DecodeTable &tab, bool n_past_on_device = false,
+                          const XchgDev *xchg = nullptr);
+// The decode kernel reads q/k/v head rows four elements at a time (sixteen bytes of f32, eight of f16) and writes the
+// optional roped copies sixteen bytes at a time.
 inline bool decode_rows_aligned(const float *q, const float *k, const float *v, long long q_head_stride,
-                                long long kv_head_stride, const float *q_roped, const float *k_roped) {
-    const uintptr_t bits = reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v) |
-                           reinterpret_cast<uintptr_t>(q_roped) | reinterpret_cast<uintptr_t>(k_roped);
-    return (bits & 15) == 0 && q_head_stride % 4 == 0 && kv_head_stride % 4 == 0;
+                                long long kv_head_stride, const float *q_roped, const float *k_roped, bool qkv_f16 = false) {
+    const uintptr_t in_bits = reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v);
+    const uintptr_t out_bits = reinterpret_cast<uintptr_t>(q_roped) | reinterpret_cast<uintptr_t>(k_roped);
+    return (in_bits & (qkv_f16 ? 7 : 15)) == 0 && (out_bits & 15) == 0 && q_head_stride % 4 == 0 && kv_head_stride % 4 == 0;
 }
 // tcgen05 prefill (head_dim 128, n_past == 0, qlen >= 128): per-call tensor maps over the f16 q staging buffer
 // [H][s_pad][D] and over the slot's caches cut at the attended length

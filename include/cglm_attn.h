@@ -72,6 +72,17 @@ typedef struct cglm_kv_arena cglm_kv_arena;
 
 /* Allocates and zero-fills the arena on the current CUDA device.  Synchronous. */
 int cglm_kv_arena_create(const cglm_attn_desc *desc, int n_slots, cglm_kv_arena **out);
+/* The same object over caches the CALLER owns, for a host that already has its kv buffer (the reference allocates one
+ * for all layers, chatglm.h:627-628) and cannot move it: k_base = f16 [n_slots][n_kv_head][max_len][head_dim], every
+ * slot's k_cache back to back; v_base = f16 [n_slots][n_kv_head][head_dim][max_len], every slot's v_cache back to back
+ * (in ggml terms: create all k_cache tensors, then all v_cache tensors, before ggml_backend_alloc_ctx_tensors).  Both
+ * device memory of the current device, 128-byte aligned; nothing is zero-filled, copied or freed by the library.
+ * angle_table: optional device memory of cglm_kv_angle_table_bytes(desc) bytes (128-byte aligned) that the library
+ * fills once with the (cos, sin) of every cache position; NULL makes the kernels evaluate the angles on the fly
+ * (same values, a few microseconds more per decode launch).  cglm_kv_arena_destroy releases only the handle. */
+int cglm_kv_arena_adopt(const cglm_attn_desc *desc, int n_slots, void *k_base, void *v_base, void *angle_table,
+                        cglm_kv_arena **out);
+size_t cglm_kv_angle_table_bytes(const cglm_attn_desc *desc);
 int cglm_kv_arena_destroy(cglm_kv_arena *arena);
 /* Device pointers of one slot's tensors (the public k_cache / v_cache members, chatglm.h:470-471). */
 void *cglm_kv_arena_k_cache(const cglm_kv_arena *arena, int slot);
@@ -94,7 +105,8 @@ int cglm_kv_slot_copy(cglm_kv_arena *arena, int slot, void *k_host, void *v_host
  *   interleaved (ChatGLM-6B v1): q = qkv, k = qkv + D,  v = qkv + 2*D,     tok_stride = 3*H*D,    head_stride = 3*D
  */
 typedef struct cglm_attn_seq {
-    const float *q, *k, *v;           /* f32 [qlen][heads][head_dim] through the strides below */
+    const float *q, *k, *v;           /* f32 [qlen][heads][head_dim] through the strides below (f16 data behind the
+                                         same pointers with CGLM_SEQ_QKV_F16; strides stay in elements) */
     long long q_tok_stride, q_head_stride;
     long long kv_tok_stride, kv_head_stride;
     int slot;                         /* which cache pair of the arena */
@@ -102,7 +114,8 @@ typedef struct cglm_attn_seq {
     int n_past;
     int n_ctx;                        /* prompt length; only CGLM_ROPE_CHATGLM derives ids from it (chatglm.cpp:1147-1151) */
     const int *position_ids;          /* optional [qlen] (or [2*qlen] for CGLM_ROPE_CHATGLM); NULL: derived from n_past, n_ctx */
-    float *out;                       /* context_layer f32 [qlen][n_head*head_dim] (chatglm.cpp:716-717); 16-byte aligned */
+    float *out;                       /* context_layer f32 [qlen][n_head*head_dim] (chatglm.cpp:716-717); 16-byte aligned
+                                         (f16, 8-byte aligned, with CGLM_SEQ_OUT_F16) */
     float *q_roped;                   /* optional f32 [qlen][n_head][head_dim]: q after RoPE, before the 1/sqrt(d) scale */
     float *k_roped;                   /* optional f32 [qlen][n_kv_head][head_dim]: k after RoPE (the reference ropes in place) */
     /* split-KV use only (zero otherwise) */
@@ -133,7 +146,14 @@ enum {
      * same slot.  When every one-token sequence of a call carries the flag, the fused decode kernel starts streaming
      * cache tiles (and pulls a few more into L2) while the previous kernel is still draining; q, k, v and the appended
      * row are still read and written only after that kernel has completed.  Without the flag nothing is read early. */
-    CGLM_SEQ_CACHE_SETTLED = 16
+    CGLM_SEQ_CACHE_SETTLED = 16,
+    /* f16 hand-off at either end of the path, for callers whose two Linears (chatglm.cpp:629, :719) produce and
+     * consume half precision: with CGLM_SEQ_QKV_F16 q, k and v point at f16 values (what an f16 query_key_value GEMM
+     * writes), with CGLM_SEQ_OUT_F16 out receives f16 (what an f16 dense GEMM reads).  RoPE, the 1/sqrt(d) scale and
+     * the softmax still run in f32 and the cache bits are those of the f32 path fed the same (f16-representable)
+     * values; the output is the f32 result rounded to nearest even.  q_roped / k_roped stay f32. */
+    CGLM_SEQ_QKV_F16 = 32,
+    CGLM_SEQ_OUT_F16 = 64
 };
 
 /* Scratch the kernels need for n_seq sequences per call with at most max_qlen tokens each. */
@@ -157,9 +177,11 @@ int cglm_seq_advance(int *n_past_dev, int n, int delta, void *cuda_stream);
  * The same call for callers whose activations live in host memory, as ggml_backend_tensor_set /
  * ggml_backend_tensor_get move them in the reference (chatglm.cpp:743, 764): copies the fused qkv rows
  * host->device, runs cglm_attn_forward, copies context_layer device->host, all on cuda_stream.
- *   qkv_host  f32 [n_tokens][(H+2G)*D], the rows of all sequences back to back (sequence i owns rows
- *             [tok_begin_i, tok_begin_i + qlen_i)); out_host f32 [n_tokens][H*D].
- * interleaved_qkv selects the v1 layout.  dev_qkv / dev_out are device staging buffers of at least those sizes.
+ *   qkv_host  f32 (or f16) [n_tokens][(H+2G)*D], the rows of all sequences back to back (sequence i owns rows
+ *             [tok_begin_i, tok_begin_i + qlen_i)); out_host f32 (or f16) [n_tokens][H*D].
+ * layout: CGLM_HOST_INTERLEAVED_QKV selects the v1 layout; CGLM_HOST_F16 says that all four buffers hold f16 instead of
+ * f32 (half the bytes across the bus; the kernels convert on load and store, see CGLM_SEQ_QKV_F16 / CGLM_SEQ_OUT_F16).
+ * dev_qkv / dev_out are device staging buffers of at least those sizes.
  * Only n_past / qlen / n_ctx / slot (and CGLM_SEQ_CACHE_SETTLED of flags) of each descriptor are read.
  * The two copies run on streams of the arena's own and the kernels on cuda_stream, chained by events, so that the
  * upload of one call and the download of another overlap the kernels between them (one call per layer: give
@@ -171,8 +193,9 @@ int cglm_seq_advance(int *n_past_dev, int n, int delta, void *cuda_stream);
  * host memory across PCIe, so nothing stands between two launches; the same drain-and-synchronise rule makes
  * out_host valid.
  */
-int cglm_attn_forward_host(cglm_kv_arena *arena, const cglm_attn_seq *seqs, int n_seq, int interleaved_qkv,
-                           const float *qkv_host, float *out_host, float *dev_qkv, float *dev_out,
+enum { CGLM_HOST_INTERLEAVED_QKV = 1, CGLM_HOST_F16 = 2 };
+int cglm_attn_forward_host(cglm_kv_arena *arena, const cglm_attn_seq *seqs, int n_seq, int layout,
+                           const void *qkv_host, void *out_host, void *dev_qkv, void *dev_out,
                            void *workspace, size_t workspace_bytes, void *cuda_stream);
 
 /* Makes cuda_stream wait for every device-to-host copy that cglm_attn_forward_host has enqueued for this arena: the
@@ -206,24 +229,31 @@ int cglm_attn_splitkv_combine(const float *partials, int n_part, int n_head, int
                               void *cuda_stream);
 
 /*
- * Split-KV exchange over peer memory instead of an all-gather.  (The reference runs on one device; this is the
- * "P2P" variant of the exchange step of a KV length split over the GPUs of one NVLink box.)
+ * Fused split-KV step over peer memory: ONE launch per rank and decode step.  (The reference runs on one device; this
+ * is the exchange step of a KV length split over the GPUs of one NVLink box, done inside the attention kernel.)
  *
  * Every rank owns an exchange buffer of cglm_attn_splitkv_xchg_bytes(n_rank, n_head, head_dim) bytes in its own
- * memory, zero-filled once, and mapped into its peers by the host (CUDA IPC, or plain pointers when the ranks are
- * contexts of one process).  The buffer holds a step counter, two sets (alternating by step) of n_rank partial
- * slots [n_head][head_dim+2], and two sets of n_rank arrival words.
+ * memory, zero-filled once, and mapped into its peers by the host (cglm_xchg_export / cglm_xchg_import between
+ * processes, plain pointers when the ranks are contexts of one process).  The buffer holds a step counter, two sets
+ * (alternating by step) of arrival words [rank][kv head] and two sets of n_rank partial slots [n_head][head_dim+2].
  *
- * cglm_attn_splitkv_push: step e = the local buffer's counter + 1.  Copies this rank's partial into slot `rank` of
- *   set e & 1 of EVERY rank's buffer (xchg[0..n_rank), device pointers valid on this GPU, entry `rank` its own) with
- *   plain stores, then publishes e in arrival word `rank` of each (release at system scope).
- * cglm_attn_splitkv_combine_arrived: waits until all n_rank arrival words of set e & 1 of the LOCAL buffer hold e,
- *   merges the n_rank partials like cglm_attn_splitkv_combine into out, and advances the local counter to e.  The
- *   wait is bounded: after timeout_us (0: one second) the kernel records CGLM_ERR_TIMEOUT in the workspace status
- *   word (cglm_attn_workspace_status reads it), leaves out untouched and still advances the counter.
- * Each rank calls push then combine_arrived once per step, on one stream.  Because the step counter lives on the
- * device, a captured CUDA graph of the step can be replayed.  Two sets suffice: a rank cannot push step e+2 before
- * its own combine of step e+1, which needs every peer's push of e+1, which follows that peer's combine of e.
+ * cglm_attn_splitkv_step runs the fused decode kernel over this rank's slice of the sequence (seq as for
+ * cglm_attn_forward with CGLM_SEQ_USE_KV_LOCAL and, on ranks that do not own position n_past, CGLM_SEQ_NO_APPEND;
+ * .out and .partial are ignored).  Step number e = the local buffer's counter + 1.  The thread block that completes a
+ * kv head writes its un-normalised (acc, m, l) rows into slot `rank` of set e & 1 of EVERY rank's buffer
+ * (xchg[0..n_rank), device pointers valid on this GPU, entry `rank` the local one) with plain stores, fences at system
+ * scope and publishes e in the arrival words (release).  With combine != 0 the block that publishes this rank's last
+ * kv head then waits until every arrival word of set e & 1 of the LOCAL buffer holds e, merges the n_rank partials
+ * (log-sum-exp) into out f32 [n_head * head_dim] and advances the local counter to e; with combine == 0 it only
+ * advances the counter (gather-to-root: only the ranks that need the result combine).  The wait is bounded: after
+ * timeout_us (0: 20 ms) the kernel records CGLM_ERR_TIMEOUT in the workspace status word, leaves out untouched and
+ * still advances the counter.  A host that reads CGLM_ERR_TIMEOUT from cglm_attn_workspace_status must stop stepping:
+ * the ranks are no longer in the same step, and every further combine would run into its bound as well.
+ * The waiting block waits for other GPUs only, never for another block or launch of its own GPU; ranks that share a
+ * GPU (tests) must therefore be launched with combine == 0 for all but the last of them.
+ * Two sets suffice: a rank cannot publish step e+2 before its own combine of step e+1, which needs every peer's step
+ * e+1, which that peer launched after its own combine of step e had completed.  Because the step counter lives on the
+ * device, a captured CUDA graph of the step can be replayed.  No TMA multicast and no library kernel touch peer memory.
  */
 size_t cglm_attn_splitkv_xchg_bytes(int n_rank, int n_head, int head_dim);
 /* Host plumbing for ranks that are separate processes (one per GPU): the owner allocates its zero-filled buffer
@@ -236,10 +266,9 @@ int cglm_xchg_alloc(size_t bytes, void **ptr);
 int cglm_xchg_free(void *ptr);
 int cglm_xchg_export(void *ptr, unsigned char handle[64]);
 int cglm_xchg_import(const unsigned char handle[64], int owner_device, void **ptr);
-int cglm_attn_splitkv_push(const float *partial, void *const *xchg, int n_rank, int rank, int n_head, int head_dim,
+int cglm_attn_splitkv_step(cglm_kv_arena *arena, const cglm_attn_seq *seq, void *const *xchg, int n_rank, int rank,
+                           float *out, int combine, unsigned int timeout_us, void *workspace, size_t workspace_bytes,
                            void *cuda_stream);
-int cglm_attn_splitkv_combine_arrived(void *xchg_local, int n_rank, int n_head, int head_dim, float *out,
-                                      void *workspace, unsigned int timeout_us, void *cuda_stream);
 
 /* P-Tuning v2 prefix load for one slot (BasicModel::load_prefix_cache, chatglm.h:580-615):
  * past_kv f16 [2][n_kv_head][n_virtual][head_dim] (device) -> cache positions [0, n_virtual), V transposed. */

@@ -109,6 +109,7 @@ class ModelContext {
 
   private:
     friend class BasicAttention;
+    friend class DecodeStep;
     // creates the (still unallocated) cache tensors of one attention module and returns its arena slot
     int register_attention(const cglm_attn_desc &desc, Tensor **k_cache, Tensor **v_cache);
     void ensure_workspace(int n_seq, int max_qlen);
@@ -168,9 +169,57 @@ class BasicAttention {
     Tensor *v_cache = nullptr;   // [#kvh, d, s]
 
   private:
+    friend class DecodeStep;
     int slot_ = -1;
     int head_size_ = 0;
     int n_ctx_ = 0;
+};
+
+// ---- the step loop (chatglm.cpp:726-755 forward_graph_compute, :886-925 generate) ------------------------------------
+// The reference rebuilds its ggml graph for every generated token.  A DecodeStep records the attention calls of ONE
+// decode step of a model (one call per layer, one sequence) in a CUDA graph whose kernels read the position from a
+// device word (CGLM_SEQ_N_PAST_DEVICE); run() replays that graph and advances the word, so nothing is rebuilt, uploaded
+// or re-validated per token.  The input and output tensors of every layer have fixed addresses: the caller's other
+// kernels (the two Linears, norms, MLP) write qkv(l) and read context(l).  A caller that wants its own kernels inside
+// the same graph records the layers itself with record(l) / record_advance() on a capturing stream instead of run().
+class DecodeStep {
+  public:
+    // layers: the model's attention modules in order (all built against mctx, fused-decode shapes: head_dim 128, at
+    // most 16 q heads per kv head, cache capacity a multiple of 8); mctx->alloc_kv() must have run.
+    DecodeStep(ModelContext *mctx, const std::vector<const BasicAttention *> &layers);
+    ~DecodeStep();
+    DecodeStep(const DecodeStep &) = delete;
+    DecodeStep &operator=(const DecodeStep &) = delete;
+
+    Tensor *qkv(int layer) const { return qkv_.at(layer).get(); }           // f32 [1, (#h + 2 #kvh) * d], device
+    Tensor *context(int layer) const { return context_.at(layer).get(); }   // f32 [1, #h * d], device
+    // position of the next token; also the value ChatGLM-6B v1 derives its 2-D ids from together with n_ctx
+    void set_n_past(int n_past);
+    int n_past() const { return n_past_; }
+    // enqueue one layer's call / the position advance on `stream` (nullptr: the step's own stream)
+    void record(int layer, void *stream = nullptr);
+    void record_advance(void *stream = nullptr);
+    // all layers, then n_past += 1.  The first call runs eagerly, the second captures the graph, and from then on
+    // every call is one graph launch; ordered after what the context's stream holds, and the context's stream is
+    // ordered after it
+    void run();
+    int graph_launches() const { return replays_; }
+    // device-side status of the step's kernels since the last query (synchronises the step's stream)
+    int status() { return cglm_attn_workspace_status(workspace_, stream_); }
+
+  private:
+    ModelContext *mctx_;
+    std::vector<const BasicAttention *> layers_;
+    std::vector<std::unique_ptr<Tensor>> qkv_, context_;
+    std::vector<cglm_attn_seq> seqs_;
+    int *n_past_dev_ = nullptr;
+    int n_past_ = 0;
+    void *workspace_ = nullptr;
+    size_t workspace_bytes_ = 0;
+    void *stream_ = nullptr;      // cudaStream_t: the step's own (capturable) stream
+    void *graph_exec_ = nullptr;  // cudaGraphExec_t
+    void *ev_in_ = nullptr, *ev_out_ = nullptr;
+    int steps_ = 0, replays_ = 0;
 };
 
 // ---- model file (chatglm.h:40-86, 107-203; chatglm.cpp:295-391, 1754-1848) ---------------------------------------

@@ -138,6 +138,78 @@ static void run_error_cases() {
     std::printf("case %-28s ok\n", "error behaviour");
 }
 
+// chatglm::DecodeStep: four layers of one sequence, six tokens; the first step is eager, the second captures, the
+// rest are graph launches.  Every token's context of every layer against the oracle, caches bit-exact at the end.
+static void run_decode_step_case() {
+    const int hidden = 4096, H = 32, G = 2, D = 128, max_length = 512, n_layer = 4, start = 131, n_token = 6;
+    ModelContext mctx(nullptr);
+    std::vector<BasicAttention> layers;
+    for (int l = 0; l < n_layer; l++) {
+        layers.emplace_back(&mctx, hidden, H, G, max_length, true, false, false, RopeType::CHATGLM2, 10000.f,
+                            AttentionMaskType::CAUSAL, 0);
+    }
+    mctx.alloc_kv();
+    oracle_cfg cfg = {H, G, D, max_length, 0, static_cast<int>(RopeType::CHATGLM2), 10000.f, ORACLE_MASK_CAUSAL, oracle_numerics_f32()};
+    std::mt19937 rng(77);
+    std::normal_distribution<float> dist(0.f, 1.f);
+    const size_t cache_elems = static_cast<size_t>(G) * max_length * D;
+    std::vector<std::vector<uint16_t>> kc(n_layer, std::vector<uint16_t>(cache_elems, 0)), vc(n_layer, std::vector<uint16_t>(cache_elems, 0));
+    // a prompt of `start` tokens through the ordinary call fills the caches on both sides
+    const int width = hidden + 2 * D * G;
+    for (int l = 0; l < n_layer; l++) {
+        std::vector<float> qkv(static_cast<size_t>(start) * width), want(static_cast<size_t>(start) * hidden);
+        for (auto &x : qkv) x = dist(rng);
+        Tensor *t = mctx.new_tensor_2d(TYPE_F32, width, start);
+        mctx.tensor_set(t, qkv.data(), 0, qkv.size() * sizeof(float));
+        layers[l].forward(&mctx, t, nullptr, nullptr, 0);
+        std::vector<int> ids = make_position_ids_glm2(start, 0);
+        oracle_attn_forward(&cfg, qkv.data(), width, D, qkv.data() + hidden, qkv.data() + hidden + G * D, width, D, kc[l].data(),
+                            vc[l].data(), ids.data(), nullptr, start, 0, want.data(), nullptr, nullptr);
+    }
+    mctx.synchronize();
+    mctx.reset_scratch();
+    std::vector<const BasicAttention *> ptrs;
+    for (auto &a : layers) ptrs.push_back(&a);
+    DecodeStep step(&mctx, ptrs);
+    step.set_n_past(start);
+    float worst = 0.f;
+    for (int tok = 0; tok < n_token; tok++) {
+        std::vector<std::vector<float>> qkv(n_layer, std::vector<float>(width));
+        for (int l = 0; l < n_layer; l++) {
+            for (auto &x : qkv[l]) x = dist(rng);
+            mctx.tensor_set(step.qkv(l), qkv[l].data(), 0, width * sizeof(float));
+        }
+        step.run();
+        for (int l = 0; l < n_layer; l++) {
+            std::vector<float> got(hidden), want(hidden);
+            mctx.tensor_get(step.context(l), got.data(), 0, hidden * sizeof(float));
+            int id = start + tok;
+            oracle_attn_forward(&cfg, qkv[l].data(), width, D, qkv[l].data() + hidden, qkv[l].data() + hidden + G * D, width, D,
+                                kc[l].data(), vc[l].data(), &id, nullptr, 1, start + tok, want.data(), nullptr, nullptr);
+            for (int i = 0; i < hidden; i++) worst = std::fmax(worst, std::fabs(got[i] - want[i]));
+        }
+    }
+    mctx.synchronize();
+    EXPECT(worst <= 2e-3f, "decode step: max abs error %g", worst);
+    EXPECT(step.n_past() == start + n_token, "decode step: position %d", step.n_past());
+    EXPECT(step.graph_launches() == n_token - 1, "decode step: %d graph launches for %d tokens", step.graph_launches(), n_token);
+    for (int l = 0; l < n_layer; l++) {
+        std::vector<uint16_t> gk(cache_elems), gv(cache_elems);
+        mctx.tensor_get(layers[l].k_cache, gk.data(), 0, gk.size() * 2);
+        mctx.tensor_get(layers[l].v_cache, gv.data(), 0, gv.size() * 2);
+        EXPECT(std::memcmp(gk.data(), kc[l].data(), cache_elems * 2) == 0, "decode step: k_cache of layer %d differs", l);
+        EXPECT(std::memcmp(gv.data(), vc[l].data(), cache_elems * 2) == 0, "decode step: v_cache of layer %d differs", l);
+    }
+    bool threw = false;
+    try {
+        step.set_n_past(max_length);
+    } catch (const std::runtime_error &) {
+        threw = true;
+    }
+    EXPECT(threw, "a position beyond the cache must throw");
+    std::printf("case %-28s max abs err %.3g, %d graph launches\n", "decode step graph", worst, step.graph_launches());
+}
+
 int main() {
     const Case cases[] = {
         {"glm3 gqa d128 blocked", 4096, 32, 2, 512, 0, false, RopeType::CHATGLM2, AttentionMaskType::CAUSAL, 5, false},
@@ -149,6 +221,7 @@ int main() {
     try {
         for (const Case &c : cases) run_case(c);
         run_error_cases();
+        run_decode_step_case();
     } catch (const std::exception &e) {
         std::printf("FAIL unexpected exception: %s\n", e.what());
         return 1;

@@ -62,10 +62,13 @@ def qkv_width(desc: AttnDesc, interleaved: bool) -> int:
 
 
 def run_decode_batch(desc: AttnDesc, n_past_list, seed=0, interleaved=False, n_ctx_list=None, check_rope=True,
-                     n_past_on_device=False):
+                     n_past_on_device=False, f16_io=False):
     """One decode step for a batch through the CUDA path and the oracle; asserts the parity gates.
     n_past_on_device: the kernel reads every position from a device word (CGLM_SEQ_N_PAST_DEVICE); the host field
-    then only carries an upper bound."""
+    then only carries an upper bound.
+    f16_io: the activations go in as f16 and the output comes back as f16 (CGLM_SEQ_QKV_F16 | CGLM_SEQ_OUT_F16); the
+    oracle is fed the same f16-representable values, so the cache bits and the RoPE bound do not change, and its
+    output is compared after the one extra rounding."""
     rng = np.random.default_rng(seed)
     n = len(n_past_list)
     V = desc.n_virtual
@@ -78,9 +81,13 @@ def run_decode_batch(desc: AttnDesc, n_past_list, seed=0, interleaved=False, n_c
         k, v = random_cache(rng, desc, V + P)
         upload_cache(arena, i, k, v)
         qkv = rng.standard_normal((1, qkv_width(desc, interleaved))).astype(np.float32)
+        if f16_io:
+            qkv = qkv.astype(np.float16).astype(np.float32)
         n_ctx = n_ctx_list[i] if n_ctx_list is not None else 0
-        call = A.SeqCall(qkv=torch.from_numpy(qkv).cuda(), slot=i, n_past=bound if n_past_on_device else P, n_ctx=n_ctx,
-                         out=torch.zeros(1, desc.n_head * desc.head_dim, device="cuda"),
+        qkv_dev = torch.from_numpy(qkv).cuda()
+        call = A.SeqCall(qkv=qkv_dev.half() if f16_io else qkv_dev, slot=i, n_past=bound if n_past_on_device else P, n_ctx=n_ctx,
+                         out=torch.zeros(1, desc.n_head * desc.head_dim, device="cuda",
+                                         dtype=torch.float16 if f16_io else torch.float32),
                          q_roped=torch.zeros(1, desc.n_head, desc.head_dim, device="cuda"),
                          k_roped=torch.zeros(1, desc.n_kv_head, desc.head_dim, device="cuda"),
                          flags=A.SEQ_N_PAST_DEVICE if n_past_on_device else 0,
@@ -96,7 +103,11 @@ def run_decode_batch(desc: AttnDesc, n_past_list, seed=0, interleaved=False, n_c
         want_g, qr, kr = O.attn_forward(cfg_g, qkv, interleaved, kg, vg, P, n_ctx=n_ctx or None, want_roped=True)
         kf, vf = k.copy(), v.copy()
         want_f = O.attn_forward(cfg_f, qkv, interleaved, kf, vf, P, n_ctx=n_ctx or None)
-        got = call.out.cpu().numpy()
+        got = call.out.float().cpu().numpy()
+        if f16_io:   # the path's own output rounding: half an f16 ulp of the value
+            assert np.abs(got - want_f).max() <= OUT_ATOL + 2.0 ** -11 * np.abs(want_f).max()
+            want_f = want_f.astype(np.float16).astype(np.float32)
+            want_g = want_g.astype(np.float16).astype(np.float32)
         assert_out_close(got, want_f, f"seq {i} n_past {P} vs f32 oracle")
         assert_out_close(got, want_g, f"seq {i} n_past {P} vs ggml-numerics oracle")
         gk, gv = download_cache(arena, i)

@@ -249,45 +249,113 @@ def test_explicit_position_ids_match_derived():
     assert torch.equal(arena.k_cache(0), arena.k_cache(1))
 
 
-def test_splitkv_peer_exchange_matches_combine_and_reports_a_missing_rank():
-    """The peer-memory exchange (push into every rank's buffer, combine once all arrival words hold the step) on one
-    device: four rank buffers, pushes issued before the combines on one stream, so no kernel ever waits for a later
-    one.  Two steps (both slot sets).  Then a step in which one rank never pushes: the bounded wait must run out,
-    set the status word and leave the context usable."""
+def test_fused_splitkv_step_four_ranks_on_one_device():
+    """cglm_attn_splitkv_step: attention over a slice, publication of the (acc, m, l) rows into every rank's exchange
+    buffer and the log-sum-exp combine in ONE launch per rank.  Four ranks on one device: four exchange buffers, four
+    arena slots holding contiguous slices of one sequence.  Ranks 0..2 only publish and rank 3, launched last, combines,
+    so that no kernel waits for a later launch.  Two steps (both sets of the buffers; the owner of position n_past
+    appends), checked against the one-pass oracle.  Then a step with a silent rank: the bounded wait runs out, the
+    status says so, `out` stays untouched and the context stays usable.  Then the silent rank comes back one step
+    late: its stale step number is not taken for the current one."""
+    from chatglm_cpp_b200 import _lib, sharding
     A = _A()
-    n_rank, H, D = 4, 32, 128
-    desc = make_desc(H, 2, D, 256)
-    ws = A.Workspace(desc, 1, 1)
-    rng = np.random.default_rng(5)
+    n_rank, H, G, D = 4, 32, 2, 128
+    P0 = 4096 + 37
+    cap = sharding.slice_capacity(P0 + 4, 0, n_rank) + 64
+    full = make_desc(H, G, D, 8192, theta=5.0e6)
+    local = make_desc(H, G, D, cap, theta=5.0e6)
+    rng = np.random.default_rng(1004)
+    k, v = random_cache(rng, full, P0)
+    arena, ws = A.KVArena(local, n_rank), A.Workspace(local, 1, 1)
+    for r in range(n_rank):
+        sl = sharding.split_kv(P0, 0, n_rank, r)
+        kl = np.zeros((G, cap, D), np.uint16); vl = np.zeros((G, D, cap), np.uint16)
+        kl[:, :sl.n_local] = k[:, sl.begin:sl.begin + sl.n_local]
+        vl[:, :, :sl.n_local] = v[:, :, sl.begin:sl.begin + sl.n_local]
+        upload_cache(arena, r, kl, vl)
     bufs = [A.SplitKVExchange.new_buffer(n_rank, H, D) for _ in range(n_rank)]
     ranks = [A.SplitKVExchange(bufs, r, H, D) for r in range(n_rank)]
+    cfg = oracle_cfg(full, "f32")
+
+    def launch(r, P, qkv_d, out, combine, timeout_us=0):
+        sl = sharding.split_kv(P, 0, n_rank, r)
+        arr = (_lib.AttnSeq * 1)()
+        flags = A.SEQ_USE_KV_LOCAL | (0 if sl.owns_new else A.SEQ_NO_APPEND)
+        A.fill_seq(arr[0], local, A.SeqCall(qkv=qkv_d, slot=r, n_past=P, kv_local=sl.n_local, flags=flags), False)
+        ranks[r].step(arena, ws, arr, out, combine=combine, timeout_us=timeout_us)
+        return sl
+
+    before = _lib.lib().cglm_launch_count()
+    P = P0
     for step in range(2):
-        parts = rng.standard_normal((n_rank, H, D + 2)).astype(np.float32)
-        parts[:, :, D + 1] = np.abs(parts[:, :, D + 1]) + 0.5            # l > 0
-        if step == 1:
-            parts[2, :, D] = -np.inf; parts[2, :, D + 1] = 0.0; parts[2, :, :D] = 0.0   # a rank that attended nothing
-        dev = torch.from_numpy(parts).cuda()
-        want = A.splitkv_combine(dev)
-        outs = [torch.zeros(H * D, device="cuda") for _ in range(n_rank)]
+        qkv = rng.standard_normal((1, qkv_width(full, False))).astype(np.float32)
+        qkv_d = torch.from_numpy(qkv).cuda()
+        want = O.attn_forward(cfg, qkv, False, k, v, P)          # appends position P to k, v
+        out = torch.zeros(H * D, device="cuda")
+        owner = None
         for r in range(n_rank):
-            ranks[r].push(dev[r])
-        for r in range(n_rank):
-            ranks[r].combine_arrived(outs[r], ws)
+            sl = launch(r, P, qkv_d, out if r == n_rank - 1 else None, combine=(r == n_rank - 1))
+            if sl.owns_new:
+                owner = (r, sl)
         torch.cuda.synchronize()
         assert ws.status() == 0
-        for r in range(n_rank):
-            assert torch.allclose(outs[r], want, rtol=1e-5, atol=1e-6), f"step {step} rank {r}"
-    # rank 3 stays silent: rank 0's combine gives up after 2 ms
+        assert_out_close(out.cpu().numpy().reshape(1, -1), want, f"fused split-KV step {step}")
+        r_own, sl = owner
+        gk, gv = download_cache(arena, r_own)
+        np.testing.assert_array_equal(gk[:, P - sl.begin], k[:, P])
+        np.testing.assert_array_equal(gv[:, :, P - sl.begin], v[:, :, P])
+        P += 1
+    assert _lib.lib().cglm_launch_count() - before == 2 * n_rank      # one launch per rank and step
+    for b in bufs:
+        assert int(b[0]) == 2                                        # every rank has finished step 2
+    # rank 1 stays silent: rank 3 gives up after 2 ms
     out = torch.full((H * D,), 7.0, device="cuda")
-    for r in range(3):
-        ranks[r].push(dev[r])
-    ranks[0].combine_arrived(out, ws, timeout_us=2000)
+    for r in (0, 2):
+        launch(r, P, qkv_d, None, combine=False)
+    launch(3, P, qkv_d, out, combine=True, timeout_us=2000)
     torch.cuda.synchronize()
-    from chatglm_cpp_b200 import _lib
     assert ws.status() == _lib.ERR_TIMEOUT
     assert ws.status() == 0                      # reading the status clears it
     assert torch.all(out == 7.0)                 # out untouched
     assert float(torch.ones(4, device="cuda").sum()) == 4.0   # the context still works
+    # rank 1 comes back: it publishes step 3 while the others are at step 4; the stale number must not be accepted
+    for r in (0, 1, 2):
+        launch(r, P, qkv_d, None, combine=False)
+    launch(3, P, qkv_d, out, combine=True, timeout_us=2000)
+    torch.cuda.synchronize()
+    assert [int(b[0]) for b in bufs] == [4, 3, 4, 4]
+    assert ws.status() == _lib.ERR_TIMEOUT
+    assert torch.all(out == 7.0)
+    arena.close()
+
+
+def test_fused_splitkv_step_single_rank_equals_plain_decode():
+    """One rank: the step degenerates to decode + normalisation and must agree with cglm_attn_forward; a sequence short
+    enough that one thread block holds a whole kv head takes the other publication path."""
+    from chatglm_cpp_b200 import _lib
+    A = _A()
+    for n_past in (40, 3000):
+        desc = make_desc(32, 2, 128, 4096)
+        rng = np.random.default_rng(n_past)
+        arena, ws = A.KVArena(desc, 2), A.Workspace(desc, 1, 1)
+        k, v = random_cache(rng, desc, n_past)
+        upload_cache(arena, 0, k, v)
+        upload_cache(arena, 1, k, v)
+        qkv = torch.from_numpy(rng.standard_normal((1, qkv_width(desc, False))).astype(np.float32)).cuda()
+        ref = torch.zeros(1, 4096, device="cuda")
+        A.forward_batch(arena, ws, [A.SeqCall(qkv=qkv, slot=0, n_past=n_past, out=ref)])
+        x = A.SplitKVExchange([A.SplitKVExchange.new_buffer(1, 32, 128)], 0, 32, 128)
+        arr = (_lib.AttnSeq * 1)()
+        A.fill_seq(arr[0], desc, A.SeqCall(qkv=qkv, slot=1, n_past=n_past), False)
+        out = torch.zeros(4096, device="cuda")
+        for _ in range(3):                       # the same step three times: both buffer sets, the same result
+            out.zero_()
+            x.step(arena, ws, arr, out)
+            torch.cuda.synchronize()
+            assert ws.status() == 0
+            assert_out_close(out.cpu().numpy().reshape(1, -1), ref.cpu().numpy(), f"n_past {n_past}")
+        assert torch.equal(arena.k_cache(0), arena.k_cache(1)) and torch.equal(arena.v_cache(0), arena.v_cache(1))
+        arena.close()
 
 
 def test_splitkv_partials_combine_to_full_attention():
@@ -433,6 +501,80 @@ def test_decode_with_4_byte_aligned_activation_takes_the_generic_path_and_agrees
     assert_out_close(outs[1].cpu().numpy(), outs[0].cpu().numpy(), "generic vs fused decode")
     assert torch.equal(arena.k_cache(0), arena.k_cache(1))
     assert torch.equal(arena.v_cache(0), arena.v_cache(1))
+    arena.close()
+
+
+def test_f16_hand_off_decode_configs():
+    """f16 activations in, f16 context out (the hand-off to f16 Linears either side of the path) on the decode shapes
+    of BASELINE configs 1, 3 and 5 and on generic-path shapes: cache bits and RoPE as with f32 inputs of the same values."""
+    run_decode_batch(make_desc(32, 2, 128, 2048), [512], seed=1001, f16_io=True)
+    rng = np.random.default_rng(1003)
+    run_decode_batch(make_desc(32, 2, 128, 8192), rng.integers(1024, 8192, 24).tolist(), seed=3, check_rope=False, f16_io=True)
+    run_decode_batch(make_desc(32, 32, 128, 4096, rope=O.ROPE_CHATGLM, mask=O.MASK_CHATGLM), [2048, 300, 5],
+                     seed=1005, interleaved=True, n_ctx_list=[17, 300, 4], f16_io=True)
+    run_decode_batch(make_desc(8, 2, 64, 256), [100], seed=10, f16_io=True)
+    run_decode_batch(make_desc(32, 2, 128, 1029, V=5), [0, 700], seed=9, f16_io=True)
+    run_decode_batch(make_desc(32, 2, 128, 2048), [33, 1999], seed=12, n_past_on_device=True, f16_io=True)
+
+
+@pytest.mark.parametrize("S,rope,mask,H,G", [(1024, O.ROPE_CHATGLM2, O.MASK_CAUSAL, 32, 2), (200, O.ROPE_CHATGLM, O.MASK_CHATGLM, 8, 8),
+                                             (37, O.ROPE_CHATGLM2, O.MASK_CAUSAL, 32, 2)])
+def test_f16_hand_off_prefill(S, rope, mask, H, G):
+    """BASELINE config 2 (and a v1 prompt, and a prompt short enough for the generic path) with f16 in / f16 out."""
+    A = _A()
+    desc = make_desc(H, G, 128, 2048, 0, rope, 10000.0, mask)
+    inter = rope == O.ROPE_CHATGLM
+    rng = np.random.default_rng(S)
+    arena, ws = A.KVArena(desc, 1), A.Workspace(desc, 1, S)
+    attn = A.BasicAttention(arena, 0, ws, inter)
+    k, v = random_cache(rng, desc, 0)
+    upload_cache(arena, 0, k, v)
+    qkv = rng.standard_normal((S, qkv_width(desc, inter))).astype(np.float16)
+    out, qr, kr = attn.forward(torch.from_numpy(qkv).cuda(), 0, n_ctx=S, want_roped=True, out_dtype=torch.float16)
+    torch.cuda.synchronize()
+    assert ws.status() == 0 and out.dtype == torch.float16
+    want, oqr, okr = O.attn_forward(oracle_cfg(desc, "f32"), qkv.astype(np.float32), inter, k, v, 0, n_ctx=S, want_roped=True)
+    assert_out_close(out.float().cpu().numpy(), want.astype(np.float16).astype(np.float32), f"prefill {S} f16")
+    assert ulp_distance(qr.cpu().numpy(), oqr).max() <= ROPE_MAX_ULP
+    assert ulp_distance(kr.cpu().numpy(), okr).max() <= ROPE_MAX_ULP
+    gk, gv = download_cache(arena, 0)
+    np.testing.assert_array_equal(gk, k)
+    np.testing.assert_array_equal(gv, v)
+    arena.close()
+
+
+@pytest.mark.parametrize("n", [3, 16])
+def test_f16_hand_off_through_host_buffers(n):
+    """cglm_attn_forward_host with CGLM_HOST_F16 (half the bytes across the bus) against the device call with f16
+    tensors: 3 sequences take the zero-copy route, 16 the staged pipeline."""
+    from chatglm_cpp_b200 import _lib
+    A = _A()
+    desc = make_desc(32, 2, 128, 1024)
+    rng = np.random.default_rng(n)
+    n_past = [int(p) for p in rng.integers(1, 1023, n)]
+    arena, ws = A.KVArena(desc, 2 * n), A.Workspace(desc, n, 1)
+    for i, P in enumerate(n_past):
+        k, v = random_cache(rng, desc, P)
+        upload_cache(arena, i, k, v)
+        upload_cache(arena, n + i, k, v)
+    qkv = torch.from_numpy(rng.standard_normal((n, qkv_width(desc, False))).astype(np.float16))
+    qkv_dev = qkv.cuda()
+    ref = torch.zeros(n, 4096, device="cuda", dtype=torch.float16)
+    A.forward_batch(arena, ws, [A.SeqCall(qkv=qkv_dev[i:i + 1], slot=i, n_past=P, out=ref[i:i + 1]) for i, P in enumerate(n_past)])
+    qkv_pinned, out_pinned = qkv.pin_memory(), torch.zeros(n, 4096, dtype=torch.float16).pin_memory()
+    dev_qkv, dev_out = torch.empty_like(qkv_dev), torch.empty_like(ref)
+    arr = (_lib.AttnSeq * n)()
+    for i, P in enumerate(n_past):
+        arr[i].slot, arr[i].qlen, arr[i].n_past = n + i, 1, P
+    stream = torch.cuda.current_stream().cuda_stream
+    _lib.check(_lib.lib().cglm_attn_forward_host(arena._h, arr, n, _lib.HOST_F16, qkv_pinned.data_ptr(), out_pinned.data_ptr(),
+                                                 dev_qkv.data_ptr(), dev_out.data_ptr(), ws.ptr, ws.bytes, stream), "forward_host")
+    _lib.check(_lib.lib().cglm_attn_host_drain(arena._h, stream), "host_drain")
+    torch.cuda.current_stream().synchronize()
+    assert ws.status() == 0
+    assert torch.equal(out_pinned, ref.cpu())
+    for i in range(n):
+        assert torch.equal(arena.k_cache(i), arena.k_cache(n + i)) and torch.equal(arena.v_cache(i), arena.v_cache(n + i))
     arena.close()
 
 
@@ -602,6 +744,40 @@ def test_chunked_prompt_second_chunk_attends_everything(H, G, D, M, V, rope, mas
     np.testing.assert_array_equal(gk, k)
     np.testing.assert_array_equal(gv, v)
     assert ws.status() == 0
+
+
+@pytest.mark.parametrize("with_table", [True, False])
+def test_adopted_caches_behave_like_an_arena_of_the_librarys_own(with_table):
+    """cglm_kv_arena_adopt: tensor maps (and optionally the angle table) over caller-owned cache memory.  Prefill on
+    tensor cores, decode steps and a chunk on the generic path give the same bits as on an allocated arena, and the
+    caller's tensors hold the caches."""
+    from chatglm_cpp_b200 import _lib
+    A = _A()
+    desc = make_desc(32, 2, 128, 1024)
+    n_slots = 3
+    k_all = torch.zeros(n_slots, 2, 1024, 128, dtype=torch.float16, device="cuda")
+    v_all = torch.zeros(n_slots, 2, 128, 1024, dtype=torch.float16, device="cuda")
+    table = torch.empty(_lib.lib().cglm_kv_angle_table_bytes(C.byref(desc)), dtype=torch.uint8, device="cuda") if with_table else None
+    own, mine = A.KVArena(desc, n_slots), A.KVArena(desc, n_slots, adopt=(k_all, v_all, table))
+    ws = A.Workspace(desc, 2, 256)
+    rng = np.random.default_rng(8)
+    n_past = 0
+    for qlen in (200, 1, 1, 5):
+        qkv = torch.from_numpy(rng.standard_normal((qlen, qkv_width(desc, False))).astype(np.float32)).cuda()
+        outs = [A.BasicAttention(arena, 1, ws).forward(qkv, n_past) for arena in (own, mine)]
+        torch.cuda.synchronize()
+        assert torch.equal(outs[0], outs[1]), (qlen, n_past)
+        n_past += qlen
+    assert ws.status() == 0
+    assert torch.equal(own.k_all(), k_all) and torch.equal(own.v_all(), v_all)
+    assert k_all[1, :, :n_past].abs().sum() > 0 and k_all[0].abs().sum() == 0 and k_all[2].abs().sum() == 0
+    mine.close()
+    assert k_all[1, :, :n_past].abs().sum() > 0          # the memory is still the caller's
+    h = C.c_void_p()
+    L = _lib.lib()
+    assert L.cglm_kv_arena_adopt(C.byref(desc), n_slots, k_all.data_ptr() + 2, v_all.data_ptr(), None, C.byref(h)) == _lib.ERR_INVALID_ARG
+    host = torch.zeros(16, dtype=torch.float16).pin_memory()
+    assert L.cglm_kv_arena_adopt(C.byref(desc), 1, host.data_ptr(), v_all.data_ptr(), None, C.byref(h)) == _lib.ERR_INVALID_ARG
 
 
 def test_argument_errors_return_codes():
