@@ -3,22 +3,26 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
 
-Default workload (the one the headline metric is quoted on): GLM-4-9B-shaped batched decode, a 40-layer
-attention stack, 32 q heads / 2 kv heads, head_dim 128, f16 caches of max_length 8192, 64 independent
-sequences per GPU with n_past drawn uniformly from [1024, 8191] by a seed.  A step is one decode step of all
-sequences through all 40 layers: 40 calls of cglm_attn_forward (fused RoPE + f16 append + attention).
-Sequences are independent, so N GPUs hold 64 sequences each and exchange nothing (weak scaling).
+Headline workload (the one the metric is quoted on): GLM-4-9B-shaped batched decode, a 40-layer attention stack,
+32 q heads / 2 kv heads, head_dim 128, f16 caches of max_length 8192, 64 independent sequences per GPU with n_past
+drawn uniformly from [1024, 8191] by a seed.  A step is one decode step of all sequences through all 40 layers:
+40 calls of cglm_attn_forward (fused RoPE + f16 append + attention).
 
-Prints ONE JSON line (rank 0).  `value` is whole-job tokens/s with inputs resident in HBM; `e2e` is the
-same metric through cglm_attn_forward_host with pinned host activations (H2D and D2H inside the timed
-region); `roofline` is the decode kernel's KV bytes per launch over its measured duration against the
-measured HBM copy bandwidth; `cpu_baseline` is the CPU restatement of the reference path timed on this
-box's host cores on a bounded sample.  --impl reference times only that CPU path.
+Prints ONE JSON line (rank 0).  `value` is whole-job tokens/s with inputs resident in HBM; `e2e` is the same metric
+through cglm_attn_forward_host with pinned host activations (H2D and D2H inside the timed region); `roofline` is the
+decode kernel's KV bytes per launch over its measured duration against the measured HBM copy bandwidth;
+`cpu_baseline` is the CPU restatement of the reference path timed on this box's host cores on a bounded sample, and
+`parity` compares that sample's outputs and cache rows with what the timed GPU launches produced.  With the default
+workload the line also carries `configs` (the other BASELINE configurations, short runs), `step_graph`, and under
+N > 1 GPUs `strong` (the 64 sequences sharded over the GPUs) and `split_kv` (one 131072-token sequence cut along its
+KV length, fused exchange).  --impl reference times only the CPU path.
+
+All inputs are synthetic: counter-based N(0,1) values (cglm_synth_fill_* on the device, oracle_synth_fill_* on the
+host: the same bits), shaped after the model configurations named in the workloads.
 """
 from __future__ import annotations
 
 import argparse
-import ctypes as C
 import json
 import os
 import sys
@@ -43,36 +47,54 @@ WORKLOADS = {
                                        theta=10000.0, interleaved=False, mask=0, seed=1003),
     "glm4_9b_batched_decode_b128": dict(H=32, G=2, D=128, M=8192, layers=20, seqs=128, n_past=(1024, 8191), rope=8,
                                         theta=10000.0, interleaved=False, mask=0, seed=1003),
-    "glm3_6b_decode_512": dict(H=32, G=2, D=128, M=2048, layers=1, seqs=1, n_past=(512, 512), rope=8, theta=10000.0,
+    # every sequence at the end of its cache: the condition the 70 %-of-HBM target is quoted on (n_past >= 8k)
+    "glm4_9b_batched_decode_8k": dict(H=32, G=2, D=128, M=8192, layers=40, seqs=64, n_past=(8191, 8191), rope=8,
+                                      theta=10000.0, interleaved=False, mask=0, seed=1003),
+    # BASELINE config 1: one sequence at n_past 512; 64 "layers" so that consecutive launches stream different slabs
+    "glm3_6b_decode_512": dict(H=32, G=2, D=128, M=2048, layers=64, seqs=1, n_past=(512, 512), rope=8, theta=10000.0,
                                interleaved=False, mask=0, seed=1001),
-    # BASELINE config 4: one sequence, KV length split over the GPUs, log-sum-exp combine after an all-gather
+    # BASELINE config 4: one sequence; with N GPUs the KV length is split and the partials are exchanged over NVLink
     "glm4_9b_long_131072": dict(H=32, G=2, D=128, M=131072 + 64, layers=1, seqs=1, n_past=(131072, 131072), rope=8,
                                 theta=5.0e6, interleaved=False, mask=0, seed=1004, split_kv=True),
     # BASELINE config 2: one 1024-token prompt into an empty cache, causal; the tcgen05 path
     "glm3_6b_prefill_1024": dict(H=32, G=2, D=128, M=2048, layers=1, seqs=1, n_past=(0, 0), rope=8, theta=10000.0,
                                  interleaved=False, mask=0, seed=1002, prefill=1024),
+    "glm3_6b_prefill_8192": dict(H=32, G=2, D=128, M=8192, layers=1, seqs=1, n_past=(0, 0), rope=8, theta=10000.0,
+                                 interleaved=False, mask=0, seed=1002, prefill=8192),
+    # BASELINE config 5: ChatGLM-6B v1, MHA, interleaved qkv, 2-D rope
     "glm1_6b_mha_decode": dict(H=32, G=32, D=128, M=4096, layers=28, seqs=4, n_past=(2048, 2048), rope=4,
                                theta=10000.0, interleaved=True, mask=1, seed=1005),
 }
+HEADLINE = "glm4_9b_batched_decode"
 HBM_FALLBACK_GBS = 6650.0   # B200 copy bandwidth from an earlier measurement, used only without MEASURED_PEAKS.json
+TENSOR_FALLBACK_TFLOPS = 1590.0
 # (dram__bytes_read.sum + dram__bytes_write.sum) / algorithmic KV bytes of one decode launch, from the ncu capture of
-# the _small workload, whose launches are identical to the default workload's (see profiles/): 316.5 MB / 303.5 MB.
+# the _small workload, whose launches are identical to the default workload's (see profiles/).
 NCU_TRAFFIC_PER_KV_BYTE = 1.043
+TID_K, TID_V, TID_QKV = 1, 2, 3   # tensor ids of the synthetic generator
 
 
 def kv_bytes(w, n_past):
     """Algorithmic bytes of one layer call: K and V^T of every attended token, f16 (4*G*D*(n_past+1))."""
-    return int(sum(4 * w["G"] * w["D"] * (p + 1) for p in n_past))
+    return int(sum(4 * w["G"] * w["D"] * (int(p) + 1) for p in n_past))
 
 
-def draw_n_past(w, rank):
+def draw_n_past(w, rank, n=None):
     rng = np.random.default_rng(w["seed"] + 7919 * rank)
     lo, hi = w["n_past"]
-    return rng.integers(lo, hi + 1, w["seqs"]).astype(np.int32)
+    return rng.integers(lo, hi + 1, n or w["seqs"]).astype(np.int32)
 
 
 def qkv_row(w):
     return 3 * w["H"] * w["D"] if w["interleaved"] else (w["H"] + 2 * w["G"]) * w["D"]
+
+
+def peak(key, fallback):
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            return float(json.load(f)[key]), "measured"
+    except Exception:
+        return fallback, "fallback"
 
 
 class ClockSampler(threading.Thread):
@@ -108,7 +130,7 @@ class ClockSampler(threading.Thread):
                         self.reasons.add(name)
             except Exception:
                 pass
-            self._halt.wait(0.05)
+            self._halt.wait(0.02)
 
     def finish(self):
         self._halt.set()
@@ -122,65 +144,93 @@ def host_threads():
     return os.cpu_count() or 1
 
 
-def cpu_leg(w, n_past, host_caches, steps, warmup):
-    """Times the CPU oracle on one layer of the workload.  Returns (tokens/s scaled to all layers, seconds/layer)."""
+# ---- synthetic data: the same bits on the host and on the device -------------------------------------------------
+class Synth:
+    def __init__(self, device=True):
+        from oracle import attn_oracle as O
+        self.O = O
+        self.t32, self.t16 = O.synth_table()
+        if device:
+            import torch
+            from chatglm_cpp_b200 import _lib
+            self.L = _lib.lib()
+            self.d32 = torch.from_numpy(self.t32).cuda()
+            self.d16 = torch.from_numpy(self.t16.view(np.int16)).cuda()
+
+    def fill(self, tensor, seed, tid, first=0):
+        import torch
+        assert tensor.is_cuda and tensor.is_contiguous()
+        stream = torch.cuda.current_stream().cuda_stream
+        if tensor.dtype == torch.float16:
+            rc = self.L.cglm_synth_fill_f16(tensor.data_ptr(), tensor.numel(), seed, tid, first, self.d16.data_ptr(), stream)
+        else:
+            rc = self.L.cglm_synth_fill_f32(tensor.data_ptr(), tensor.numel(), seed, tid, first, self.d32.data_ptr(), stream)
+        assert rc == 0
+
+    def host_f16(self, n, seed, tid, first):
+        return self.O.synth_fill(n, seed, tid, first, self.t16)
+
+    def host_f32(self, n, seed, tid, first):
+        return self.O.synth_fill(n, seed, tid, first, self.t32)
+
+    def host_caches(self, w, seed, slots):
+        """(k, v) uint16 arrays of the given arena slots, as the device fill wrote them."""
+        G, M, D = w["G"], w["M"], w["D"]
+        per = G * M * D
+        return [(self.host_f16(per, seed, TID_K, s * per).reshape(G, M, D), self.host_f16(per, seed, TID_V, s * per).reshape(G, D, M))
+                for s in slots]
+
+
+# ---- the CPU path (our restatement of the reference's) --------------------------------------------------------------
+def cpu_decode_layer(w, n_past, n_ctx, qkv, caches, reps, warmup):
+    """One layer call of the workload on the host cores.  Returns (seconds per call, outputs [n][H*D], threads)."""
     from oracle import attn_oracle as O
     cfg = O.make_cfg(w["H"], w["G"], w["D"], w["M"], 0, w["rope"], w["theta"], w["mask"], "ggml")
-    rng = np.random.default_rng(w["seed"])
     n, H, G, D = len(n_past), w["H"], w["G"], w["D"]
-    qkv = rng.standard_normal((n, qkv_row(w))).astype(np.float32)
     if w["interleaved"]:
         q = [qkv[i] for i in range(n)]; k = [qkv[i][D:] for i in range(n)]; v = [qkv[i][2 * D:] for i in range(n)]
         hs = 3 * D
     else:
         q = [qkv[i] for i in range(n)]; k = [qkv[i][H * D:] for i in range(n)]; v = [qkv[i][(H + G) * D:] for i in range(n)]
         hs = D
-    kc = [c[0] for c in host_caches]
-    vc = [c[1] for c in host_caches]
-    n_ctx = np.maximum(n_past // 2, 2).astype(np.int32)
+    kc = [c[0] for c in caches]
+    vc = [c[1] for c in caches]
     thr = host_threads()
-    times = []
-    for it in range(warmup + steps):
+    times, out = [], None
+    for it in range(warmup + reps):
         t0 = time.perf_counter()
-        O.attn_decode_batch(cfg, q, k, v, hs, hs, kc, vc, n_past, n_ctx, n_threads=thr)
+        out = O.attn_decode_batch(cfg, q, k, v, hs, hs, kc, vc, n_past, n_ctx, n_threads=thr)
         dt = time.perf_counter() - t0
         if it >= warmup:
             times.append(dt)
-    per_layer = float(np.mean(times))
-    return n / (per_layer * w["layers"]), per_layer, thr
+    return float(np.mean(times)), np.asarray(out), thr
 
 
-def synth_host_caches(w, n_past, seed):
-    """Host caches for the reference arm: N(0,1) f16 tiled from a 4M-value pool (fast to make, same distribution)."""
-    rng = np.random.default_rng(seed)
-    pool = rng.standard_normal(1 << 22).astype(np.float16).view(np.uint16)
-    G, M, D = w["G"], w["M"], w["D"]
-    out = []
-    for i, p in enumerate(n_past):
-        n = G * M * D
-        off = (i * 104729) % (pool.size // 2)
-        k = np.resize(pool[off:], n).reshape(G, M, D).copy()
-        v = np.resize(pool[off + 17:], n).reshape(G, D, M).copy()
-        out.append((k, v))
-    return out
-
-
-def run_reference(args, w):
-    """--impl reference: the reference's CPU path (our CPU restatement of it: the reference's own arithmetic lives
-    in the ggml submodule, which is absent and unpinned, so it cannot be compiled here)."""
+def run_reference(args, name, w):
+    """--impl reference: the reference's CPU path (our CPU restatement of it: the reference's own arithmetic lives in
+    the ggml submodule, which is absent and unpinned, so it cannot be compiled here).  Same synthetic bits as the GPU arm."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
+    if w.get("prefill") or w.get("split_kv"):
+        print(json.dumps({"impl": "reference", "unavailable": "the CPU arm times the batched decode workloads only"}), flush=True)
+        return
+    syn = Synth(device=False)
     n_past = draw_n_past(w, 0)
-    caches = synth_host_caches(w, n_past, w["seed"])
+    n = len(n_past)
+    n_ctx = np.maximum(n_past // 2, 2).astype(np.int32)
+    caches = syn.host_caches(w, w["seed"], range(n))      # layer 0: slots [0, n)
+    qkv = syn.host_f32(n * qkv_row(w), w["seed"], TID_QKV, 0).reshape(n, qkv_row(w))
     # each step: one of the workload's layers over all sequences
-    tps, per_layer, thr = cpu_leg(w, n_past, caches, args.steps, max(1, min(args.warmup, 3)))
-    sample = f"1 of {w['layers']} layers x {w['seqs']} sequences per step, scaled to {w['layers']} layers"
+    per_layer, _, thr = cpu_decode_layer(w, n_past, n_ctx, qkv, caches, args.steps, max(1, min(args.warmup, 3)))
+    tps = n / (per_layer * w["layers"])
+    sample = (f"1 of {w['layers']} layers x {w['seqs']} sequences per step (independent layers of identical shape), "
+              f"time scaled to {w['layers']} layers")
     line = {
         "impl": "reference", "metric": "decode_attention_tokens_per_s", "value": tps, "unit": "tokens/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": per_layer * w["layers"] * 1e3,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
-        "config": workload_config(args, w, n_past),
+        "config": workload_config(name, w, n_past, args.gpus),
         "cpu_baseline": {"value": tps, "unit": "tokens/s", "cores": thr, "kind": "port", "sample": sample},
         "e2e": {"value": tps, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -188,214 +238,278 @@ def run_reference(args, w):
     print(json.dumps(line), flush=True)
 
 
-def workload_config(args, w, n_past):
-    return {"workload": args.workload, "n_head": w["H"], "n_kv_head": w["G"], "head_dim": w["D"],
-            "max_length": w["M"], "layers": w["layers"], "seqs_per_gpu": w["seqs"],
-            "global_batch": w["seqs"] * args.gpus, "n_past_range": list(w["n_past"]),
-            "n_past_mean": float(np.mean(n_past)), "parallelism": f"sequence-sharded x{args.gpus}, no collective",
+def workload_config(name, w, n_past, gpus):
+    return {"workload": name, "n_head": w["H"], "n_kv_head": w["G"], "head_dim": w["D"],
+            "max_length": w["M"], "layers": w["layers"], "seqs_per_gpu": len(n_past),
+            "global_batch": len(n_past) * gpus, "n_past_range": list(w["n_past"]),
+            "n_past_mean": float(np.mean(n_past)), "parallelism": f"sequence-sharded x{gpus}, no collective",
             "l2_policy": "inputs larger than L2 (each launch streams its own cache slabs; a step touches every layer's)"}
 
 
-def run_split_kv(args, w):
-    """Config 4: strong scaling of ONE long sequence.  Rank r holds a contiguous slice of the KV length in its own
-    arena, runs the fused decode over it into an (acc, m, l) partial, the partials are all-gathered (NCCL) into
-    every rank's memory and merged by the log-sum-exp combine kernel.  Each step rotates through enough copies of
-    the slice that the working set is at least four times the L2."""
+# ---- distributed plumbing -----------------------------------------------------------------------------------------
+class Dist:
+    def __init__(self):
+        import torch
+        self.rank = int(os.environ.get("RANK", "0"))
+        self.world = int(os.environ.get("WORLD_SIZE", "1"))
+        self.local = int(os.environ.get("LOCAL_RANK", "0"))
+        self.dist = None
+        if not torch.cuda.is_available():
+            raise SystemExit("bench.py needs a CUDA device (there is no CPU fallback); use --impl reference for the CPU path")
+        torch.cuda.set_device(self.local)
+        if self.world > 1:
+            import torch.distributed as dist
+            os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+            dist.init_process_group("nccl", device_id=torch.device("cuda", self.local))
+            self.dist = dist
+
+    def barrier(self):
+        import torch
+        if self.world > 1:
+            self.dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_ms(self, ms):
+        import torch
+        if self.world > 1:
+            t = torch.tensor([ms], device="cuda", dtype=torch.float64)
+            self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
+            return float(t.item())
+        return ms
+
+    def close(self):
+        if self.world > 1:
+            import torch
+            torch.cuda.synchronize()
+            killer = threading.Timer(30.0, lambda: os._exit(0))   # a slow teardown must not outlive the measurement
+            killer.daemon = True
+            killer.start()
+            self.dist.barrier()
+            self.dist.destroy_process_group()
+            killer.cancel()
+
+
+def timed(dd, fn, steps, warmup):
+    """W untimed calls, then K timed calls between CUDA events on the launching stream, barrier + device synchronise on
+    both sides, max over ranks.  Returns (milliseconds for the K calls, this library's launches on this rank)."""
     import torch
-    import torch.distributed as dist
-
-    from chatglm_cpp_b200 import _lib, sharding
-    from chatglm_cpp_b200 import attention as A
-
-    rank = int(os.environ.get("RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    torch.cuda.set_device(local)
-    if world > 1:
-        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    from chatglm_cpp_b200 import _lib
     L = _lib.lib()
-    H, G, D = w["H"], w["G"], w["D"]
-    P = w["n_past"][0]
-    sl = sharding.split_kv(P, 0, world, rank)
-    cap = sharding.slice_capacity(P, 0, world) + 64
-    desc = _lib.AttnDesc(H, G, D, cap, 0, w["rope"], w["theta"], w["mask"])
-    local_bytes = 4 * G * D * (sl.n_local + (1 if sl.owns_new else 0))
-    n_rot = max(2, int(np.ceil(4 * 126e6 / max(local_bytes, 1))))
-    arena = A.KVArena(desc, n_rot)
-    g = torch.Generator(device="cuda"); g.manual_seed(w["seed"] + rank)
-    arena.k_all().view(-1).copy_(torch.randn(arena.k_all().numel(), device="cuda", generator=g).half())
-    arena.v_all().view(-1).copy_(torch.randn(arena.v_all().numel(), device="cuda", generator=g).half())
-    ws = A.Workspace(desc, 1, 1)
-    g0 = torch.Generator(device="cuda"); g0.manual_seed(w["seed"])           # q is replicated on every rank
-    qkv = torch.randn(1, qkv_row(w), device="cuda", generator=g0)
-    partial = torch.zeros(H, D + 2, device="cuda")
-    gathered = torch.zeros(world, H, D + 2, device="cuda")
-    # Exchange of the partials: "p2p" = every rank stores its partial into every peer's exchange buffer over NVLink
-    # (buffers mapped with CUDA IPC) and the combine waits for the arrival words; "nccl" = all-gather + combine.
-    xchg = None
-    if world > 1 and args.exchange == "p2p":
-        # every kernel of the step runs once locally before the ranks meet (module loading happens here, not inside
-        # the first bounded wait)
-        solo = A.SplitKVExchange([A.SplitKVExchange.new_buffer(1, H, D)], 0, H, D)
-        warm = (_lib.AttnSeq * 1)()
-        A.fill_seq(warm[0], desc, A.SeqCall(qkv=qkv, slot=0, n_past=P, kv_local=sl.n_local,
-                                            flags=_lib.SEQ_USE_KV_LOCAL | _lib.SEQ_NO_APPEND), False)
-        solo.step(arena, ws, warm, torch.zeros(H * D, device="cuda"))
-        torch.cuda.synchronize()
-        mine, handle = A.SplitKVExchange.alloc_exported(world, H, D)
-        handles = [None] * world
-        dist.all_gather_object(handles, (local, handle))
-        # imported with this rank's device current (the mapping must belong to the context whose kernels use it)
-        peers = [mine if r == rank else A.SplitKVExchange.import_handle(handles[r][1], handles[r][0]) for r in range(world)]
-        xchg = A.SplitKVExchange(peers, rank, H, D)
-        dist.barrier()
-    out = torch.zeros(1, H * D, device="cuda")
-    settled = 0 if args.no_settled else _lib.SEQ_CACHE_SETTLED     # no step writes rows below n_past of any slot
-    flags = settled | ((_lib.SEQ_USE_KV_LOCAL | (0 if sl.owns_new else _lib.SEQ_NO_APPEND)) if world > 1 else 0)
-    if world > 1 and xchg is None:
-        flags |= _lib.SEQ_PARTIAL
-    arrs = []
-    for s in range(n_rot):
-        arr = (_lib.AttnSeq * 1)()
-        A.fill_seq(arr[0], desc, A.SeqCall(qkv=qkv, slot=s, n_past=P, out=out if world == 1 else None,
-                                           partial=partial if flags & _lib.SEQ_PARTIAL else None,
-                                           kv_local=sl.n_local if world > 1 else 0, flags=flags), False)
-        arrs.append(arr)
-    it = [0]
-    timeout_us = 50000   # a rank that is more than 50 ms behind is treated as gone
+    for _ in range(warmup):
+        fn()
+    dd.barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    launches0 = L.cglm_launch_count()
+    e0.record()
+    for _ in range(steps):
+        fn()
+    e1.record()
+    dd.barrier()
+    return dd.max_ms(e0.elapsed_time(e1)), L.cglm_launch_count() - launches0
 
-    def step():
-        """One decode step of the long sequence.  1 GPU: one fused decode launch.  N GPUs, peer stores: one fused launch
-        per rank (attention over the slice + exchange + combine).  N GPUs, NCCL: decode, all-gather, combine kernel."""
-        stream = torch.cuda.current_stream().cuda_stream
-        arr = arrs[it[0] % n_rot]
-        it[0] += 1
-        if xchg is not None:
-            xchg.step(arena, ws, arr, out, combine=True, timeout_us=timeout_us)
-            return
-        rc = L.cglm_attn_forward(arena._h, arr, 1, ws.ptr, ws.bytes, stream)
-        if rc != 0:
-            raise _lib.CglmError(rc, "cglm_attn_forward")
-        if world > 1:
-            dist.all_gather_into_tensor(gathered, partial)
-            A.splitkv_combine(gathered, out.view(-1))
 
-    def barrier():
-        if world > 1:
-            dist.barrier()
+# ---- batched decode (configs 1, 3, 5 and the batch-size / length variants) ----------------------------------------------
+class DecodeState:
+    """Caches of (layers x sequences) in one arena, activations per layer, all filled by the counter-based generator."""
+
+    def __init__(self, w, rank, syn, layers=None, seqs=None):
+        import torch
+        from chatglm_cpp_b200 import _lib
+        from chatglm_cpp_b200 import attention as A
+        self.w, self.syn, self.A, self._lib = w, syn, A, _lib
+        self.layers, self.n = layers or w["layers"], seqs or w["seqs"]
+        self.seed = w["seed"] + 7919 * rank
+        self.desc = _lib.AttnDesc(w["H"], w["G"], w["D"], w["M"], 0, w["rope"], w["theta"], w["mask"])
+        self.arena = A.KVArena(self.desc, self.layers * self.n)
+        syn.fill(self.arena.k_all(), self.seed, TID_K)
+        syn.fill(self.arena.v_all(), self.seed, TID_V)
+        self.ws = A.Workspace(self.desc, max(self.n, 128), 1)
+        self.row, self.orow = qkv_row(w), w["H"] * w["D"]
+        self.qkv = torch.empty(self.layers, self.n, self.row, device="cuda")
+        syn.fill(self.qkv, self.seed, TID_QKV)
+        self.out = torch.empty(self.layers, self.n, self.orow, device="cuda")
         torch.cuda.synchronize()
 
-    for _ in range(max(args.warmup, 3)):
-        step()
-    barrier()
-    st = ws.status()
-    if st != 0:   # e.g. a peer's partial never arrived: every further step would run into the same bounded wait
-        raise SystemExit(f"[rank {rank}] device-side status {st} after the warm-up steps")
-    # A step is three launches (decode over the slice, all-gather, combine) of 20-50 us in total: issued one by one
-    # from Python the host is the bottleneck, so one pass over the rotating slices is captured in a CUDA graph and
-    # the timed region replays it.  --no-graph times the eager loop instead.
-    graph = None
-    steps = args.steps
-    launches_per_step = 1 if (xchg is not None or world == 1) else 2   # this library's kernels: decode (+ combine)
-    if not args.no_graph:
-        it[0] = 0
+    def seq_arrays(self, n_past, n_ctx, seq_ids=None, layers=None, flags=0, n_past_dev=None):
+        """One descriptor array per layer: slot of (layer l, sequence i) is l * n + i."""
+        A, _lib = self.A, self._lib
+        seq_ids = list(range(len(n_past))) if seq_ids is None else seq_ids
+        arrays = []
+        for l in range(layers or self.layers):
+            arr = (_lib.AttnSeq * len(seq_ids))()
+            for j, i in enumerate(seq_ids):
+                call = A.SeqCall(qkv=self.qkv[l, i:i + 1], slot=l * self.n + i, n_past=int(n_past[j]), n_ctx=int(n_ctx[j]),
+                                 out=self.out[l, i:i + 1], flags=flags,
+                                 n_past_dev=None if n_past_dev is None else n_past_dev[j:j + 1])
+                A.fill_seq(arr[j], self.desc, call, self.w["interleaved"])
+            arrays.append(arr)
+        return arrays
+
+    def close(self):
+        self.arena.close()
+
+
+def decode_measure(dd, st, name, n_past, args, seq_ids=None, layers=None, device=True, e2e=True, step_graph=False, steps=None):
+    """Times one decode workload on the state's arena.  Returns a dict of results (launch counts are this rank's; times
+    are the max over ranks)."""
+    import torch
+    from chatglm_cpp_b200 import _lib
+    L = _lib.lib()
+    w = st.w
+    layers = layers or st.layers
+    steps = steps or args.steps
+    n = len(n_past)
+    n_ctx = np.maximum(np.asarray(n_past) // 2, 2).astype(np.int32)
+    # Every layer call reads cache rows that no kernel of the step writes (a call appends at n_past of its own layer's
+    # slots only), which is what CGLM_SEQ_CACHE_SETTLED promises.
+    flags = 0 if args.no_settled else _lib.SEQ_CACHE_SETTLED
+    arrays = st.seq_arrays(n_past, n_ctx, seq_ids, layers, flags)
+    stream = torch.cuda.current_stream().cuda_stream
+    res = {"workload": name, "n_seq": n, "layers": layers, "kv_bytes_per_launch": kv_bytes(w, n_past)}
+
+    def step_device():
+        for l in range(layers):
+            rc = L.cglm_attn_forward(st.arena._h, arrays[l], n, st.ws.ptr, st.ws.bytes, stream)
+            if rc != 0:
+                raise _lib.CglmError(rc, "cglm_attn_forward")
+
+    if device:
+        ms, launches = timed(dd, step_device, steps, args.warmup)
+        if st.ws.status() != 0:
+            raise SystemExit(f"{name}: device-side status is not clean after the timed region")
+        res.update(ms_per_step=ms / steps, launches=int(launches), steps=steps)
+
+    if e2e:
+        # the same step through host buffers: the activations (f16: the hand-off the library offers to f16 Linears;
+        # f32 with --e2e-f32) cross the bus in both directions inside the timed region
+        host_dt = torch.float32 if args.e2e_f32 else torch.float16
+        ids = list(range(n)) if seq_ids is None else seq_ids
+        qkv_host = st.qkv[:layers][:, ids].to(host_dt).cpu().pin_memory()
+        out_host = torch.empty(layers, n, st.orow, dtype=host_dt).pin_memory()
+        n_stage = 3
+        stage_qkv = [torch.empty(n, st.row, device="cuda", dtype=host_dt) for _ in range(n_stage)]
+        stage_out = [torch.empty(n, st.orow, device="cuda", dtype=host_dt) for _ in range(n_stage)]
+        layout = (_lib.HOST_INTERLEAVED_QKV if w["interleaved"] else 0) | (0 if args.e2e_f32 else _lib.HOST_F16)
+
+        def step_host():
+            for l in range(layers):
+                rc = L.cglm_attn_forward_host(st.arena._h, arrays[l], n, layout, qkv_host[l].data_ptr(), out_host[l].data_ptr(),
+                                              stage_qkv[l % n_stage].data_ptr(), stage_out[l % n_stage].data_ptr(),
+                                              st.ws.ptr, st.ws.bytes, stream)
+                if rc != 0:
+                    raise _lib.CglmError(rc, "cglm_attn_forward_host")
+            rc = L.cglm_attn_host_drain(st.arena._h, stream)   # the step's results are read back here
+            if rc != 0:
+                raise _lib.CglmError(rc, "cglm_attn_host_drain")
+
+        e2e_steps = max(3, steps // 2)
+        ms_e2e, _ = timed(dd, step_host, e2e_steps, max(3, args.warmup))
+        if st.ws.status() != 0:
+            raise SystemExit(f"{name}: device-side status is not clean after the host-buffer region")
+        esz = 4 if args.e2e_f32 else 2
+        res["e2e"] = {"ms_per_step": ms_e2e / e2e_steps, "steps": e2e_steps, "activation_dtype": "f32" if args.e2e_f32 else "f16",
+                      "h2d_bytes_per_step": layers * n * st.row * esz, "d2h_bytes_per_step": layers * n * st.orow * esz}
+        res["_out_host"] = out_host
+
+    if step_graph:
+        # The step issued as ONE CUDA graph whose layer calls read n_past from device words (CGLM_SEQ_N_PAST_DEVICE): the
+        # form a caller replays for every new token without rebuilding anything.  The words are advanced by 0 here so
+        # that every replay is the step the other figures measure.
+        n_past_dev = torch.tensor([int(p) for p in n_past], dtype=torch.int32, device="cuda")
+        dyn = st.seq_arrays(n_past, n_ctx, seq_ids, layers, _lib.SEQ_N_PAST_DEVICE, n_past_dev)
+
+        def step_dyn():
+            s2 = torch.cuda.current_stream().cuda_stream
+            for l in range(layers):
+                rc = L.cglm_attn_forward(st.arena._h, dyn[l], n, st.ws.ptr, st.ws.bytes, s2)
+                if rc != 0:
+                    raise _lib.CglmError(rc, "cglm_attn_forward")
+            rc = L.cglm_seq_advance(n_past_dev.data_ptr(), n, 0, s2)
+            if rc != 0:
+                raise _lib.CglmError(rc, "cglm_seq_advance")
+
         side = torch.cuda.Stream()
         side.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(side):
-            for _ in range(2):
-                step()
+            step_dyn()
         torch.cuda.current_stream().wait_stream(side)
-        barrier()
-        it[0] = 0
+        torch.cuda.synchronize()
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph):
-            for _ in range(n_rot):
-                step()
-        replays = max(1, (args.steps + n_rot - 1) // n_rot)
-        steps = replays * n_rot
-        for _ in range(2):
-            graph.replay()
-        barrier()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    sampler = ClockSampler(local); sampler.start()
-    e0.record()
-    if graph is not None:
-        for _ in range(replays):
-            graph.replay()
-    else:
-        for _ in range(steps):
-            step()
-    e1.record()
-    barrier()
-    clocks = sampler.finish()
-    launches = steps * launches_per_step
-    ms = e0.elapsed_time(e1)
-    if world > 1:
-        t = torch.tensor([ms], device="cuda", dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms = float(t.item())
-    if ws.status() != 0:
-        raise SystemExit("device-side status is not clean after the timed region")
-    peak, peak_src = HBM_FALLBACK_GBS, "fallback"
-    try:
-        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
-            peak, peak_src = float(json.load(f)["hbm_gbs"]), "measured"
-    except Exception:
-        pass
-    if rank == 0:
-        step_ms = ms / steps
-        achieved = local_bytes / (step_ms * 1e-3) / 1e9
-        line = {
-            "metric": "decode_attention_tokens_per_s", "value": steps / (ms * 1e-3), "unit": "tokens/s",
-            "n_gpus": world, "steps": steps, "warmup": max(args.warmup, 3), "ms_per_step": step_ms,
-            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
-            "config": {"workload": args.workload, "n_head": H, "n_kv_head": G, "head_dim": D, "n_past": P,
-                       "kv_bytes_total": 4 * G * D * (P + 1), "kv_bytes_this_rank": local_bytes,
-                       "parallelism": ("one GPU, one fused decode launch per step" if world == 1 else
-                                       f"KV length split x{world}, " +
-                                       ("one fused launch per rank: attention + peer stores of the partial rows + LSE combine"
-                                        if xchg is not None else "decode + NCCL all-gather + combine kernel") +
-                                       f", {H * (D + 2) * 4} B per rank"),
-                       "l2_policy": f"rotates through {n_rot} copies of the slice (working set >= 4 x L2)",
-                       "issue": "eager" if graph is None else f"CUDA graph of {n_rot} steps, replayed"},
-            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "peak_source": peak_src, "kernel": "decode_kernel (the step time includes the exchange and the combine)",
-                         "algorithmic_bytes_per_launch": local_bytes, "launch_us": step_ms * 1e3, "traffic": None},
-            "cpu_baseline": None, "e2e": None, "gpu_launches": int(launches) * world, "clocks": clocks,
-        }
-        print(json.dumps(line), flush=True)
-    if world > 1:
-        # a captured graph holds the communicator's resources: release it before the group goes away, and do not let
-        # a slow teardown outlive the measurement
+            step_dyn()
+        ms_graph, _ = timed(dd, graph.replay, steps, args.warmup)
+        if st.ws.status() != 0:
+            raise SystemExit(f"{name}: device-side status is not clean after the step-graph region")
+        res["step_graph"] = {"ms_per_step": ms_graph / steps, "launches_per_step": layers + 1,
+                             "note": "one CUDA graph per decode step, n_past read from device words, replayed"}
         graph = None
-        torch.cuda.synchronize()
-        killer = threading.Timer(30.0, lambda: os._exit(0))
-        killer.daemon = True
-        killer.start()
-        dist.barrier()
-        dist.destroy_process_group()
-        killer.cancel()
+    return res
 
 
-def run_prefill(args, w):
-    """Config 2: a step is one prefill call (RoPE + f16 cache write + causal attention over the prompt).  Slots
-    rotate so that consecutive steps do not reuse a warm cache slab; q/k/v activations (f32) and the output are
-    re-read / re-written every step by construction."""
+def decode_summary(res, world, hbm_peak):
+    """The short per-config entry of the JSON line."""
+    launch_ms = res["ms_per_step"] / res["layers"]
+    achieved = res["kv_bytes_per_launch"] / (launch_ms * 1e-3) / 1e9
+    out = {"value": res["n_seq"] * world / (res["ms_per_step"] * 1e-3), "unit": "tokens/s", "ms_per_step": res["ms_per_step"],
+           "steps": res["steps"], "launch_us": launch_ms * 1e3,
+           "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak,
+                        "algorithmic_bytes_per_launch": res["kv_bytes_per_launch"]}}
+    if "e2e" in res:
+        e = res["e2e"]
+        out["e2e"] = {"value": res["n_seq"] * world / (e["ms_per_step"] * 1e-3), "unit": "tokens/s", "ms_per_step": e["ms_per_step"],
+                      "h2d_bytes_per_step": e["h2d_bytes_per_step"], "d2h_bytes_per_step": e["d2h_bytes_per_step"],
+                      "activation_dtype": e["activation_dtype"]}
+    if "step_graph" in res:
+        g = res["step_graph"]
+        out["step_graph"] = dict(g, value=res["n_seq"] * world / (g["ms_per_step"] * 1e-3), unit="tokens/s")
+    return out
+
+
+def parity_check(st, n_past, out_host_l0, reps=3):
+    """Layer 0 of the workload on the host cores (same bits: the host twin of the generator rebuilds the caches and the
+    activations) against what the timed GPU launches left behind: outputs of layer 0 and the appended cache rows.
+    Also the cpu_baseline timing.  Returns (cpu_baseline dict, parity dict)."""
     import torch
+    w, syn, n = st.w, st.syn, len(n_past)
+    n_ctx = np.maximum(np.asarray(n_past) // 2, 2).astype(np.int32)
+    caches = syn.host_caches(w, st.seed, range(n))
+    qkv = syn.host_f32(n * st.row, st.seed, TID_QKV, 0).reshape(n, st.row)
+    per_layer, want, thr = cpu_decode_layer(w, n_past, n_ctx, qkv, caches, reps, 1)
+    got = st.out[0, :n].cpu().numpy()
+    err = float(np.abs(got - want).max())
+    bit_exact = True
+    for i, p in enumerate(n_past):
+        gk = st.arena.k_cache(i)[:, int(p)].cpu().numpy().view(np.uint16)
+        gv = st.arena.v_cache(i)[:, :, int(p)].cpu().numpy().view(np.uint16)
+        bit_exact = bit_exact and np.array_equal(gk, caches[i][0][:, int(p)]) and np.array_equal(gv, caches[i][1][:, :, int(p)])
+    parity = {"max_abs": err, "tolerance": 2e-3, "cache_bit_exact": bool(bit_exact),
+              "checked": f"layer 0, {n} sequences: outputs of the device-resident run and the appended cache rows against the CPU restatement"}
+    if out_host_l0 is not None:   # the host-buffer run's layer 0 (f16 in, f16 out unless --e2e-f32)
+        parity["e2e_max_abs"] = float(np.abs(out_host_l0.float().numpy() - want).max())
+        # f16 hand-off: inputs rounded to f16 (2^-11 relative each) and the output rounded once more
+        parity["e2e_tolerance"] = 2e-3 if out_host_l0.dtype == torch.float32 else 6e-3
+    tps = n / (per_layer * w["layers"])
+    cpu = {"value": tps, "unit": "tokens/s", "cores": thr, "kind": "port",
+           "sample": f"layer 0 of {w['layers']} x {n} sequences (same bits as the GPU arm), {reps} repetitions, scaled to {w['layers']} layers"}
+    return cpu, parity
 
+
+# ---- prefill (config 2) -------------------------------------------------------------------------------------------------
+def prefill_measure(dd, name, w, args, syn, steps=None):
+    """A step is one prefill call (RoPE + f16 cache write + causal attention over the prompt).  Slots rotate so that
+    consecutive steps do not reuse a warm cache slab; q/k/v activations and the output are re-read / re-written."""
+    import torch
     from chatglm_cpp_b200 import _lib
     from chatglm_cpp_b200 import attention as A
-
-    torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
     L = _lib.lib()
     H, G, D, S = w["H"], w["G"], w["D"], w["prefill"]
+    steps = steps or args.steps
     desc = _lib.AttnDesc(H, G, D, w["M"], 0, w["rope"], w["theta"], w["mask"])
-    n_rot = 16
+    n_rot = 16 if S <= 2048 else 4
     arena = A.KVArena(desc, n_rot)
     ws = A.Workspace(desc, 1, S)
-    g = torch.Generator(device="cuda"); g.manual_seed(w["seed"])
-    qkv = [torch.randn(S, qkv_row(w), device="cuda", generator=g) for _ in range(n_rot)]
+    qkv = torch.empty(n_rot, S, qkv_row(w), device="cuda")
+    syn.fill(qkv, w["seed"], TID_QKV)
     out = [torch.empty(S, H * D, device="cuda") for _ in range(n_rot)]
     arrs = []
     for s in range(n_rot):
@@ -411,239 +525,281 @@ def run_prefill(args, w):
             raise _lib.CglmError(rc, "cglm_attn_forward")
         it[0] += 1
 
+    ms, launches = timed(dd, step, steps, max(args.warmup, 3))
+    if ws.status() != 0:
+        raise SystemExit(f"{name}: device-side status is not clean after the timed region")
+    ms /= steps
+    flops = 4.0 * H * D * S * (S + 1) / 2          # useful (causal) FLOPs of QK^T and PV
+    pk, src = peak("bf16_tflops", TENSOR_FALLBACK_TFLOPS)
+    achieved = flops / (ms * 1e-3) / 1e12
+    arena.close()
+    return {"metric": "prefill_attention_tokens_per_s", "value": S / (ms * 1e-3), "unit": "tokens/s", "ms_per_step": ms,
+            "steps": steps, "launches": int(launches), "prompt_tokens": S,
+            "l2_policy": f"rotates through {n_rot} slots and activation buffers",
+            "roofline": {"bound": "tensor", "achieved": achieved, "peak": pk, "unit": "TFLOP/s", "frac": achieved / pk,
+                         "peak_source": src, "kernel": "prefill kernels (whole call)", "useful_flops_per_call": flops}}
+
+
+# ---- one long sequence (config 4) ----------------------------------------------------------------------------------------
+def split_kv_measure(dd, name, w, args, syn, steps=None):
+    """Strong scaling of ONE long sequence.  1 GPU: one fused decode launch per step.  N GPUs: rank r holds a contiguous
+    slice of the KV length in its own arena; `p2p`: one fused launch per rank and step (attention over the slice, peer
+    stores of the partial rows into every rank's exchange buffer, bounded wait, log-sum-exp combine); `nccl`: decode,
+    all-gather, combine kernel.  Each step rotates through enough copies of the slice that the working set is at
+    least four times the L2.  The steps of one rotation are captured in a CUDA graph and the timed region replays it."""
+    import torch
+    from chatglm_cpp_b200 import _lib, sharding
+    from chatglm_cpp_b200 import attention as A
+    L = _lib.lib()
+    rank, world = dd.rank, dd.world
+    H, G, D = w["H"], w["G"], w["D"]
+    P = w["n_past"][0]
+    steps = steps or args.steps
+    sl = sharding.split_kv(P, 0, world, rank)
+    cap = sharding.slice_capacity(P, 0, world) + 64
+    desc = _lib.AttnDesc(H, G, D, cap, 0, w["rope"], w["theta"], w["mask"])
+    local_bytes = 4 * G * D * (sl.n_local + (1 if sl.owns_new else 0))
+    n_rot = max(2, int(np.ceil(4 * 126e6 / max(local_bytes, 1))))
+    arena = A.KVArena(desc, n_rot)
+    syn.fill(arena.k_all(), w["seed"] + rank, TID_K)
+    syn.fill(arena.v_all(), w["seed"] + rank, TID_V)
+    ws = A.Workspace(desc, 1, 1)
+    qkv = torch.empty(1, qkv_row(w), device="cuda")
+    syn.fill(qkv, w["seed"], TID_QKV)                       # q is replicated on every rank
+    partial = torch.zeros(H, D + 2, device="cuda")
+    gathered = torch.zeros(world, H, D + 2, device="cuda")
+    out = torch.zeros(1, H * D, device="cuda")
+    xchg = None
+    if world > 1 and args.exchange == "p2p":
+        # every kernel of the step runs once locally before the ranks meet (module loading happens here, not inside the
+        # first bounded wait)
+        solo = A.SplitKVExchange([A.SplitKVExchange.new_buffer(1, H, D)], 0, H, D)
+        warm = (_lib.AttnSeq * 1)()
+        A.fill_seq(warm[0], desc, A.SeqCall(qkv=qkv, slot=0, n_past=P, kv_local=max(sl.n_local, 1),
+                                            flags=_lib.SEQ_USE_KV_LOCAL | _lib.SEQ_NO_APPEND), False)
+        solo.step(arena, ws, warm, torch.zeros(H * D, device="cuda"))
+        torch.cuda.synchronize()
+        mine, handle = A.SplitKVExchange.alloc_exported(world, H, D)
+        handles = [None] * world
+        dd.dist.all_gather_object(handles, (dd.local, handle))
+        # imported with this rank's device current (the mapping must belong to the context whose kernels use it)
+        peers = [mine if r == rank else A.SplitKVExchange.import_handle(handles[r][1], handles[r][0]) for r in range(world)]
+        xchg = A.SplitKVExchange(peers, rank, H, D)
+        dd.barrier()
+    settled = 0 if args.no_settled else _lib.SEQ_CACHE_SETTLED     # no step writes rows below n_past of any slot
+    flags = settled | ((_lib.SEQ_USE_KV_LOCAL | (0 if sl.owns_new else _lib.SEQ_NO_APPEND)) if world > 1 else 0)
+    if world > 1 and xchg is None:
+        flags |= _lib.SEQ_PARTIAL
+    arrs = []
+    for s in range(n_rot):
+        arr = (_lib.AttnSeq * 1)()
+        A.fill_seq(arr[0], desc, A.SeqCall(qkv=qkv, slot=s, n_past=P, out=out if world == 1 else None,
+                                           partial=partial if flags & _lib.SEQ_PARTIAL else None,
+                                           kv_local=sl.n_local if world > 1 else 0, flags=flags), False)
+        arrs.append(arr)
+    it = [0]
+    timeout_us = 50000   # a rank that is more than 50 ms behind is treated as gone
+
+    def step():
+        stream = torch.cuda.current_stream().cuda_stream
+        arr = arrs[it[0] % n_rot]
+        it[0] += 1
+        if xchg is not None:
+            xchg.step(arena, ws, arr, out, combine=True, timeout_us=timeout_us)
+            return
+        rc = L.cglm_attn_forward(arena._h, arr, 1, ws.ptr, ws.bytes, stream)
+        if rc != 0:
+            raise _lib.CglmError(rc, "cglm_attn_forward")
+        if world > 1:
+            dd.dist.all_gather_into_tensor(gathered, partial)
+            A.splitkv_combine(gathered, out.view(-1))
+
+    def check_status(where):
+        # a peer's rows never arrived: every further step would run into the same bounded wait, so stop here
+        st = torch.tensor([ws.status()], device="cuda", dtype=torch.int32)
+        if world > 1:
+            dd.dist.all_reduce(st, op=dd.dist.ReduceOp.MIN)
+        if int(st.item()) != 0:
+            raise SystemExit(f"[rank {rank}] device-side status {int(st.item())} {where}")
+
     for _ in range(max(args.warmup, 3)):
         step()
-    torch.cuda.synchronize()
-    sampler = ClockSampler(0); sampler.start()
+    dd.barrier()
+    check_status("after the warm-up steps")
+    launches_per_step = 1 if (xchg is not None or world == 1) else 2   # this library's kernels: decode (+ combine)
+    it[0] = 0
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for _ in range(2):
+            step()
+    torch.cuda.current_stream().wait_stream(side)
+    dd.barrier()
+    it[0] = 0
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        for _ in range(n_rot):
+            step()
+    replays = max(1, (steps + n_rot - 1) // n_rot)
+    steps = replays * n_rot
+    for _ in range(2):
+        graph.replay()
+    dd.barrier()
+    check_status("after the first graph replays")
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    launches0 = L.cglm_launch_count()
     e0.record()
-    for _ in range(args.steps):
-        step()
+    for _ in range(replays):
+        graph.replay()
     e1.record()
+    dd.barrier()
+    ms = dd.max_ms(e0.elapsed_time(e1))
+    check_status("after the timed region")
+    step_ms = ms / steps
+    pk, src = peak("hbm_gbs", HBM_FALLBACK_GBS)
+    achieved = local_bytes / (step_ms * 1e-3) / 1e9
+    res = {"metric": "decode_attention_tokens_per_s", "value": steps / (ms * 1e-3), "unit": "tokens/s", "ms_per_step": step_ms,
+           "steps": steps, "launches": steps * launches_per_step, "n_past": P, "kv_bytes_total": 4 * G * D * (P + 1),
+           "kv_bytes_this_rank": local_bytes,
+           "parallelism": ("one GPU, one fused decode launch per step" if world == 1 else
+                           f"KV length split x{world}, " +
+                           ("one fused launch per rank: attention + peer stores of the partial rows + LSE combine"
+                            if xchg is not None else "decode + NCCL all-gather + combine kernel") +
+                           f", {H * (D + 2) * 4} B per rank"),
+           "l2_policy": f"rotates through {n_rot} copies of the slice (working set >= 4 x L2)",
+           "issue": f"CUDA graph of {n_rot} steps, replayed",
+           "roofline": {"bound": "hbm", "achieved": achieved, "peak": pk, "unit": "GB/s", "frac": achieved / pk, "peak_source": src,
+                        "kernel": "decode_kernel (the step time includes the exchange and the combine)",
+                        "algorithmic_bytes_per_launch": local_bytes, "launch_us": step_ms * 1e3}}
+    graph = None
     torch.cuda.synchronize()
-    clocks = sampler.finish()
-    ms = e0.elapsed_time(e1) / args.steps
-    if ws.status() != 0:
-        raise SystemExit("device-side status is not clean after the timed region")
-    flops = 4.0 * H * D * S * (S + 1) / 2          # useful (causal) FLOPs of QK^T and PV
-    peak, peak_src = 1590.0, "fallback"
-    try:
-        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
-            peak, peak_src = float(json.load(f)["bf16_tflops"]), "measured"
-    except Exception:
-        pass
-    achieved = flops / (ms * 1e-3) / 1e12
-    line = {"metric": "prefill_attention_tokens_per_s", "value": S / (ms * 1e-3), "unit": "tokens/s", "n_gpus": 1,
-            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
-            "config": {"workload": args.workload, "n_head": H, "n_kv_head": G, "head_dim": D, "prompt_tokens": S,
-                       "l2_policy": f"rotates through {n_rot} slots and activation buffers (560 MB)"},
-            "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
-                         "peak_source": peak_src, "kernel": "prefill_prepare_kernel + prefill_attn_kernel (whole call)",
-                         "useful_flops_per_call": flops, "traffic": None},
-            "cpu_baseline": None, "e2e": None, "gpu_launches": int(L.cglm_launch_count() - launches0), "clocks": clocks}
-    print(json.dumps(line), flush=True)
+    arena.close()
+    return res
 
 
-def run_ours(args, w):
-    if w.get("split_kv"):
-        return run_split_kv(args, w)
-    if w.get("prefill"):
-        return run_prefill(args, w)
-    import torch
-    import torch.distributed as dist
+# ---- drivers ------------------------------------------------------------------------------------------------------------
+def base_line(args, dd, metric="decode_attention_tokens_per_s", scaling="weak"):
+    return {"metric": metric, "unit": "tokens/s", "n_gpus": dd.world, "steps": args.steps, "warmup": args.warmup,
+            "higher_is_better": True, "scaling": scaling, "vs_baseline": None, "dtype": "f16", "data": "synthetic"}
 
-    from chatglm_cpp_b200 import _lib
-    from chatglm_cpp_b200 import attention as A
 
-    rank = int(os.environ.get("RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    if not torch.cuda.is_available():
-        raise SystemExit("bench.py needs a CUDA device (there is no CPU fallback); use --impl reference for the CPU path")
-    torch.cuda.set_device(local)
-    if world > 1:
-        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-    L = _lib.lib()
-    H, G, D, M, layers, n = w["H"], w["G"], w["D"], w["M"], w["layers"], w["seqs"]
-    desc = _lib.AttnDesc(H, G, D, M, 0, w["rope"], w["theta"], w["mask"])
-    n_past = draw_n_past(w, rank)
-    n_ctx = np.maximum(n_past // 2, 2).astype(np.int32)
+def decode_line(args, dd, name, w, n_past, r, s, src, cpu, parity, clocks):
+    line = dict(base_line(args, dd), value=s["value"], ms_per_step=s["ms_per_step"],
+                config=workload_config(name, w, n_past, dd.world),
+                roofline=dict(s["roofline"], peak_source=src, kernel="decode_kernel", launch_us=s["launch_us"],
+                              traffic=NCU_TRAFFIC_PER_KV_BYTE * r["kv_bytes_per_launch"],
+                              frac_of_nominal_8000=s["roofline"]["achieved"] / 8000.0),
+                cpu_baseline=cpu, e2e=s.get("e2e"), gpu_launches=r["launches"] * dd.world, clocks=clocks)
+    if parity is not None:
+        line["parity"] = parity
+    if "step_graph" in s:
+        line["step_graph"] = s["step_graph"]
+    return line
 
-    # ---- state: caches for every (layer, sequence), filled with N(0,1) f16 on the device ------------------
-    arena = A.KVArena(desc, layers * n)
-    g = torch.Generator(device="cuda")
-    g.manual_seed(w["seed"] + rank)
-    for view in (arena.k_all(), arena.v_all()):
-        flat = view.view(-1)
-        step = 1 << 28
-        for o in range(0, flat.numel(), step):
-            seg = flat[o:o + step]
-            seg.copy_(torch.randn(seg.numel(), device="cuda", generator=g, dtype=torch.float32).half())
-    ws = A.Workspace(desc, n, 1)
-    row, orow = qkv_row(w), H * D
-    qkv_dev = torch.randn(layers, n, row, device="cuda", generator=g)
-    out_dev = torch.empty(layers, n, orow, device="cuda")
-    qkv_host = qkv_dev.cpu().pin_memory()
-    out_host = torch.empty(layers, n, orow).pin_memory()
-    n_stage = 3   # staging pairs rotated over the layers so that a layer's copies overlap its neighbours' kernels
-    stage_qkv = [torch.empty(n, row, device="cuda") for _ in range(n_stage)]
-    stage_out = [torch.empty(n, orow, device="cuda") for _ in range(n_stage)]
 
-    # one descriptor array per layer, built once: slot of (layer l, sequence i) is l*n + i.  Every layer call reads
-    # cache rows that no kernel of the step writes (a call appends at n_past of its own layer's slots only), which is
-    # what CGLM_SEQ_CACHE_SETTLED promises: a launch may stream cache tiles while the previous layer's launch drains.
-    seq_flags = 0 if args.no_settled else _lib.SEQ_CACHE_SETTLED
-    seq_arrays = []
-    for l in range(layers):
-        arr = (_lib.AttnSeq * n)()
-        for i in range(n):
-            call = A.SeqCall(qkv=qkv_dev[l, i:i + 1], slot=l * n + i, n_past=int(n_past[i]), n_ctx=int(n_ctx[i]),
-                             out=out_dev[l, i:i + 1], flags=seq_flags)
-            A.fill_seq(arr[i], desc, call, w["interleaved"])
-        seq_arrays.append(arr)
-    stream = torch.cuda.current_stream().cuda_stream
-
-    def step_device():
-        for l in range(layers):
-            rc = L.cglm_attn_forward(arena._h, seq_arrays[l], n, ws.ptr, ws.bytes, stream)
-            if rc != 0:
-                raise _lib.CglmError(rc, "cglm_attn_forward")
-
-    def step_host():
-        for l in range(layers):
-            rc = L.cglm_attn_forward_host(arena._h, seq_arrays[l], n, int(w["interleaved"]), qkv_host[l].data_ptr(),
-                                          out_host[l].data_ptr(), stage_qkv[l % n_stage].data_ptr(),
-                                          stage_out[l % n_stage].data_ptr(), ws.ptr, ws.bytes, stream)
-            if rc != 0:
-                raise _lib.CglmError(rc, "cglm_attn_forward_host")
-        rc = L.cglm_attn_host_drain(arena._h, stream)   # the step's results are read back here
-        if rc != 0:
-            raise _lib.CglmError(rc, "cglm_attn_host_drain")
-
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    def timed(fn, steps, warmup):
-        for _ in range(warmup):
-            fn()
-        barrier()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        launches0 = L.cglm_launch_count()
-        e0.record()
-        for _ in range(steps):
-            fn()
-        e1.record()
-        barrier()
-        ms = e0.elapsed_time(e1)
-        if world > 1:
-            t = torch.tensor([ms], device="cuda", dtype=torch.float64)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            ms = float(t.item())
-        return ms, L.cglm_launch_count() - launches0
-
-    sampler = ClockSampler(local)
+def run_single(args, dd, name, w):
+    """--workload NAME: that workload alone as the line (used for profiling and for the tables in the documents)."""
+    syn = Synth()
+    pk, src = peak("hbm_gbs", HBM_FALLBACK_GBS)
+    sampler = ClockSampler(dd.local)
     sampler.start()
-    ms, launches = timed(step_device, args.steps, args.warmup)
+    if w.get("prefill"):
+        r = prefill_measure(dd, name, w, args, syn)
+        line = dict(base_line(args, dd, r["metric"]), value=r["value"], ms_per_step=r["ms_per_step"],
+                    config={"workload": name, "n_head": w["H"], "n_kv_head": w["G"], "head_dim": w["D"],
+                            "prompt_tokens": w["prefill"], "l2_policy": r["l2_policy"]},
+                    roofline=dict(r["roofline"], traffic=None), cpu_baseline=None, e2e=None, gpu_launches=r["launches"],
+                    clocks=sampler.finish())
+    elif w.get("split_kv"):
+        r = split_kv_measure(dd, name, w, args, syn)
+        line = dict(base_line(args, dd, scaling="strong"), value=r["value"], ms_per_step=r["ms_per_step"], steps=r["steps"],
+                    config={"workload": name, "n_head": w["H"], "n_kv_head": w["G"], "head_dim": w["D"], "n_past": r["n_past"],
+                            "kv_bytes_total": r["kv_bytes_total"], "kv_bytes_this_rank": r["kv_bytes_this_rank"],
+                            "parallelism": r["parallelism"], "l2_policy": r["l2_policy"], "issue": r["issue"]},
+                    roofline=dict(r["roofline"], traffic=None), cpu_baseline=None, e2e=None,
+                    gpu_launches=r["launches"] * dd.world, clocks=sampler.finish())
+    else:
+        st = DecodeState(w, dd.rank, syn)
+        n_past = draw_n_past(w, dd.rank)
+        r = decode_measure(dd, st, name, n_past, args, e2e=True, step_graph=args.step_graph)
+        clocks = sampler.finish()
+        s = decode_summary(r, dd.world, pk)
+        cpu = parity = None
+        if dd.rank == 0 and dd.world == 1 and not args.no_cpu_baseline:
+            cpu, parity = parity_check(st, n_past, r["_out_host"][0])
+        line = decode_line(args, dd, name, w, n_past, r, s, src, cpu, parity, clocks)
+        st.close()
+    return line
+
+
+def run_default(args, dd):
+    """The headline workload plus, in the same line, the other BASELINE configurations and the multi-GPU partitions."""
+    import torch
+    name, w = HEADLINE, WORKLOADS[HEADLINE]
+    syn = Synth()
+    pk, src = peak("hbm_gbs", HBM_FALLBACK_GBS)
+    st = DecodeState(w, dd.rank, syn)
+    n_past = draw_n_past(w, dd.rank)
+    sampler = ClockSampler(dd.local)
+    sampler.start()
+    r = decode_measure(dd, st, name, n_past, args, e2e=False)
     clocks = sampler.finish()
-    if ws.status() != 0:
-        raise SystemExit("device-side status is not clean after the timed region")
-    ms_e2e, _ = timed(step_host, max(3, args.steps // 2), max(3, args.warmup))
-    e2e_steps = max(3, args.steps // 2)
-
-    # Optional: the same step issued as ONE CUDA graph whose layer calls read n_past from device words
-    # (CGLM_SEQ_N_PAST_DEVICE), the form a caller uses to replay a decode step for every new token without rebuilding
-    # anything.  The words are advanced by 0 here so that every replay is the step the other figures measure.
-    step_graph = None
-    if args.step_graph:
-        n_past_dev = torch.tensor([int(p) for p in n_past], dtype=torch.int32, device="cuda")
-        dyn_arrays = []
-        for l in range(layers):
-            arr = (_lib.AttnSeq * n)()
-            for i in range(n):
-                call = A.SeqCall(qkv=qkv_dev[l, i:i + 1], slot=l * n + i, n_past=int(n_past[i]), n_ctx=int(n_ctx[i]),
-                                 out=out_dev[l, i:i + 1], flags=_lib.SEQ_N_PAST_DEVICE, n_past_dev=n_past_dev[i:i + 1])
-                A.fill_seq(arr[i], desc, call, w["interleaved"])
-            dyn_arrays.append(arr)
-
-        def step_dyn():
-            st = torch.cuda.current_stream().cuda_stream
-            for l in range(layers):
-                rc = L.cglm_attn_forward(arena._h, dyn_arrays[l], n, ws.ptr, ws.bytes, st)
-                if rc != 0:
-                    raise _lib.CglmError(rc, "cglm_attn_forward")
-            rc = L.cglm_seq_advance(n_past_dev.data_ptr(), n, 0, st)
-            if rc != 0:
-                raise _lib.CglmError(rc, "cglm_seq_advance")
-
-        side = torch.cuda.Stream()
-        side.wait_stream(torch.cuda.current_stream())
-        with torch.cuda.stream(side):
-            step_dyn()
-        torch.cuda.current_stream().wait_stream(side)
-        torch.cuda.synchronize()
-        graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph):
-            step_dyn()
-        ms_graph, _ = timed(graph.replay, args.steps, args.warmup)
-        if ws.status() != 0:
-            raise SystemExit("device-side status is not clean after the step-graph region")
-        step_graph = {"value": n * world * args.steps / (ms_graph * 1e-3), "unit": "tokens/s",
-                      "ms_per_step": ms_graph / args.steps, "launches_per_step": layers + 1,
-                      "note": "one CUDA graph per decode step, n_past read from device words, replayed"}
-        graph = None
-
-    tokens_per_step = n * world
-    value = tokens_per_step * args.steps / (ms * 1e-3)
-    e2e_value = tokens_per_step * e2e_steps / (ms_e2e * 1e-3)
-    bytes_per_launch = kv_bytes(w, n_past)
-    launch_ms = ms / (args.steps * layers)
-    achieved = bytes_per_launch / (launch_ms * 1e-3) / 1e9
-    peak, peak_src = HBM_FALLBACK_GBS, "fallback"
-    try:
-        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
-            peak, peak_src = float(json.load(f)["hbm_gbs"]), "measured"
-    except Exception:
-        pass
-
-    cpu = None
-    if rank == 0 and world == 1 and not args.no_cpu_baseline:
-        # bounded sample: layer 0 of the same workload, with the device's cache contents
-        torch.cuda.synchronize()
-        host_caches = [(arena.k_cache(i).cpu().numpy().view(np.uint16), arena.v_cache(i).cpu().numpy().view(np.uint16))
-                       for i in range(n)]
-        tps, per_layer, thr = cpu_leg(w, n_past, host_caches, 3, 1)
-        cpu = {"value": tps, "unit": "tokens/s", "cores": thr, "kind": "port",
-               "sample": f"layer 0 of {layers} x {n} sequences (same cache bits), 3 repetitions, scaled to {layers} layers"}
-
-    if rank == 0:
-        line = {
-            "metric": "decode_attention_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world,
-            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
-            "config": workload_config(args, w, n_past),
-            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "peak_source": peak_src, "kernel": "decode_kernel",
-                         "algorithmic_bytes_per_launch": bytes_per_launch, "launch_us": launch_ms * 1e3,
-                         "traffic": (NCU_TRAFFIC_PER_KV_BYTE * bytes_per_launch
-                                     if NCU_TRAFFIC_PER_KV_BYTE is not None else None),
-                         "frac_of_nominal_8000": achieved / 8000.0},
-            "cpu_baseline": cpu,
-            "e2e": {"value": e2e_value, "unit": "tokens/s", "ms_per_step": ms_e2e / e2e_steps,
-                    "h2d_bytes_per_step": layers * n * row * 4, "d2h_bytes_per_step": layers * n * orow * 4},
-            "gpu_launches": int(launches) * world,
-            "clocks": clocks,
-        }
-        if step_graph is not None:
-            line["step_graph"] = step_graph
-        print(json.dumps(line), flush=True)
-    if world > 1:
-        dist.barrier()
-        dist.destroy_process_group()
+    cpu = parity = None
+    check = dd.rank == 0 and dd.world == 1 and not args.no_cpu_baseline
+    if check:
+        # st.out holds what the last timed step wrote; the CPU leg recomputes layer 0 from the same bits
+        got_dev = st.out[0].clone()
+    r.update(decode_measure(dd, st, name, n_past, args, device=False, e2e=True, step_graph=True))
+    if check:
+        st.out[0].copy_(got_dev)
+        cpu, parity = parity_check(st, n_past, r["_out_host"][0])
+    s = decode_summary(r, dd.world, pk)
+    line = decode_line(args, dd, name, w, n_past, r, s, src, cpu, parity, clocks)
+    short = max(5, min(args.steps, 10))
+    configs = {}
+    if not args.headline_only:
+        # same arena, other batch sizes and lengths (slots are addressed as layer * 64 + sequence)
+        for nm, ids, npast in (
+            ("glm4_9b_batched_decode_8k", list(range(64)), np.full(64, 8191, np.int32)),
+            ("glm4_9b_batched_decode_b32", list(range(32)), n_past[:32]),
+        ):
+            rr = decode_measure(dd, st, nm, npast, args, seq_ids=ids, e2e=False, steps=short)
+            configs[nm] = decode_summary(rr, dd.world, pk)
+        if dd.world > 1:
+            # strong scaling of BASELINE config 3: the SAME 64 sequences (lengths of rank 0's draw) sharded over the GPUs
+            from chatglm_cpp_b200 import sharding
+            glob = draw_n_past(w, 0)
+            mine = sharding.shard_sequences(len(glob), dd.world, dd.rank)
+            rr = decode_measure(dd, st, name + "_strong", glob[mine], args, seq_ids=list(range(len(mine))), e2e=True, steps=args.steps)
+            ss = decode_summary(rr, 1, pk)
+            total = len(glob)
+            line["strong"] = {"global_batch": total, "seqs_per_gpu": len(mine), "value": total / (rr["ms_per_step"] * 1e-3),
+                              "unit": "tokens/s", "ms_per_step": rr["ms_per_step"], "launch_us": ss["launch_us"],
+                              "roofline_frac_rank0": ss["roofline"]["frac"],
+                              "e2e": {"value": total / (rr["e2e"]["ms_per_step"] * 1e-3), "unit": "tokens/s",
+                                      "ms_per_step": rr["e2e"]["ms_per_step"]},
+                              "note": "the 64 sequences of the 1-GPU workload, sequence i on GPU i mod N, no collective"}
+    st.close()
+    del st
+    torch.cuda.empty_cache()
+    if not args.headline_only:
+        for nm in ("glm3_6b_decode_512", "glm1_6b_mha_decode"):
+            ww = WORKLOADS[nm]
+            s2 = DecodeState(ww, dd.rank, syn)
+            rr = decode_measure(dd, s2, nm, draw_n_past(ww, dd.rank), args, e2e=True, step_graph=(nm == "glm3_6b_decode_512"), steps=short)
+            configs[nm] = decode_summary(rr, dd.world, pk)
+            s2.close()
+        for nm in ("glm3_6b_prefill_1024", "glm3_6b_prefill_8192"):
+            rr = prefill_measure(dd, nm, WORKLOADS[nm], args, syn, steps=short)
+            configs[nm] = {k: rr[k] for k in ("metric", "value", "unit", "ms_per_step", "steps", "prompt_tokens", "roofline")}
+        nm = "glm4_9b_long_131072"
+        rr = split_kv_measure(dd, nm, WORKLOADS[nm], args, syn, steps=short)
+        entry = {k: rr[k] for k in ("value", "unit", "ms_per_step", "steps", "parallelism", "kv_bytes_this_rank", "roofline", "issue")}
+        if dd.world > 1:
+            line["split_kv"] = entry
+        else:
+            configs[nm] = entry
+    line["configs"] = configs
+    return line
 
 
 def main():
@@ -652,21 +808,35 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
-    ap.add_argument("--workload", choices=sorted(WORKLOADS), default="glm4_9b_batched_decode")
+    ap.add_argument("--workload", choices=sorted(WORKLOADS), default=None,
+                    help="run this workload alone (default: the headline workload plus the other configurations)")
+    ap.add_argument("--headline-only", action="store_true", help="default run without the other configurations")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-settled", action="store_true",
                     help="decode workloads: do not pass CGLM_SEQ_CACHE_SETTLED (every launch waits for the previous one to drain)")
-    ap.add_argument("--no-graph", action="store_true", help="split-KV workload: issue every step eagerly")
+    ap.add_argument("--e2e-f32", action="store_true", help="host-buffer runs with f32 activations instead of the f16 hand-off")
     ap.add_argument("--exchange", choices=["p2p", "nccl"], default="p2p", help="split-KV workload: how partials travel")
     ap.add_argument("--step-graph", action="store_true",
-                    help="batched decode workloads: also time the step as one replayed CUDA graph (device-side n_past)")
+                    help="with --workload: also time the step as one replayed CUDA graph (device-side n_past)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
-    w = WORKLOADS[args.workload]
     if args.impl == "reference":
-        run_reference(args, w)
+        name = args.workload or HEADLINE
+        run_reference(args, name, WORKLOADS[name])
+        return
+    dd = Dist()
+    if args.workload:
+        line = run_single(args, dd, args.workload, WORKLOADS[args.workload])
     else:
-        run_ours(args, w)
+        line = run_default(args, dd)
+    if dd.rank == 0:
+        par = line.get("parity")
+        print(json.dumps(line), flush=True)
+        if par is not None and (par["max_abs"] > par["tolerance"] or not par["cache_bit_exact"] or
+                                par.get("e2e_max_abs", 0.0) > par.get("e2e_tolerance", 1.0)):
+            dd.close()
+            raise SystemExit(f"parity check failed: {par}")
+    dd.close()
 
 
 if __name__ == "__main__":

@@ -81,6 +81,8 @@ SYMBOLS = {
     "cglm_attn_splitkv_step": (C.c_int, [C.c_void_p, C.POINTER(AttnSeq), C.POINTER(C.c_void_p), C.c_int, C.c_int, C.c_void_p,
                                          C.c_int, C.c_uint, C.c_void_p, C.c_size_t, C.c_void_p]),
     "cglm_kv_load_prefix": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_void_p]),
+    "cglm_synth_fill_f16": (C.c_int, [C.c_void_p, C.c_longlong, C.c_ulonglong, C.c_ulonglong, C.c_longlong, C.c_void_p, C.c_void_p]),
+    "cglm_synth_fill_f32": (C.c_int, [C.c_void_p, C.c_longlong, C.c_ulonglong, C.c_ulonglong, C.c_longlong, C.c_void_p, C.c_void_p]),
     "cglm_status_string": (C.c_char_p, [C.c_int]),
     "cglm_last_error_string": (C.c_char_p, []),
     "cglm_launch_count": (C.c_ulonglong, []),

@@ -75,8 +75,42 @@ struct ItemOut {
     float *out, *partial;
     int flags;
 };
+// How the line of tiles is cut into the CTAs' spans.  Every item start inside a span costs the CTA a switch (fold of the
+// four warps' states, partial store, a new q tile): about the time of two or three tiles.  The cut therefore balances
+// cost, not tiles: on the *charged* line every item is preceded by `charge` pseudo-tiles, the charged line is cut into
+// nb equal pieces, and a piece's pseudo-tiles are dropped again.  A span that contains an item start gets that many
+// fewer tiles.  charge = 0 gives the plain equal-tile cut.  The cut depends on (prefix, G, nb, charge) only.
+struct Geo {
+    const int *prefix;     // shared-memory copy of the launch's tile prefix sums (per sequence, per kv head)
+    long long total, nb;   // tiles on the line, CTAs with work
+    int n_seq, G, charge;
+    // tile position of charged position x
+    __device__ __forceinline__ long long uncharge(long long x) const {
+        if (charge == 0) return x;
+        int lo = 0, hi = n_seq - 1;   // last sequence whose charged start is <= x
+        while (lo < hi) {
+            const int mid = (lo + hi + 1) >> 1;
+            if (static_cast<long long>(prefix[mid] + mid * charge) * G <= x) lo = mid; else hi = mid - 1;
+        }
+        const int n = prefix[lo + 1] - prefix[lo];
+        const int off = static_cast<int>(x - static_cast<long long>(prefix[lo] + lo * charge) * G);   // < G * (n + charge)
+        const int g = off / (n + charge);
+        const int o2 = off - g * (n + charge);
+        return static_cast<long long>(prefix[lo]) * G + static_cast<long long>(g) * n + (o2 > charge ? o2 - charge : 0);
+    }
+    __device__ __forceinline__ long long charged_total() const { return total + static_cast<long long>(n_seq) * G * charge; }
+    __device__ __forceinline__ long long span_start(long long b) const { return b >= nb ? total : uncharge(b * charged_total() / nb); }
+    // the span that holds tile `tile` of item (seq, g), whose first tile sits at item_begin on the line
+    __device__ __forceinline__ long long span_of(int seq, int g, long long item_begin, int tile) const {
+        const long long x = item_begin + static_cast<long long>(seq * G + g + 1) * charge + tile;
+        long long b = x * nb / charged_total();
+        while (span_start(b + 1) <= item_begin + tile) ++b;
+        return b;
+    }
+};
+
 struct MergeCtx {
-    long long total, nb;   // tiles on the line, CTAs of the launch
+    Geo geo;
     int *counters;         // per item: parts delivered (short items) or groups delivered (long items)
     int *gcounters;        // per (CTA group, slot): parts of the long item in that slot delivered
     float *partials;       // per (CTA, slot)
@@ -128,9 +162,6 @@ static_assert(sizeof(QBuf) % 16 == 0, "ldmatrix rows of the second q tile stay 1
 // two CTAs per SM: 2 * (dynamic shared memory + 1 KiB alignment slack + 1 KiB reserved per CTA) <= 228 KiB
 static_assert(2 * (sizeof(DecodeSmem) + 2048) <= 233472, "two decode CTAs must fit one SM");
 
-__device__ __forceinline__ long long span_start(long long b, long long total, long long nb) {
-    return b * total / nb;
-}
 
 // Position on the line -> (sequence, kv head, tile) using the per-sequence prefix of tile counts.
 __device__ __forceinline__ ItemPos locate(const int *prefix, int n_seq, int G, long long pos) {
@@ -153,14 +184,6 @@ __device__ __forceinline__ int attended_len(int kv_before, int flags) {
     return kv_before + ((flags & CGLM_SEQ_NO_APPEND) ? 0 : 1);
 }
 
-// CTAs b0..b1 of an nb-CTA launch hold parts of the item spanning [item_begin, item_end) on the line.
-__device__ __forceinline__ void item_ctas(long long item_begin, long long item_end, long long total, long long nb,
-                                          long long &b0, long long &b1) {
-    b0 = item_begin * nb / total;
-    while (span_start(b0 + 1, total, nb) <= item_begin) ++b0;
-    b1 = (item_end - 1) * nb / total;
-    while (span_start(b1 + 1, total, nb) <= item_end - 1) ++b1;
-}
 // A CTA keeps at most two partials: slot 0 for its first segment, slot 1 for its last.
 
 // ---- per-warp tile math ---------------------------------------------------------------------------------
@@ -658,13 +681,13 @@ __device__ __noinline__ void deliver_part(const DeliverArgs *da, long long b, in
         if (t == 0) v = count_part(ctr, expected);
         return __shfl_sync(0xffffffffu, v, 0);
     };
-    long long b0, b1;
-    item_ctas(ip.item_begin, ip.item_begin + ip.n_tiles, mc.total, mc.nb, b0, b1);
+    // CTAs b0..b1 hold parts of the item
+    const long long b0 = mc.geo.span_of(ip.seq, ip.g, ip.item_begin, 0), b1 = mc.geo.span_of(ip.seq, ip.g, ip.item_begin, ip.n_tiles - 1);
     const int n_parts = static_cast<int>(b1 - b0 + 1);
     const int item = ip.seq * sh.G + ip.g;
     // Slot of the first source at each level: the CTA (group) in which the item begins holds it in its second slot
     // unless the item begins exactly where the CTA's span (the group's first span) does.
-    const int first_cta_slot = span_start(b0, mc.total, mc.nb) >= ip.item_begin ? 0 : 1;
+    const int first_cta_slot = mc.geo.span_start(b0) >= ip.item_begin ? 0 : 1;
     const long long g0 = b0 / kMergeFan, g1 = b1 / kMergeFan;
     const int first_grp_slot = group_slot(g0, b0);
     const bool out_f16 = (sq.flags & CGLM_SEQ_OUT_F16) != 0;
@@ -793,8 +816,11 @@ decode_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__
     // empty span between two parts of an item would be counted as a part that never arrives
     const long long nb = min(static_cast<long long>(gridDim.x), total);
     const bool idle = blockIdx.x >= nb;
-    const long long span_lo = idle ? 0 : span_start(blockIdx.x, total, nb);
-    const long long span_hi = idle ? 0 : span_start(blockIdx.x + 1, total, nb);
+    // item starts are charged only when the spans are long against the charge (no span may come out empty)
+    const Geo geo{sm.prefix, total, nb, n_seq, G,
+                  (nb > 0 && (total + static_cast<long long>(n_seq) * G * tab.charge) / nb >= 8LL * tab.charge) ? tab.charge : 0};
+    const long long span_lo = idle ? 0 : geo.span_start(blockIdx.x);
+    const long long span_hi = idle ? 0 : geo.span_start(blockIdx.x + 1);
     // Launched with programmatic stream serialization: everything that reads only kernel parameters (barrier
     // set-up, the tables above, the first segment's descriptor, the tensor maps) runs while the previous kernel of
     // the stream is still draining.  A read of parameter space at a computed index costs about a microsecond when
@@ -864,7 +890,7 @@ decode_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__
         }
     } else if (warp == kHelperWarp) {
         // ================================ helper warp ==================================================
-        const MergeCtx mc{total, nb, counters, gcounters, partials, gpartials};
+        const MergeCtx mc{geo, counters, gcounters, partials, gpartials};
         long long pos = span_lo;
         unsigned int sidx = 0;
         int prev_slot = 0;   // partial slot of the previous segment: 0 for the CTA's first segment, else 1
@@ -1106,7 +1132,7 @@ decode_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__
             if (!whole_item && seg_end == span_hi) {
                 // end of the span: nothing left to overlap with, all four warps complete the item if it is theirs to
                 // complete.  The team barrier inside deliver_part also orders every warp's partial stores before the count.
-                const MergeCtx mc{total, nb, counters, gcounters, partials, gpartials};
+                const MergeCtx mc{geo, counters, gcounters, partials, gpartials};
                 DeliverArgs &da = sm.dargs[warp];   // every warp parks its own copy: no barrier needed before the call
                 if (lane == 0) { da.ip = ip; da.io = ItemOut{out_ptr, partial_ptr, flags}; da.mc = mc; da.G = G; da.R = R; da.xs = kXchg ? &sm.xs : nullptr; }
                 __syncwarp();

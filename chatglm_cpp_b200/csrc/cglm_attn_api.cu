@@ -107,6 +107,16 @@ int decode_l2_ahead() {
     }();
     return v;
 }
+// Tiles by which a decode CTA's span is shortened for every item start inside it (see Geo in attn_decode.cu).
+// CGLM_DECODE_CHARGE overrides the default (tuning knob, read once).
+int decode_charge() {
+    static const int v = [] {
+        const char *e = std::getenv("CGLM_DECODE_CHARGE");
+        const int x = e ? std::atoi(e) : 2;
+        return x < 0 ? 0 : (x > 8 ? 8 : x);
+    }();
+    return v;
+}
 // When a decode CTA releases the next kernel of the stream (see DecodeTable::trigger).  CGLM_DECODE_TRIGGER overrides.
 int decode_trigger() {
     static const int v = [] {
@@ -680,7 +690,7 @@ int cglm_attn_forward(cglm_kv_arena *a, const cglm_attn_seq *seqs, int n_seq, vo
                 tab.n_seq = filled;
                 tab.settled = settled && !dyn ? 1 + decode_l2_ahead() : 0;
                 tab.trigger = decode_trigger();
-                tab.pad = 0;
+                tab.charge = decode_charge();
                 CGLM_CUDA(launch_decode(cx, tab, dyn));
                 filled = 0;
                 dyn = false;
@@ -969,7 +979,7 @@ int cglm_attn_splitkv_step(cglm_kv_arena *a, const cglm_attn_seq *seq, void *con
     tab.n_seq = 1;
     tab.settled = (s.flags & CGLM_SEQ_CACHE_SETTLED) ? 1 + decode_l2_ahead() : 0;
     tab.trigger = decode_trigger();
-    tab.pad = 0;
+    tab.charge = decode_charge();
     tab.prefix[0] = 0;
     tab.prefix[1] = (kv_before + appended + kDecodeTile - 1) / kDecodeTile;
     CGLM_CUDA(launch_decode(cx, tab, false, &xd));

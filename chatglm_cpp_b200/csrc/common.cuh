@@ -307,7 +307,7 @@ struct DecodeTable {
     int n_seq;
     int settled;   // 0, or 1 + tiles per CTA to pull into L2 ahead of the ring: every sequence carries CGLM_SEQ_CACHE_SETTLED
     int trigger;   // when a CTA releases the next kernel of the stream: 0 at its start, 1 last tile requested, 2 last tile consumed
-    int pad;
+    int charge;    // tiles a CTA's span is shortened by for every item start inside it (cost-balanced cut of the line)
     int prefix[kDecodeMaxSeqPerLaunch + 2];   // prefix[i] = 64-token tiles of sequences [0, i), per kv head
     SeqDev seqs[kDecodeMaxSeqPerLaunch];
 };

@@ -274,6 +274,17 @@ int cglm_attn_splitkv_step(cglm_kv_arena *arena, const cglm_attn_seq *seq, void 
  * past_kv f16 [2][n_kv_head][n_virtual][head_dim] (device) -> cache positions [0, n_virtual), V transposed. */
 int cglm_kv_load_prefix(cglm_kv_arena *arena, int slot, const void *past_kv, void *cuda_stream);
 
+/*
+ * Counter-based synthetic data (no counterpart in the reference; for benchmarks and tests): element first + i of tensor
+ * tensor_id under a seed is table[splitmix64(seed * 0x9E3779B97F4A7C15 + tensor_id * 0xBF58476D1CE4E5B9 + first + i) >> 48],
+ * table being 65536 values in device memory (e.g. the N(0,1) quantiles).  Integer arithmetic only: a host loop over
+ * the same expression yields the same bits, so a CPU arm can rebuild any part of a 20 GiB cache without a download.
+ */
+int cglm_synth_fill_f16(void *dst, long long n, unsigned long long seed, unsigned long long tensor_id, long long first,
+                        const void *table_f16, void *cuda_stream);
+int cglm_synth_fill_f32(float *dst, long long n, unsigned long long seed, unsigned long long tensor_id, long long first,
+                        const float *table_f32, void *cuda_stream);
+
 const char *cglm_status_string(int status);
 /* Text of the last CUDA error seen by this thread inside the library ("" if none). */
 const char *cglm_last_error_string(void);

@@ -560,3 +560,53 @@ int oracle_attn_decode_batch(const oracle_cfg *cfg, int n_seq, const float *cons
     free(qr);
     return 0;
 }
+
+/* ---- counter-based synthetic data: the host twin of the library's cglm_synth_fill_* (test infrastructure) --------
+ * element first + i of tensor tensor_id under seed = table[splitmix64(seed * C1 + tensor_id * C2 + first + i) >> 48].
+ * Integer arithmetic only, so host and device agree bit for bit; the reference has no counterpart (its tests read
+ * fixtures from files, chatglm_test.cpp:296-304). */
+static inline uint64_t synth_mix(uint64_t z) {
+    z ^= z >> 30; z *= 0xBF58476D1CE4E5B9ull;
+    z ^= z >> 27; z *= 0x94D049BB133111EBull;
+    z ^= z >> 31;
+    return z;
+}
+
+void oracle_synth_fill_f16(uint16_t *dst, long long n, unsigned long long seed, unsigned long long tensor_id, long long first,
+                           const uint16_t *table) {
+    const uint64_t base = (uint64_t)seed * 0x9E3779B97F4A7C15ull + (uint64_t)tensor_id * 0xBF58476D1CE4E5B9ull;
+#pragma omp parallel for schedule(static)
+    for (long long i = 0; i < n; i++) {
+        dst[i] = table[synth_mix(base + (uint64_t)(first + i)) >> 48];
+    }
+}
+
+void oracle_synth_fill_f32(float *dst, long long n, unsigned long long seed, unsigned long long tensor_id, long long first,
+                           const float *table) {
+    const uint64_t base = (uint64_t)seed * 0x9E3779B97F4A7C15ull + (uint64_t)tensor_id * 0xBF58476D1CE4E5B9ull;
+#pragma omp parallel for schedule(static)
+    for (long long i = 0; i < n; i++) {
+        dst[i] = table[synth_mix(base + (uint64_t)(first + i)) >> 48];
+    }
+}
+
+/* ---- Linear (chatglm.cpp:418-426): y = ggml_mul_mat(weight, x) (+ bias), the module either side of the attention path ---
+ * x [n_tok][in] f32, weight [out][in] (f32, or f16 bits when w_is_f16), bias [out] or NULL, y [n_tok][out] f32.
+ * round_x_f16: ggml's CPU mul_mat against an f16 matrix first converts the activation row to f16 [ggml-recall];
+ * products are accumulated in f32. */
+void oracle_linear(const float *x, int n_tok, int in, const void *weight, int w_is_f16, const float *bias, int out,
+                   int round_x_f16, float *y) {
+#pragma omp parallel for collapse(2) schedule(static)
+    for (int t = 0; t < n_tok; t++) {
+        for (int o = 0; o < out; o++) {
+            float acc = 0.f;
+            for (int k = 0; k < in; k++) {
+                const float w = w_is_f16 ? oracle_f16_to_f32(((const uint16_t *)weight)[(long)o * in + k])
+                                         : ((const float *)weight)[(long)o * in + k];
+                const float xv = round_x_f16 ? oracle_f16_to_f32(oracle_f32_to_f16(x[(long)t * in + k])) : x[(long)t * in + k];
+                acc += w * xv;
+            }
+            y[(long)t * out + o] = acc + (bias ? bias[o] : 0.f);
+        }
+    }
+}

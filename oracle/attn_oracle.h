@@ -124,6 +124,19 @@ int oracle_attn_decode_batch(const oracle_cfg *cfg, int n_seq, const float *cons
                              uint16_t *const *k_cache, uint16_t *const *v_cache, const int *n_past,
                              const int *n_ctx, float *const *out, int n_threads);
 
+/* Host twin of the library's counter-based synthetic data (cglm_synth_fill_f16 / _f32): same integer expression,
+ * same bits.  table: 65536 values. */
+void oracle_synth_fill_f16(uint16_t *dst, long long n, unsigned long long seed, unsigned long long tensor_id, long long first,
+                           const uint16_t *table);
+void oracle_synth_fill_f32(float *dst, long long n, unsigned long long seed, unsigned long long tensor_id, long long first,
+                           const float *table);
+
+/* Linear::forward (chatglm.cpp:418-426): y [n_tok][out] = x [n_tok][in] . weight[out][in]^T (+ bias).  weight is f32, or
+ * f16 bits with w_is_f16; round_x_f16 rounds the activations to f16 first, as ggml's CPU backend does against an f16
+ * matrix; accumulation in f32. */
+void oracle_linear(const float *x, int n_tok, int in, const void *weight, int w_is_f16, const float *bias, int out,
+                   int round_x_f16, float *y);
+
 #ifdef __cplusplus
 }
 #endif

@@ -71,7 +71,43 @@ def lib():
         _lib.oracle_attn_decode_batch.argtypes = [C.POINTER(Cfg), C.c_int, C.POINTER(fp), C.POINTER(fp),
                                                   C.POINTER(fp), C.c_long, C.c_long, C.POINTER(u16p),
                                                   C.POINTER(u16p), ip, ip, C.POINTER(fp), C.c_int]
+        _lib.oracle_linear.argtypes = [fp, C.c_int, C.c_int, C.c_void_p, C.c_int, fp, C.c_int, C.c_int, fp]
+        _lib.oracle_synth_fill_f16.argtypes = [u16p, C.c_longlong, C.c_ulonglong, C.c_ulonglong, C.c_longlong, u16p]
+        _lib.oracle_synth_fill_f32.argtypes = [fp, C.c_longlong, C.c_ulonglong, C.c_ulonglong, C.c_longlong, fp]
     return _lib
+
+
+def linear(x: np.ndarray, weight: np.ndarray, bias: np.ndarray | None = None, round_x_f16: bool = False) -> np.ndarray:
+    """Linear::forward (chatglm.cpp:418-426).  x [n_tok, in] f32; weight [out, in] f32 or f16; bias [out] or None."""
+    x = np.ascontiguousarray(np.atleast_2d(x), np.float32)
+    w_f16 = weight.dtype == np.float16
+    weight = np.ascontiguousarray(weight)
+    out_f, in_f = weight.shape
+    assert x.shape[1] == in_f
+    y = np.zeros((x.shape[0], out_f), np.float32)
+    b = None if bias is None else np.ascontiguousarray(bias, np.float32)
+    lib().oracle_linear(_fp(x), x.shape[0], in_f, weight.ctypes.data_as(C.c_void_p), int(w_f16),
+                        _fp(b) if b is not None else None, out_f, int(round_x_f16), _fp(y))
+    return y
+
+
+def synth_table():
+    """The 65536-point N(0,1) quantile table (f32, and the same values rounded to f16) the synthetic data draws from."""
+    from scipy.special import ndtri
+    t32 = ndtri((np.arange(65536, dtype=np.float64) + 0.5) / 65536.0).astype(np.float32)
+    return t32, t32.astype(np.float16).view(np.uint16)
+
+
+def synth_fill(n: int, seed: int, tensor_id: int, first: int, table: np.ndarray) -> np.ndarray:
+    """Elements [first, first + n) of synthetic tensor `tensor_id`: the host twin of cglm_synth_fill_f16 / _f32."""
+    table = np.ascontiguousarray(table)
+    if table.dtype == np.uint16:
+        out = np.empty(n, np.uint16)
+        lib().oracle_synth_fill_f16(_u16p(out), n, seed, tensor_id, first, _u16p(table))
+    else:
+        out = np.empty(n, np.float32)
+        lib().oracle_synth_fill_f32(_fp(out), n, seed, tensor_id, first, _fp(table))
+    return out
 
 
 def _fp(a):

@@ -182,6 +182,21 @@ def make_rope_hf():
     print("rope_d128_hf.npz written")
 
 
+def convert_linear(ref_dir):
+    """tests/data/linear.data (tests/test_convert.py:192-207; read by chatglm_test.cpp:392-405): weight [32, 64], bias [32],
+    x [2, 64], torch F.linear(x, w, b) [2, 32], then the same for the vector x[0]."""
+    with open(os.path.join(ref_dir, "tests", "data", "linear.data"), "rb") as f:
+        w = _rd(f, 32 * 64).reshape(32, 64)
+        b = _rd(f, 32)
+        x = _rd(f, 2 * 64).reshape(2, 64)
+        y = _rd(f, 2 * 32).reshape(2, 32)
+        vx = _rd(f, 64)
+        vy = _rd(f, 32)
+        assert f.read() == b""
+    np.savez_compressed(os.path.join(HERE, "linear.npz"), w=w, b=b, x=x, y=y, vec_x=vx, vec_y=vy)
+    print("linear.npz written")
+
+
 def make_rope_modes_hf():
     """Full-head GPTJ and NEOX rotary and the ChatGLM-6B 2-D rotary at head_dim 128, through the rotary helpers of
     Hugging Face transformers (GPT-J: rotate_every_two; LLaMA / GPT-NeoX: rotate_half) with float64 angles.  The
@@ -229,6 +244,7 @@ if __name__ == "__main__":
     a = ap.parse_args()
     for n in FIXTURES:
         convert(a.reference, n)
+    convert_linear(a.reference)
     if not a.skip_hf:
         make_rope_hf()
         make_rope_modes_hf()

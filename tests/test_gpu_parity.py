@@ -780,6 +780,39 @@ def test_adopted_caches_behave_like_an_arena_of_the_librarys_own(with_table):
     assert L.cglm_kv_arena_adopt(C.byref(desc), 1, host.data_ptr(), v_all.data_ptr(), None, C.byref(h)) == _lib.ERR_INVALID_ARG
 
 
+def test_second_device_in_one_process_gets_its_own_kernel_attributes():
+    """One host process driving two GPUs: the opt-in to large dynamic shared memory is a per-device attribute of a
+    kernel, so the first fused launch on each device must set it there.  Decode and tensor-core prefill on device 0,
+    then the same on device 1, must agree bit for bit.  (Skipped on a one-GPU box.)"""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs in one process")
+    from chatglm_cpp_b200 import _lib
+    A = _A()
+    desc = make_desc(32, 2, 128, 1024)
+    rng = np.random.default_rng(2)
+    qkv_p = rng.standard_normal((300, qkv_width(desc, False))).astype(np.float32)
+    qkv_d = rng.standard_normal((1, qkv_width(desc, False))).astype(np.float32)
+    results = []
+    for dev in (0, 1):
+        with torch.cuda.device(dev):
+            arena, ws = A.KVArena(desc, 1), A.Workspace(desc, 1, 300)
+            attn = A.BasicAttention(arena, 0, ws)
+            o1 = attn.forward(torch.from_numpy(qkv_p).cuda(), 0)
+            o2 = attn.forward(torch.from_numpy(qkv_d).cuda(), 300)
+            torch.cuda.synchronize()
+            assert ws.status() == 0
+            results.append((o1.cpu(), o2.cpu(), arena.k_cache(0).cpu(), arena.v_cache(0).cpu()))
+            # an arena of another device is refused by the call that carries its own scratch
+            arr = (_lib.AttnSeq * 1)()
+            A.fill_seq(arr[0], desc, A.SeqCall(qkv=torch.from_numpy(qkv_d).cuda(), slot=0, n_past=301,
+                                               out=torch.zeros(1, 4096, device="cuda")), False)
+            with torch.cuda.device(1 - dev):
+                assert _lib.lib().cglm_attn_decode_static(arena._h, arr, 1, 1, None) == _lib.ERR_INVALID_ARG
+            arena.close()
+    for a, b in zip(*results):
+        assert torch.equal(a, b)
+
+
 def test_argument_errors_return_codes():
     from chatglm_cpp_b200 import _lib
     A = _A()

@@ -55,6 +55,19 @@ def test_committed_fixture_matches_reference_file(name):
     np.testing.assert_array_equal(raw[-tail.size:], tail)
 
 
+def test_oracle_linear_matches_reference_fixture():
+    """Linear (chatglm.cpp:418-426) against the reference's tests/data/linear.data, with the reference's own
+    tolerances per weight type (chatglm_test.cpp:430-436): f32 1e-5, f16 weights atol 1e-2 + rtol 5e-4."""
+    z = np.load(os.path.join(os.path.dirname(__file__), "golden", "linear.npz"))
+    for x, y in ((z["x"], z["y"]), (z["vec_x"][None], z["vec_y"][None])):
+        got = O.linear(x, z["w"], z["b"])
+        assert np.abs(got - y).max() <= 1e-5
+        for round_x in (False, True):
+            got16 = O.linear(x, z["w"].astype(np.float16), z["b"], round_x_f16=round_x)
+            assert (np.abs(got16 - y) <= 1e-2 + 5e-4 * np.abs(y)).all()
+        assert np.abs(O.linear(x, z["w"], None) + z["b"] - y).max() <= 1e-5
+
+
 def test_f16_conversion_matches_ieee_rne():
     rng = np.random.default_rng(0)
     xs = np.concatenate([
