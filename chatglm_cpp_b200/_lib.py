@@ -14,7 +14,7 @@ OK, ERR_INVALID_ARG, ERR_CUDA, ERR_WORKSPACE, ERR_UNSUPPORTED, ERR_TIMEOUT, ERR_
 ROPE_GPTJ, ROPE_NEOX, ROPE_CHATGLM, ROPE_CHATGLM2, ROPE_DISABLED = 0, 2, 4, 8, 10000
 MASK_CAUSAL, MASK_CHATGLM = 0, 1
 SEQ_NO_APPEND, SEQ_PARTIAL, SEQ_USE_KV_LOCAL, SEQ_N_PAST_DEVICE, SEQ_CACHE_SETTLED = 1, 2, 4, 8, 16
-SEQ_QKV_F16, SEQ_OUT_F16 = 32, 64
+SEQ_QKV_F16, SEQ_OUT_F16, SEQ_Q_ROPED = 32, 64, 128
 HOST_INTERLEAVED_QKV, HOST_F16 = 1, 2
 
 
@@ -67,6 +67,8 @@ SYMBOLS = {
     "cglm_attn_workspace_init": (C.c_int, [C.c_void_p, C.c_size_t, C.c_void_p]),
     "cglm_attn_workspace_status": (C.c_int, [C.c_void_p, C.c_void_p]),
     "cglm_attn_forward": (C.c_int, [C.c_void_p, C.POINTER(AttnSeq), C.c_int, C.c_void_p, C.c_size_t, C.c_void_p]),
+    "cglm_qkv_linear_forward": (C.c_int, [C.c_void_p, C.POINTER(AttnSeq), C.c_int, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p,
+                                          C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]),
     "cglm_seq_advance": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_void_p]),
     "cglm_attn_forward_host": (C.c_int, [C.c_void_p, C.POINTER(AttnSeq), C.c_int, C.c_int, C.c_void_p, C.c_void_p,
                                          C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]),

@@ -384,7 +384,7 @@ __device__ __forceinline__ void prepare_segment(QBuf &qb, const AttnShape &sh, c
     // the arena's table in the same round trip.
     int pos_id = 0, block_id = 0;
     float2 cs0 = make_float2(1.f, 0.f), cs1 = make_float2(1.f, 0.f);
-    const int mode = sh.rope_type;
+    const int mode = (sq.flags & CGLM_SEQ_Q_ROPED) ? static_cast<int>(CGLM_ROPE_DISABLED) : sh.rope_type;
     if (mode != CGLM_ROPE_DISABLED && !dry) {
         derive_positions(sq, mode, 0, pos_id, block_id);
         const bool tab0 = pos_id >= 0 && pos_id < rope_tab_len;

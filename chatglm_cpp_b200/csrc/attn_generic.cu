@@ -37,7 +37,7 @@ rope_append_kernel(AttnShape sh, const SeqDev *__restrict__ seqs, int n_seq, uin
     const SeqDev sq = seqs[s_seq];
     const int s = s_tok;
     const int D = sh.D, H = sh.H, G = sh.G, M = sh.M;
-    const int n_pairs = rope_n_pairs(sh.rope_type, D);
+    const int n_pairs = (sq.flags & CGLM_SEQ_Q_ROPED) ? 0 : rope_n_pairs(sh.rope_type, D);
     const int ladder_len = rope_n_dims(sh.rope_type, D) / 2;
 
     int pos, block;

@@ -621,7 +621,8 @@ int cglm_attn_forward(cglm_kv_arena *a, const cglm_attn_seq *seqs, int n_seq, vo
             (reinterpret_cast<uintptr_t>(s.q) & in_mask) || (reinterpret_cast<uintptr_t>(s.k) & in_mask) ||
             (reinterpret_cast<uintptr_t>(s.v) & in_mask))
             return CGLM_ERR_INVALID_ARG;
-        if ((s.flags & CGLM_SEQ_NO_APPEND) && (!partial || s.qlen != 1)) return CGLM_ERR_INVALID_ARG;
+        if ((s.flags & CGLM_SEQ_NO_APPEND) && ((!partial && !(s.flags & CGLM_SEQ_Q_ROPED)) || s.qlen != 1)) return CGLM_ERR_INVALID_ARG;
+        if ((s.flags & CGLM_SEQ_Q_ROPED) && s.qlen != 1) return CGLM_ERR_INVALID_ARG;
         if ((s.flags & CGLM_SEQ_USE_KV_LOCAL) && (s.kv_local < 0 || s.qlen != 1)) return CGLM_ERR_INVALID_ARG;
         const bool dyn_past = (s.flags & CGLM_SEQ_N_PAST_DEVICE) != 0;
         if (dyn_past && (!s.n_past_dev || (reinterpret_cast<uintptr_t>(s.n_past_dev) & 3) || s.qlen != 1 ||
@@ -983,6 +984,54 @@ int cglm_attn_splitkv_step(cglm_kv_arena *a, const cglm_attn_seq *seq, void *con
     tab.prefix[0] = 0;
     tab.prefix[1] = (kv_before + appended + kDecodeTile - 1) / kDecodeTile;
     CGLM_CUDA(launch_decode(cx, tab, false, &xd));
+    return CGLM_OK;
+}
+
+int cglm_qkv_linear_forward(cglm_kv_arena *a, const cglm_attn_seq *seqs, int n_seq, const void *x_f16, int hidden,
+                            const void *weight_f16, const float *bias, float *q_roped, void *workspace, size_t workspace_bytes,
+                            void *cuda_stream) {
+    if (!a || !seqs || n_seq <= 0 || !x_f16 || !weight_f16 || !q_roped || hidden <= 0) return CGLM_ERR_INVALID_ARG;
+    if (!workspace || workspace_bytes < sizeof(WsHeader)) return CGLM_ERR_WORKSPACE;
+    const cglm_attn_desc &d = a->desc;
+    if (!a->has_tmaps || d.head_dim != 128 || (d.rope_type != CGLM_ROPE_CHATGLM2 && d.rope_type != CGLM_ROPE_DISABLED) ||
+        hidden % 64 != 0 || n_seq > 128) {
+        std::snprintf(g_err, sizeof(g_err), "the fused qkv Linear needs head_dim 128, the GLM-2/3/4 rope mode (or none), hidden %% 64 == 0 and at most 128 sequences");
+        return CGLM_ERR_UNSUPPORTED;
+    }
+    if ((reinterpret_cast<uintptr_t>(x_f16) | reinterpret_cast<uintptr_t>(weight_f16) | reinterpret_cast<uintptr_t>(q_roped)) & 15)
+        return CGLM_ERR_INVALID_ARG;
+    int slots[128], n_past[128];
+    for (int i = 0; i < n_seq; ++i) {
+        const cglm_attn_seq &s = seqs[i];
+        if (s.qlen != 1 || s.n_past < 0 || s.slot < 0 || s.slot >= a->n_slots) return CGLM_ERR_INVALID_ARG;
+        if (static_cast<long long>(d.n_virtual) + s.n_past + 1 > d.max_len) return CGLM_ERR_INVALID_ARG;
+        slots[i] = s.slot;
+        n_past[i] = s.n_past;
+    }
+    EncodeTiledFn enc = encode_tiled_fn();
+    if (!enc) return CGLM_ERR_CUDA;
+    const int n_feat = (d.n_head + 2 * d.n_kv_head) * d.head_dim;
+    CUtensorMap x_map, w_map;
+    {
+        const cuuint32_t estr[2] = {1, 1};
+        cuuint64_t xdims[2] = {static_cast<cuuint64_t>(hidden), static_cast<cuuint64_t>(n_seq)};
+        cuuint64_t strides[1] = {static_cast<cuuint64_t>(hidden) * 2};
+        cuuint32_t xbox[2] = {64, 128};
+        cuuint64_t wdims[2] = {static_cast<cuuint64_t>(hidden), static_cast<cuuint64_t>(n_feat)};
+        cuuint32_t wbox[2] = {64, 32};
+        if (enc(&x_map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void *>(x_f16), xdims, strides, xbox, estr,
+                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS ||
+            enc(&w_map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void *>(weight_f16), wdims, strides, wbox, estr,
+                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS) {
+            std::snprintf(g_err, sizeof(g_err), "cuTensorMapEncodeTiled failed for the qkv Linear");
+            return CGLM_ERR_CUDA;
+        }
+    }
+    const WsLayout lay = ws_layout(d, a->n_sm, 1, 0, 0);
+    LaunchCtx cx = make_launch_ctx(a, static_cast<uint8_t *>(workspace), lay, static_cast<cudaStream_t>(cuda_stream));
+    CGLM_CUDA(launch_qkv_linear(cx, x_map, w_map, slots, n_past, n_seq, hidden, n_feat, bias, q_roped));
     return CGLM_OK;
 }
 

@@ -1,0 +1,235 @@
+// query_key_value Linear with the front half of the attention path in its epilogue, for decode-sized batches (sm_100a).
+//
+// Covers chatglm.cpp:629 (query_key_value.forward = ggml_mul_mat(weight, x) + bias, Linear::forward chatglm.cpp:418-426)
+// together with what the attention path does to its result before any score is computed: RoPE on q and k
+// (chatglm.cpp:655-656, GLM-2/3/4 half-rotary mode) and the f16 append of the K row and the V^T column at n_past
+// (chatglm.cpp:668-675).  The fused qkv activation never reaches memory; what leaves the kernel is the roped q (f32,
+// for the decode kernel, which then runs with CGLM_SEQ_Q_ROPED | CGLM_SEQ_NO_APPEND) and the two cache updates.
+//
+// One token per sequence, up to 128 sequences per launch.  The GEMM is C[token][feature] = x[token][:] . W[feature][:]
+// with f16 operands and f32 accumulation on the 5th-generation tensor cores: the (zero-padded) 128 tokens are the M
+// rows of tcgen05.mma, a CTA owns 32 output features (N = 32), so 4608 features of a GLM-4 layer are 144 CTAs, one per
+// SM, each streaming its 32 x K slice of the weight exactly once.  Operands are staged by TMA (128-byte swizzle, K-major,
+// 64 k per stage, kStages deep), the accumulator lives in 32 columns of tensor memory, and the epilogue reads it back
+// with tcgen05.ld: thread t holds the 32 features of token t, so a rotary pair (2i, 2i+1) sits in one thread.
+// The kernel is bound by the weight stream (HBM) and by the re-read of x from L2, not by the tensor pipe.
+#include "common.cuh"
+
+namespace cglm {
+
+namespace {
+
+constexpr int kTok = 128;            // M of the MMA: tokens, zero padded
+constexpr int kFeat = 32;            // N of the MMA: output features per CTA
+constexpr int kKStep = 64;           // k per stage: one 128-byte swizzled row of f16
+constexpr int kStages = 6;
+constexpr int kXBytes = kTok * 128;  // x tile [128 tokens][64 k]
+constexpr int kWBytes = kFeat * 128; // W tile [32 features][64 k]
+constexpr int kThreads = 6 * 32;     // 4 epilogue warps (TMEM lanes 0..127), TMA warp, MMA warp
+constexpr int kTmaWarp = 4, kMmaWarp = 5;
+// instruction descriptor of tcgen05.mma.kind::f16: D = f32, A = B = f16, both K-major, N = 32, M = 128
+constexpr uint32_t kIdesc = (1u << 4) | ((static_cast<uint32_t>(kFeat) >> 3) << 17) | ((128u >> 4) << 24);
+
+struct __align__(1024) QkvSmem {
+    uint8_t x[kStages][kXBytes];
+    uint8_t w[kStages][kWBytes];
+    uint64_t full[kStages];
+    uint64_t empty[kStages];
+    uint64_t acc_full;
+    uint32_t tmem_base;
+    int abort_flag;
+};
+
+__device__ __forceinline__ uint64_t smem_desc(uint32_t saddr) {   // K-major operand, 128-byte swizzle, 8-row groups 1024 B apart
+    return static_cast<uint64_t>((saddr & 0x3ffffu) >> 4) | (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
+}
+__device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(kIdesc), "r"(accumulate), "r"(0u)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t *bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+// What the kernel knows about its tokens (kernel parameter): cache slot and position of every sequence.
+struct QkvTable {
+    int n_tok;
+    int slot[kTok];
+    int n_past[kTok];
+};
+
+__global__ void __launch_bounds__(kThreads, 1)
+qkv_linear_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constant__ CUtensorMap w_map,
+                  const __grid_constant__ QkvTable tab, AttnShape sh, int K, const float *__restrict__ bias,
+                  float *__restrict__ q_out, uint16_t *__restrict__ k_base, uint16_t *__restrict__ v_base,
+                  const float2 *__restrict__ rope_tab, int rope_tab_len, WsHeader *hdr) {
+    extern __shared__ uint8_t smem_raw[];
+    QkvSmem &sm = *reinterpret_cast<QkvSmem *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int f0 = blockIdx.x * kFeat;        // first output feature of this CTA
+    const int n_k = K / kKStep;
+
+    if (tid == 0) {
+        sm.abort_flag = 0;
+        for (int s = 0; s < kStages; ++s) {
+            mbar_init(&sm.full[s], 1);
+            mbar_init(&sm.empty[s], 1);
+        }
+        mbar_init(&sm.acc_full, 1);
+        fence_mbar_init();
+    }
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sm.tmem_base)), "r"(32) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = sm.tmem_base;
+    // x is the previous kernel's output (the layer's input norm): nothing is read before it has completed
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+
+    if (warp == kTmaWarp) {
+        if (lane == 0) {
+            tma_prefetch_desc(&x_map);
+            tma_prefetch_desc(&w_map);
+            for (int i = 0; i < n_k; ++i) {
+                const int st = i % kStages;
+                if (i >= kStages && !mbar_wait_bounded(&sm.empty[st], ((i / kStages) - 1) & 1u, &sm.abort_flag)) break;
+                // rows of x past n_tok are outside the tensor map and arrive as zeros: the box is always 128 tokens
+                mbar_arrive_expect_tx(&sm.full[st], kXBytes + kWBytes);
+                tma_load_2d(sm.x[st], &x_map, i * kKStep, 0, &sm.full[st]);
+                tma_load_2d(sm.w[st], &w_map, i * kKStep, f0, &sm.full[st]);
+            }
+        }
+    } else if (warp == kMmaWarp) {
+        if (lane == 0) {
+            for (int i = 0; i < n_k; ++i) {
+                const int st = i % kStages;
+                if (!mbar_wait_bounded(&sm.full[st], (i / kStages) & 1u, &sm.abort_flag)) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+                for (int ks = 0; ks < kKStep / 16; ++ks) {
+                    umma_f16(tmem, smem_desc(smem_u32(sm.x[st]) + ks * 32), smem_desc(smem_u32(sm.w[st]) + ks * 32), (i | ks) != 0);
+                }
+                umma_commit(&sm.empty[st]);   // the stage may be refilled once these MMAs have read it
+            }
+            umma_commit(&sm.acc_full);
+        }
+    } else {
+        // ================================ epilogue: thread t = token t ==============================================
+        const int tok = tid;
+        const bool ok = mbar_wait_bounded(&sm.acc_full, 0, &sm.abort_flag);
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        float acc[kFeat];
+        {
+            uint32_t r[kFeat];
+            const uint32_t taddr = tmem + (static_cast<uint32_t>(32 * warp) << 16);
+            asm volatile(
+                "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+                "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n\t"
+                "tcgen05.wait::ld.sync.aligned;"
+                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+                  "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+                  "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+                  "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                : "r"(taddr)
+                : "memory");
+#pragma unroll
+            for (int i = 0; i < kFeat; ++i) acc[i] = __uint_as_float(r[i]);
+        }
+        if (ok && tok < tab.n_tok) {
+            const int H = sh.H, G = sh.G, D = sh.D;
+            if (bias) {
+#pragma unroll
+                for (int i = 0; i < kFeat; ++i) acc[i] = __fadd_rn(acc[i], __ldg(bias + f0 + i));
+            }
+            // which part of the fused row these 32 features are (blocked layout, chatglm.cpp:646-652): a multiple of 32
+            // never straddles a head (head_dim 128)
+            const int q_feats = H * D, k_feats = G * D;
+            const int kind = f0 < q_feats ? 0 : (f0 < q_feats + k_feats ? 1 : 2);
+            const int rel = kind == 0 ? f0 : (kind == 1 ? f0 - q_feats : f0 - q_feats - k_feats);
+            const int head = rel / D, d0 = rel % D;
+            const int pos = tab.n_past[tok];
+            if (kind != 2 && sh.rope_type == CGLM_ROPE_CHATGLM2 && d0 < D / 2) {
+                // pairs (2i, 2i+1) of the first half of the head, ladder step i = (d0 + 2j) / 2 at this token's position
+#pragma unroll
+                for (int j = 0; j < kFeat / 2; ++j) {
+                    const int li = d0 / 2 + j;
+                    float c, s;
+                    if (pos < rope_tab_len) {
+                        const float2 cs = __ldg(rope_tab + static_cast<long long>(pos) * 32 + li);
+                        c = cs.x; s = cs.y;
+                    } else {
+                        rope_cos_sin(pos, li, sh.theta_scale, c, s);
+                    }
+                    float y0, y1;
+                    rope_rotate(acc[2 * j], acc[2 * j + 1], c, s, y0, y1);
+                    acc[2 * j] = y0; acc[2 * j + 1] = y1;
+                }
+            }
+            const long long row = static_cast<long long>(tab.slot[tok]) * G + head;   // cache row of (slot, kv head)
+            const int cache_pos = sh.V + pos;
+            if (kind == 0) {          // roped q, f32 [token][H * D]
+                float4 *dst = reinterpret_cast<float4 *>(q_out + static_cast<long long>(tok) * q_feats + f0);
+#pragma unroll
+                for (int i = 0; i < kFeat / 4; ++i) dst[i] = make_float4(acc[4 * i], acc[4 * i + 1], acc[4 * i + 2], acc[4 * i + 3]);
+            } else if (kind == 1) {   // k_cache[row][cache_pos][d0 .. d0 + 32)
+                uint4 *dst = reinterpret_cast<uint4 *>(k_base + (row * sh.M + cache_pos) * D + d0);
+#pragma unroll
+                for (int i = 0; i < kFeat / 8; ++i) {
+                    dst[i] = make_uint4(pack_half2(acc[8 * i], acc[8 * i + 1]), pack_half2(acc[8 * i + 2], acc[8 * i + 3]),
+                                        pack_half2(acc[8 * i + 4], acc[8 * i + 5]), pack_half2(acc[8 * i + 6], acc[8 * i + 7]));
+                }
+            } else {                  // v_cache[row][d0 + i][cache_pos]
+                uint16_t *col = v_base + (row * D + d0) * sh.M + cache_pos;
+#pragma unroll
+                for (int i = 0; i < kFeat; ++i) col[static_cast<long long>(i) * sh.M] = __half_as_ushort(__float2half_rn(acc[i]));
+            }
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 0) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(32) : "memory");
+    }
+    if (sm.abort_flag && tid == 0) atomicExch(&hdr->status, static_cast<int>(CGLM_ERR_TIMEOUT));
+}
+
+}  // namespace
+
+// x_map: f16 {K, n_tok}, box {64, 128}; w_map: f16 {K, n_feat}, box {64, 32}; both 128-byte swizzled.
+cudaError_t launch_qkv_linear(const LaunchCtx &cx, const CUtensorMap &x_map, const CUtensorMap &w_map, const int *slots,
+                              const int *n_past, int n_tok, int K, int n_feat, const float *bias, float *q_out) {
+    static PerDeviceOnce configured;
+    const int smem_bytes = static_cast<int>(sizeof(QkvSmem)) + 1024;
+    if (configured.needed(cx.device)) {
+        cudaError_t e = require_current_device(cx.device);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(qkv_linear_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
+        if (e != cudaSuccess) return e;
+        configured.mark(cx.device);
+    }
+    static thread_local QkvTable tab;
+    tab.n_tok = n_tok;
+    for (int i = 0; i < n_tok; ++i) { tab.slot[i] = slots[i]; tab.n_past[i] = n_past[i]; }
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(n_feat / kFeat);
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = smem_bytes;
+    cfg.stream = cx.stream;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, qkv_linear_kernel, x_map, w_map, tab, cx.shape, K, bias, q_out, cx.k_base, cx.v_base,
+                                       cx.rope_tab, cx.rope_tab_len, cx.hdr);
+    g_launch_count += 1;
+    return e != cudaSuccess ? e : cudaGetLastError();
+}
+
+}  // namespace cglm

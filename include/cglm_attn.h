@@ -153,7 +153,12 @@ enum {
      * the softmax still run in f32 and the cache bits are those of the f32 path fed the same (f16-representable)
      * values; the output is the f32 result rounded to nearest even.  q_roped / k_roped stay f32. */
     CGLM_SEQ_QKV_F16 = 32,
-    CGLM_SEQ_OUT_F16 = 64
+    CGLM_SEQ_OUT_F16 = 64,
+    /* q has been through RoPE already (cglm_qkv_linear_forward ropes it in its epilogue): the kernels skip the rotation.
+     * One-token sequences only.  Combined with CGLM_SEQ_NO_APPEND | CGLM_SEQ_USE_KV_LOCAL (kv_local = n_virtual + n_past
+     * + 1) it is the attention call that follows the fused qkv Linear, which has appended K and V itself; k and v are
+     * then not read and may alias q. */
+    CGLM_SEQ_Q_ROPED = 128
 };
 
 /* Scratch the kernels need for n_seq sequences per call with at most max_qlen tokens each. */
@@ -170,6 +175,22 @@ int cglm_attn_workspace_status(void *workspace, void *cuda_stream);
  */
 int cglm_attn_forward(cglm_kv_arena *arena, const cglm_attn_seq *seqs, int n_seq, void *workspace,
                       size_t workspace_bytes, void *cuda_stream);
+/*
+ * query_key_value Linear of a decode step with the front half of the attention path in its epilogue (chatglm.cpp:629 =
+ * Linear::forward, chatglm.cpp:418-426, then :655-656 and :668-675): for n_seq one-token sequences
+ *   qkv = x . weight^T + bias           x f16 [n_seq][hidden] (device), weight f16 [(H + 2G) * D][hidden] as the model file
+ *                                       stores it, bias f32 [(H + 2G) * D] or NULL; tcgen05 tensor cores, f32 accumulation
+ *   q_roped[i] = RoPE(q part)           f32 [n_seq][H * D], what the following attention call takes as q with
+ *                                       CGLM_SEQ_Q_ROPED | CGLM_SEQ_NO_APPEND | CGLM_SEQ_USE_KV_LOCAL
+ *   k_cache / v_cache of seqs[i].slot   RoPE(k part) and the v part appended as f16 at position n_virtual + n_past
+ * The fused qkv activation itself is never written.  Only slot and n_past of each descriptor are read.  Arenas with
+ * head_dim 128, blocked qkv layout and CGLM_ROPE_CHATGLM2 or CGLM_ROPE_DISABLED; hidden a multiple of 64; at most 128
+ * sequences per call; other shapes return CGLM_ERR_UNSUPPORTED (run the Linear elsewhere and call cglm_attn_forward).
+ * x, weight and q_roped 16-byte aligned.  Asynchronous on cuda_stream; workspace as for cglm_attn_forward (status word).
+ */
+int cglm_qkv_linear_forward(cglm_kv_arena *arena, const cglm_attn_seq *seqs, int n_seq, const void *x_f16, int hidden,
+                            const void *weight_f16, const float *bias, float *q_roped, void *workspace,
+                            size_t workspace_bytes, void *cuda_stream);
 /* n_past_dev[i] += delta for i in [0, n): the last node of a captured decode step (see CGLM_SEQ_N_PAST_DEVICE). */
 int cglm_seq_advance(int *n_past_dev, int n, int delta, void *cuda_stream);
 

@@ -578,6 +578,77 @@ def test_f16_hand_off_through_host_buffers(n):
     arena.close()
 
 
+@pytest.mark.parametrize("n_seq,rope", [(1, O.ROPE_CHATGLM2), (9, O.ROPE_CHATGLM2), (64, O.ROPE_CHATGLM2), (128, O.ROPE_DISABLED)])
+def test_fused_qkv_linear_feeds_the_decode_kernel(n_seq, rope):
+    """cglm_qkv_linear_forward (tcgen05 GEMM of the layer input with the f16 query_key_value weight, bias, RoPE and the
+    K/V append in its epilogue) followed by the attention call with CGLM_SEQ_Q_ROPED | CGLM_SEQ_NO_APPEND, against the
+    oracle's Linear (chatglm.cpp:418-426) followed by its attention path.  The GEMM's f32 sums differ from the oracle's
+    in the last bits (another summation order), so the appended f16 rows may differ by one f16 ulp in a few places."""
+    from chatglm_cpp_b200 import _lib
+    A = _A()
+    L = _lib.lib()
+    H, G, D, M, hidden = 32, 2, 128, 1024, 4096
+    desc = make_desc(H, G, D, M, rope=rope)
+    rng = np.random.default_rng(1000 + n_seq)
+    n_past = [int(p) for p in rng.integers(0, M - 1, n_seq)]
+    arena, ws = A.KVArena(desc, n_seq), A.Workspace(desc, n_seq, 1)
+    host = []
+    for i, P in enumerate(n_past):
+        k, v = random_cache(rng, desc, P)
+        upload_cache(arena, i, k, v)
+        host.append((k, v))
+    x = rng.standard_normal((n_seq, hidden)).astype(np.float16)
+    w = (rng.standard_normal(((H + 2 * G) * D, hidden)) / np.sqrt(hidden)).astype(np.float16)
+    bias = rng.standard_normal((H + 2 * G) * D).astype(np.float32)
+    x_d, w_d, b_d = torch.from_numpy(x).cuda(), torch.from_numpy(w).cuda(), torch.from_numpy(bias).cuda()
+    q_roped = torch.zeros(n_seq, H * D, device="cuda")
+    out = torch.zeros(n_seq, H * D, device="cuda")
+    arr = (_lib.AttnSeq * n_seq)()
+    for i, P in enumerate(n_past):
+        arr[i].slot, arr[i].qlen, arr[i].n_past = i, 1, P
+    stream = torch.cuda.current_stream().cuda_stream
+    before = L.cglm_launch_count()
+    rc = L.cglm_qkv_linear_forward(arena._h, arr, n_seq, x_d.data_ptr(), hidden, w_d.data_ptr(), b_d.data_ptr(),
+                                   q_roped.data_ptr(), ws.ptr, ws.bytes, stream)
+    assert rc == 0, L.cglm_last_error_string()
+    calls = [A.SeqCall(qkv=q_roped[i:i + 1], slot=i, n_past=P, out=out[i:i + 1], kv_local=P + 1,
+                       flags=A.SEQ_NO_APPEND | A.SEQ_USE_KV_LOCAL | _lib.SEQ_Q_ROPED) for i, P in enumerate(n_past)]
+    arr2 = (_lib.AttnSeq * n_seq)()
+    for i, c in enumerate(calls):       # q only: k and v alias q and are not read
+        base = c.qkv.data_ptr()
+        arr2[i].q = arr2[i].k = arr2[i].v = base
+        arr2[i].q_head_stride = arr2[i].kv_head_stride = D
+        arr2[i].q_tok_stride = arr2[i].kv_tok_stride = H * D
+        arr2[i].slot, arr2[i].qlen, arr2[i].n_past, arr2[i].kv_local = i, 1, c.n_past, c.kv_local
+        arr2[i].flags, arr2[i].out = c.flags, c.out.data_ptr()
+    _lib.check(L.cglm_attn_forward(arena._h, arr2, n_seq, ws.ptr, ws.bytes, stream), "cglm_attn_forward")
+    torch.cuda.synchronize()
+    assert ws.status() == 0
+    assert L.cglm_launch_count() - before == 2          # the Linear and the decode kernel
+    qkv = O.linear(x.astype(np.float32), w, bias)        # [n, (H + 2G) D] f32
+    cfg = oracle_cfg(desc, "f32")
+    n_bad = 0
+    for i, P in enumerate(n_past):
+        k, v = host[i]
+        want, qr, kr = O.attn_forward(cfg, qkv[i:i + 1], False, k, v, P, want_roped=True)
+        got_q = q_roped[i].cpu().numpy().reshape(H, D)
+        assert np.abs(got_q - qr[0]).max() <= 2e-3, i
+        gk, gv = download_cache(arena, i)
+        for got, exp in ((gk[:, P], k[:, P]), (gv[:, :, P], v[:, :, P])):
+            d16 = np.abs(got.view(np.int16).astype(np.int32) - exp.view(np.int16).astype(np.int32))
+            assert d16.max() <= 1, (i, int(d16.max()))
+            n_bad += int((d16 > 0).sum())
+        np.testing.assert_array_equal(np.delete(gk, P, axis=1), np.delete(k, P, axis=1))   # nothing else was touched
+        np.testing.assert_array_equal(np.delete(gv, P, axis=2), np.delete(v, P, axis=2))
+        assert_out_close(out[i:i + 1].cpu().numpy(), want, f"seq {i} n_past {P}")
+    assert n_bad <= 0.02 * n_seq * 2 * G * D
+    # shapes the fused Linear does not take are refused, not served by another path
+    v1 = A.KVArena(make_desc(8, 8, 128, 256, rope=O.ROPE_CHATGLM, mask=O.MASK_CHATGLM), 1)
+    assert L.cglm_qkv_linear_forward(v1._h, arr, 1, x_d.data_ptr(), hidden, w_d.data_ptr(), None, q_roped.data_ptr(),
+                                     ws.ptr, ws.bytes, stream) == _lib.ERR_UNSUPPORTED
+    arena.close()
+
+
 def test_decode_with_settled_caches_streams_early_and_gives_the_same_bits():
     """CGLM_SEQ_CACHE_SETTLED lets a launch read cache tiles while the previous launch of the stream drains.  Eight
     layer calls back to back, each on its own slots, with and without the flag: same output bits, same caches, and

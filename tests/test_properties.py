@@ -104,11 +104,14 @@ def test_oracle_matches_numpy_twin_on_random_shapes(sh):
     got = O.attn_forward(cfg, qkv, inter, kc, vc, n_past, n_ctx=n_ctx)
     want = twin_forward(H, G, D, V, rope, mask, theta, qkv, inter, kt, vt, n_past, n_ctx)
     assert np.abs(got - want).max() <= 2e-4 * (1 + 1e-3 * (n_past + S)), (sh, float(np.abs(got - want).max()))
-    # the appended rows: f16 round-to-nearest-even of the roped k / of v; the f32 ladder may move a value across a
-    # rounding boundary at large angles, so allow one f16 ulp on K, none on V; nothing outside the appended range
+    # the appended rows: V is a plain f16 rounding (bit-exact); a roped K value comes out of x0 c - x1 s with f32-ladder
+    # angles on one side and float64 angles on the other, so it may land on a neighbouring f16 value (or, where the
+    # two products cancel, a few ulps of a small number away): compare values, and bits wherever nothing was appended
     np.testing.assert_array_equal(vc, vt)
-    dk = np.abs(kc.view(np.int16).astype(np.int32) - kt.view(np.int16).astype(np.int32))
-    assert dk.max() <= 1 and (dk > 0).mean() < 0.02
+    kf, tf = kc.view(np.float16).astype(np.float32), kt.view(np.float16).astype(np.float32)
+    assert np.abs(kf - tf).max() <= 4e-3 and (kc != kt).mean() < 0.02
+    rows = np.r_[0:V + n_past, V + n_past + S:M]
+    np.testing.assert_array_equal(kc[:, rows], kt[:, rows])
 
 
 @settings(max_examples=40, deadline=None)
