@@ -361,8 +361,9 @@ def decode_measure(dd, st, name, n_past, args, seq_ids=None, layers=None, device
     n = len(n_past)
     n_ctx = np.maximum(np.asarray(n_past) // 2, 2).astype(np.int32)
     # Every layer call reads cache rows that no kernel of the step writes (a call appends at n_past of its own layer's
-    # slots only), which is what CGLM_SEQ_CACHE_SETTLED promises.
-    flags = 0 if args.no_settled else _lib.SEQ_CACHE_SETTLED
+    # slots only), which is what CGLM_SEQ_CACHE_SETTLED promises; measured, it gains nothing once the launches hand
+    # over late (the default), so it is off unless asked for.
+    flags = _lib.SEQ_CACHE_SETTLED if args.settled else 0
     arrays = st.seq_arrays(n_past, n_ctx, seq_ids, layers, flags)
     stream = torch.cuda.current_stream().cuda_stream
     res = {"workload": name, "n_seq": n, "layers": layers, "kv_bytes_per_launch": kv_bytes(w, n_past)}
@@ -586,7 +587,7 @@ def split_kv_measure(dd, name, w, args, syn, steps=None):
         peers = [mine if r == rank else A.SplitKVExchange.import_handle(handles[r][1], handles[r][0]) for r in range(world)]
         xchg = A.SplitKVExchange(peers, rank, H, D)
         dd.barrier()
-    settled = 0 if args.no_settled else _lib.SEQ_CACHE_SETTLED     # no step writes rows below n_past of any slot
+    settled = _lib.SEQ_CACHE_SETTLED if args.settled else 0     # no step writes rows below n_past of any slot
     flags = settled | ((_lib.SEQ_USE_KV_LOCAL | (0 if sl.owns_new else _lib.SEQ_NO_APPEND)) if world > 1 else 0)
     if world > 1 and xchg is None:
         flags |= _lib.SEQ_PARTIAL
@@ -812,8 +813,8 @@ def main():
                     help="run this workload alone (default: the headline workload plus the other configurations)")
     ap.add_argument("--headline-only", action="store_true", help="default run without the other configurations")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--no-settled", action="store_true",
-                    help="decode workloads: do not pass CGLM_SEQ_CACHE_SETTLED (every launch waits for the previous one to drain)")
+    ap.add_argument("--settled", action="store_true",
+                    help="decode workloads: pass CGLM_SEQ_CACHE_SETTLED (a launch may stream cache tiles while the previous one drains)")
     ap.add_argument("--e2e-f32", action="store_true", help="host-buffer runs with f32 activations instead of the f16 hand-off")
     ap.add_argument("--exchange", choices=["p2p", "nccl"], default="p2p", help="split-KV workload: how partials travel")
     ap.add_argument("--step-graph", action="store_true",

@@ -130,8 +130,23 @@ struct XchgShared {
     int H, G, R;
 };
 
+// Which CTAs hold parts of an item, worked out (a few 64-bit divisions and a search of the tile prefix) when a segment
+// starts, i.e. while its tiles are still on their way, not between its last tile and the merge.
+struct ItemSpans {
+    long long b0, b1;   // CTAs b0..b1 hold parts of the item
+    int first_slot;     // CTA b0 holds its part in its second slot unless the item begins exactly where b0's span does
+};
+__device__ __forceinline__ ItemSpans item_spans(const Geo &geo, const ItemPos &ip) {
+    ItemSpans is;
+    is.b0 = geo.span_of(ip.seq, ip.g, ip.item_begin, 0);
+    is.b1 = geo.span_of(ip.seq, ip.g, ip.item_begin, ip.n_tiles - 1);
+    is.first_slot = geo.span_start(is.b0) >= ip.item_begin ? 0 : 1;
+    return is;
+}
+
 struct DeliverArgs {
     ItemPos ip;
+    ItemSpans is;
     ItemOut io;
     MergeCtx mc;
     int G, R;
@@ -328,16 +343,6 @@ __device__ __forceinline__ void load_seq_desc(SeqDev &dst, const SeqDev &src, in
 //   CHATGLM:  each 64-dim half rotates as pairs (i, i+32) by ladder angle i, the first half by the position id and
 //             the second by the block position id: the partner of lane l sits in lane l ^ 8.
 __device__ __forceinline__ float4 ldg4(const float *p) { return __ldg(reinterpret_cast<const float4 *>(p)); }
-// four consecutive activations starting at element index e of a row that is f32, or f16 with CGLM_SEQ_QKV_F16
-__device__ __forceinline__ float4 ld_act4(const float *row, long long e, bool f16) {
-    if (f16) {
-        const uint2 u = __ldg(reinterpret_cast<const uint2 *>(reinterpret_cast<const __half *>(row) + e));
-        const float2 a = __half22float2(*reinterpret_cast<const __half2 *>(&u.x));
-        const float2 b = __half22float2(*reinterpret_cast<const __half2 *>(&u.y));
-        return make_float4(a.x, a.y, b.x, b.y);
-    }
-    return ldg4(row + e);
-}
 // four consecutive outputs at element index e of an f32 row, or of an f16 row with CGLM_SEQ_OUT_F16
 __device__ __forceinline__ void st_out4(float *row, long long e, bool f16, float a, float b, float c, float d) {
     if (f16) {
@@ -370,16 +375,37 @@ __device__ __forceinline__ void prepare_segment(QBuf &qb, const AttnShape &sh, c
     const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
     float4 x[kRows + 1], xv = zero4;   // x[kRows]: the new k row
     const bool in_f16 = (sq.flags & CGLM_SEQ_QKV_F16) != 0;   // element strides either way
-    {
-        long long e = static_cast<long long>(g) * R * sq.q_head_stride + 4 * lane;
+    // one branch around each batch of loads, not one per load: all 18 requests leave before anything waits for one
+    if (in_f16) {
+        uint2 raw[kRows + 2];
+        const __half *qh = reinterpret_cast<const __half *>(sq.q) + static_cast<long long>(g) * R * sq.q_head_stride + 4 * lane;
 #pragma unroll
         for (int r = 0; r < kRows; ++r) {
-            x[r] = (r < R && !dry) ? ld_act4(sq.q, e, in_f16) : zero4;
-            e += sq.q_head_stride;
+            raw[r] = (r < R && !dry) ? __ldg(reinterpret_cast<const uint2 *>(qh)) : make_uint2(0u, 0u);
+            qh += sq.q_head_stride;
         }
+        raw[kRows] = (k_needed && !dry) ? __ldg(reinterpret_cast<const uint2 *>(reinterpret_cast<const __half *>(sq.k) + g * sq.kv_head_stride + 4 * lane))
+                                        : make_uint2(0u, 0u);
+        raw[kRows + 1] = (appender && !dry) ? __ldg(reinterpret_cast<const uint2 *>(reinterpret_cast<const __half *>(sq.v) + g * sq.kv_head_stride + 4 * lane))
+                                            : make_uint2(0u, 0u);
+        auto widen = [](uint2 u) {
+            const float2 a = __half22float2(*reinterpret_cast<const __half2 *>(&u.x));
+            const float2 c = __half22float2(*reinterpret_cast<const __half2 *>(&u.y));
+            return make_float4(a.x, a.y, c.x, c.y);
+        };
+#pragma unroll
+        for (int r = 0; r <= kRows; ++r) x[r] = widen(raw[r]);
+        xv = widen(raw[kRows + 1]);
+    } else {
+        const float *src = sq.q + static_cast<long long>(g) * R * sq.q_head_stride + 4 * lane;
+#pragma unroll
+        for (int r = 0; r < kRows; ++r) {
+            x[r] = (r < R && !dry) ? ldg4(src) : zero4;
+            src += sq.q_head_stride;
+        }
+        x[kRows] = (k_needed && !dry) ? ldg4(sq.k + g * sq.kv_head_stride + 4 * lane) : zero4;
+        if (appender && !dry) xv = ldg4(sq.v + g * sq.kv_head_stride + 4 * lane);
     }
-    x[kRows] = (k_needed && !dry) ? ld_act4(sq.k, g * sq.kv_head_stride + 4 * lane, in_f16) : zero4;
-    if (appender && !dry) xv = ld_act4(sq.v, g * sq.kv_head_stride + 4 * lane, in_f16);
     // Lane l fetches ladder angle l of the position stream (and of the block-position stream in CHATGLM mode) from
     // the arena's table in the same round trip.
     int pos_id = 0, block_id = 0;
@@ -681,13 +707,12 @@ __device__ __noinline__ void deliver_part(const DeliverArgs *da, long long b, in
         if (t == 0) v = count_part(ctr, expected);
         return __shfl_sync(0xffffffffu, v, 0);
     };
-    // CTAs b0..b1 hold parts of the item
-    const long long b0 = mc.geo.span_of(ip.seq, ip.g, ip.item_begin, 0), b1 = mc.geo.span_of(ip.seq, ip.g, ip.item_begin, ip.n_tiles - 1);
+    const long long b0 = da->is.b0, b1 = da->is.b1;   // CTAs b0..b1 hold parts of the item
     const int n_parts = static_cast<int>(b1 - b0 + 1);
     const int item = ip.seq * sh.G + ip.g;
     // Slot of the first source at each level: the CTA (group) in which the item begins holds it in its second slot
     // unless the item begins exactly where the CTA's span (the group's first span) does.
-    const int first_cta_slot = mc.geo.span_start(b0) >= ip.item_begin ? 0 : 1;
+    const int first_cta_slot = da->is.first_slot;
     const long long g0 = b0 / kMergeFan, g1 = b1 / kMergeFan;
     const int first_grp_slot = group_slot(g0, b0);
     const bool out_f16 = (sq.flags & CGLM_SEQ_OUT_F16) != 0;
@@ -896,6 +921,7 @@ decode_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__
         int prev_slot = 0;   // partial slot of the previous segment: 0 for the CTA's first segment, else 1
         bool prev_partial = false;
         ItemPos prev_ip{};
+        ItemSpans prev_is{};
         ItemOut prev_sq{};
         while (pos < span_hi && !sm.abort_flag) {
             const ItemPos ip = locate(sm.prefix, n_seq, G, pos);
@@ -944,7 +970,7 @@ decode_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__
                 mbar_wait_bounded(&sm.pdone[prev_slot], 0, &sm.abort_flag);   // each used once: a CTA has <= 2 partials
                 {
                     DeliverArgs &da = sm.dargs[kConsumerWarps];
-                    if (lane == 0) { da.ip = prev_ip; da.io = prev_sq; da.mc = mc; da.G = G; da.R = R; da.xs = kXchg ? &sm.xs : nullptr; }
+                    if (lane == 0) { da.ip = prev_ip; da.is = prev_is; da.io = prev_sq; da.mc = mc; da.G = G; da.R = R; da.xs = kXchg ? &sm.xs : nullptr; }
                     __syncwarp();
                     deliver_part(&da, blockIdx.x, lane, 32, nullptr);
                     __syncwarp();
@@ -954,6 +980,7 @@ decode_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__
             prev_partial = !(pos == ip.item_begin && has_last_tile) && seg_end < span_hi;
             prev_slot = sidx == 0 ? 0 : 1;
             prev_ip = ip;
+            if (prev_partial) prev_is = item_spans(geo, ip);   // while the consumers stream the segment
             prev_sq = ItemOut{sq.out, sq.partial, sq.flags};
             pos = seg_end;
             ++sidx;
@@ -962,7 +989,7 @@ decode_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__
             mbar_wait_bounded(&sm.pdone[prev_slot], 0, &sm.abort_flag);
             {
                     DeliverArgs &da = sm.dargs[kConsumerWarps];
-                    if (lane == 0) { da.ip = prev_ip; da.io = prev_sq; da.mc = mc; da.G = G; da.R = R; da.xs = kXchg ? &sm.xs : nullptr; }
+                    if (lane == 0) { da.ip = prev_ip; da.is = prev_is; da.io = prev_sq; da.mc = mc; da.G = G; da.R = R; da.xs = kXchg ? &sm.xs : nullptr; }
                     __syncwarp();
                     deliver_part(&da, blockIdx.x, lane, 32, nullptr);
                     __syncwarp();
@@ -984,6 +1011,9 @@ decode_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__
             const int last_tile = ip.n_tiles - 1;
             const QBuf &qb = sm.qb[sidx & 1];
 
+            // the span's last segment is finished by these warps themselves: park the item's geometry now, while the
+            // helper warp is still preparing the segment
+            if (!whole_item && seg_end == span_hi && lane == 0) sm.dargs[warp].is = item_spans(geo, ip);
             // what the helper warp prepared: the sequence's scalars and the q tile (A fragments: 8 k-steps of 16 dims)
             mbar_wait_bounded(&sm.qfull[sidx & 1], (sidx >> 1) & 1u, &sm.abort_flag);
             const int kv_before = qb.kv_before, flags = qb.flags;

@@ -635,9 +635,9 @@ def test_fused_qkv_linear_feeds_the_decode_kernel(n_seq, rope):
         assert np.abs(got_q - qr[0]).max() <= 2e-3, i
         gk, gv = download_cache(arena, i)
         for got, exp in ((gk[:, P], k[:, P]), (gv[:, :, P], v[:, :, P])):
-            d16 = np.abs(got.view(np.int16).astype(np.int32) - exp.view(np.int16).astype(np.int32))
-            assert d16.max() <= 1, (i, int(d16.max()))
-            n_bad += int((d16 > 0).sum())
+            gf, ef = got.view(np.float16).astype(np.float32), exp.view(np.float16).astype(np.float32)
+            assert np.abs(gf - ef).max() <= 4e-3, (i, float(np.abs(gf - ef).max()))   # a neighbouring f16 value at most
+            n_bad += int((got != exp).sum())
         np.testing.assert_array_equal(np.delete(gk, P, axis=1), np.delete(k, P, axis=1))   # nothing else was touched
         np.testing.assert_array_equal(np.delete(gv, P, axis=2), np.delete(v, P, axis=2))
         assert_out_close(out[i:i + 1].cpu().numpy(), want, f"seq {i} n_past {P}")
