@@ -126,7 +126,7 @@ struct XchgShared {
     XchgDev xd;
     WsHeader *hdr;
     unsigned int epoch;    // this step's number = the local buffer's counter + 1
-    int slot_words;        // n_head * (head_dim + 2)
+    int slot_words;        // kv heads * kDecodePartialFloats
     int H, G, R;
 };
 
@@ -508,13 +508,15 @@ constexpr int kMergeFan = kDecodeMergeFan;
 __device__ __forceinline__ int group_slot(long long grp, long long b0) { return b0 < grp * kMergeFan ? 0 : 1; }
 
 // 16 dims of one q row merged over sources k0..k1 in one pass with a running maximum, four sources in flight at a
-// time.  Sources are CTA partials (level 0) or group partials (level 1): source k sits at base + 2k slots, except
-// that source k_first uses its second slot when first_slot is 1 (the CTA or group in which the item begins holds
-// the end of the previous item in its first slot).  Every caller goes through this routine with the same source
-// order, so the result does not depend on which CTA or warp happens to complete the item.
+// time.  Sources are CTA partials (level 0) or group partials (level 1): source k sits at base + 2k slots (stride 2),
+// except that source k_first uses its second slot when first_slot is 1 (the CTA or group in which the item begins
+// holds the end of the previous item in its first slot).  The fused split-KV step merges the ranks' copies of a kv
+// head with the same routine: source = rank, stride = kv heads per rank slot.  Every caller goes through this routine with the same source
+// order, so the result does not depend on which CTA or warp happens to complete the item.  Out of line: one copy of
+// the code, which the combine of a fused split-KV step finds warm in the instruction cache right after the item's own merge.
 // dst_kind 0: the result is a group partial (un-normalised) at dst; 1: the sequence's (acc, m, l) row; 2: its f32
 // output; 3: its f16 output.
-__device__ __forceinline__ void merge_row_chunk(const float *base, long long k_first, int first_slot, long long k0,
+__device__ __noinline__ void merge_row_chunk(const float *base, int stride, long long k_first, int first_slot, long long k0,
                                                 long long k1, float *dst, int dst_kind, int r, int d0) {
     float m_run = -INFINITY, den = 0.f;
     float acc[16];
@@ -528,7 +530,7 @@ __device__ __forceinline__ void merge_row_chunk(const float *base, long long k_f
         for (int u = 0; u < 4; ++u) {
             const bool ok = k + u <= k1;
             const long long ks = ok ? k + u : k;
-            const float *pp = base + (ks * 2 + (ks == k_first ? first_slot : 0)) * kDecodePartialFloats;
+            const float *pp = base + (ks * stride + (ks == k_first ? first_slot : 0)) * kDecodePartialFloats;
             mv[u] = ok ? __ldcg(pp + kRows * kD + r) : -INFINITY;
             lv[u] = __ldcg(pp + kRows * kD + kRows + r);
 #pragma unroll
@@ -585,12 +587,16 @@ __device__ __forceinline__ int count_part(int *ctr, int expected) {
 
 
 // ---- fused split-KV step: publish an item's rows to the peers, combine when everything has arrived --------------------
-// Called by the team (n_thr threads, index t) that has just written the (acc, m, l) rows of kv head g into this rank's
-// slot of the LOCAL exchange buffer.  The team copies the rows into the same slot of every peer's buffer with plain
-// peer stores, fences at system scope and publishes the step number in the arrival word [rank][g] of every buffer
-// (release).  The team that publishes this rank's last kv head then waits, with a bound, until the arrival words of
-// every rank and kv head in the local buffer hold the step number, merges the n_rank partials (log-sum-exp) into
-// xd.out and advances the local step counter.  Nothing here waits for another CTA of this grid, only for other GPUs.
+// A rank's slot of an exchange buffer holds, per kv head, one block in the layout of a CTA partial
+// (acc[16][128] | m[16] | l[16], un-normalised, log2 domain): what the ranks exchange is what the CTAs of one
+// launch exchange, and the final combine is merge_row_chunk with source = rank.
+// Called by the team (n_thr threads, index t) that has just written the block of kv head g into this rank's slot of
+// the LOCAL exchange buffer.  The team copies the block into the same slot of every peer's buffer with plain peer
+// stores; after a team barrier its leader fences at system scope and writes the step number into the arrival word
+// [rank][g] of every buffer.  The team that publishes this rank's last kv head then waits, with a bound, until the
+// arrival words of every rank and kv head in the local buffer hold the step number, merges the n_rank blocks of
+// every kv head into xd.out and advances the local step counter.  Nothing here waits for another CTA of this grid,
+// only for other GPUs.
 __device__ __noinline__ void xchg_finish(const XchgShared *xs, int g, int t, int n_thr, int *cta_flag) {
     const XchgDev &xd = xs->xd;
     const unsigned int e = xs->epoch;
@@ -609,22 +615,39 @@ __device__ __noinline__ void xchg_finish(const XchgShared *xs, int g, int t, int
         }
         return __all_sync(0xffffffffu, v != 0);
     };
-    team_sync();   // the rows written by the other members are visible
+    team_sync();   // the block written by the other members is visible
     unsigned int *local = xd.peer[rank];
-    const size_t row0 = static_cast<size_t>(g) * R * (kD + 2);   // first float of the item's rows inside a slot
-    const int n2 = R * (kD + 2) / 2;                              // the item's rows as float2 units
-    const float2 *src = reinterpret_cast<const float2 *>(reinterpret_cast<const float *>(local + xchg_slot_word(set, rank, n_rank, xs->slot_words)) + row0);
-    for (int p = 0; p < n_rank; ++p) {
-        if (p == rank) continue;
-        float2 *dst = reinterpret_cast<float2 *>(reinterpret_cast<float *>(xd.peer[p] + xchg_slot_word(set, rank, n_rank, xs->slot_words)) + row0);
-        for (int i = t; i < n2; i += n_thr) dst[i] = __ldcg(src + i);
+    const size_t blk0 = xchg_slot_word(set, rank, n_rank, xs->slot_words) + static_cast<size_t>(g) * kDecodePartialFloats;
+    if (n_rank > 1) {
+        // every member reads its share once (all loads in flight together: one trip to L2), then stores it to every peer
+        constexpr int kShare = 5, kUnits = kDecodePartialFloats / 4;   // 520 float4 over >= 128 threads; a warp team takes 4 passes
+        const float4 *src = reinterpret_cast<const float4 *>(local + blk0);
+#pragma unroll 1
+        for (int i0 = 0; i0 < kUnits; i0 += kShare * n_thr) {
+            float4 mine[kShare];
+#pragma unroll
+            for (int c = 0; c < kShare; ++c) {
+                const int i = i0 + c * n_thr + t;
+                mine[c] = i < kUnits ? __ldcg(src + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+#pragma unroll 1
+            for (int p = 0; p < n_rank; ++p) {
+                if (p == rank) continue;
+                float4 *dst = reinterpret_cast<float4 *>(xd.peer[p] + blk0);
+#pragma unroll
+                for (int c = 0; c < kShare; ++c) {
+                    const int i = i0 + c * n_thr + t;
+                    if (i < kUnits) dst[i] = mine[c];
+                }
+            }
+        }
     }
-    __threadfence_system();
-    team_sync();
+    team_sync();   // every member's peer stores precede the leader's fence
     int last = 0;
     if (t == 0) {
+        __threadfence_system();   // one fence, then the words: a release per word would wait for each peer in turn
         for (int p = 0; p < n_rank; ++p) {
-            asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(xd.peer[p] + xchg_flag_word(set, rank, g)), "r"(e) : "memory");
+            asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(xd.peer[p] + xchg_flag_word(set, rank, g)), "r"(e) : "memory");
         }
         last = atomicAdd(&xs->hdr->xchg_items, 1) == G - 1;
         if (last) atomicExch(&xs->hdr->xchg_items, 0);   // ready for the next step
@@ -657,24 +680,15 @@ __device__ __noinline__ void xchg_finish(const XchgShared *xs, int g, int t, int
         }
         ok = team_and(ok);
         if (ok) {
-            const int H = xs->H, sw = xs->slot_words;
-            const float *slots = reinterpret_cast<const float *>(local + xchg_slot_word(set, 0, n_rank, sw));
-            for (int u = t; u < H * (kD / 4); u += n_thr) {   // one q head's four dims per unit
-                const int h = u / (kD / 4), d0 = 4 * (u % (kD / 4));
-                float m_star = -INFINITY;
-                for (int p = 0; p < n_rank; ++p) m_star = fmaxf(m_star, __ldcg(slots + static_cast<size_t>(p) * sw + h * (kD + 2) + kD));
-                float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f, den = 0.f;
-                for (int p = 0; p < n_rank; ++p) {
-                    const float *pp = slots + static_cast<size_t>(p) * sw + h * (kD + 2);
-                    const float m = __ldcg(pp + kD);
-                    const float w = m == -INFINITY ? 0.f : __expf(m - m_star);
-                    const float2 x01 = __ldcg(reinterpret_cast<const float2 *>(pp + d0));
-                    const float2 x23 = __ldcg(reinterpret_cast<const float2 *>(pp + d0 + 2));
-                    a0 += w * x01.x; a1 += w * x01.y; a2 += w * x23.x; a3 += w * x23.y;
-                    den += w * __ldcg(pp + kD + 1);
+            // source = rank: rank p's block of kv head gg sits G blocks after rank p - 1's
+            const float *slots = reinterpret_cast<const float *>(local + xchg_slot_word(set, 0, n_rank, xs->slot_words));
+#pragma unroll 1
+            for (int c = t; c < G * kRows * 8; c += n_thr) {
+                const int gg = c / (kRows * 8), r = (c >> 3) & (kRows - 1);
+                if (r < R) {
+                    merge_row_chunk(slots + static_cast<size_t>(gg) * kDecodePartialFloats, G, -1, 0, 0, n_rank - 1,
+                                    xd.out + static_cast<size_t>(gg) * R * kD, 2, r, (c & 7) * 16);
                 }
-                const float inv = 1.f / den;
-                *reinterpret_cast<float4 *>(xd.out + static_cast<size_t>(h) * kD + d0) = make_float4(a0 * inv, a1 * inv, a2 * inv, a3 * inv);
             }
         } else if (t == 0) {
             atomicExch(&xs->hdr->status, static_cast<int>(CGLM_ERR_TIMEOUT));
@@ -719,13 +733,17 @@ __device__ __noinline__ void deliver_part(const DeliverArgs *da, long long b, in
     float *final_dst = (sq.flags & CGLM_SEQ_PARTIAL) ? sq.partial + static_cast<long long>(ip.g) * sh.R * (kD + 2)
                        : out_f16 ? reinterpret_cast<float *>(reinterpret_cast<__half *>(sq.out) + static_cast<long long>(ip.g) * sh.R * kD)
                                  : sq.out + static_cast<long long>(ip.g) * sh.R * kD;
-    const int final_kind = (sq.flags & CGLM_SEQ_PARTIAL) ? 1 : (out_f16 ? 3 : 2);
+    int final_kind = (sq.flags & CGLM_SEQ_PARTIAL) ? 1 : (out_f16 ? 3 : 2);
+    if (da->xs) {   // fused split-KV step: the item's block of this rank's exchange slot, in the partial layout
+        final_dst = sq.partial + static_cast<long long>(ip.g) * kDecodePartialFloats;
+        final_kind = 0;
+    }
     // one merge loop for the three uses below (the arguments vary, the code does not)
     auto merge = [&](const float *base, long long k_first, int first_slot, long long k0, long long k1, float *dst, int kind) {
 #pragma unroll 1
         for (int chunk = t; chunk < kRows * 8; chunk += n_thr) {
             const int r = chunk >> 3;
-            if (r < sh.R) merge_row_chunk(base, k_first, first_slot, k0, k1, dst, kind, r, (chunk & 7) * 16);
+            if (r < sh.R) merge_row_chunk(base, 2, k_first, first_slot, k0, k1, dst, kind, r, (chunk & 7) * 16);
         }
     };
     const float *base = mc.partials;
@@ -793,7 +811,7 @@ decode_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__
         if (kXchg) {
             sm.xs.xd = xchg;
             sm.xs.hdr = hdr;
-            sm.xs.slot_words = sh.H * (kD + 2);
+            sm.xs.slot_words = sh.G * kDecodePartialFloats;
             sm.xs.H = sh.H; sm.xs.G = sh.G; sm.xs.R = sh.R;
         }
     }
@@ -1115,7 +1133,11 @@ decode_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__
                 const bool want_partial = (flags & CGLM_SEQ_PARTIAL) != 0;
                 const int head = g * R + rr;
                 const float inv = 1.f / l_sum;
-                float *scratch = partials + (static_cast<long long>(blockIdx.x) * 2 + (first_segment ? 0 : 1)) * kDecodePartialFloats;
+                // a part goes to this CTA's partial slot; a whole kv head of a fused split-KV step goes to its block of the
+                // exchange slot in the same layout
+                const bool as_partial = !whole_item || kXchg;
+                float *scratch = (kXchg && whole_item) ? partial_ptr + static_cast<long long>(g) * kDecodePartialFloats
+                                 : partials + (static_cast<long long>(blockIdx.x) * 2 + (first_segment ? 0 : 1)) * kDecodePartialFloats;
 #pragma unroll
                 for (int jj = 0; jj < 4; ++jj) {
                     const int q = 8 * warp + 4 * hf + (jj ^ hf);   // the two lanes of a row start on different banks
@@ -1127,7 +1149,7 @@ decode_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__
                     float4 acc;
                     acc.x = ((v0.x + v1.x) + v2.x) + v3.x; acc.y = ((v0.y + v1.y) + v2.y) + v3.y;
                     acc.z = ((v0.z + v1.z) + v2.z) + v3.z; acc.w = ((v0.w + v1.w) + v2.w) + v3.w;
-                    if (!whole_item) {
+                    if (as_partial) {
                         __stcg(reinterpret_cast<float4 *>(scratch + rr * kD + 4 * q), acc);
                     } else if (rr < R) {
                         if (want_partial) {   // rows of kD + 2 floats: 8-byte aligned only
@@ -1141,7 +1163,7 @@ decode_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__
                     }
                 }
                 if (warp == 0 && hf == 0) {
-                    if (!whole_item) {
+                    if (as_partial) {
                         __stcg(&scratch[kRows * kD + rr], m_star);
                         __stcg(&scratch[kRows * kD + kRows + rr], l_sum);
                     } else if (want_partial && rr < R) {

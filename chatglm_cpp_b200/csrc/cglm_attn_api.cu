@@ -875,7 +875,9 @@ int cglm_attn_splitkv_combine(const float *partials, int n_part, int n_head, int
 
 size_t cglm_attn_splitkv_xchg_bytes(int n_rank, int n_head, int head_dim) {
     if (n_rank <= 0 || n_rank > kXchgMaxRanks || n_head <= 0 || head_dim <= 0 || (head_dim & 1)) return 0;
-    return sizeof(unsigned int) * xchg_slot_word(2, 0, n_rank, n_head * (head_dim + 2));
+    // a rank's slot holds one block in the layout of a decode partial per kv head; sized for as many kv heads as heads
+    const int g_max = n_head < kXchgMaxKvHeads ? n_head : kXchgMaxKvHeads;
+    return sizeof(unsigned int) * xchg_slot_word(2, 0, n_rank, g_max * kDecodePartialFloats);
 }
 
 int cglm_xchg_alloc(size_t bytes, void **ptr) {
