@@ -560,7 +560,9 @@ def split_kv_measure(dd, name, w, args, syn, steps=None):
     cap = sharding.slice_capacity(P, 0, world) + 64
     desc = _lib.AttnDesc(H, G, D, cap, 0, w["rope"], w["theta"], w["mask"])
     local_bytes = 4 * G * D * (sl.n_local + (1 if sl.owns_new else 0))
-    n_rot = max(2, int(np.ceil(4 * 126e6 / max(local_bytes, 1))))
+    # the same number of copies on every rank (the ranks' slices differ by a few tokens; a rotation count taken from the
+    # local slice came out 15 on three ranks and 16 on the fourth, and the ranks then ran different numbers of steps)
+    n_rot = max(2, int(np.ceil(4 * 126e6 / (4 * G * D * (cap - 64)))))
     arena = A.KVArena(desc, n_rot)
     syn.fill(arena.k_all(), w["seed"] + rank, TID_K)
     syn.fill(arena.v_all(), w["seed"] + rank, TID_V)
@@ -599,7 +601,10 @@ def split_kv_measure(dd, name, w, args, syn, steps=None):
                                            kv_local=sl.n_local if world > 1 else 0, flags=flags), False)
         arrs.append(arr)
     it = [0]
-    timeout_us = 50000   # a rank that is more than 50 ms behind is treated as gone
+    timeout_us = 200000   # a rank that is more than 200 ms behind is treated as gone
+    # NCCL's collectives inside a replayed graph did not complete at 4 ranks here (no output for 300 s); that exchange is the
+    # comparison path, so beyond 2 ranks it is issued eagerly
+    use_graph = args.issue == "graph" and not (world > 2 and xchg is None)
 
     def step():
         stream = torch.cuda.current_stream().cuda_stream
@@ -621,7 +626,12 @@ def split_kv_measure(dd, name, w, args, syn, steps=None):
         if world > 1:
             dd.dist.all_reduce(st, op=dd.dist.ReduceOp.MIN)
         if int(st.item()) != 0:
-            raise SystemExit(f"[rank {rank}] device-side status {int(st.item())} {where}")
+            detail = ""
+            if xchg is not None:   # which arrival words are missing: [set][rank][kv head], and this rank's step counter
+                words = xchg.read_words(32 + 2 * 16 * 32)
+                flags = [[[int(words[32 + (s_ * 16 + r_) * 32 + g_]) for g_ in range(G)] for r_ in range(world)] for s_ in range(2)]
+                detail = f"; step counter {int(words[0])}, arrival words {flags}"
+            raise SystemExit(f"[rank {rank}] device-side status {int(st.item())} {where}{detail}")
 
     for _ in range(max(args.warmup, 3)):
         step()
@@ -637,20 +647,33 @@ def split_kv_measure(dd, name, w, args, syn, steps=None):
     torch.cuda.current_stream().wait_stream(side)
     dd.barrier()
     it[0] = 0
-    graph = torch.cuda.CUDAGraph()
-    with torch.cuda.graph(graph):
-        for _ in range(n_rot):
-            step()
+    graph = None
+    if use_graph:
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for _ in range(n_rot):
+                step()
+
+    def rotation():
+        if graph is not None:
+            graph.replay()
+        else:
+            for _ in range(n_rot):
+                step()
+
     replays = max(1, (steps + n_rot - 1) // n_rot)
     steps = replays * n_rot
+    # instantiating a graph takes a different time on every rank: the ranks meet again before the first replay, whose
+    # bounded waits would otherwise count the slowest rank's instantiation
+    dd.barrier()
     for _ in range(2):
-        graph.replay()
+        rotation()
     dd.barrier()
     check_status("after the first graph replays")
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(replays):
-        graph.replay()
+        rotation()
     e1.record()
     dd.barrier()
     ms = dd.max_ms(e0.elapsed_time(e1))
@@ -667,7 +690,7 @@ def split_kv_measure(dd, name, w, args, syn, steps=None):
                             if xchg is not None else "decode + NCCL all-gather + combine kernel") +
                            f", {H * (D + 2) * 4} B per rank"),
            "l2_policy": f"rotates through {n_rot} copies of the slice (working set >= 4 x L2)",
-           "issue": f"CUDA graph of {n_rot} steps, replayed",
+           "issue": f"CUDA graph of {n_rot} steps, replayed" if use_graph else "eager launches",
            "roofline": {"bound": "hbm", "achieved": achieved, "peak": pk, "unit": "GB/s", "frac": achieved / pk, "peak_source": src,
                         "kernel": "decode_kernel (the step time includes the exchange and the combine)",
                         "algorithmic_bytes_per_launch": local_bytes, "launch_us": step_ms * 1e3}}
@@ -817,6 +840,7 @@ def main():
                     help="decode workloads: pass CGLM_SEQ_CACHE_SETTLED (a launch may stream cache tiles while the previous one drains)")
     ap.add_argument("--e2e-f32", action="store_true", help="host-buffer runs with f32 activations instead of the f16 hand-off")
     ap.add_argument("--exchange", choices=["p2p", "nccl"], default="p2p", help="split-KV workload: how partials travel")
+    ap.add_argument("--issue", choices=["graph", "eager"], default="graph", help="split-KV workload: replayed CUDA graph or eager launches")
     ap.add_argument("--step-graph", action="store_true",
                     help="with --workload: also time the step as one replayed CUDA graph (device-side n_past)")
     args = ap.parse_args()

@@ -78,6 +78,7 @@ SYMBOLS = {
     "cglm_attn_splitkv_xchg_bytes": (C.c_size_t, [C.c_int, C.c_int, C.c_int]),
     "cglm_xchg_alloc": (C.c_int, [C.c_size_t, C.POINTER(C.c_void_p)]),
     "cglm_xchg_free": (C.c_int, [C.c_void_p]),
+    "cglm_xchg_read": (C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t]),
     "cglm_xchg_export": (C.c_int, [C.c_void_p, C.c_char_p]),
     "cglm_xchg_import": (C.c_int, [C.c_char_p, C.c_int, C.POINTER(C.c_void_p)]),
     "cglm_attn_splitkv_step": (C.c_int, [C.c_void_p, C.POINTER(AttnSeq), C.POINTER(C.c_void_p), C.c_int, C.c_int, C.c_void_p,

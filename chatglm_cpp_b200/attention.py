@@ -243,6 +243,16 @@ class SplitKVExchange:
     def new_buffer(n_rank: int, n_head: int, head_dim: int) -> torch.Tensor:
         return torch.zeros((SplitKVExchange.bytes(n_rank, n_head, head_dim) + 3) // 4, dtype=torch.int32, device="cuda")
 
+    def read_words(self, n: int):
+        """The first n 32-bit words of the local buffer (step counter, arrival words), for diagnostics."""
+        host = torch.empty(n, dtype=torch.int32)
+        buf = self.buffers[self.rank]
+        if isinstance(buf, torch.Tensor):
+            torch.cuda.synchronize()
+            return buf.view(torch.int32)[:n].cpu().numpy().view("uint32")
+        check(_lib.lib().cglm_xchg_read(C.c_void_p(self._local), host.data_ptr(), n * 4), "cglm_xchg_read")
+        return host.numpy().view("uint32")
+
     def step(self, arena: "KVArena", ws: "Workspace", seq_array, out: Optional[torch.Tensor], combine: bool = True,
              timeout_us: int = 0) -> None:
         """One fused launch: attention over this rank's slice, rows published to every rank, merged into ``out``."""

@@ -894,6 +894,13 @@ int cglm_xchg_free(void *ptr) {
     return CGLM_OK;
 }
 
+int cglm_xchg_read(const void *ptr, void *host, size_t bytes) {
+    if (!ptr || !host || bytes == 0) return CGLM_ERR_INVALID_ARG;
+    CGLM_CUDA(cudaDeviceSynchronize());
+    CGLM_CUDA(cudaMemcpy(host, ptr, bytes, cudaMemcpyDeviceToHost));
+    return CGLM_OK;
+}
+
 int cglm_xchg_export(void *ptr, unsigned char handle[64]) {
     static_assert(sizeof(cudaIpcMemHandle_t) == 64, "handle size is part of the ABI");
     if (!ptr || !handle) return CGLM_ERR_INVALID_ARG;

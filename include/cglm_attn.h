@@ -285,6 +285,9 @@ size_t cglm_attn_splitkv_xchg_bytes(int n_rank, int n_head, int head_dim);
  * exits. */
 int cglm_xchg_alloc(size_t bytes, void **ptr);
 int cglm_xchg_free(void *ptr);
+/* Diagnostics: waits for the device, then copies the first `bytes` bytes of a buffer (step counter at word 0, arrival
+ * words [set][rank 0..15][kv head 0..31] from word 32) to host memory. */
+int cglm_xchg_read(const void *ptr, void *host, size_t bytes);
 int cglm_xchg_export(void *ptr, unsigned char handle[64]);
 int cglm_xchg_import(const unsigned char handle[64], int owner_device, void **ptr);
 int cglm_attn_splitkv_step(cglm_kv_arena *arena, const cglm_attn_seq *seq, void *const *xchg, int n_rank, int rank,
