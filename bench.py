@@ -80,9 +80,12 @@ def kv_bytes(w, n_past):
 
 
 def draw_n_past(w, rank, n=None):
-    rng = np.random.default_rng(w["seed"] + 7919 * rank)
+    """The workload's sequence lengths.  Every rank gets the SAME lengths in its own order (weak scaling means the same
+    work per GPU: lengths drawn per rank differed by up to 8 % in total bytes, and the step time, a maximum over ranks,
+    followed the heaviest rank)."""
     lo, hi = w["n_past"]
-    return rng.integers(lo, hi + 1, n or w["seqs"]).astype(np.int32)
+    lengths = np.random.default_rng(w["seed"]).integers(lo, hi + 1, n or w["seqs"]).astype(np.int32)
+    return lengths if rank == 0 else np.random.default_rng(w["seed"] + 7919 * rank).permutation(lengths)
 
 
 def qkv_row(w):
@@ -257,6 +260,15 @@ class Dist:
         if not torch.cuda.is_available():
             raise SystemExit("bench.py needs a CUDA device (there is no CPU fallback); use --impl reference for the CPU path")
         torch.cuda.set_device(self.local)
+        self.cores = None
+        if self.world > 1 and hasattr(os, "sched_setaffinity") and not os.environ.get("CGLM_BENCH_NO_PIN"):
+            # every rank on its own share of the cores this job may use: the ranks' host threads (launches, the copies of the
+            # host-buffer path) otherwise migrate over the same cores
+            avail = sorted(os.sched_getaffinity(0))
+            share = len(avail) // self.world
+            if share >= 2:
+                self.cores = avail[self.local * share:(self.local + 1) * share]
+                os.sched_setaffinity(0, self.cores)
         if self.world > 1:
             import torch.distributed as dist
             os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
@@ -793,7 +805,8 @@ def run_default(args, dd):
             from chatglm_cpp_b200 import sharding
             glob = draw_n_past(w, 0)
             mine = sharding.shard_sequences(len(glob), dd.world, dd.rank)
-            rr = decode_measure(dd, st, name + "_strong", glob[mine], args, seq_ids=list(range(len(mine))), e2e=True, steps=args.steps)
+            rr = decode_measure(dd, st, name + "_strong", glob[mine], args, seq_ids=list(range(len(mine))), e2e=True, step_graph=True,
+                                steps=args.steps)
             ss = decode_summary(rr, 1, pk)
             total = len(glob)
             line["strong"] = {"global_batch": total, "seqs_per_gpu": len(mine), "value": total / (rr["ms_per_step"] * 1e-3),
@@ -801,6 +814,10 @@ def run_default(args, dd):
                               "roofline_frac_rank0": ss["roofline"]["frac"],
                               "e2e": {"value": total / (rr["e2e"]["ms_per_step"] * 1e-3), "unit": "tokens/s",
                                       "ms_per_step": rr["e2e"]["ms_per_step"]},
+                              # few sequences per GPU make a launch shorter than an eager call through Python takes to issue:
+                              # the replayed step graph is the same work without the host in the loop
+                              "step_graph": {"ms_per_step": rr["step_graph"]["ms_per_step"], "unit": "tokens/s",
+                                             "value": total / (rr["step_graph"]["ms_per_step"] * 1e-3)},
                               "note": "the 64 sequences of the 1-GPU workload, sequence i on GPU i mod N, no collective"}
     st.close()
     del st
