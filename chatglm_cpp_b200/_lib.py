@@ -60,6 +60,7 @@ SYMBOLS = {
     "cglm_kv_arena_k_cache": (C.c_void_p, [C.c_void_p, C.c_int]),
     "cglm_kv_arena_v_cache": (C.c_void_p, [C.c_void_p, C.c_int]),
     "cglm_kv_arena_n_slots": (C.c_int, [C.c_void_p]),
+    "cglm_kv_arena_pitch": (C.c_int, [C.c_void_p]),
     "cglm_kv_arena_desc": (C.POINTER(AttnDesc), [C.c_void_p]),
     "cglm_kv_slot_bytes": (C.c_size_t, [C.POINTER(AttnDesc)]),
     "cglm_kv_slot_copy": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]),

@@ -26,8 +26,10 @@ def _stream_ptr() -> int:
 class _DevView:
     """Zero-copy torch view of library-owned device memory."""
 
-    def __init__(self, ptr: int, shape, typestr: str):
+    def __init__(self, ptr: int, shape, typestr: str, strides=None):
         self.__cuda_array_interface__ = {"shape": tuple(shape), "typestr": typestr, "data": (ptr, False), "version": 3}
+        if strides is not None:
+            self.__cuda_array_interface__["strides"] = tuple(strides)   # bytes
 
 
 class KVArena:
@@ -49,6 +51,21 @@ class KVArena:
             check(_lib.lib().cglm_kv_arena_adopt(C.byref(desc), n_slots, adopt[0].data_ptr(), adopt[1].data_ptr(), table,
                                                  C.byref(handle)), "cglm_kv_arena_adopt")
         self._h = handle
+        # tokens between two cache rows as laid out (>= max_len: see cglm_kv_arena_pitch); the views below keep the
+        # reference's extents and carry the pitch in their strides
+        self.pitch = int(_lib.lib().cglm_kv_arena_pitch(self._h))
+
+    def _k_view(self, ptr, lead):
+        d, P = self.desc, self.pitch
+        shape = lead + (d.n_kv_head, d.max_len, d.head_dim)
+        strides = ((d.n_kv_head * P * d.head_dim * 2,) if lead else ()) + (P * d.head_dim * 2, d.head_dim * 2, 2)
+        return torch.as_tensor(_DevView(ptr, shape, "<f2", None if P == d.max_len else strides), device="cuda")
+
+    def _v_view(self, ptr, lead):
+        d, P = self.desc, self.pitch
+        shape = lead + (d.n_kv_head, d.head_dim, d.max_len)
+        strides = ((d.n_kv_head * P * d.head_dim * 2,) if lead else ()) + (d.head_dim * P * 2, P * 2, 2)
+        return torch.as_tensor(_DevView(ptr, shape, "<f2", None if P == d.max_len else strides), device="cuda")
 
     def close(self):
         if self._h:
@@ -65,25 +82,25 @@ class KVArena:
         """f16 [n_kv_head, max_len, head_dim] view of the slot's k_cache (chatglm.h:470)."""
         d = self.desc
         ptr = _lib.lib().cglm_kv_arena_k_cache(self._h, slot)
-        return torch.as_tensor(_DevView(ptr, (d.n_kv_head, d.max_len, d.head_dim), "<f2"), device="cuda")
+        return self._k_view(ptr, ())
 
     def v_cache(self, slot: int) -> torch.Tensor:
         """f16 [n_kv_head, head_dim, max_len] view of the slot's transposed v_cache (chatglm.h:471)."""
         d = self.desc
         ptr = _lib.lib().cglm_kv_arena_v_cache(self._h, slot)
-        return torch.as_tensor(_DevView(ptr, (d.n_kv_head, d.head_dim, d.max_len), "<f2"), device="cuda")
+        return self._v_view(ptr, ())
 
     def k_all(self) -> torch.Tensor:
         """f16 [n_slots, n_kv_head, max_len, head_dim] view of every k_cache (the arena keeps them contiguous)."""
         d = self.desc
         ptr = _lib.lib().cglm_kv_arena_k_cache(self._h, 0)
-        return torch.as_tensor(_DevView(ptr, (self.n_slots, d.n_kv_head, d.max_len, d.head_dim), "<f2"), device="cuda")
+        return self._k_view(ptr, (self.n_slots,))
 
     def v_all(self) -> torch.Tensor:
         """f16 [n_slots, n_kv_head, head_dim, max_len] view of every v_cache."""
         d = self.desc
         ptr = _lib.lib().cglm_kv_arena_v_cache(self._h, 0)
-        return torch.as_tensor(_DevView(ptr, (self.n_slots, d.n_kv_head, d.head_dim, d.max_len), "<f2"), device="cuda")
+        return self._v_view(ptr, (self.n_slots,))
 
     def load_prefix(self, slot: int, past_kv: torch.Tensor) -> None:
         """past_kv: f16 [2, n_kv_head, n_virtual, head_dim] on the device (chatglm.h:580-615)."""

@@ -21,7 +21,8 @@ static_assert(sizeof(cglm_attn_seq) == 128 && offsetof(cglm_attn_seq, position_i
               "cglm_attn_seq layout");
 
 struct cglm_kv_arena {
-    cglm_attn_desc desc;
+    cglm_attn_desc desc;        // as the kernels see it: max_len is the PITCH of a cache row in tokens
+    cglm_attn_desc user_desc;   // as the caller gave it: max_len is the capacity the calls are checked against
     int n_slots;
     int device;
     int n_sm;
@@ -390,6 +391,12 @@ int cglm_kv_arena_create(const cglm_attn_desc *desc, int n_slots, cglm_kv_arena 
     cglm_kv_arena *a = new (std::nothrow) cglm_kv_arena();
     if (!a) return CGLM_ERR_INVALID_ARG;
     a->desc = *desc;
+    a->user_desc = *desc;
+    // A row of V^T is `pitch` tokens long and TMA wants row pitches in multiples of 16 bytes: caches of the library's
+    // own are laid out with the capacity rounded up to a multiple of 8 tokens (a P-Tuning prefix makes max_length +
+    // num_virtual_tokens odd-sized), so such models keep the fused kernels.  Calls are still checked against max_len.
+    if (desc->head_dim == 128) a->desc.max_len = (desc->max_len + 7) / 8 * 8;
+    desc = &a->desc;
     a->n_slots = n_slots;
     a->n_sm = n_sm;
     cudaGetDevice(&a->device);
@@ -474,6 +481,7 @@ int cglm_kv_arena_adopt(const cglm_attn_desc *desc, int n_slots, void *k_base, v
     cglm_kv_arena *a = new (std::nothrow) cglm_kv_arena();
     if (!a) return CGLM_ERR_INVALID_ARG;
     a->desc = *desc;
+    a->user_desc = *desc;   // caller-owned caches keep the caller's pitch
     a->n_slots = n_slots;
     a->n_sm = n_sm;
     cudaGetDevice(&a->device);
@@ -538,7 +546,8 @@ void *cglm_kv_arena_v_cache(const cglm_kv_arena *a, int slot) {
     return a->v_base + a->k_slot_elems * slot;
 }
 int cglm_kv_arena_n_slots(const cglm_kv_arena *a) { return a ? a->n_slots : 0; }
-const cglm_attn_desc *cglm_kv_arena_desc(const cglm_kv_arena *a) { return a ? &a->desc : nullptr; }
+const cglm_attn_desc *cglm_kv_arena_desc(const cglm_kv_arena *a) { return a ? &a->user_desc : nullptr; }
+int cglm_kv_arena_pitch(const cglm_kv_arena *a) { return a ? a->desc.max_len : 0; }
 
 int cglm_kv_slot_copy(cglm_kv_arena *a, int slot, void *k_host, void *v_host, int to_device, void *cuda_stream) {
     if (!a || slot < 0 || slot >= a->n_slots) return CGLM_ERR_INVALID_ARG;
@@ -630,7 +639,7 @@ int cglm_attn_forward(cglm_kv_arena *a, const cglm_attn_seq *seqs, int n_seq, vo
             return CGLM_ERR_INVALID_ARG;
         const int kv_before = (s.flags & CGLM_SEQ_USE_KV_LOCAL) ? s.kv_local : d.n_virtual + s.n_past;
         const int appended = (s.flags & CGLM_SEQ_NO_APPEND) ? 0 : s.qlen;
-        if (static_cast<long long>(kv_before) + appended > d.max_len) return CGLM_ERR_INVALID_ARG;
+        if (static_cast<long long>(kv_before) + appended > a->user_desc.max_len) return CGLM_ERR_INVALID_ARG;
         if (d.rope_type == CGLM_ROPE_CHATGLM && !s.position_ids && s.n_ctx < 2) return CGLM_ERR_INVALID_ARG;
         const int L = kv_before + appended;
         is_fast[i] = fast_ok && s.qlen == 1 && L >= 1 &&
@@ -951,7 +960,7 @@ int cglm_attn_splitkv_step(cglm_kv_arena *a, const cglm_attn_seq *seq, void *con
     if ((s.flags & CGLM_SEQ_USE_KV_LOCAL) && s.kv_local < 0) return CGLM_ERR_INVALID_ARG;
     const int kv_before = (s.flags & CGLM_SEQ_USE_KV_LOCAL) ? s.kv_local : d.n_virtual + s.n_past;
     const int appended = (s.flags & CGLM_SEQ_NO_APPEND) ? 0 : 1;
-    if (static_cast<long long>(kv_before) + appended > d.max_len) return CGLM_ERR_INVALID_ARG;
+    if (static_cast<long long>(kv_before) + appended > a->user_desc.max_len) return CGLM_ERR_INVALID_ARG;
     if (kv_before + appended < 1) {
         std::snprintf(g_err, sizeof(g_err), "a rank of a fused split-KV step must hold at least one attended position");
         return CGLM_ERR_UNSUPPORTED;
@@ -1013,7 +1022,7 @@ int cglm_qkv_linear_forward(cglm_kv_arena *a, const cglm_attn_seq *seqs, int n_s
     for (int i = 0; i < n_seq; ++i) {
         const cglm_attn_seq &s = seqs[i];
         if (s.qlen != 1 || s.n_past < 0 || s.slot < 0 || s.slot >= a->n_slots) return CGLM_ERR_INVALID_ARG;
-        if (static_cast<long long>(d.n_virtual) + s.n_past + 1 > d.max_len) return CGLM_ERR_INVALID_ARG;
+        if (static_cast<long long>(d.n_virtual) + s.n_past + 1 > a->user_desc.max_len) return CGLM_ERR_INVALID_ARG;
         slots[i] = s.slot;
         n_past[i] = s.n_past;
     }

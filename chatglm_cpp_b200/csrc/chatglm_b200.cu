@@ -72,9 +72,18 @@ void ModelContext::alloc_kv() {
     CHATGLM_CHECK(have_desc_ && !kv_tensors_.empty()) << "no attention module registered";
     const int n_slots = static_cast<int>(kv_tensors_.size() / 2);
     CHATGLM_CHECK_CGLM(cglm_kv_arena_create(&desc_, n_slots, &arena_));
+    // the library lays a cache row out with a pitch that may exceed max_length + v (rounded up to 8 tokens at
+    // head_dim 128): the tensors keep the reference's extents and carry the pitch in their byte strides
+    const int64_t pitch = cglm_kv_arena_pitch(arena_);
     for (int s = 0; s < n_slots; ++s) {
-        kv_tensors_[2 * s]->data = cglm_kv_arena_k_cache(arena_, s);
-        kv_tensors_[2 * s + 1]->data = cglm_kv_arena_v_cache(arena_, s);
+        Tensor *k = kv_tensors_[2 * s].get(), *v = kv_tensors_[2 * s + 1].get();
+        k->data = cglm_kv_arena_k_cache(arena_, s);
+        v->data = cglm_kv_arena_v_cache(arena_, s);
+        k->nb[2] = k->nb[1] * pitch;
+        k->nb[3] = k->nb[2] * k->ne[2];
+        v->nb[1] = v->nb[0] * pitch;
+        v->nb[2] = v->nb[1] * v->ne[1];
+        v->nb[3] = v->nb[2] * v->ne[2];
     }
 }
 
@@ -114,16 +123,45 @@ void ModelContext::reset_scratch() {
     scratch_.clear();
 }
 
+// A cache tensor of an arena whose row pitch exceeds its extent is not contiguous: such a tensor is copied whole
+// (offset 0, all of it) as a 2-D copy of its contiguous runs.  Returns false for a contiguous tensor.
+static bool pitched_runs(const Tensor *t, size_t *width, size_t *height, size_t *pitch) {
+    size_t run = element_size(t->type);
+    for (int i = 0; i < 4; ++i) {
+        if (static_cast<size_t>(t->nb[i]) != run) {
+            *width = run;
+            *pitch = static_cast<size_t>(t->nb[i]);
+            *height = 1;
+            for (int j = i; j < 4; ++j) *height *= static_cast<size_t>(t->ne[j]);
+            return true;
+        }
+        run *= static_cast<size_t>(t->ne[i]);
+    }
+    return false;
+}
+
 void ModelContext::tensor_set(Tensor *t, const void *host, size_t offset, size_t size) {
     CHATGLM_CHECK(offset + size <= nbytes(t)) << "tensor_set out of range";
+    size_t w, h, pitch;
+    if (pitched_runs(t, &w, &h, &pitch)) {
+        CHATGLM_CHECK(offset == 0 && size == nbytes(t)) << "a pitched tensor is copied whole";
+        CHATGLM_CHECK_CUDA(cudaMemcpy2DAsync(t->data, pitch, host, w, w, h, cudaMemcpyHostToDevice, static_cast<cudaStream_t>(stream_)));
+        return;
+    }
     CHATGLM_CHECK_CUDA(cudaMemcpyAsync(static_cast<char *>(t->data) + offset, host, size, cudaMemcpyHostToDevice,
                                        static_cast<cudaStream_t>(stream_)));
 }
 
 void ModelContext::tensor_get(const Tensor *t, void *host, size_t offset, size_t size) {
     CHATGLM_CHECK(offset + size <= nbytes(t)) << "tensor_get out of range";
-    CHATGLM_CHECK_CUDA(cudaMemcpyAsync(host, static_cast<const char *>(t->data) + offset, size, cudaMemcpyDeviceToHost,
-                                       static_cast<cudaStream_t>(stream_)));
+    size_t w, h, pitch;
+    if (pitched_runs(t, &w, &h, &pitch)) {
+        CHATGLM_CHECK(offset == 0 && size == nbytes(t)) << "a pitched tensor is copied whole";
+        CHATGLM_CHECK_CUDA(cudaMemcpy2DAsync(host, w, t->data, pitch, w, h, cudaMemcpyDeviceToHost, static_cast<cudaStream_t>(stream_)));
+    } else {
+        CHATGLM_CHECK_CUDA(cudaMemcpyAsync(host, static_cast<const char *>(t->data) + offset, size, cudaMemcpyDeviceToHost,
+                                           static_cast<cudaStream_t>(stream_)));
+    }
     CHATGLM_CHECK_CUDA(cudaStreamSynchronize(static_cast<cudaStream_t>(stream_)));
 }
 

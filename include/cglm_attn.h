@@ -89,6 +89,11 @@ void *cglm_kv_arena_k_cache(const cglm_kv_arena *arena, int slot);
 void *cglm_kv_arena_v_cache(const cglm_kv_arena *arena, int slot);
 int cglm_kv_arena_n_slots(const cglm_kv_arena *arena);
 const cglm_attn_desc *cglm_kv_arena_desc(const cglm_kv_arena *arena);
+/* Tokens between two rows of a cache as laid out: k_cache is [n_kv_head][pitch][head_dim], v_cache
+ * [n_kv_head][head_dim][pitch], of which the first max_len tokens are used.  pitch = max_len for adopted caches; an arena
+ * of the library's own rounds it up to a multiple of 8 at head_dim 128 (TMA wants 16-byte row pitches), so that a model
+ * whose max_length + num_virtual_tokens is not a multiple of 8 (P-Tuning v2) keeps the fused kernels. */
+int cglm_kv_arena_pitch(const cglm_kv_arena *arena);
 /* Bytes of one slot (k_cache + v_cache). */
 size_t cglm_kv_slot_bytes(const cglm_attn_desc *desc);
 /* Whole-slot copies between host and device, the counterpart of ggml_backend_tensor_set/get on the cache

@@ -217,6 +217,8 @@ int main() {
         {"glm1 mha interleaved 2d-rope", 1024, 8, 8, 256, 0, true, RopeType::CHATGLM, AttentionMaskType::CHATGLM, 7, true},
         {"glm1 derived position ids", 1024, 8, 8, 256, 0, true, RopeType::CHATGLM, AttentionMaskType::CHATGLM, 7, false},
         {"glm3 p-tuning prefix d4", 32, 8, 2, 8, 5, false, RopeType::CHATGLM2, AttentionMaskType::CAUSAL, 3, false},
+        // max_length + num_virtual_tokens = 133: the arena's rows have a pitch of 136 tokens, the tensors keep ne = 133
+        {"glm3 p-tuning prefix d128 odd capacity", 1024, 8, 2, 128, 5, false, RopeType::CHATGLM2, AttentionMaskType::CAUSAL, 9, false},
     };
     try {
         for (const Case &c : cases) run_case(c);

@@ -93,10 +93,28 @@ def test_decode_virtual_tokens_d128():
     run_decode_batch(make_desc(32, 2, 128, 1024 + 8, V=8), [0, 5, 900], seed=8)
 
 
+def test_decode_ptuning_capacity_not_a_multiple_of_8_stays_on_the_fused_kernel():
+    """max_length + num_virtual_tokens = 1029: the arena lays its rows out with a pitch of 1032 tokens, the views keep
+    the reference's extents, the calls are checked against 1029 (the last position fills the cache exactly), and the
+    step is ONE fused launch, not the generic path's two."""
+    from chatglm_cpp_b200 import _lib
+    before = _lib.lib().cglm_launch_count()
+    run_decode_batch(make_desc(32, 2, 128, 1029, V=5), [0, 700, 1023], seed=9)
+    assert _lib.lib().cglm_launch_count() - before == 1
+    A = _A()
+    desc = make_desc(32, 2, 128, 1029, V=5)
+    arena = A.KVArena(desc, 1)
+    assert arena.pitch == 1032 and tuple(arena.v_cache(0).shape) == (2, 128, 1029) and arena.v_cache(0).stride(1) == 1032
+    ws = A.Workspace(desc, 1, 1)
+    call = A.SeqCall(qkv=torch.zeros(1, qkv_width(desc, False), device="cuda"), slot=0, n_past=1024,
+                     out=torch.zeros(1, 32 * 128, device="cuda"))
+    with pytest.raises(_lib.CglmError):          # position 1024 would be token 1030 of a cache of 1029
+        A.forward_batch(arena, ws, [call], False)
+    arena.close()
+
+
 def test_decode_generic_shapes():
-    """Shapes only the generic kernel covers: capacity not a multiple of 8, head_dim 64, 32 q heads per kv head,
-    full-head rope modes."""
-    run_decode_batch(make_desc(32, 2, 128, 1029, V=5), [0, 700], seed=9)
+    """Shapes only the generic kernel covers: head_dim 64, 32 q heads per kv head, full-head rope modes."""
     run_decode_batch(make_desc(8, 2, 64, 256), [100], seed=10)
     run_decode_batch(make_desc(32, 1, 128, 256), [100], seed=11)
     run_decode_batch(make_desc(4, 4, 32, 128, rope=O.ROPE_GPTJ), [50], seed=12)
@@ -168,6 +186,7 @@ def test_prefill_then_decode(H, G, D, M, V, rope, mask, S):
     (32, 2, 2048, 0, O.ROPE_CHATGLM2, O.MASK_CAUSAL, 128),
     (8, 2, 512, 0, O.ROPE_CHATGLM2, O.MASK_CAUSAL, 129),
     (8, 2, 512 + 8, 8, O.ROPE_CHATGLM2, O.MASK_CAUSAL, 300),  # P-Tuning prefix in front of the prompt
+    (8, 2, 512 + 5, 5, O.ROPE_CHATGLM2, O.MASK_CAUSAL, 300),  # the same with a capacity that is not a multiple of 8
     (8, 8, 512, 0, O.ROPE_CHATGLM, O.MASK_CHATGLM, 200),      # v1: MHA, interleaved qkv, 2-D rope, prefix mask
     (4, 1, 264, 0, O.ROPE_DISABLED, O.MASK_CAUSAL, 256),
 ])
