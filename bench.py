@@ -451,9 +451,11 @@ def decode_measure(dd, st, name, n_past, args, seq_ids=None, layers=None, device
         with torch.cuda.graph(graph):
             step_dyn()
         ms_graph, _ = timed(dd, graph.replay, steps, args.warmup)
+        ms_dyn, _ = timed(dd, step_dyn, steps, args.warmup)   # the same launches issued eagerly: what the graph itself costs or saves
         if st.ws.status() != 0:
             raise SystemExit(f"{name}: device-side status is not clean after the step-graph region")
         res["step_graph"] = {"ms_per_step": ms_graph / steps, "launches_per_step": layers + 1,
+                             "same_launches_eager_ms_per_step": ms_dyn / steps,
                              "note": "one CUDA graph per decode step, n_past read from device words, replayed"}
         graph = None
     return res

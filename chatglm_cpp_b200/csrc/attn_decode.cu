@@ -512,11 +512,10 @@ __device__ __forceinline__ int group_slot(long long grp, long long b0) { return 
 // except that source k_first uses its second slot when first_slot is 1 (the CTA or group in which the item begins
 // holds the end of the previous item in its first slot).  The fused split-KV step merges the ranks' copies of a kv
 // head with the same routine: source = rank, stride = kv heads per rank slot.  Every caller goes through this routine with the same source
-// order, so the result does not depend on which CTA or warp happens to complete the item.  Out of line: one copy of
-// the code, which the combine of a fused split-KV step finds warm in the instruction cache right after the item's own merge.
+// order, so the result does not depend on which CTA or warp happens to complete the item.
 // dst_kind 0: the result is a group partial (un-normalised) at dst; 1: the sequence's (acc, m, l) row; 2: its f32
 // output; 3: its f16 output.
-__device__ __noinline__ void merge_row_chunk(const float *base, int stride, long long k_first, int first_slot, long long k0,
+__device__ __forceinline__ void merge_row_chunk(const float *base, int stride, long long k_first, int first_slot, long long k0,
                                                 long long k1, float *dst, int dst_kind, int r, int d0) {
     float m_run = -INFINITY, den = 0.f;
     float acc[16];
@@ -585,6 +584,12 @@ __device__ __forceinline__ int count_part(int *ctr, int expected) {
     return last;
 }
 
+
+// Out of line for the combine of a fused split-KV step (inlined into the item merge above, where a call per chunk
+// cost batch-1 decode 0.4 us per launch).
+__device__ __noinline__ void merge_row_chunk_ool(const float *base, int stride, long long k1, float *dst, int dst_kind, int r, int d0) {
+    merge_row_chunk(base, stride, -1, 0, 0, k1, dst, dst_kind, r, d0);
+}
 
 // ---- fused split-KV step: publish an item's rows to the peers, combine when everything has arrived --------------------
 // A rank's slot of an exchange buffer holds, per kv head, one block in the layout of a CTA partial
@@ -686,8 +691,8 @@ __device__ __noinline__ void xchg_finish(const XchgShared *xs, int g, int t, int
             for (int c = t; c < G * kRows * 8; c += n_thr) {
                 const int gg = c / (kRows * 8), r = (c >> 3) & (kRows - 1);
                 if (r < R) {
-                    merge_row_chunk(slots + static_cast<size_t>(gg) * kDecodePartialFloats, G, -1, 0, 0, n_rank - 1,
-                                    xd.out + static_cast<size_t>(gg) * R * kD, 2, r, (c & 7) * 16);
+                    merge_row_chunk_ool(slots + static_cast<size_t>(gg) * kDecodePartialFloats, G, n_rank - 1,
+                                        xd.out + static_cast<size_t>(gg) * R * kD, 2, r, (c & 7) * 16);
                 }
             }
         } else if (t == 0) {
