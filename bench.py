@@ -70,7 +70,7 @@ HBM_FALLBACK_GBS = 6650.0   # B200 copy bandwidth from an earlier measurement, u
 TENSOR_FALLBACK_TFLOPS = 1590.0
 # (dram__bytes_read.sum + dram__bytes_write.sum) / algorithmic KV bytes of one decode launch, from the ncu capture of
 # the _small workload, whose launches are identical to the default workload's (see profiles/).
-NCU_TRAFFIC_PER_KV_BYTE = 1.043
+NCU_TRAFFIC_PER_KV_BYTE = 1.050
 TID_K, TID_V, TID_QKV = 1, 2, 3   # tensor ids of the synthetic generator
 
 
