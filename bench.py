@@ -59,6 +59,14 @@ WORKLOADS = {
     # BASELINE config 2: one 1024-token prompt into an empty cache, causal; the tcgen05 path
     "glm3_6b_prefill_1024": dict(H=32, G=2, D=128, M=2048, layers=1, seqs=1, n_past=(0, 0), rope=8, theta=10000.0,
                                  interleaved=False, mask=0, seed=1002, prefill=1024),
+    # the query_key_value Linear in front of the path, fused with RoPE and the K/V append (decode-sized batch; a step is the
+    # 40 layers' Linears, every layer its own 37.7 MB f16 weight, so the weights stream from HBM)
+    "glm4_9b_qkv_linear_b64": dict(H=32, G=2, D=128, M=8192, layers=40, seqs=64, n_past=(1024, 8191), rope=8, theta=5.0e6,
+                                   interleaved=False, mask=0, seed=1003, qkv_linear=4096),
+    "glm4_9b_qkv_linear_b8": dict(H=32, G=2, D=128, M=8192, layers=40, seqs=8, n_past=(1024, 8191), rope=8, theta=5.0e6,
+                                  interleaved=False, mask=0, seed=1003, qkv_linear=4096),
+    "glm4_9b_qkv_linear_b128": dict(H=32, G=2, D=128, M=8192, layers=40, seqs=128, n_past=(1024, 8191), rope=8, theta=5.0e6,
+                                    interleaved=False, mask=0, seed=1003, qkv_linear=4096),
     "glm3_6b_prefill_8192": dict(H=32, G=2, D=128, M=8192, layers=1, seqs=1, n_past=(0, 0), rope=8, theta=10000.0,
                                  interleaved=False, mask=0, seed=1002, prefill=8192),
     # BASELINE config 5: ChatGLM-6B v1, MHA, interleaved qkv, 2-D rope
@@ -555,6 +563,70 @@ def prefill_measure(dd, name, w, args, syn, steps=None):
                          "peak_source": src, "kernel": "prefill kernels (whole call)", "useful_flops_per_call": flops}}
 
 
+# ---- the Linear in front of the path ------------------------------------------------------------------------------------
+def qkv_linear_measure(dd, name, w, args, syn, steps=None):
+    """A step is the fused query_key_value Linear (bias, RoPE, K/V append in the epilogue) of every layer for a batch of
+    one-token sequences: `layers` launches, each streaming its own f16 weight.  Bound: the weight bytes over HBM."""
+    import torch
+    from chatglm_cpp_b200 import _lib
+    from chatglm_cpp_b200 import attention as A
+    L = _lib.lib()
+    H, G, D, hidden, layers, n = w["H"], w["G"], w["D"], w["qkv_linear"], w["layers"], w["seqs"]
+    steps = steps or args.steps
+    n_feat = (H + 2 * G) * D
+    desc = _lib.AttnDesc(H, G, D, w["M"], 0, w["rope"], w["theta"], w["mask"])
+    arena = A.KVArena(desc, n)            # the layers append into the same slots: irrelevant for the timing
+    ws = A.Workspace(desc, n, 1)
+    weight = torch.empty(layers, n_feat, hidden, device="cuda", dtype=torch.float16)
+    syn.fill(weight, w["seed"], 11)
+    weight.mul_(1.0 / np.sqrt(hidden))
+    x = torch.empty(n, hidden, device="cuda", dtype=torch.float16)
+    syn.fill(x, w["seed"], 12)
+    bias = torch.zeros(n_feat, device="cuda")
+    q_roped = torch.empty(n, H * D, device="cuda")
+    n_past = draw_n_past(w, dd.rank)
+    arr = (_lib.AttnSeq * n)()
+    for i in range(n):
+        arr[i].slot, arr[i].qlen, arr[i].n_past = i, 1, int(n_past[i])
+
+    def step():
+        stream = torch.cuda.current_stream().cuda_stream
+        for l in range(layers):
+            rc = L.cglm_qkv_linear_forward(arena._h, arr, n, x.data_ptr(), hidden, weight[l].data_ptr(), bias.data_ptr(),
+                                           q_roped.data_ptr(), ws.ptr, ws.bytes, stream)
+            if rc != 0:
+                raise _lib.CglmError(rc, "cglm_qkv_linear_forward")
+
+    # the step as a replayed CUDA graph: an eager call (two tensor maps encoded on the host per call, through ctypes) takes
+    # about as long to issue as the kernel runs
+    ms_eager, launches = timed(dd, step, steps, max(args.warmup, 3))
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        step()
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        step()
+    ms, _ = timed(dd, graph.replay, steps, max(args.warmup, 3))
+    graph = None
+    if ws.status() != 0:
+        raise SystemExit(f"{name}: device-side status is not clean after the timed region")
+    ms /= steps
+    pk, src = peak("hbm_gbs", HBM_FALLBACK_GBS)
+    w_bytes = n_feat * hidden * 2
+    achieved = w_bytes * layers / (ms * 1e-3) / 1e9
+    arena.close()
+    return {"metric": "qkv_linear_tokens_per_s", "value": n * dd.world / (ms * 1e-3), "unit": "tokens/s", "ms_per_step": ms,
+            "steps": steps, "launches": int(launches), "tokens": n,
+            "l2_policy": f"every layer call streams its own {w_bytes / 1e6:.1f} MB weight ({layers} layers > L2)",
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": pk, "unit": "GB/s", "frac": achieved / pk,
+                         "peak_source": src, "kernel": "qkv_linear_kernel", "algorithmic_bytes_per_launch": w_bytes,
+                         "launch_us": ms * 1e3 / layers, "issue": "CUDA graph of the step, replayed",
+                         "eager_launch_us": ms_eager / steps * 1e3 / layers}}
+
+
 # ---- one long sequence (config 4) ----------------------------------------------------------------------------------------
 def split_kv_measure(dd, name, w, args, syn, steps=None):
     """Strong scaling of ONE long sequence.  1 GPU: one fused decode launch per step.  N GPUs: rank r holds a contiguous
@@ -747,6 +819,13 @@ def run_single(args, dd, name, w):
                             "prompt_tokens": w["prefill"], "l2_policy": r["l2_policy"]},
                     roofline=dict(r["roofline"], traffic=None), cpu_baseline=None, e2e=None, gpu_launches=r["launches"],
                     clocks=sampler.finish())
+    elif w.get("qkv_linear"):
+        r = qkv_linear_measure(dd, name, w, args, syn)
+        line = dict(base_line(args, dd, r["metric"]), value=r["value"], ms_per_step=r["ms_per_step"],
+                    config={"workload": name, "n_head": w["H"], "n_kv_head": w["G"], "head_dim": w["D"], "hidden": w["qkv_linear"],
+                            "layers": w["layers"], "tokens": r["tokens"], "l2_policy": r["l2_policy"]},
+                    roofline=dict(r["roofline"], traffic=None), cpu_baseline=None, e2e=None, gpu_launches=r["launches"] * dd.world,
+                    clocks=sampler.finish())
     elif w.get("split_kv"):
         r = split_kv_measure(dd, name, w, args, syn)
         line = dict(base_line(args, dd, scaling="strong"), value=r["value"], ms_per_step=r["ms_per_step"], steps=r["steps"],
@@ -834,6 +913,9 @@ def run_default(args, dd):
         for nm in ("glm3_6b_prefill_1024", "glm3_6b_prefill_8192"):
             rr = prefill_measure(dd, nm, WORKLOADS[nm], args, syn, steps=short)
             configs[nm] = {k: rr[k] for k in ("metric", "value", "unit", "ms_per_step", "steps", "prompt_tokens", "roofline")}
+        nm = "glm4_9b_qkv_linear_b64"
+        rr = qkv_linear_measure(dd, nm, WORKLOADS[nm], args, syn, steps=short)
+        configs[nm] = {k: rr[k] for k in ("metric", "value", "unit", "ms_per_step", "steps", "tokens", "roofline")}
         nm = "glm4_9b_long_131072"
         rr = split_kv_measure(dd, nm, WORKLOADS[nm], args, syn, steps=short)
         entry = {k: rr[k] for k in ("value", "unit", "ms_per_step", "steps", "parallelism", "kv_bytes_this_rank", "roofline", "issue")}

@@ -1034,7 +1034,7 @@ int cglm_qkv_linear_forward(cglm_kv_arena *a, const cglm_attn_seq *seqs, int n_s
         const cuuint32_t estr[2] = {1, 1};
         cuuint64_t xdims[2] = {static_cast<cuuint64_t>(hidden), static_cast<cuuint64_t>(n_seq)};
         cuuint64_t strides[1] = {static_cast<cuuint64_t>(hidden) * 2};
-        cuuint32_t xbox[2] = {64, 128};
+        cuuint32_t xbox[2] = {64, static_cast<cuuint32_t>(qkv_linear_x_rows(n_seq))};
         cuuint64_t wdims[2] = {static_cast<cuuint64_t>(hidden), static_cast<cuuint64_t>(n_feat)};
         cuuint32_t wbox[2] = {64, 32};
         if (enc(&x_map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void *>(x_f16), xdims, strides, xbox, estr,
