@@ -53,6 +53,9 @@ struct cglm_kv_arena {
     HostCall host_calls[kHostCalls];
     int host_next;
     bool host_ready;
+    // calls served straight from mapped host memory (no staging): the last such call's kernel, for cglm_attn_host_drain
+    cudaEvent_t direct_done;
+    bool direct_ready, direct_used;
     std::mutex mu;
 };
 
@@ -443,6 +446,7 @@ int cglm_kv_arena_create(const cglm_attn_desc *desc, int n_slots, cglm_kv_arena 
         cudaEventCreateWithFlags(&a->ring_events[i], cudaEventDisableTiming);
     }
     a->host_ready = false;
+    a->direct_ready = a->direct_used = false;
     a->host_next = 0;
     *out = a;
     return CGLM_OK;
@@ -514,6 +518,7 @@ int cglm_kv_arena_adopt(const cglm_attn_desc *desc, int n_slots, void *k_base, v
         cudaEventCreateWithFlags(&a->ring_events[i], cudaEventDisableTiming);
     }
     a->host_ready = false;
+    a->direct_ready = a->direct_used = false;
     a->host_next = 0;
     *out = a;
     return CGLM_OK;
@@ -529,6 +534,7 @@ int cglm_kv_arena_destroy(cglm_kv_arena *a) {
         cudaStreamDestroy(a->copy_in);
         cudaStreamDestroy(a->copy_out);
     }
+    if (a->direct_ready) cudaEventDestroy(a->direct_done);
     for (int i = 0; i < a->ring_slots; ++i) cudaEventDestroy(a->ring_events[i]);
     delete[] a->ring_events;
     if (a->ring) cudaFreeHost(a->ring);
@@ -813,7 +819,21 @@ int cglm_attn_forward_host(cglm_kv_arena *a, const cglm_attn_seq *seqs, int n_se
         void *dout = din ? mapped(out_host) : nullptr;
         if (din && dout) {
             point_at(din, dout);
-            return cglm_attn_forward(a, dev_seqs.data(), n_seq, workspace, workspace_bytes, cuda_stream);
+            const int rc = cglm_attn_forward(a, dev_seqs.data(), n_seq, workspace, workspace_bytes, cuda_stream);
+            if (rc != CGLM_OK) return rc;
+            // the kernel stores the outputs into host memory itself: a drain enqueued on ANOTHER stream has to wait for it
+            cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+            cudaStreamIsCapturing(static_cast<cudaStream_t>(cuda_stream), &cap);
+            if (cap == cudaStreamCaptureStatusNone) {
+                std::lock_guard<std::mutex> lock(a->mu);
+                if (!a->direct_ready) {
+                    CGLM_CUDA(cudaEventCreateWithFlags(&a->direct_done, cudaEventDisableTiming));
+                    a->direct_ready = true;
+                }
+                CGLM_CUDA(cudaEventRecord(a->direct_done, static_cast<cudaStream_t>(cuda_stream)));
+                a->direct_used = true;
+            }
+            return CGLM_OK;
         }
     }
     point_at(dev_qkv, dev_out);
@@ -864,9 +884,10 @@ int cglm_attn_forward_host(cglm_kv_arena *a, const cglm_attn_seq *seqs, int n_se
 
 int cglm_attn_host_drain(cglm_kv_arena *a, void *cuda_stream) {
     if (!a) return CGLM_ERR_INVALID_ARG;
-    if (!a->host_ready) return CGLM_OK;
     cudaStream_t st = static_cast<cudaStream_t>(cuda_stream);
     std::lock_guard<std::mutex> lock(a->mu);
+    if (a->direct_used) CGLM_CUDA(cudaStreamWaitEvent(st, a->direct_done, 0));
+    if (!a->host_ready) return CGLM_OK;
     for (auto &c : a->host_calls) {
         if (c.used) CGLM_CUDA(cudaStreamWaitEvent(st, c.d2h, 0));
     }

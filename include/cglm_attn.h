@@ -224,8 +224,10 @@ int cglm_attn_forward_host(cglm_kv_arena *arena, const cglm_attn_seq *seqs, int 
                            const void *qkv_host, void *out_host, void *dev_qkv, void *dev_out,
                            void *workspace, size_t workspace_bytes, void *cuda_stream);
 
-/* Makes cuda_stream wait for every device-to-host copy that cglm_attn_forward_host has enqueued for this arena: the
- * point where a step's results are read back (ggml_backend_tensor_get at the end of a step, chatglm.cpp:764). */
+/* Makes cuda_stream wait for every device-to-host copy that cglm_attn_forward_host has enqueued for this arena, and for
+ * the last kernel that stored its outputs into pinned host memory itself: the point where a step's results are read
+ * back (ggml_backend_tensor_get at the end of a step, chatglm.cpp:764).  cuda_stream may be any stream.  (A
+ * cglm_attn_forward_host call issued while its stream is being captured records nothing: drain on the same stream.) */
 int cglm_attn_host_drain(cglm_kv_arena *arena, void *cuda_stream);
 
 /*

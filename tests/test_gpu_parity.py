@@ -451,6 +451,44 @@ def test_forward_host_roundtrip_matches_device_call(pinned):
         assert torch.equal(arena.v_cache(i), arena.v_cache(n + i))
 
 
+def test_forward_host_drain_on_another_stream_and_uninitialised_workspace():
+    """The drain may be enqueued on a stream other than the one the host-buffer calls ran on, also when pinned buffers
+    made the kernel write the outputs into host memory itself: the other stream then waits for that kernel.  And a
+    workspace that never went through cglm_attn_workspace_init is reported by the status query."""
+    from chatglm_cpp_b200 import _lib
+    A = _A()
+    L = _lib.lib()
+    desc = make_desc(32, 2, 128, 1024)
+    rng = np.random.default_rng(32)
+    n, n_past = 4, [900, 1000, 1023, 700]
+    arena, ws = A.KVArena(desc, 2 * n), A.Workspace(desc, n, 1)
+    qkv = rng.standard_normal((n, qkv_width(desc, False))).astype(np.float32)
+    for i, P in enumerate(n_past):
+        k, v = random_cache(rng, desc, P)
+        upload_cache(arena, i, k, v)
+        upload_cache(arena, n + i, k, v)
+    calls = [A.SeqCall(qkv=torch.from_numpy(qkv[i:i + 1]).cuda(), slot=i, n_past=P, out=torch.zeros(1, 4096, device="cuda"))
+             for i, P in enumerate(n_past)]
+    A.forward_batch(arena, ws, calls)
+    torch.cuda.synchronize()
+    qkv_pinned, out_pinned = torch.from_numpy(qkv).pin_memory(), torch.zeros(n, 4096).pin_memory()
+    dev_qkv, dev_out = torch.empty(n, qkv.shape[1], device="cuda"), torch.empty(n, 4096, device="cuda")
+    arr = (_lib.AttnSeq * n)()
+    for i, P in enumerate(n_past):
+        arr[i].slot, arr[i].qlen, arr[i].n_past = n + i, 1, P
+    work, other = torch.cuda.Stream(), torch.cuda.Stream()
+    _lib.check(L.cglm_attn_forward_host(arena._h, arr, n, 0, qkv_pinned.data_ptr(), out_pinned.data_ptr(), dev_qkv.data_ptr(),
+                                        dev_out.data_ptr(), ws.ptr, ws.bytes, work.cuda_stream), "forward_host")
+    _lib.check(L.cglm_attn_host_drain(arena._h, other.cuda_stream), "host_drain")
+    other.synchronize()                       # only the OTHER stream is waited for
+    for i in range(n):
+        assert torch.equal(out_pinned[i], calls[i].out[0].cpu())
+    torch.cuda.synchronize()
+    raw = torch.zeros(ws.bytes, dtype=torch.uint8, device="cuda")          # never initialised
+    assert L.cglm_attn_workspace_status(raw.data_ptr(), None) == _lib.ERR_WORKSPACE
+    arena.close()
+
+
 def test_forward_host_pipeline_reuses_staging_buffers():
     """Six host-buffer calls in a row over two staging pairs (copies overlap neighbouring kernels): every call's
     output must equal the plain device call's, i.e. the reuse of a staging buffer is ordered correctly."""
