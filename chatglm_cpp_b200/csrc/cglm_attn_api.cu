@@ -1051,26 +1051,39 @@ int cglm_qkv_linear_forward(cglm_kv_arena *a, const cglm_attn_seq *seqs, int n_s
     if (!enc) return CGLM_ERR_CUDA;
     const int n_feat = (d.n_head + 2 * d.n_kv_head) * d.head_dim;
     CUtensorMap x_map, w_map;
-    {
-        const cuuint32_t estr[2] = {1, 1};
-        cuuint64_t xdims[2] = {static_cast<cuuint64_t>(hidden), static_cast<cuuint64_t>(n_seq)};
-        cuuint64_t strides[1] = {static_cast<cuuint64_t>(hidden) * 2};
-        cuuint32_t xbox[2] = {64, static_cast<cuuint32_t>(qkv_linear_x_rows(n_seq))};
-        cuuint64_t wdims[2] = {static_cast<cuuint64_t>(hidden), static_cast<cuuint64_t>(n_feat)};
-        cuuint32_t wbox[2] = {64, 32};
-        if (enc(&x_map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void *>(x_f16), xdims, strides, xbox, estr,
+    // Both operands as 3-D tensors {64 k of a block, rows, k blocks}: one box brings `kb` consecutive 64-k blocks of its
+    // rows, which land in shared memory as kb consecutive K-major tiles (fewer, larger TMA operations per byte).
+    int kb = qkv_linear_k_blocks(n_seq, hidden);
+    {   // CGLM_QKV_K_BLOCKS overrides the choice (tuning knob, read once; a value that does not divide hidden / 64 or leaves
+        // fewer than two stages is ignored)
+        static const int forced = [] { const char *e = std::getenv("CGLM_QKV_K_BLOCKS"); return e ? std::atoi(e) : 0; }();
+        if (forced >= 1 && forced <= 16 && (hidden / 64) % forced == 0 &&
+            forced * (qkv_linear_x_rows(n_seq) * 128 + 4096) <= 200 * 1024) kb = forced;
+    }
+    const int x_rows = qkv_linear_x_rows(n_seq);
+    for (;; kb = 1) {
+        const cuuint32_t estr[3] = {1, 1, 1};
+        cuuint64_t xdims[3] = {64, static_cast<cuuint64_t>(n_seq), static_cast<cuuint64_t>(hidden / 64)};
+        cuuint64_t strides[2] = {static_cast<cuuint64_t>(hidden) * 2, 128};
+        cuuint32_t xbox[3] = {64, static_cast<cuuint32_t>(x_rows), static_cast<cuuint32_t>(kb)};
+        cuuint64_t wdims[3] = {64, static_cast<cuuint64_t>(n_feat), static_cast<cuuint64_t>(hidden / 64)};
+        cuuint32_t wbox[3] = {64, 32, static_cast<cuuint32_t>(kb)};
+        if (enc(&x_map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, const_cast<void *>(x_f16), xdims, strides, xbox, estr,
                 CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS ||
-            enc(&w_map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void *>(weight_f16), wdims, strides, wbox, estr,
+                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS &&
+            enc(&w_map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, const_cast<void *>(weight_f16), wdims, strides, wbox, estr,
                 CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS) {
+                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS) {
+            break;
+        }
+        if (kb == 1) {
             std::snprintf(g_err, sizeof(g_err), "cuTensorMapEncodeTiled failed for the qkv Linear");
             return CGLM_ERR_CUDA;
         }
     }
     const WsLayout lay = ws_layout(d, a->n_sm, 1, 0, 0);
     LaunchCtx cx = make_launch_ctx(a, static_cast<uint8_t *>(workspace), lay, static_cast<cudaStream_t>(cuda_stream));
-    CGLM_CUDA(launch_qkv_linear(cx, x_map, w_map, slots, n_past, n_seq, hidden, n_feat, bias, q_roped));
+    CGLM_CUDA(launch_qkv_linear(cx, x_map, w_map, slots, n_past, n_seq, hidden, n_feat, kb, bias, q_roped));
     return CGLM_OK;
 }
 

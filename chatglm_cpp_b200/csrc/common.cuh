@@ -329,11 +329,13 @@ size_t prefill_q_half_bytes(int H, int S);
 cudaError_t launch_prefill(const LaunchCtx &cx, const SeqDev &sq, const CUtensorMap &q_map, const CUtensorMap &k_map,
                            const CUtensorMap &v_map, __half *q_half);
 constexpr int kPrefillMinTokens = 128;
-// fused query_key_value Linear + RoPE + append for one-token sequences (tcgen05): x_map f16 {K, n_tok} box
-// {64, qkv_linear_x_rows(n_tok)}, w_map f16 {K, n_feat} box {64, 32}, both 128-byte swizzled
+// fused query_key_value Linear + RoPE + append for one-token sequences (tcgen05): x_map f16 {64, n_tok, K/64} box
+// {64, qkv_linear_x_rows(n_tok), kb}, w_map f16 {64, n_feat, K/64} box {64, 32, kb}, both 128-byte swizzled;
+// kb (64-k blocks per box) <= qkv_linear_k_blocks(n_tok, K)
 int qkv_linear_x_rows(int n_tok);
+int qkv_linear_k_blocks(int n_tok, int K);
 cudaError_t launch_qkv_linear(const LaunchCtx &cx, const CUtensorMap &x_map, const CUtensorMap &w_map, const int *slots,
-                              const int *n_past, int n_tok, int K, int n_feat, const float *bias, float *q_out);
+                              const int *n_past, int n_tok, int K, int n_feat, int kb, const float *bias, float *q_out);
 int decode_max_ctas(int n_sm);
 constexpr int kDecodeMergeFan = 16;   // CTAs per group of the two-level merge
 constexpr int kDecodePartialFloats = 16 * 128 + 32;   // acc[16][128] | m[16] | l[16]

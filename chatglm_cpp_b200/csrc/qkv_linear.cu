@@ -13,13 +13,15 @@
 // 64 k per stage), the accumulator lives in 32 columns of tensor memory, and the epilogue reads it back with
 // tcgen05.ld: thread t holds the 32 features of token t, so a rotary pair (2i, 2i+1) sits in one thread.
 // A stage holds only as many x rows as there are tokens (rounded up to 8; the MMA still reads 128 rows, the rest is
-// whatever the shared memory holds and lands in accumulator rows nobody reads), so a small batch gets a deep ring
-// (32 stages of 5 KB for 8 tokens, 10 stages of 20 KB for 128) out of the same 200 KB.
-// Measured (B200, 4608 x 4096 f16 weight, every call another layer's weight): 29 us per launch for 8, 64 and 128
-// tokens alike, 1.3 TB/s of weight stream.  Timer stamps inside the kernel: the first stage's data is there 1.9 us
-// after entry, then one 64-k stage every 0.4 us whatever the ring depth (6 or 32 stages in flight), the token count or
-// the order in which the CTAs walk k; with one MMA per stage instead of four, 0.3 us: the four MMAs of a stage cost
-// 0.03 us each and are not the limiter, the arrival of 128-byte weight rows at 8 KiB stride is.
+// whatever the shared memory holds and lands in accumulator rows nobody reads) and `kb` consecutive 64-k blocks: both
+// operands are described to TMA as 3-D tensors {64 k, rows, k blocks}, so ONE box brings kb blocks, which land as kb
+// consecutive K-major tiles.  kb is as large as leaves two stages in the ring (8 blocks up to 64 tokens, 4 for 128).
+// Measured (B200, 4608 x 4096 f16 weight, every call another layer's weight, the step replayed as a graph): with one
+// 64-k block per box the kernel took 29 us per launch for 8, 64 and 128 tokens alike, one stage every 0.4 us
+// whatever the ring depth (6 or 32 stages), the token count or the order in which the CTAs walk k, while the four
+// MMAs of a stage cost 0.03 us each: the number of TMA operations was the limiter, not the bytes in flight.  With kb
+// blocks per box: 17.3 / 18.2 / 23.1 us for 8 / 64 / 128 tokens (2.1 TB/s of weight stream at 64 tokens).  The first
+// round of the ring is filled with weights before the dependency wait; x follows after it.
 #include "common.cuh"
 
 namespace cglm {
@@ -32,7 +34,16 @@ constexpr int kKStep = 64;           // k per stage: one 128-byte swizzled row o
 constexpr int kMaxStages = 32;
 constexpr int kXBytes = kTok * 128;  // what the MMA reads from an x tile: [128 tokens][64 k]
 constexpr int kWBytes = kFeat * 128; // W tile [32 features][64 k]
-constexpr int kRingBudget = 232448 - 2048 - kXBytes;   // dynamic shared memory minus alignment slack, header, read-over slack
+// One CTA per SM with all of its shared memory (two per SM with half each, so that consecutive launches overlap, was
+// measured: 17.0 / 20.1 / 30.0 us for 8 / 64 / 128 tokens against 17.7 / 18.7 / 23.8 us: box size matters more).
+constexpr int kSmemPerCta = 232448;
+// bytes the MMA reads past the end of the ring's last x tile that the W tiles behind it do not already cover
+constexpr int read_over_slack(int x_rows, int kb) {
+    return (kTok - x_rows) * 128 > kb * kWBytes ? (kTok - x_rows) * 128 - kb * kWBytes : 0;
+}
+constexpr int ring_stages(int x_rows, int kb) {
+    return (kSmemPerCta - 2048 - read_over_slack(x_rows, kb)) / (kb * (x_rows * 128 + kWBytes));
+}
 constexpr int kThreads = 6 * 32;     // 4 epilogue warps (TMEM lanes 0..127), TMA warp, MMA warp
 constexpr int kTmaWarp = 4, kMmaWarp = 5;
 // instruction descriptor of tcgen05.mma.kind::f16: D = f32, A = B = f16, both K-major, N = 32, M = 128
@@ -44,8 +55,8 @@ struct __align__(1024) QkvSmem {
     uint64_t acc_full;
     uint32_t tmem_base;
     int abort_flag;
-    // 1024-byte aligned: n_stages stages of (x tile of x_rows rows | W tile), then kXBytes of slack: the MMA reads
-    // 128 rows from every x tile, whatever x_rows is
+    // 1024-byte aligned: n_stages stages of (kb x tiles of x_rows rows | kb W tiles), then read_over_slack(): the MMA
+    // reads 128 rows from every x tile, whatever x_rows is
     __align__(1024) uint8_t ring[1];
 };
 
@@ -72,15 +83,16 @@ struct QkvTable {
 
 __global__ void __launch_bounds__(kThreads, 1)
 qkv_linear_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constant__ CUtensorMap w_map,
-                  const __grid_constant__ QkvTable tab, AttnShape sh, int K, int x_rows, int n_stages, const float *__restrict__ bias,
+                  const __grid_constant__ QkvTable tab, AttnShape sh, int K, int x_rows, int kb, int n_stages, const float *__restrict__ bias,
                   float *__restrict__ q_out, uint16_t *__restrict__ k_base, uint16_t *__restrict__ v_base,
                   const float2 *__restrict__ rope_tab, int rope_tab_len, WsHeader *hdr) {
     extern __shared__ uint8_t smem_raw[];
     QkvSmem &sm = *reinterpret_cast<QkvSmem *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int f0 = blockIdx.x * kFeat;        // first output feature of this CTA
-    const int n_k = K / kKStep;
-    const int x_bytes = x_rows * 128, stage_bytes = x_bytes + kWBytes;
+    const int n_k = K / (kKStep * kb);                       // stages of kb 64-k blocks each
+    const int x_tile = x_rows * 128, x_bytes = kb * x_tile;   // kb x tiles, then kb W tiles
+    const int stage_bytes = x_bytes + kb * kWBytes;
     const int k_first = static_cast<int>(blockIdx.x) % n_k;
 
     if (tid == 0) {
@@ -100,24 +112,31 @@ qkv_linear_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_consta
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem = sm.tmem_base;
-    // x is the previous kernel's output (the layer's input norm): nothing is read before it has completed
-    asm volatile("griddepcontrol.wait;" ::: "memory");
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    // x is the previous kernel's output (the layer's input norm) and the caches and q_out may still be read by it: only
+    // the weights are touched before it has completed (the first round of the ring is filled with them ahead of the wait)
 
     if (warp == kTmaWarp) {
         if (lane == 0) {
             tma_prefetch_desc(&x_map);
             tma_prefetch_desc(&w_map);
-            for (int i = 0, st = 0, round = 0; i < n_k; ++i) {
-                if (round > 0 && !mbar_wait_bounded(&sm.empty[st], (round - 1) & 1u, &sm.abort_flag)) break;
-                // rows of x past n_tok are outside the tensor map and arrive as zeros: the box is x_rows tokens
+            // CTA b walks k from its own starting column and wraps, so that the 4608 weight rows are not all read at the
+            // same offset inside their 8 KiB at the same time
+            const int pre = n_stages < n_k ? n_stages : n_k;
+            for (int i = 0; i < pre; ++i) {
+                mbar_arrive_expect_tx(&sm.full[i], stage_bytes);
+                tma_load_3d(sm.ring + i * stage_bytes + x_bytes, &w_map, 0, f0, ((i + k_first) % n_k) * kb, &sm.full[i]);
+            }
+            asm volatile("griddepcontrol.wait;" ::: "memory");
+            asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+            // rows of x past n_tok are outside the tensor map and arrive as zeros: the box is x_rows tokens
+            for (int i = 0; i < pre; ++i) tma_load_3d(sm.ring + i * stage_bytes, &x_map, 0, 0, ((i + k_first) % n_k) * kb, &sm.full[i]);
+            for (int i = pre, st = 0, round = 1; i < n_k; ++i) {
+                if (!mbar_wait_bounded(&sm.empty[st], (round - 1) & 1u, &sm.abort_flag)) break;
                 uint8_t *stage = sm.ring + st * stage_bytes;
                 mbar_arrive_expect_tx(&sm.full[st], stage_bytes);
-                // CTA b walks k from its own starting column and wraps, so that the 4608 weight rows are not all read at the
-                // same offset inside their 8 KiB at the same time
                 const int kk = (i + k_first) % n_k;
-                tma_load_2d(stage, &x_map, kk * kKStep, 0, &sm.full[st]);
-                tma_load_2d(stage + x_bytes, &w_map, kk * kKStep, f0, &sm.full[st]);
+                tma_load_3d(stage, &x_map, 0, 0, kk * kb, &sm.full[st]);
+                tma_load_3d(stage + x_bytes, &w_map, 0, f0, kk * kb, &sm.full[st]);
                 if (++st == n_stages) { st = 0; ++round; }
             }
         }
@@ -127,9 +146,12 @@ qkv_linear_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_consta
                 if (!mbar_wait_bounded(&sm.full[st], round & 1u, &sm.abort_flag)) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t xs = smem_u32(sm.ring + st * stage_bytes), wsm = xs + x_bytes;
+#pragma unroll 1
+                for (int b = 0; b < kb; ++b) {
 #pragma unroll
-                for (int ks = 0; ks < kKStep / 16; ++ks) {
-                    umma_f16(tmem, smem_desc(xs + ks * 32), smem_desc(wsm + ks * 32), (i | ks) != 0);
+                    for (int ks = 0; ks < kKStep / 16; ++ks) {
+                        umma_f16(tmem, smem_desc(xs + b * x_tile + ks * 32), smem_desc(wsm + b * kWBytes + ks * 32), (i | b | ks) != 0);
+                    }
                 }
                 umma_commit(&sm.empty[st]);   // the stage may be refilled once these MMAs have read it
                 if (++st == n_stages) { st = 0; ++round; }
@@ -139,6 +161,7 @@ qkv_linear_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_consta
     } else {
         // ================================ epilogue: thread t = token t ==============================================
         const int tok = tid;
+        asm volatile("griddepcontrol.wait;" ::: "memory");   // before this thread writes q_out and the caches
         const bool ok = mbar_wait_bounded(&sm.acc_full, 0, &sm.abort_flag);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         float acc[kFeat];
@@ -219,19 +242,30 @@ qkv_linear_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_consta
 }  // namespace
 
 int qkv_linear_x_rows(int n_tok) { return n_tok <= 8 ? 8 : (n_tok + 7) / 8 * 8; }
+// 64-k blocks per TMA box: as many as leave two stages in the ring (measured: large boxes matter more than depth;
+// 29 us per launch with one block per box and 32 stages, 18-20 us with 8 or 4 blocks per box)
+int qkv_linear_k_blocks(int n_tok, int K) {
+    const int x_rows = qkv_linear_x_rows(n_tok);
+    for (int kb = 8; kb > 1; kb >>= 1) {
+        if ((K / kKStep) % kb == 0 && ring_stages(x_rows, kb) >= 2) return kb;
+    }
+    return 1;
+}
 
-// x_map: f16 {K, n_tok}, box {64, qkv_linear_x_rows(n_tok)}; w_map: f16 {K, n_feat}, box {64, 32}; both 128-byte swizzled.
+// x_map: f16 {64, n_tok, K/64}, box {64, qkv_linear_x_rows(n_tok), kb}; w_map: f16 {64, n_feat, K/64}, box {64, 32, kb};
+// both 128-byte swizzled.
 cudaError_t launch_qkv_linear(const LaunchCtx &cx, const CUtensorMap &x_map, const CUtensorMap &w_map, const int *slots,
-                              const int *n_past, int n_tok, int K, int n_feat, const float *bias, float *q_out) {
+                              const int *n_past, int n_tok, int K, int n_feat, int kb, const float *bias, float *q_out) {
     static PerDeviceOnce configured;
-    const int x_rows = qkv_linear_x_rows(n_tok), stage_bytes = x_rows * 128 + kWBytes;
-    int n_stages = kRingBudget / stage_bytes;
+    const int x_rows = qkv_linear_x_rows(n_tok), stage_bytes = kb * (x_rows * 128 + kWBytes);
+    int n_stages = ring_stages(x_rows, kb);
+    if (n_stages < 1) return cudaErrorInvalidValue;
     n_stages = n_stages > kMaxStages ? kMaxStages : n_stages;
-    const int smem_bytes = 2048 + n_stages * stage_bytes + kXBytes;
+    const int smem_bytes = 2048 + n_stages * stage_bytes + read_over_slack(x_rows, kb);
     static_assert(offsetof(QkvSmem, ring) == 1024, "header, then the ring");
     if (configured.needed(cx.device)) {
         cudaError_t e = require_current_device(cx.device);
-        if (e == cudaSuccess) e = cudaFuncSetAttribute(qkv_linear_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(qkv_linear_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemPerCta);
         if (e != cudaSuccess) return e;
         configured.mark(cx.device);
     }
@@ -248,7 +282,7 @@ cudaError_t launch_qkv_linear(const LaunchCtx &cx, const CUtensorMap &x_map, con
     cfg.stream = cx.stream;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, qkv_linear_kernel, x_map, w_map, tab, cx.shape, K, x_rows, n_stages, bias, q_out, cx.k_base, cx.v_base,
+    cudaError_t e = cudaLaunchKernelEx(&cfg, qkv_linear_kernel, x_map, w_map, tab, cx.shape, K, x_rows, kb, n_stages, bias, q_out, cx.k_base, cx.v_base,
                                        cx.rope_tab, cx.rope_tab_len, cx.hdr);
     g_launch_count += 1;
     return e != cudaSuccess ? e : cudaGetLastError();
