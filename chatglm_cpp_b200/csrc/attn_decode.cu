@@ -1231,9 +1231,20 @@ cudaError_t launch_decode(const LaunchCtx &cx, const DecodeTable &tab, bool n_pa
     // on B200 for 4 k to 19 k tiles per launch: fewer, longer spans mean fewer partials and merges, and an SM that
     // hosts a single CTA gives it the whole SM; two full CTAs on every SM came out 1.5-2 % slower than 1.5-1.75,
     // one per SM only wins below about 5 k tiles.
+    // A launch with fewer tiles than SMs (batch-1 decode of a short context) is all latency, and what costs is the number
+    // of parts an item is delivered in: measured on one 512-token sequence (2 items of 9 tiles), 18 CTAs of one tile
+    // 11.0 us per launch, 9 CTAs of two tiles (spans that straddle the items) 17.2 us, 6 CTAs of three tiles 9.6 us, 2
+    // CTAs of nine tiles 11.4 us.  Such a launch is cut into at most four parts per item (one batch of the merge) of
+    // about three tiles each; with items of equal length the spans then end where the items do.
     const long long lo_ctas = cx.n_sm, hi_ctas = 7LL * cx.n_sm / 4;
     long long want = total_tiles / 36;
     want = want < lo_ctas ? lo_ctas : (want > hi_ctas ? hi_ctas : want);
+    if (total_tiles < lo_ctas) {
+        const long long n_items = static_cast<long long>(tab.n_seq) * cx.shape.G;
+        long long parts = (total_tiles / n_items + 2) / 3;
+        parts = parts < 1 ? 1 : (parts > 4 ? 4 : parts);
+        want = n_items * parts;
+    }
     const int grid = static_cast<int>(total_tiles < want ? total_tiles : want);
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(grid);
