@@ -616,7 +616,9 @@ int cglm_attn_forward(cglm_kv_arena *a, const cglm_attn_seq *seqs, int n_seq, vo
     long long gen_tokens = 0, decode_tiles = 0;
     int n_fast = 0, n_prefill = 0;
     size_t prefill_bytes = 0;
-    std::vector<unsigned char> is_fast(n_seq);   // 0: generic path, 1: fused decode, 2: tcgen05 prefill
+    // 0: generic path, 1: fused decode, 2: tcgen05 prefill (per thread and reused: no allocation per call once it has grown)
+    static thread_local std::vector<unsigned char> is_fast;
+    is_fast.assign(static_cast<size_t>(n_seq), 0);
     const bool prefill_ok = a->has_tmaps && d.head_dim == 128 && d.max_len % 8 == 0 &&
                             (d.rope_type == CGLM_ROPE_CHATGLM2 || d.rope_type == CGLM_ROPE_CHATGLM ||
                              d.rope_type == CGLM_ROPE_DISABLED);
@@ -769,7 +771,8 @@ int cglm_attn_forward_host(cglm_kv_arena *a, const cglm_attn_seq *seqs, int n_se
         if (seqs[i].qlen <= 0) return CGLM_ERR_INVALID_ARG;
     }
     long long n_tok = 0;
-    std::vector<cglm_attn_seq> dev_seqs(seqs, seqs + n_seq);
+    static thread_local std::vector<cglm_attn_seq> dev_seqs;   // reused: no allocation per call once it has grown
+    dev_seqs.assign(seqs, seqs + n_seq);
     // descriptors over a packed [tokens][row] activation at in_base and a packed [tokens][orow] output at out_base
     auto point_at = [&](const void *in_base, void *out_base) {
         n_tok = 0;
