@@ -61,6 +61,27 @@ def test_decode_tile_edges(n_past):
     run_decode_batch(make_desc(32, 2, 128, 2048), [n_past], seed=n_past)
 
 
+@pytest.mark.parametrize("seed", range(12))
+def test_decode_random_shapes_grid(seed):
+    """A seeded grid over what the decode path's geometry depends on: kv heads, q heads per kv head (1 ... 16 on the fused
+    kernel, 32 on the generic one), virtual tokens, capacity (also not a multiple of 8), batch size and lengths from an
+    empty cache to a full one, rope mode and qkv layout.  Small launches (fewer tiles than SMs) and large ones."""
+    rng = np.random.default_rng(7000 + seed)
+    G = int(rng.choice([1, 2, 4, 8]))
+    R = int(rng.choice([1, 2, 4, 8, 16, 32] if G <= 2 else [1, 2, 4]))
+    V = int(rng.choice([0, 0, 3, 8]))
+    v1 = R == 1                                         # the v1 family: MHA, interleaved qkv, 2-D rope, its own mask
+    M = int(rng.choice([256, 517, 1024, 2048 + V])) if not v1 else 512
+    n_seq = int(rng.choice([1, 2, 5, 17]))
+    cap = M - V - 1
+    n_past = [int(x) for x in rng.integers(0, cap + 1, n_seq)]
+    n_past[0] = cap if seed % 2 else 0                 # a full cache, or an empty one
+    desc = make_desc(G * R, G, 128, M, V=V, rope=O.ROPE_CHATGLM if v1 else O.ROPE_CHATGLM2,
+                     mask=O.MASK_CHATGLM if v1 else O.MASK_CAUSAL, theta=10000.0 if seed % 2 else 5.0e6)
+    n_ctx = [max(2, p // 2 + 1) for p in n_past] if v1 else None
+    run_decode_batch(desc, n_past, seed=seed, interleaved=v1, n_ctx_list=n_ctx, f16_io=seed % 4 == 3)
+
+
 def test_decode_batch_mixed_lengths_spans_and_merges():
     """64 sequences of uniformly random length: spans cross item boundaries, items are merged from partials."""
     rng = np.random.default_rng(1003)
