@@ -29,6 +29,8 @@
 // the kernel and its first tile.
 // Both caches are already contraction-contiguous for the B operand: K is [token][d] for QK^T and V^T is
 // [d][token] for PV.
+#include <cstdlib>
+
 #include "common.cuh"
 
 namespace cglm {
@@ -1227,23 +1229,28 @@ cudaError_t launch_decode(const LaunchCtx &cx, const DecodeTable &tab, bool n_pa
         if (e != cudaSuccess) return e;
         configured.mark(cx.device);
     }
-    // Grid: about 36 tiles (1.1 MiB of cache) per CTA, at least one CTA per SM and at most 1.75 per SM.  Measured
-    // on B200 for 4 k to 19 k tiles per launch: fewer, longer spans mean fewer partials and merges, and an SM that
-    // hosts a single CTA gives it the whole SM; two full CTAs on every SM came out 1.5-2 % slower than 1.5-1.75,
-    // one per SM only wins below about 5 k tiles.
+    // Grid: about 18 tiles (0.6 MiB of cache) per CTA, at least one CTA per SM and at most 1.75 per SM.  Measured on
+    // B200: 64 sequences (9.3 k tiles) 61.8 us per launch with 259 CTAs, 63.3 with 228, 68.3 with 148, 62.7 with 296;
+    // 32 sequences (4.7 k tiles) 39.9 us with 259 against 42.2 with 148; the MHA shape 34.9 us with 200 against 37.9
+    // with 148; 16 and 8 sequences and the one long sequence do not care between 96 and 228.
     // A launch with fewer tiles than SMs (batch-1 decode of a short context) is all latency, and what costs is the number
     // of parts an item is delivered in: measured on one 512-token sequence (2 items of 9 tiles), 18 CTAs of one tile
     // 11.0 us per launch, 9 CTAs of two tiles (spans that straddle the items) 17.2 us, 6 CTAs of three tiles 9.6 us, 2
     // CTAs of nine tiles 11.4 us.  Such a launch is cut into at most four parts per item (one batch of the merge) of
     // about three tiles each; with items of equal length the spans then end where the items do.
     const long long lo_ctas = cx.n_sm, hi_ctas = 7LL * cx.n_sm / 4;
-    long long want = total_tiles / 36;
+    long long want = total_tiles / 18;
     want = want < lo_ctas ? lo_ctas : (want > hi_ctas ? hi_ctas : want);
+    if (static_cast<long long>(tab.n_seq) * cx.shape.G * 16 < lo_ctas) want = lo_ctas;   // a few very long items: every extra CTA is one more part per item
     if (total_tiles < lo_ctas) {
         const long long n_items = static_cast<long long>(tab.n_seq) * cx.shape.G;
         long long parts = (total_tiles / n_items + 2) / 3;
         parts = parts < 1 ? 1 : (parts > 4 ? 4 : parts);
         want = n_items * parts;
+    }
+    {   // CGLM_DECODE_GRID forces the number of CTAs (tuning knob, read once; clamped to what the scratch is sized for)
+        static const int forced = [] { const char *e = std::getenv("CGLM_DECODE_GRID"); return e ? std::atoi(e) : 0; }();
+        if (forced > 0) want = forced < 2 * cx.n_sm ? forced : 2 * cx.n_sm;
     }
     const int grid = static_cast<int>(total_tiles < want ? total_tiles : want);
     cudaLaunchConfig_t cfg = {};
