@@ -972,6 +972,25 @@ decode_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__
                 if (sidx == 0 && !dry && !kDynPast) {
                     asm volatile("griddepcontrol.wait;" ::: "memory");
                 }
+                if (sidx == 0 && !dry && (tab.gate[0] || tab.gate[1])) {
+                    // host-buffer call: the activations are in place / the output buffer is free once the copy engines have
+                    // written these words (see DecodeTable::gate)
+                    if (lane == 0) {
+                        for (int gi = 0; gi < 2; ++gi) {
+                            const unsigned int *gp = tab.gate[gi];
+                            if (!gp) continue;
+                            bool seen = false;
+                            for (unsigned int spin = 0; spin < kSpinLimit && !sm.abort_flag; ++spin) {
+                                unsigned int v;
+                                asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(gp) : "memory");
+                                if (v == tab.gate_value[gi]) { seen = true; break; }
+                                __nanosleep(200);
+                            }
+                            if (!seen) sm.abort_flag = 1;
+                        }
+                    }
+                    __syncwarp();
+                }
                 if (kXchg && !dry) {
                     // this step's number, and where this rank's rows go inside the local exchange buffer
                     if (sidx == 0) {

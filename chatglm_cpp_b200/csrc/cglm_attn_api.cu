@@ -47,8 +47,14 @@ struct cglm_kv_arena {
         const void *dev_in;
         const void *dev_out;
         cudaEvent_t h2d, kernel, d2h;
+        unsigned int seq;   // this call's number: what its two gate words hold once its copies have completed
         bool used;
     };
+    // gate words of the host-buffer calls: device words [2 * record + {0: input staged, 1: output copied back}] and
+    // the pinned host words they are copied from (the copy streams write them right behind the data)
+    unsigned int *gate_dev;
+    unsigned int *gate_host;
+    unsigned int host_seq;
     cudaStream_t copy_in, copy_out;
     HostCall host_calls[kHostCalls];
     int host_next;
@@ -533,6 +539,8 @@ int cglm_kv_arena_destroy(cglm_kv_arena *a) {
         }
         cudaStreamDestroy(a->copy_in);
         cudaStreamDestroy(a->copy_out);
+        cudaFree(a->gate_dev);
+        cudaFreeHost(a->gate_host);
     }
     if (a->direct_ready) cudaEventDestroy(a->direct_done);
     for (int i = 0; i < a->ring_slots; ++i) cudaEventDestroy(a->ring_events[i]);
@@ -604,8 +612,27 @@ int cglm_attn_workspace_status(void *workspace, void *cuda_stream) {
     return h.status;
 }
 
+namespace {
+// What a host-buffer call waits for before its kernels may read the staged activations / write the staged outputs:
+// device words written by the copy streams for the fused decode kernel (polled inside the kernel, see
+// DecodeTable::gate), and the matching events for every other kernel (waited for on the stream).
+struct HostGates {
+    const unsigned int *word[2];
+    unsigned int value[2];
+    cudaEvent_t event[2];   // null: nothing to wait for
+};
+int forward_impl(cglm_kv_arena *a, const cglm_attn_seq *seqs, int n_seq, void *workspace, size_t workspace_bytes,
+                 void *cuda_stream, const HostGates *gates);
+}  // namespace
+
 int cglm_attn_forward(cglm_kv_arena *a, const cglm_attn_seq *seqs, int n_seq, void *workspace,
                       size_t workspace_bytes, void *cuda_stream) {
+    return forward_impl(a, seqs, n_seq, workspace, workspace_bytes, cuda_stream, nullptr);
+}
+
+namespace {
+int forward_impl(cglm_kv_arena *a, const cglm_attn_seq *seqs, int n_seq, void *workspace, size_t workspace_bytes,
+                 void *cuda_stream, const HostGates *gates) {
     if (!a || !seqs || n_seq <= 0) return CGLM_ERR_INVALID_ARG;
     if (!workspace) return CGLM_ERR_WORKSPACE;
     const cglm_attn_desc &d = a->desc;
@@ -687,6 +714,13 @@ int cglm_attn_forward(cglm_kv_arena *a, const cglm_attn_seq *seqs, int n_seq, vo
     };
     uint8_t *ws = static_cast<uint8_t *>(workspace);
     LaunchCtx cx = make_launch_ctx(a, ws, lay, st);
+    // a host-buffer call served by anything but fused decode launches alone waits on the stream
+    const bool gate_in_kernel = gates && n_fast == n_seq;
+    if (gates && !gate_in_kernel) {
+        for (int gi = 0; gi < 2; ++gi) {
+            if (gates->event[gi]) CGLM_CUDA(cudaStreamWaitEvent(st, gates->event[gi], 0));
+        }
+    }
 
     // fused decode: descriptors and tile prefix travel as kernel parameters, kDecodeMaxSeqPerLaunch per launch
     if (n_fast > 0) {
@@ -709,6 +743,10 @@ int cglm_attn_forward(cglm_kv_arena *a, const cglm_attn_seq *seqs, int n_seq, vo
                 tab.settled = settled && !dyn ? 1 + decode_l2_ahead() : 0;
                 tab.trigger = decode_trigger();
                 tab.charge = decode_charge();
+                for (int gi = 0; gi < 2; ++gi) {
+                    tab.gate[gi] = gate_in_kernel && gates->event[gi] ? gates->word[gi] : nullptr;
+                    tab.gate_value[gi] = gate_in_kernel ? gates->value[gi] : 0;
+                }
                 CGLM_CUDA(launch_decode(cx, tab, dyn));
                 filled = 0;
                 dyn = false;
@@ -754,6 +792,7 @@ int cglm_attn_forward(cglm_kv_arena *a, const cglm_attn_seq *seqs, int n_seq, vo
     (void)decode_tiles;
     return CGLM_OK;
 }
+}  // namespace
 
 int cglm_attn_forward_host(cglm_kv_arena *a, const cglm_attn_seq *seqs, int n_seq, int layout,
                            const void *qkv_host, void *out_host, void *dev_qkv, void *dev_out, void *workspace,
@@ -852,6 +891,12 @@ int cglm_attn_forward_host(cglm_kv_arena *a, const cglm_attn_seq *seqs, int n_se
             c.used = false;
             c.dev_in = c.dev_out = nullptr;
         }
+        CGLM_CUDA(cudaMalloc(reinterpret_cast<void **>(&a->gate_dev), 2 * cglm_kv_arena::kHostCalls * sizeof(unsigned int)));
+        CGLM_CUDA(cudaMemset(a->gate_dev, 0, 2 * cglm_kv_arena::kHostCalls * sizeof(unsigned int)));
+        CGLM_CUDA(cudaHostAlloc(reinterpret_cast<void **>(&a->gate_host), 2 * cglm_kv_arena::kHostCalls * sizeof(unsigned int),
+                                cudaHostAllocDefault));
+        CGLM_CUDA(cudaDeviceSynchronize());
+        a->host_seq = 0;
         a->host_ready = true;
     }
     cglm_kv_arena::HostCall &me = a->host_calls[a->host_next];
@@ -866,18 +911,33 @@ int cglm_attn_forward_host(cglm_kv_arena *a, const cglm_attn_seq *seqs, int n_se
         if (!last_in && c.dev_in == dev_qkv) last_in = &c;
         if (!last_out && c.dev_out == dev_out) last_out = &c;
     }
+    const int rec = a->host_next;
     a->host_next = (a->host_next + 1) % cglm_kv_arena::kHostCalls;
+    me.seq = ++a->host_seq;
+    if (me.seq == 0) me.seq = ++a->host_seq;   // 0 is what a fresh gate word holds
     lock.unlock();
+    // A stream wait between two launches would end their programmatic overlap (the stream takes up the wait only once
+    // the earlier launch has completed): decode launches instead poll two device words that the copy streams write
+    // right behind the data, and the stream carries only event records.  Other kernels wait on the stream as before.
+    a->gate_host[2 * rec] = a->gate_host[2 * rec + 1] = me.seq;
     if (last_in) CGLM_CUDA(cudaStreamWaitEvent(a->copy_in, last_in->kernel, 0));
     CGLM_CUDA(cudaMemcpyAsync(dev_qkv, qkv_host, esz * n_tok * row, cudaMemcpyHostToDevice, a->copy_in));
+    CGLM_CUDA(cudaMemcpyAsync(a->gate_dev + 2 * rec, a->gate_host + 2 * rec, sizeof(unsigned int), cudaMemcpyHostToDevice, a->copy_in));
     CGLM_CUDA(cudaEventRecord(me.h2d, a->copy_in));
-    CGLM_CUDA(cudaStreamWaitEvent(st, me.h2d, 0));
-    if (last_out) CGLM_CUDA(cudaStreamWaitEvent(st, last_out->d2h, 0));
-    const int rc = cglm_attn_forward(a, dev_seqs.data(), n_seq, workspace, workspace_bytes, cuda_stream);
+    HostGates gates;
+    gates.word[0] = a->gate_dev + 2 * rec;
+    gates.value[0] = me.seq;
+    gates.event[0] = me.h2d;
+    const int last_out_rec = last_out ? static_cast<int>(last_out - a->host_calls) : 0;
+    gates.word[1] = last_out ? a->gate_dev + 2 * last_out_rec + 1 : nullptr;
+    gates.value[1] = last_out ? last_out->seq : 0;
+    gates.event[1] = last_out ? last_out->d2h : nullptr;
+    const int rc = forward_impl(a, dev_seqs.data(), n_seq, workspace, workspace_bytes, cuda_stream, &gates);
     if (rc != CGLM_OK) return rc;
     CGLM_CUDA(cudaEventRecord(me.kernel, st));
     CGLM_CUDA(cudaStreamWaitEvent(a->copy_out, me.kernel, 0));
     CGLM_CUDA(cudaMemcpyAsync(out_host, dev_out, esz * n_tok * orow, cudaMemcpyDeviceToHost, a->copy_out));
+    CGLM_CUDA(cudaMemcpyAsync(a->gate_dev + 2 * rec + 1, a->gate_host + 2 * rec + 1, sizeof(unsigned int), cudaMemcpyHostToDevice, a->copy_out));
     CGLM_CUDA(cudaEventRecord(me.d2h, a->copy_out));
     me.dev_in = dev_qkv;
     me.dev_out = dev_out;
@@ -1023,6 +1083,7 @@ int cglm_attn_splitkv_step(cglm_kv_arena *a, const cglm_attn_seq *seq, void *con
     tab.settled = (s.flags & CGLM_SEQ_CACHE_SETTLED) ? 1 + decode_l2_ahead() : 0;
     tab.trigger = decode_trigger();
     tab.charge = decode_charge();
+    tab.gate[0] = tab.gate[1] = nullptr;
     tab.prefix[0] = 0;
     tab.prefix[1] = (kv_before + appended + kDecodeTile - 1) / kDecodeTile;
     CGLM_CUDA(launch_decode(cx, tab, false, &xd));
