@@ -657,6 +657,16 @@ def qkv_linear_measure(dd, name, w, args, syn, steps=None):
 
 
 # ---- one long sequence (config 4) ----------------------------------------------------------------------------------------
+def split_kv_rotation(n_past, world, n_kv_head, head_dim):
+    """Copies of a rank's KV slice the split-KV workload rotates through, so that the working set is at least four times
+    the L2.  The same on every rank: it is taken from the slice CAPACITY (the ranks' slices differ by a few tokens; a
+    count taken from the local slice came out 15 on three ranks and 16 on the fourth, and the ranks then captured graphs
+    of different lengths and ran different numbers of steps)."""
+    from chatglm_cpp_b200 import sharding
+    cap = sharding.slice_capacity(n_past, 0, world)
+    return max(2, int(np.ceil(4 * 126e6 / (4 * n_kv_head * head_dim * cap))))
+
+
 def split_kv_measure(dd, name, w, args, syn, steps=None):
     """Strong scaling of ONE long sequence.  1 GPU: one fused decode launch per step.  N GPUs: rank r holds a contiguous
     slice of the KV length in its own arena; `p2p`: one fused launch per rank and step (attention over the slice, peer
@@ -675,9 +685,7 @@ def split_kv_measure(dd, name, w, args, syn, steps=None):
     cap = sharding.slice_capacity(P, 0, world) + 64
     desc = _lib.AttnDesc(H, G, D, cap, 0, w["rope"], w["theta"], w["mask"])
     local_bytes = 4 * G * D * (sl.n_local + (1 if sl.owns_new else 0))
-    # the same number of copies on every rank (the ranks' slices differ by a few tokens; a rotation count taken from the
-    # local slice came out 15 on three ranks and 16 on the fourth, and the ranks then ran different numbers of steps)
-    n_rot = max(2, int(np.ceil(4 * 126e6 / (4 * G * D * (cap - 64)))))
+    n_rot = split_kv_rotation(P, world, G, D)
     arena = A.KVArena(desc, n_rot)
     syn.fill(arena.k_all(), w["seed"] + rank, TID_K)
     syn.fill(arena.v_all(), w["seed"] + rank, TID_V)
