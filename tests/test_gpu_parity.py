@@ -548,6 +548,55 @@ def test_forward_host_pipeline_reuses_staging_buffers():
     assert torch.equal(arena.k_all()[:half], arena.k_all()[half:])
 
 
+def test_forward_host_gates_with_one_staging_pair_two_launches_per_call_and_a_prompt_in_between():
+    """Host-buffer calls of 130 sequences (two fused launches per call, both behind the same gate words) through ONE
+    staging pair, so that every call has to find its input staged and the previous call's output copied back; the third
+    call carries a prompt, which is served by kernels that wait on the stream instead.  Outputs and caches must equal the
+    plain device calls'."""
+    from chatglm_cpp_b200 import _lib
+    A = _A()
+    L = _lib.lib()
+    desc = make_desc(32, 2, 128, 256)
+    rng = np.random.default_rng(43)
+    n_calls, n = 6, 130
+    n_past = [int(x) for x in rng.integers(0, 255, n)]
+    arena, ws = A.KVArena(desc, 2 * n), A.Workspace(desc, n, 64)
+    arena.k_all().normal_(); arena.v_all().normal_()
+    arena.k_all()[n:].copy_(arena.k_all()[:n]); arena.v_all()[n:].copy_(arena.v_all()[:n])
+    width = qkv_width(desc, False)
+    stream = torch.cuda.current_stream().cuda_stream
+    stage_in, stage_out = torch.empty(n + 64, width, device="cuda"), torch.empty(n + 64, 4096, device="cuda")
+    outs_host, outs_ref = [], []
+    for c in range(n_calls):
+        prompt = c == 2
+        qlens = [40 if (prompt and i == 0) else 1 for i in range(n)]
+        past = [0 if (prompt and i == 0) else n_past[i] for i in range(n)]
+        tok = sum(qlens)
+        qkv = torch.from_numpy(rng.standard_normal((tok, width)).astype(np.float32))
+        qkv_pinned, out_pinned = qkv.pin_memory(), torch.zeros(tok, 4096).pin_memory()
+        qkv_dev, out_ref = qkv.cuda(), torch.zeros(tok, 4096, device="cuda")
+        calls, t0 = [], 0
+        for i in range(n):
+            calls.append(A.SeqCall(qkv=qkv_dev[t0:t0 + qlens[i]], slot=i, n_past=past[i], out=out_ref[t0:t0 + qlens[i]]))
+            t0 += qlens[i]
+        A.forward_batch(arena, ws, calls)
+        arr = (_lib.AttnSeq * n)()
+        for i in range(n):
+            arr[i].slot, arr[i].qlen, arr[i].n_past = n + i, qlens[i], past[i]
+        _lib.check(L.cglm_attn_forward_host(arena._h, arr, n, 0, qkv_pinned.data_ptr(), out_pinned.data_ptr(), stage_in.data_ptr(),
+                                            stage_out.data_ptr(), ws.ptr, ws.bytes, stream), "forward_host")
+        outs_host.append((qkv_pinned, out_pinned)); outs_ref.append(out_ref)
+        if prompt:
+            n_past[0] = 40
+    _lib.check(L.cglm_attn_host_drain(arena._h, stream), "host_drain")
+    torch.cuda.current_stream().synchronize()
+    assert ws.status() == 0
+    for (_, got), want in zip(outs_host, outs_ref):
+        assert torch.equal(got, want.cpu())
+    assert torch.equal(arena.k_all()[:n], arena.k_all()[n:]) and torch.equal(arena.v_all()[:n], arena.v_all()[n:])
+    arena.close()
+
+
 def test_decode_with_4_byte_aligned_activation_takes_the_generic_path_and_agrees():
     """The fused decode kernel reads q/k/v rows 16 bytes at a time; an activation that is only 4-byte aligned must be
     routed to the generic CUDA path (same launch count as any generic call) and give the same output and cache."""
