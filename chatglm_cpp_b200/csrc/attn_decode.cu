@@ -31,6 +31,8 @@
 // [d][token] for PV.
 #include <cstdlib>
 
+#include <type_traits>
+
 #include "common.cuh"
 
 namespace cglm {
@@ -792,7 +794,8 @@ __device__ __forceinline__ void tma_prefetch_l2_2d(const CUtensorMap *map, int c
 template <bool kDynPast, bool kXchg>
 __global__ void __launch_bounds__(kThreads, 2)
 decode_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map,
-              const __grid_constant__ DecodeTable tab, AttnShape sh, uint16_t *__restrict__ k_base,
+              const __grid_constant__ typename std::conditional<kDynPast, DecodeTableDyn, DecodeTable>::type tab, AttnShape sh,
+              uint16_t *__restrict__ k_base,
               uint16_t *__restrict__ v_base, WsHeader *hdr, int *counters, int *gcounters, float *partials,
               float *gpartials, const float2 *__restrict__ rope_tab, int rope_tab_len,
               const __grid_constant__ XchgDev xchg) {
@@ -831,13 +834,15 @@ decode_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__
     // stream; tab.settled - 1 further tiles per CTA are pulled into L2 behind the ring.
     const bool settled = !kDynPast && tab.settled != 0;
     const int trigger = tab.trigger;
-    if (kDynPast) {
+    if constexpr (kDynPast) {
         asm volatile("griddepcontrol.wait;" ::: "memory");
         if (trigger == 0) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+        static_assert(kDecodeMaxSeqPerLaunch <= 4 * 32, "the tile prefix is scanned by one warp, four sequences per lane");
         for (int i = tid; i < n_seq; i += kThreads) {
-            int np = tab.seqs[i].n_past;
-            if (tab.seqs[i].flags & CGLM_SEQ_N_PAST_DEVICE) {
-                np = *reinterpret_cast<const volatile int *>(tab.seqs[i].n_past_dev);
+            int np = tab.n_past_of[i];
+            const int fl = tab.flags_of[i];
+            if (fl & CGLM_SEQ_N_PAST_DEVICE) {
+                np = *reinterpret_cast<const volatile int *>(tab.n_past_dev_of[i]);
                 const int np_max = sh.M - sh.V - 1;   // the appended token must fit the cache
                 if (np < 0 || np > np_max) {
                     np = np < 0 ? 0 : np_max;
@@ -845,14 +850,32 @@ decode_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__
                 }
             }
             sm.npast[i] = np;
-            sm.slot[i] = tab.seqs[i].slot;
-            const int L = sh.V + np + ((tab.seqs[i].flags & CGLM_SEQ_NO_APPEND) ? 0 : 1);
+            sm.slot[i] = tab.slot_of[i];
+            const int L = sh.V + np + ((fl & CGLM_SEQ_NO_APPEND) ? 0 : 1);
             sm.prefix[i + 1] = (L + kTile - 1) / kTile;
         }
         __syncthreads();
-        if (tid == 0) {
-            sm.prefix[0] = 0;
-            for (int i = 0; i < n_seq; ++i) sm.prefix[i + 1] += sm.prefix[i];
+        if (warp == 0) {   // inclusive scan of the tile counts: four per lane, then across the lanes
+            int v[4], run = 0;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int e = 4 * lane + j;
+                run += e < n_seq ? sm.prefix[e + 1] : 0;
+                v[j] = run;
+            }
+            int before = run;
+#pragma unroll
+            for (int d = 1; d < 32; d <<= 1) {
+                const int o = __shfl_up_sync(0xffffffffu, before, d);
+                if (lane >= d) before += o;
+            }
+            before -= run;   // exclusive
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int e = 4 * lane + j;
+                if (e < n_seq) sm.prefix[e + 1] = before + v[j];
+            }
+            if (lane == 0) sm.prefix[0] = 0;
         }
     } else {
         for (int i = tid; i <= n_seq; i += kThreads) {
@@ -1232,7 +1255,7 @@ decode_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__
 
 int decode_max_ctas(int n_sm) { return 2 * n_sm; }   // bound used to size scratch; launch_decode picks the grid
 
-cudaError_t launch_decode(const LaunchCtx &cx, const DecodeTable &tab, bool n_past_on_device, const XchgDev *xchg) {
+cudaError_t launch_decode(const LaunchCtx &cx, const DecodeTableDyn &tab, bool n_past_on_device, const XchgDev *xchg) {
     // with device-side positions tab.prefix holds the tile counts of the host's upper bounds: good for sizing only
     const long long total_tiles = static_cast<long long>(tab.prefix[tab.n_seq]) * cx.shape.G;
     if (tab.n_seq == 0 || total_tiles == 0) {
@@ -1285,9 +1308,15 @@ cudaError_t launch_decode(const LaunchCtx &cx, const DecodeTable &tab, bool n_pa
     if (xchg && (n_past_on_device || tab.n_seq != 1)) return cudaErrorInvalidValue;
     static const XchgDev no_xchg = {};
     const XchgDev &xd = xchg ? *xchg : no_xchg;
-    auto kernel = xchg ? decode_kernel<false, true> : (n_past_on_device ? decode_kernel<true, false> : decode_kernel<false, false>);
-    cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, *cx.k_map, *cx.v_map, tab, cx.shape, cx.k_base, cx.v_base, cx.hdr, cx.counters,
-                                       cx.gcounters, cx.partials, cx.gpartials, cx.rope_tab, cx.rope_tab_len, xd);
+    cudaError_t e;
+    if (n_past_on_device) {   // the only instantiation that takes the larger table
+        e = cudaLaunchKernelEx(&cfg, decode_kernel<true, false>, *cx.k_map, *cx.v_map, tab, cx.shape, cx.k_base, cx.v_base, cx.hdr,
+                               cx.counters, cx.gcounters, cx.partials, cx.gpartials, cx.rope_tab, cx.rope_tab_len, xd);
+    } else {
+        auto kernel = xchg ? decode_kernel<false, true> : decode_kernel<false, false>;
+        e = cudaLaunchKernelEx(&cfg, kernel, *cx.k_map, *cx.v_map, static_cast<const DecodeTable &>(tab), cx.shape, cx.k_base,
+                               cx.v_base, cx.hdr, cx.counters, cx.gcounters, cx.partials, cx.gpartials, cx.rope_tab, cx.rope_tab_len, xd);
+    }
     g_launch_count += 1;
     return e != cudaSuccess ? e : cudaGetLastError();
 }

@@ -724,7 +724,7 @@ int forward_impl(cglm_kv_arena *a, const cglm_attn_seq *seqs, int n_seq, void *w
 
     // fused decode: descriptors and tile prefix travel as kernel parameters, kDecodeMaxSeqPerLaunch per launch
     if (n_fast > 0) {
-        static thread_local DecodeTable tab;
+        static thread_local DecodeTableDyn tab;
         int filled = 0;
         bool dyn = false, settled = true;
         tab.prefix[0] = 0;
@@ -747,6 +747,7 @@ int forward_impl(cglm_kv_arena *a, const cglm_attn_seq *seqs, int n_seq, void *w
                     tab.gate[gi] = gate_in_kernel && gates->event[gi] ? gates->word[gi] : nullptr;
                     tab.gate_value[gi] = gate_in_kernel ? gates->value[gi] : 0;
                 }
+                if (dyn) decode_table_finish(tab);
                 CGLM_CUDA(launch_decode(cx, tab, dyn));
                 filled = 0;
                 dyn = false;
@@ -1067,7 +1068,7 @@ int cglm_attn_splitkv_step(cglm_kv_arena *a, const cglm_attn_seq *seq, void *con
     xd.combine = combine != 0;
     xd.timeout_us = timeout_us ? timeout_us : 20000u;
     LaunchCtx cx = make_launch_ctx(a, static_cast<uint8_t *>(workspace), lay, static_cast<cudaStream_t>(cuda_stream));
-    static thread_local DecodeTable tab;
+    static thread_local DecodeTableDyn tab;
     SeqDev &o = tab.seqs[0];
     o = SeqDev{};
     o.q = s.q; o.k = s.k; o.v = s.v;

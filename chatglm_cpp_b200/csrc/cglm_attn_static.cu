@@ -94,7 +94,7 @@ extern "C" int cglm_attn_decode_static(cglm_kv_arena *arena, const cglm_attn_seq
     cudaStream_t st = static_cast<cudaStream_t>(cuda_stream);
 
     const int n_slots = cglm_kv_arena_n_slots(arena);
-    static thread_local DecodeTable tab;
+    static thread_local DecodeTableDyn tab;
     tab.n_seq = n_seq;
     tab.settled = 0;
     tab.trigger = 2;

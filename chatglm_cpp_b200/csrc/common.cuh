@@ -317,9 +317,28 @@ struct DecodeTable {
     int prefix[kDecodeMaxSeqPerLaunch + 2];   // prefix[i] = 64-token tiles of sequences [0, i), per kv head
     SeqDev seqs[kDecodeMaxSeqPerLaunch];
 };
+// The table of a launch with device-side positions: what every CTA reads of EVERY sequence after the dependency wait,
+// once more as arrays (decode_table_finish fills them): thread i reading seqs[i].flags touches one 128-byte descriptor
+// per lane, and parameter space serves a warp one address at a time.  Only that instantiation takes the larger table
+// (2.5 KiB more kernel parameters cost the other launches 0.4 us each, measured).
+struct DecodeTableDyn : DecodeTable {
+    int slot_of[kDecodeMaxSeqPerLaunch];
+    int flags_of[kDecodeMaxSeqPerLaunch];
+    int n_past_of[kDecodeMaxSeqPerLaunch];
+    const int *n_past_dev_of[kDecodeMaxSeqPerLaunch];
+};
+inline void decode_table_finish(DecodeTableDyn &t) {
+    for (int i = 0; i < t.n_seq; ++i) {
+        t.slot_of[i] = t.seqs[i].slot;
+        t.flags_of[i] = t.seqs[i].flags;
+        t.n_past_of[i] = t.seqs[i].n_past;
+        t.n_past_dev_of[i] = (t.seqs[i].flags & CGLM_SEQ_N_PAST_DEVICE) ? t.seqs[i].n_past_dev : nullptr;
+    }
+}
 // xchg != null: the single sequence of tab is one rank's slice of a split-KV step (CGLM_SEQ_PARTIAL semantics); the
 // kernel publishes its (acc, m, l) rows into every rank's exchange buffer and, on ranks that combine, merges them.
-cudaError_t launch_decode(const LaunchCtx &cx, const DecodeTable &tab, bool n_past_on_device = false,
+// n_past_on_device: tab must have been through decode_table_finish
+cudaError_t launch_decode(const LaunchCtx &cx, const DecodeTableDyn &tab, bool n_past_on_device = false,
                           const XchgDev *xchg = nullptr);
 // The decode kernel reads q/k/v head rows four elements at a time (sixteen bytes of f32, eight of f16) and writes the
 // optional roped copies sixteen bytes at a time.
