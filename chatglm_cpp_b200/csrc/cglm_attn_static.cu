@@ -113,7 +113,8 @@ extern "C" int cglm_attn_decode_static(cglm_kv_arena *arena, const cglm_attn_seq
             set_last_error("q, k, v rows must be 16-byte aligned (pointers and head strides)");
             return CGLM_ERR_UNSUPPORTED;
         }
-        if (static_cast<long long>(shape.V) + s.n_past + 1 > shape.M) return CGLM_ERR_INVALID_ARG;
+        // against the capacity the caller asked for (shape.M is the row pitch, which an arena may have rounded up)
+        if (static_cast<long long>(shape.V) + s.n_past + 1 > cglm_kv_arena_desc(arena)->max_len) return CGLM_ERR_INVALID_ARG;
         if (shape.rope_type == CGLM_ROPE_CHATGLM && !s.position_ids && s.n_ctx < 2) return CGLM_ERR_INVALID_ARG;
         SeqDev &o = tab.seqs[i];
         o.q = s.q; o.k = s.k; o.v = s.v;
