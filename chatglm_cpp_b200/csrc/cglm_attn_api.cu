@@ -122,8 +122,8 @@ int decode_l2_ahead() {
 int decode_charge() {
     static const int v = [] {
         const char *e = std::getenv("CGLM_DECODE_CHARGE");
-        const int x = e ? std::atoi(e) : 3;
-        return x < 0 ? 0 : (x > 8 ? 8 : x);
+        const int x = e ? std::atoi(e) : 6;
+        return x < 0 ? 0 : (x > 12 ? 12 : x);
     }();
     return v;
 }

@@ -98,7 +98,7 @@ extern "C" int cglm_attn_decode_static(cglm_kv_arena *arena, const cglm_attn_seq
     tab.n_seq = n_seq;
     tab.settled = 0;
     tab.trigger = 2;
-    tab.charge = 3;
+    tab.charge = 6;
     tab.gate[0] = tab.gate[1] = nullptr;
     tab.prefix[0] = 0;
     for (int i = 0; i < n_seq; ++i) {
