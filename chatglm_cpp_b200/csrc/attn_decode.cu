@@ -66,6 +66,8 @@ struct alignas(16) QBuf {
     float *partial;
     int kv_before;
     int flags;
+    int seq, g, tile, n_tiles;   // the segment's ItemPos: the consumers take it from here instead of searching the
+    long long item_begin;        // tile prefix themselves between two segments (0.7 us, measured)
 };
 
 // A position on the line of tiles: which (sequence, kv head) item it falls in and where.
@@ -174,6 +176,8 @@ struct __align__(1024) DecodeSmem {
     uint64_t hstart;                               // helper -> producer: the first segment's loads are on their way
     int last_flag;                                 // end-of-span partial: this CTA completed the item
     uint64_t pdone[2];                             // consumers -> helper: partial 0 / 1 of this CTA is in scratch
+    uint64_t isready;                              // helper -> consumers: last_is holds the geometry of the span's final item
+    ItemSpans last_is;
     int abort_flag;
 };
 
@@ -817,6 +821,7 @@ decode_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__
         mbar_init(&sm.hstart, 1);
         mbar_init(&sm.pdone[0], kConsumerWarps);
         mbar_init(&sm.pdone[1], kConsumerWarps);
+        mbar_init(&sm.isready, 1);
         fence_mbar_init();
         if (kXchg) {
             sm.xs.xd = xchg;
@@ -1035,8 +1040,23 @@ decode_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__
                 prepare_segment(sm.qb[b], sh, sq, ip.g, sq.slot * G + ip.g, has_last_tile, appender, lane, k_base, v_base,
                                 rope_tab, rope_tab_len, (sidx == 0 && !dry) ? &sm.hstart : nullptr, dry);
             }
+            if (lane == 0) {
+                QBuf &qo = sm.qb[b];
+                qo.seq = ip.seq; qo.g = ip.g; qo.tile = ip.tile; qo.n_tiles = ip.n_tiles; qo.item_begin = ip.item_begin;
+            }
             __syncwarp();
             if (lane == 0) mbar_arrive(&sm.qfull[b]);
+            // The span's last segment is delivered by the consumer warps themselves; which CTAs hold parts of its item (a few
+            // 64-bit divisions and searches of the tile prefix) is worked out here, by the warp that has nothing else to do,
+            // and not by the consumers between two segments: there it stood between the fold of one item and the first
+            // tile of the next for 4.5 us (measured), which was most of what an item start inside a span cost.
+            if (seg_end == span_hi && !(pos == ip.item_begin && has_last_tile)) {
+                if (lane == 0) {
+                    sm.last_is = item_spans(geo, ip);
+                    mbar_arrive(&sm.isready);
+                }
+                __syncwarp();
+            }
             if (prev_partial) {   // the consumers are still on the previous segment, or just left it
                 mbar_wait_bounded(&sm.pdone[prev_slot], 0, &sm.abort_flag);   // each used once: a CTA has <= 2 partials
                 {
@@ -1073,20 +1093,22 @@ decode_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__
         unsigned int n = 0, sidx = 0;
         bool first_segment = true;
         while (pos < span_hi) {
-            const ItemPos ip = locate(sm.prefix, n_seq, G, pos);
+            const QBuf &qb = sm.qb[sidx & 1];
+            // what the helper warp prepared: where the segment lies, the sequence's scalars and the q tile (A fragments: 8
+            // k-steps of 16 dims)
+            const bool q_ok = mbar_wait_bounded(&sm.qfull[sidx & 1], (sidx >> 1) & 1u, &sm.abort_flag);
+            ItemPos ip;
+            if (q_ok) {
+                ip.seq = qb.seq; ip.g = qb.g; ip.tile = qb.tile; ip.n_tiles = qb.n_tiles; ip.item_begin = qb.item_begin;
+            } else {   // a wait ran out: the launch is abandoned, but every warp still walks its span to the end in step
+                ip = locate(sm.prefix, n_seq, G, pos);
+            }
             const int g = ip.g;
             const long long item_end = ip.item_begin + ip.n_tiles;
             const long long seg_end = min(span_hi, item_end);
             const bool has_last_tile = seg_end == item_end;
             const bool whole_item = pos == ip.item_begin && has_last_tile;
             const int last_tile = ip.n_tiles - 1;
-            const QBuf &qb = sm.qb[sidx & 1];
-
-            // the span's last segment is finished by these warps themselves: park the item's geometry now, while the
-            // helper warp is still preparing the segment
-            if (!whole_item && seg_end == span_hi && lane == 0) sm.dargs[warp].is = item_spans(geo, ip);
-            // what the helper warp prepared: the sequence's scalars and the q tile (A fragments: 8 k-steps of 16 dims)
-            mbar_wait_bounded(&sm.qfull[sidx & 1], (sidx >> 1) & 1u, &sm.abort_flag);
             const int kv_before = qb.kv_before, flags = qb.flags;
             float *const out_ptr = qb.out, *const partial_ptr = qb.partial;
             const int L = attended_len(kv_before, flags);
@@ -1239,7 +1261,11 @@ decode_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__
                 // complete.  The team barrier inside deliver_part also orders every warp's partial stores before the count.
                 const MergeCtx mc{geo, counters, gcounters, partials, gpartials};
                 DeliverArgs &da = sm.dargs[warp];   // every warp parks its own copy: no barrier needed before the call
-                if (lane == 0) { da.ip = ip; da.io = ItemOut{out_ptr, partial_ptr, flags}; da.mc = mc; da.G = G; da.R = R; da.xs = kXchg ? &sm.xs : nullptr; }
+                mbar_wait_bounded(&sm.isready, 0, &sm.abort_flag);   // long since there: the helper warp wrote it while the tiles streamed
+                if (lane == 0) {
+                    da.ip = ip; da.is = sm.last_is; da.io = ItemOut{out_ptr, partial_ptr, flags}; da.mc = mc; da.G = G; da.R = R;
+                    da.xs = kXchg ? &sm.xs : nullptr;
+                }
                 __syncwarp();
                 deliver_part(&da, blockIdx.x, tid, kConsumerThreads, &sm.last_flag);
             } else if (kXchg && whole_item) {
