@@ -308,14 +308,14 @@ struct DecodeTable {
     int settled;   // 0, or 1 + tiles per CTA to pull into L2 ahead of the ring: every sequence carries CGLM_SEQ_CACHE_SETTLED
     int trigger;   // when a CTA releases the next kernel of the stream: 0 at its start, 1 last tile requested, 2 last tile consumed
     int charge;    // tiles a CTA's span is shortened by for every item start inside it (cost-balanced cut of the line)
+    int prefix[kDecodeMaxSeqPerLaunch + 2];   // prefix[i] = 64-token tiles of sequences [0, i), per kv head
+    SeqDev seqs[kDecodeMaxSeqPerLaunch];
     // Gates (host-buffer calls): device words that copy engines write, gate[i] null or a word that must hold
     // gate_value[i] before the launch reads its activations (0) / writes its outputs (1).  Every CTA's helper warp polls
     // them, with a bound, after the dependency wait; the stream itself carries no wait between two launches, so
     // consecutive launches keep their programmatic overlap.
     const unsigned int *gate[2];
     unsigned int gate_value[2];
-    int prefix[kDecodeMaxSeqPerLaunch + 2];   // prefix[i] = 64-token tiles of sequences [0, i), per kv head
-    SeqDev seqs[kDecodeMaxSeqPerLaunch];
 };
 // The table of a launch with device-side positions: what every CTA reads of EVERY sequence after the dependency wait,
 // once more as arrays (decode_table_finish fills them): thread i reading seqs[i].flags touches one 128-byte descriptor
