@@ -348,6 +348,10 @@ def test_fused_splitkv_step_four_ranks_on_one_device():
     assert _lib.lib().cglm_launch_count() - before == 2 * n_rank      # one launch per rank and step
     for b in bufs:
         assert int(b[0]) == 2                                        # every rank has finished step 2
+    words = ranks[3].read_words(32 + 2 * 16 * 32)                    # the diagnostics view: step counter, arrival words
+    assert int(words[0]) == 2
+    assert all(int(words[32 + (0 * 16 + r) * 32 + g]) == 2 for r in range(n_rank) for g in range(G))   # set 0 holds step 2
+    assert all(int(words[32 + (1 * 16 + r) * 32 + g]) == 1 for r in range(n_rank) for g in range(G))   # set 1 holds step 1
     # rank 1 stays silent: rank 3 gives up after 2 ms
     out = torch.full((H * D,), 7.0, device="cuda")
     for r in (0, 2):
