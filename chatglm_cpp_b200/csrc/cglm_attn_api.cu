@@ -60,8 +60,6 @@ struct cglm_kv_arena {
     int host_next;
     bool host_ready;
     // calls served straight from mapped host memory (no staging): the last such call's kernel, for cglm_attn_host_drain
-    cudaEvent_t direct_done;
-    bool direct_ready, direct_used;
     std::mutex mu;
 };
 
@@ -452,7 +450,6 @@ int cglm_kv_arena_create(const cglm_attn_desc *desc, int n_slots, cglm_kv_arena 
         cudaEventCreateWithFlags(&a->ring_events[i], cudaEventDisableTiming);
     }
     a->host_ready = false;
-    a->direct_ready = a->direct_used = false;
     a->host_next = 0;
     *out = a;
     return CGLM_OK;
@@ -524,7 +521,6 @@ int cglm_kv_arena_adopt(const cglm_attn_desc *desc, int n_slots, void *k_base, v
         cudaEventCreateWithFlags(&a->ring_events[i], cudaEventDisableTiming);
     }
     a->host_ready = false;
-    a->direct_ready = a->direct_used = false;
     a->host_next = 0;
     *out = a;
     return CGLM_OK;
@@ -542,7 +538,6 @@ int cglm_kv_arena_destroy(cglm_kv_arena *a) {
         cudaFree(a->gate_dev);
         cudaFreeHost(a->gate_host);
     }
-    if (a->direct_ready) cudaEventDestroy(a->direct_done);
     for (int i = 0; i < a->ring_slots; ++i) cudaEventDestroy(a->ring_events[i]);
     delete[] a->ring_events;
     if (a->ring) cudaFreeHost(a->ring);
@@ -837,48 +832,10 @@ int cglm_attn_forward_host(cglm_kv_arena *a, const cglm_attn_seq *seqs, int n_se
             n_tok += seqs[i].qlen;
         }
     };
-    // ---- small decode steps on pinned host buffers: no staging at all ------------------------------------------
-    // Pinned (page-locked) host memory is mapped into the device's address space.  For a decode call of a few
-    // sequences the kernel reads the activations across PCIe where it would have read the staging copy, and stores
-    // the outputs straight into the host buffer: the same bytes cross the bus, but no copy, no event and no stream
-    // wait stands between two launches (measured: 28 -> 15 us per call for one sequence).  Results are in host
-    // memory once the stream has been synchronised.  Beyond about 128 KiB of activations the bus latency of the
-    // many small reads and their repetition by every CTA that holds a part of a sequence cost more than the copies
-    // (64 sequences: half the throughput of the staged pipeline), so larger calls, pageable host memory and
-    // prompts keep the staged pipeline below.
-    {
-        constexpr long long kZeroCopyMaxBytes = 128 * 1024;
-        bool decode_only = fast_decode_shape(a) && static_cast<long long>(n_seq) * row * static_cast<long long>(esz) <= kZeroCopyMaxBytes;
-        for (int i = 0; i < n_seq && decode_only; ++i) decode_only = seqs[i].qlen == 1;
-        auto mapped = [](const void *p) -> void * {
-            cudaPointerAttributes at;
-            if (cudaPointerGetAttributes(&at, p) != cudaSuccess) {
-                cudaGetLastError();
-                return nullptr;
-            }
-            return at.type == cudaMemoryTypeHost ? at.devicePointer : nullptr;
-        };
-        void *din = decode_only ? mapped(qkv_host) : nullptr;
-        void *dout = din ? mapped(out_host) : nullptr;
-        if (din && dout) {
-            point_at(din, dout);
-            const int rc = cglm_attn_forward(a, dev_seqs.data(), n_seq, workspace, workspace_bytes, cuda_stream);
-            if (rc != CGLM_OK) return rc;
-            // the kernel stores the outputs into host memory itself: a drain enqueued on ANOTHER stream has to wait for it
-            cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
-            cudaStreamIsCapturing(static_cast<cudaStream_t>(cuda_stream), &cap);
-            if (cap == cudaStreamCaptureStatusNone) {
-                std::lock_guard<std::mutex> lock(a->mu);
-                if (!a->direct_ready) {
-                    CGLM_CUDA(cudaEventCreateWithFlags(&a->direct_done, cudaEventDisableTiming));
-                    a->direct_ready = true;
-                }
-                CGLM_CUDA(cudaEventRecord(a->direct_done, static_cast<cudaStream_t>(cuda_stream)));
-                a->direct_used = true;
-            }
-            return CGLM_OK;
-        }
-    }
+    // Pinned host buffers are not read by the kernels directly, although the device could map them: with the copies
+    // gated by device words (below) the staged pipeline is faster at every size.  Measured per decode step through
+    // host buffers: one sequence, 28 calls, 0.99 ms staged against 1.11 ms direct; 8 sequences of 9 KiB, 40 calls,
+    // 1.45 against 3.45 ms (every thread block that holds a part of a sequence repeats the small reads across the bus).
     point_at(dev_qkv, dev_out);
     // ---- pipeline: H2D on copy_in, kernel on the caller's stream, D2H on copy_out ---------------------------------
     std::unique_lock<std::mutex> lock(a->mu);
@@ -950,7 +907,6 @@ int cglm_attn_host_drain(cglm_kv_arena *a, void *cuda_stream) {
     if (!a) return CGLM_ERR_INVALID_ARG;
     cudaStream_t st = static_cast<cudaStream_t>(cuda_stream);
     std::lock_guard<std::mutex> lock(a->mu);
-    if (a->direct_used) CGLM_CUDA(cudaStreamWaitEvent(st, a->direct_done, 0));
     if (!a->host_ready) return CGLM_OK;
     for (auto &c : a->host_calls) {
         if (c.used) CGLM_CUDA(cudaStreamWaitEvent(st, c.d2h, 0));

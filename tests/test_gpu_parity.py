@@ -442,8 +442,8 @@ def test_splitkv_partials_combine_to_full_attention():
 
 @pytest.mark.parametrize("pinned", [True, False])
 def test_forward_host_roundtrip_matches_device_call(pinned):
-    """Host-buffer call against the plain device call.  Pinned host buffers are read and written by the decode kernel
-    directly (one launch, no copies); pageable ones go through the staged copy pipeline."""
+    """Host-buffer call against the plain device call, from pinned host buffers (asynchronous copies, the decode launch
+    gated by the device word behind its input copy) and from pageable ones."""
     from chatglm_cpp_b200 import _lib
     A = _A()
     desc = make_desc(32, 2, 128, 1024)
@@ -477,9 +477,9 @@ def test_forward_host_roundtrip_matches_device_call(pinned):
 
 
 def test_forward_host_drain_on_another_stream_and_uninitialised_workspace():
-    """The drain may be enqueued on a stream other than the one the host-buffer calls ran on, also when pinned buffers
-    made the kernel write the outputs into host memory itself: the other stream then waits for that kernel.  And a
-    workspace that never went through cglm_attn_workspace_init is reported by the status query."""
+    """The drain may be enqueued on a stream other than the one the host-buffer calls ran on: that stream then waits for
+    the calls' device-to-host copies.  And a workspace that never went through cglm_attn_workspace_init is reported by
+    the status query."""
     from chatglm_cpp_b200 import _lib
     A = _A()
     L = _lib.lib()
@@ -521,7 +521,7 @@ def test_forward_host_pipeline_reuses_staging_buffers():
     A = _A()
     desc = make_desc(32, 2, 128, 2048)
     rng = np.random.default_rng(41)
-    n_layers, n = 6, 8          # 8 x 18 KiB of activations per call: above the zero-copy limit, so the staged path
+    n_layers, n = 6, 8          # 8 x 18 KiB of activations per call
     n_past = [1500, 20, 700, 2047, 64, 1, 1023, 333]
     arena, ws = A.KVArena(desc, 2 * n_layers * n), A.Workspace(desc, n, 1)
     arena.k_all().normal_(); arena.v_all().normal_()
@@ -677,7 +677,7 @@ def test_f16_hand_off_prefill(S, rope, mask, H, G):
 @pytest.mark.parametrize("n", [3, 16])
 def test_f16_hand_off_through_host_buffers(n):
     """cglm_attn_forward_host with CGLM_HOST_F16 (half the bytes across the bus) against the device call with f16
-    tensors: 3 sequences take the zero-copy route, 16 the staged pipeline."""
+    tensors, for a small and a larger call."""
     from chatglm_cpp_b200 import _lib
     A = _A()
     desc = make_desc(32, 2, 128, 1024)
