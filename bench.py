@@ -67,6 +67,9 @@ WORKLOADS = {
     # 40 layers' Linears, every layer its own 37.7 MB f16 weight, so the weights stream from HBM)
     "glm4_9b_qkv_linear_b64": dict(H=32, G=2, D=128, M=8192, layers=40, seqs=64, n_past=(1024, 8191), rope=8, theta=5.0e6,
                                    interleaved=False, mask=0, seed=1003, qkv_linear=4096),
+    # BasicAttention::forward as the reference calls it, per layer: fused query_key_value GEMM, decode kernel, dense GEMM
+    "glm4_9b_attention_block_b64": dict(H=32, G=2, D=128, M=8192, layers=40, seqs=64, n_past=(1024, 8191), rope=8, theta=5.0e6,
+                                        mask=0, interleaved=False, seed=20240603, attention_block=4096),
     "glm4_9b_qkv_linear_b8": dict(H=32, G=2, D=128, M=8192, layers=40, seqs=8, n_past=(1024, 8191), rope=8, theta=5.0e6,
                                   interleaved=False, mask=0, seed=1003, qkv_linear=4096),
     "glm4_9b_qkv_linear_b128": dict(H=32, G=2, D=128, M=8192, layers=40, seqs=128, n_past=(1024, 8191), rope=8, theta=5.0e6,
@@ -656,6 +659,100 @@ def qkv_linear_measure(dd, name, w, args, syn, steps=None):
                          "eager_launch_us": ms_eager / steps * 1e3 / layers}}
 
 
+def attention_block_measure(dd, name, w, args, syn, steps=None):
+    """A step is BasicAttention::forward (chatglm.cpp:625-722) of every layer for a batch of one-token sequences:
+    hidden_states f16 -> query_key_value GEMM with bias, RoPE and the K/V append in its epilogue -> decode kernel over the
+    cache (roped q in f32, context out in f16) -> dense GEMM -> attn_output f32.  Three launches per layer, each layer
+    with its own weights and caches.  Bound: KV bytes plus both weights over HBM."""
+    import torch
+    from chatglm_cpp_b200 import _lib
+    from chatglm_cpp_b200 import attention as A
+    L = _lib.lib()
+    H, G, D, hidden, layers, n = w["H"], w["G"], w["D"], w["attention_block"], w["layers"], w["seqs"]
+    steps = steps or args.steps
+    n_feat = (H + 2 * G) * D
+    seed = w["seed"] + 7919 * dd.rank
+    desc = _lib.AttnDesc(H, G, D, w["M"], 0, w["rope"], w["theta"], w["mask"])
+    arena = A.KVArena(desc, layers * n)
+    syn.fill(arena.k_all(), seed, TID_K)
+    syn.fill(arena.v_all(), seed, TID_V)
+    ws = A.Workspace(desc, max(n, 128), 1)
+    w_qkv = torch.empty(layers, n_feat, hidden, device="cuda", dtype=torch.float16)
+    w_dense = torch.empty(layers, hidden, H * D, device="cuda", dtype=torch.float16)
+    syn.fill(w_qkv, seed, 11)
+    syn.fill(w_dense, seed, 13)
+    w_qkv.mul_(1.0 / np.sqrt(hidden))
+    w_dense.mul_(1.0 / np.sqrt(H * D))
+    x = torch.empty(n, hidden, device="cuda", dtype=torch.float16)
+    syn.fill(x, seed, 12)
+    bias = torch.zeros(n_feat, device="cuda")
+    q_roped = torch.empty(2, n, H * D, device="cuda")                       # two sets: a layer's GEMM may run ahead
+    context = torch.empty(2, n, H * D, device="cuda", dtype=torch.float16)
+    out = torch.empty(layers, n, hidden, device="cuda")
+    n_past = draw_n_past(w, dd.rank)
+    lin_arr, att_arr = [], []
+    for l in range(layers):
+        a1, a2 = (_lib.AttnSeq * n)(), (_lib.AttnSeq * n)()
+        for i in range(n):
+            P = int(n_past[i])
+            a1[i].slot, a1[i].qlen, a1[i].n_past = l * n + i, 1, P
+            q = q_roped[l % 2, i].data_ptr()
+            a2[i].q = a2[i].k = a2[i].v = q                                  # k and v are not read
+            a2[i].q_head_stride = a2[i].kv_head_stride = D
+            a2[i].q_tok_stride = a2[i].kv_tok_stride = H * D
+            a2[i].slot, a2[i].qlen, a2[i].n_past, a2[i].kv_local = l * n + i, 1, P, P + 1
+            a2[i].flags = _lib.SEQ_Q_ROPED | _lib.SEQ_NO_APPEND | _lib.SEQ_USE_KV_LOCAL | _lib.SEQ_OUT_F16
+            a2[i].out = context[l % 2, i].data_ptr()
+        lin_arr.append(a1)
+        att_arr.append(a2)
+
+    def step():
+        stream = torch.cuda.current_stream().cuda_stream
+        for l in range(layers):
+            rc = L.cglm_qkv_linear_forward(arena._h, lin_arr[l], n, x.data_ptr(), hidden, w_qkv[l].data_ptr(), bias.data_ptr(),
+                                           q_roped[l % 2].data_ptr(), ws.ptr, ws.bytes, stream)
+            if rc == 0:
+                rc = L.cglm_attn_forward(arena._h, att_arr[l], n, ws.ptr, ws.bytes, stream)
+            if rc == 0:
+                rc = L.cglm_linear_forward(context[l % 2].data_ptr(), n, H * D, w_dense[l].data_ptr(), hidden, None,
+                                           out[l].data_ptr(), 0, ws.ptr, ws.bytes, stream)
+            if rc != 0:
+                raise _lib.CglmError(rc, "attention block")
+
+    # issued as a replayed CUDA graph (an eager GEMM call encodes two tensor maps on the host, through ctypes, and takes
+    # about as long to issue as the kernel runs); the eager figure is reported beside it
+    ms_eager, launches = timed(dd, step, max(3, steps // 4), max(args.warmup, 3))
+    ms_eager /= max(3, steps // 4)
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        step()
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        step()
+    ms, _ = timed(dd, graph.replay, steps, max(args.warmup, 3))
+    graph = None
+    if ws.status() != 0:
+        raise SystemExit(f"{name}: device-side status is not clean after the timed region")
+    if not bool(torch.isfinite(out).all()):
+        raise SystemExit(f"{name}: non-finite attn_output")
+    ms /= steps
+    pk, src = peak("hbm_gbs", HBM_FALLBACK_GBS)
+    w_bytes = (n_feat * hidden + hidden * H * D) * 2
+    kv = kv_bytes(w, n_past)
+    achieved = (w_bytes + kv) * layers / (ms * 1e-3) / 1e9
+    arena.close()
+    return {"metric": "attention_block_tokens_per_s", "value": n * dd.world / (ms * 1e-3), "unit": "tokens/s", "ms_per_step": ms,
+            "steps": steps, "launches": int(launches) // max(3, steps // 4) * steps, "tokens": n,
+            "l2_policy": f"every layer streams its own caches ({kv / 1e6:.0f} MB) and weights ({w_bytes / 1e6:.1f} MB): {layers} layers > L2",
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": pk, "unit": "GB/s", "frac": achieved / pk,
+                         "peak_source": src, "kernel": "qkv_linear_kernel<false> + decode_kernel + qkv_linear_kernel<true>",
+                         "algorithmic_bytes_per_layer": w_bytes + kv, "layer_us": ms * 1e3 / layers,
+                         "issue": "CUDA graph of the step, replayed", "eager_layer_us": ms_eager * 1e3 / layers}}
+
+
 # ---- one long sequence (config 4) ----------------------------------------------------------------------------------------
 def split_kv_rotation(n_past, world, n_kv_head, head_dim):
     """Copies of a rank's KV slice the split-KV workload rotates through, so that the working set is at least four times
@@ -863,6 +960,13 @@ def run_single(args, dd, name, w):
                             "layers": w["layers"], "tokens": r["tokens"], "l2_policy": r["l2_policy"]},
                     roofline=dict(r["roofline"], traffic=None), cpu_baseline=None, e2e=None, gpu_launches=r["launches"] * dd.world,
                     clocks=sampler.finish())
+    elif w.get("attention_block"):
+        r = attention_block_measure(dd, name, w, args, syn)
+        line = dict(base_line(args, dd, r["metric"]), value=r["value"], ms_per_step=r["ms_per_step"],
+                    config={"workload": name, "n_head": w["H"], "n_kv_head": w["G"], "head_dim": w["D"], "hidden": w["attention_block"],
+                            "layers": w["layers"], "tokens": r["tokens"], "l2_policy": r["l2_policy"]},
+                    roofline=dict(r["roofline"], traffic=None), cpu_baseline=None, e2e=None, gpu_launches=r["launches"] * dd.world,
+                    clocks=sampler.finish())
     elif w.get("split_kv"):
         r = split_kv_measure(dd, name, w, args, syn)
         line = dict(base_line(args, dd, scaling="strong"), value=r["value"], ms_per_step=r["ms_per_step"], steps=r["steps"],
@@ -953,6 +1057,10 @@ def run_default(args, dd):
         nm = "glm4_9b_qkv_linear_b64"
         rr = qkv_linear_measure(dd, nm, WORKLOADS[nm], args, syn, steps=short)
         configs[nm] = {k: rr[k] for k in ("metric", "value", "unit", "ms_per_step", "steps", "tokens", "roofline")}
+        nm = "glm4_9b_attention_block_b64"
+        rr = attention_block_measure(dd, nm, WORKLOADS[nm], args, syn, steps=short)
+        configs[nm] = {k: rr[k] for k in ("metric", "value", "unit", "ms_per_step", "steps", "tokens", "roofline")}
+        torch.cuda.empty_cache()
         nm = "glm4_9b_long_131072"
         rr = split_kv_measure(dd, nm, WORKLOADS[nm], args, syn, steps=short)
         entry = {k: rr[k] for k in ("value", "unit", "ms_per_step", "steps", "parallelism", "kv_bytes_this_rank", "roofline", "issue")}

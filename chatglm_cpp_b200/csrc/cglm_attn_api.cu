@@ -303,6 +303,21 @@ __global__ void combine_kernel(const float *__restrict__ partials, int n_part, i
     }
 }
 
+// activation cast in front of an f16 Linear (ggml converts the f32 activation row the same way before it multiplies by
+// an f16 matrix): round to nearest even, grid-stride over groups of 4
+__global__ void f32_to_f16_kernel(const float *__restrict__ src, __half *__restrict__ dst, size_t n) {
+    const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x * 4;
+    const bool vec = ((reinterpret_cast<uintptr_t>(src) & 15) | (reinterpret_cast<uintptr_t>(dst) & 7)) == 0;
+    for (size_t i = (static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x) * 4; i < n; i += stride) {
+        if (vec && i + 4 <= n) {
+            const float4 v = *reinterpret_cast<const float4 *>(src + i);
+            *reinterpret_cast<uint2 *>(dst + i) = make_uint2(pack_half2(v.x, v.y), pack_half2(v.z, v.w));
+        } else {
+            for (size_t j = i; j < n && j < i + 4; ++j) dst[j] = __float2half_rn(src[j]);
+        }
+    }
+}
+
 __global__ void seq_advance_kernel(int *__restrict__ n_past, int n, int delta) {
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) n_past[i] += delta;
@@ -1105,6 +1120,67 @@ int cglm_qkv_linear_forward(cglm_kv_arena *a, const cglm_attn_seq *seqs, int n_s
     const WsLayout lay = ws_layout(d, a->n_sm, 1, 0, 0);
     LaunchCtx cx = make_launch_ctx(a, static_cast<uint8_t *>(workspace), lay, static_cast<cudaStream_t>(cuda_stream));
     CGLM_CUDA(launch_qkv_linear(cx, x_map, w_map, slots, n_past, n_seq, hidden, n_feat, kb, bias, q_roped));
+    return CGLM_OK;
+}
+
+int cglm_linear_forward(const void *x_f16, int n_tok, int in_features, const void *weight_f16, int out_features,
+                        const float *bias, void *out, int out_is_f16, void *workspace, size_t workspace_bytes, void *cuda_stream) {
+    if (!x_f16 || !weight_f16 || !out || n_tok <= 0 || in_features <= 0 || out_features <= 0) return CGLM_ERR_INVALID_ARG;
+    if (!workspace || workspace_bytes < sizeof(WsHeader)) return CGLM_ERR_WORKSPACE;
+    if (in_features % 64 != 0 || out_features % 32 != 0) {
+        std::snprintf(g_err, sizeof(g_err), "the Linear kernel needs in_features %% 64 == 0 and out_features %% 32 == 0");
+        return CGLM_ERR_UNSUPPORTED;
+    }
+    if ((reinterpret_cast<uintptr_t>(x_f16) | reinterpret_cast<uintptr_t>(weight_f16) | reinterpret_cast<uintptr_t>(out)) & 15)
+        return CGLM_ERR_INVALID_ARG;
+    int device = -1;
+    CGLM_CUDA(cudaGetDevice(&device));
+    if (device < 0 || device >= kMaxDevices) return CGLM_ERR_NO_DEVICE;
+    {   // tcgen05: compute capability 10.x only (checked once per device)
+        static std::atomic<int> major_of[kMaxDevices];
+        int major = major_of[device].load(std::memory_order_relaxed);
+        if (major == 0) {
+            CGLM_CUDA(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, device));
+            major_of[device].store(major, std::memory_order_relaxed);
+        }
+        if (major != 10) return CGLM_ERR_NO_DEVICE;
+    }
+    EncodeTiledFn enc = encode_tiled_fn();
+    if (!enc) return CGLM_ERR_CUDA;
+    const int tile_tok = n_tok < 128 ? n_tok : 128;
+    const int x_rows = qkv_linear_x_rows(tile_tok);
+    CUtensorMap x_map, w_map;
+    for (int kb = qkv_linear_k_blocks(tile_tok, in_features);; kb = 1) {
+        const cuuint32_t estr[3] = {1, 1, 1};
+        cuuint64_t xdims[3] = {64, static_cast<cuuint64_t>(n_tok), static_cast<cuuint64_t>(in_features / 64)};
+        cuuint64_t strides[2] = {static_cast<cuuint64_t>(in_features) * 2, 128};
+        cuuint32_t xbox[3] = {64, static_cast<cuuint32_t>(x_rows), static_cast<cuuint32_t>(kb)};
+        cuuint64_t wdims[3] = {64, static_cast<cuuint64_t>(out_features), static_cast<cuuint64_t>(in_features / 64)};
+        cuuint32_t wbox[3] = {64, 32, static_cast<cuuint32_t>(kb)};
+        if (enc(&x_map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, const_cast<void *>(x_f16), xdims, strides, xbox, estr,
+                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS &&
+            enc(&w_map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, const_cast<void *>(weight_f16), wdims, strides, wbox, estr,
+                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS) {
+            CGLM_CUDA(launch_linear_plain(device, static_cast<cudaStream_t>(cuda_stream), static_cast<WsHeader *>(workspace), x_map,
+                                          w_map, n_tok, in_features, out_features, kb, bias, out, out_is_f16 != 0));
+            return CGLM_OK;
+        }
+        if (kb == 1) break;
+    }
+    std::snprintf(g_err, sizeof(g_err), "cuTensorMapEncodeTiled failed for the Linear");
+    return CGLM_ERR_CUDA;
+}
+
+int cglm_convert_f32_to_f16(const float *src, void *dst_f16, size_t n, void *cuda_stream) {
+    if (!src || !dst_f16) return CGLM_ERR_INVALID_ARG;
+    if (n == 0) return CGLM_OK;
+    const size_t blocks = (n + 1023) / 1024;
+    f32_to_f16_kernel<<<static_cast<unsigned>(blocks < 4096 ? blocks : 4096), 256, 0, static_cast<cudaStream_t>(cuda_stream)>>>(
+        src, static_cast<__half *>(dst_f16), n);
+    g_launch_count += 1;
+    CGLM_CUDA(cudaGetLastError());
     return CGLM_OK;
 }
 

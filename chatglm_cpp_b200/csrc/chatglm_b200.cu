@@ -39,6 +39,9 @@ ModelContext::ModelContext(void *cuda_stream) : stream_(cuda_stream) {}
 ModelContext::~ModelContext() {
     cudaStreamSynchronize(static_cast<cudaStream_t>(stream_));
     reset_scratch();
+    for (auto &t : weights_) {
+        if (t->owned && t->data) cudaFree(t->data);
+    }
     if (workspace_) cudaFree(workspace_);
     if (arena_) cglm_kv_arena_destroy(arena_);
 }
@@ -101,6 +104,27 @@ void ModelContext::ensure_workspace(int n_seq, int max_qlen) {
         CHATGLM_CHECK_CGLM(cglm_attn_workspace_init(workspace_, workspace_bytes_, stream_));
     }
 }
+
+void ModelContext::ensure_status_workspace() {
+    if (workspace_) return;
+    const size_t bytes = 4096;
+    CHATGLM_CHECK_CUDA(cudaMalloc(&workspace_, bytes));
+    workspace_bytes_ = bytes;
+    CHATGLM_CHECK_CGLM(cglm_attn_workspace_init(workspace_, workspace_bytes_, stream_));
+}
+
+Tensor *ModelContext::new_weight_2d(TensorType type, int64_t ne0, int64_t ne1) {
+    auto t = std::make_unique<Tensor>();
+    set_contiguous(t.get(), type, ne0, ne1, 1);
+    const size_t bytes = std::max<size_t>(nbytes(t.get()), 16);
+    CHATGLM_CHECK_CUDA(cudaMalloc(&t->data, bytes));
+    CHATGLM_CHECK_CUDA(cudaMemsetAsync(t->data, 0, bytes, static_cast<cudaStream_t>(stream_)));
+    t->owned = true;
+    weights_.push_back(std::move(t));
+    return weights_.back().get();
+}
+
+Tensor *ModelContext::new_weight_1d(TensorType type, int64_t ne0) { return new_weight_2d(type, ne0, 1); }
 
 Tensor *ModelContext::new_tensor_2d(TensorType type, int64_t ne0, int64_t ne1) {
     auto t = std::make_unique<Tensor>();
@@ -188,8 +212,45 @@ std::vector<int> make_position_ids_glm(int qlen, int n_past, int n_ctx) {
     return ids;
 }
 
+// ---- Linear -------------------------------------------------------------------------------------------------------
+Linear::Linear(ModelContext *mctx, int in_features, int out_features, bool use_bias) {
+    CHATGLM_CHECK(mctx != nullptr) << "null context";
+    CHATGLM_CHECK(in_features > 0 && out_features > 0) << "invalid Linear shape";
+    weight = mctx->new_weight_2d(TYPE_F16, in_features, out_features);
+    bias = use_bias ? mctx->new_weight_1d(TYPE_F32, out_features) : nullptr;
+}
+
+// f16 view of an activation: the tensor itself, or its rounded copy in mctx's scratch
+static Tensor *as_f16(ModelContext *mctx, Tensor *t) {
+    if (t->type == TYPE_F16) return t;
+    CHATGLM_CHECK(t->type == TYPE_F32) << "activations are f32 or f16";
+    CHATGLM_CHECK(t->nb[1] == t->nb[0] * static_cast<size_t>(t->ne[0])) << "activation rows must be contiguous";
+    Tensor *h = mctx->new_tensor_2d(TYPE_F16, t->ne[0], t->ne[1]);
+    CHATGLM_CHECK_CGLM(cglm_convert_f32_to_f16(static_cast<const float *>(t->data), h->data,
+                                               static_cast<size_t>(t->ne[0] * t->ne[1]), mctx->stream()));
+    return h;
+}
+
+Tensor *Linear::forward(ModelContext *mctx, Tensor *input, TensorType out_type) const {
+    CHATGLM_CHECK(mctx != nullptr && weight != nullptr) << "Linear without parameters";
+    CHATGLM_CHECK(input && input->data && input->ne[0] == weight->ne[0])
+        << "input row is " << (input ? input->ne[0] : 0) << ", expected " << weight->ne[0];
+    CHATGLM_CHECK(out_type == TYPE_F32 || out_type == TYPE_F16) << "output is f32 or f16";
+    CHATGLM_CHECK(weight->type == TYPE_F16) << "weights are f16";
+    Tensor *x = as_f16(mctx, input);
+    CHATGLM_CHECK(x->nb[1] == 2 * static_cast<size_t>(x->ne[0])) << "activation rows must be contiguous";
+    const int n_tok = static_cast<int>(x->ne[1]);
+    Tensor *output = mctx->new_tensor_2d(out_type, weight->ne[1], n_tok);   // [seqlen, out_features]
+    mctx->ensure_status_workspace();
+    CHATGLM_CHECK_CGLM(cglm_linear_forward(x->data, n_tok, in_features(), weight->data, out_features(),
+                                           bias ? static_cast<const float *>(bias->data) : nullptr, output->data,
+                                           out_type == TYPE_F16, mctx->workspace_, mctx->workspace_bytes_, mctx->stream_));
+    return output;
+}
+
+// ---- BasicAttention -------------------------------------------------------------------------------------------------
 BasicAttention::BasicAttention(ModelContext *mctx, int hidden_size, int num_attention_heads, int num_key_value_heads,
-                               int max_length, bool /*use_qkv_bias*/, bool /*use_dense_bias*/, bool interleaved_qkv,
+                               int max_length, bool use_qkv_bias, bool use_dense_bias, bool interleaved_qkv,
                                RopeType rope_type, float rope_theta, AttentionMaskType attn_mask_type,
                                int num_virtual_tokens)
     : num_attention_heads(num_attention_heads), num_key_value_heads(num_key_value_heads),
@@ -198,6 +259,8 @@ BasicAttention::BasicAttention(ModelContext *mctx, int hidden_size, int num_atte
     CHATGLM_CHECK(mctx != nullptr) << "null context";
     CHATGLM_CHECK(num_attention_heads > 0 && hidden_size % num_attention_heads == 0) << "invalid head count";
     head_size_ = hidden_size / num_attention_heads;
+    query_key_value = Linear(mctx, hidden_size, hidden_size + 2 * head_size_ * num_key_value_heads, use_qkv_bias);
+    dense = Linear(mctx, hidden_size, hidden_size, use_dense_bias);
     cglm_attn_desc desc;
     desc.n_head = num_attention_heads;
     desc.n_kv_head = num_key_value_heads;
@@ -210,10 +273,11 @@ BasicAttention::BasicAttention(ModelContext *mctx, int hidden_size, int num_atte
     slot_ = mctx->register_attention(desc, &k_cache, &v_cache);
 }
 
-Tensor *BasicAttention::forward(ModelContext *mctx, Tensor *qkv, Tensor * /*attention_mask*/, Tensor *position_ids,
-                                int n_past) const {
+Tensor *BasicAttention::attend(ModelContext *mctx, Tensor *qkv, Tensor * /*attention_mask*/, Tensor *position_ids,
+                               int n_past, TensorType out_type) const {
     CHATGLM_CHECK(mctx && mctx->kv_allocated()) << "kv buffer not allocated";
-    CHATGLM_CHECK(qkv && qkv->type == TYPE_F32 && qkv->data) << "qkv must be an f32 device tensor";
+    CHATGLM_CHECK(qkv && (qkv->type == TYPE_F32 || qkv->type == TYPE_F16) && qkv->data) << "qkv must be an f32 or f16 device tensor";
+    CHATGLM_CHECK(out_type == TYPE_F32 || out_type == TYPE_F16) << "context_layer is f32 or f16";
     const int64_t hidden_size = static_cast<int64_t>(num_attention_heads) * head_size_;
     const int64_t qkv_width = hidden_size + 2LL * head_size_ * num_key_value_heads;
     CHATGLM_CHECK(qkv->ne[0] == qkv_width) << "qkv row is " << qkv->ne[0] << ", expected " << qkv_width;
@@ -221,14 +285,17 @@ Tensor *BasicAttention::forward(ModelContext *mctx, Tensor *qkv, Tensor * /*atte
     const int num_shared_q_heads = num_attention_heads / num_key_value_heads;
 
     cglm_attn_seq seq{};
-    const float *base = static_cast<const float *>(qkv->data);
-    const long long row = static_cast<long long>(qkv->nb[1] / sizeof(float));
+    // pointers are typed float in the descriptor; with CGLM_SEQ_QKV_F16 they address f16 values, strides in elements
+    const size_t esz = element_size(qkv->type);
+    const char *base = static_cast<const char *>(qkv->data);
+    auto at = [&](long long elems) { return reinterpret_cast<const float *>(base + elems * static_cast<long long>(esz)); };
+    const long long row = static_cast<long long>(qkv->nb[1] / esz);
     if (interleaved_qkv) {   // chatglm.cpp:636-644
         CHATGLM_CHECK(num_shared_q_heads == 1) << "interleaved qkv is not supported for GQA";
-        seq.q = base; seq.k = base + head_size_; seq.v = base + 2 * head_size_;
+        seq.q = at(0); seq.k = at(head_size_); seq.v = at(2 * head_size_);
         seq.q_head_stride = seq.kv_head_stride = 3 * head_size_;
     } else {                 // chatglm.cpp:646-652
-        seq.q = base; seq.k = base + hidden_size; seq.v = base + hidden_size + static_cast<long long>(head_size_) * num_key_value_heads;
+        seq.q = at(0); seq.k = at(hidden_size); seq.v = at(hidden_size + static_cast<long long>(head_size_) * num_key_value_heads);
         seq.q_head_stride = seq.kv_head_stride = head_size_;
     }
     seq.q_tok_stride = seq.kv_tok_stride = row;
@@ -236,17 +303,61 @@ Tensor *BasicAttention::forward(ModelContext *mctx, Tensor *qkv, Tensor * /*atte
     seq.qlen = qlen;
     seq.n_past = n_past;
     seq.n_ctx = n_ctx_;
+    seq.flags = (qkv->type == TYPE_F16 ? CGLM_SEQ_QKV_F16 : 0) | (out_type == TYPE_F16 ? CGLM_SEQ_OUT_F16 : 0);
     if (position_ids) {
         const int64_t want = rope_type == RopeType::CHATGLM ? 2 * qlen : qlen;
         CHATGLM_CHECK(position_ids->type == TYPE_I32 && position_ids->ne[0] == want)
             << "invalid position ids size " << position_ids->ne[0];
         seq.position_ids = static_cast<const int *>(position_ids->data);
     }
-    Tensor *context_layer = mctx->new_tensor_2d(TYPE_F32, hidden_size, qlen);   // [s, #h * d]
+    Tensor *context_layer = mctx->new_tensor_2d(out_type, hidden_size, qlen);   // [s, #h * d]
     seq.out = static_cast<float *>(context_layer->data);
     mctx->ensure_workspace(1, qlen);
     CHATGLM_CHECK_CGLM(cglm_attn_forward(mctx->arena_, &seq, 1, mctx->workspace_, mctx->workspace_bytes_, mctx->stream_));
     return context_layer;
+}
+
+Tensor *BasicAttention::forward(ModelContext *mctx, Tensor *hidden_states, Tensor *attention_mask, Tensor *position_ids,
+                                int n_past) const {
+    CHATGLM_CHECK(mctx && mctx->kv_allocated()) << "kv buffer not allocated";
+    CHATGLM_CHECK(hidden_states && hidden_states->data) << "null hidden_states";
+    const int64_t hidden_size = static_cast<int64_t>(num_attention_heads) * head_size_;
+    CHATGLM_CHECK(hidden_states->ne[0] == hidden_size) << "hidden_states row is " << hidden_states->ne[0] << ", expected " << hidden_size;
+    const int qlen = static_cast<int>(hidden_states->ne[1]);
+    Tensor *context_layer = nullptr;
+    // one decode token of a GLM-2/3/4 shaped module: bias, RoPE and the cache append ride in the GEMM's epilogue
+    const bool fused = qlen == 1 && !position_ids && !interleaved_qkv && head_size_ == 128 && hidden_size % 64 == 0 &&
+                       (rope_type == RopeType::CHATGLM2 || rope_type == RopeType::DISABLED) &&
+                       query_key_value.weight && query_key_value.weight->type == TYPE_F16;
+    if (fused) {
+        Tensor *x = as_f16(mctx, hidden_states);
+        Tensor *q_roped = mctx->new_tensor_2d(TYPE_F32, hidden_size, 1);
+        cglm_attn_seq seq{};
+        seq.slot = slot_;
+        seq.qlen = 1;
+        seq.n_past = n_past;
+        mctx->ensure_workspace(1, 1);
+        const int rc = cglm_qkv_linear_forward(
+            mctx->arena_, &seq, 1, x->data, static_cast<int>(hidden_size), query_key_value.weight->data,
+            query_key_value.bias ? static_cast<const float *>(query_key_value.bias->data) : nullptr,
+            static_cast<float *>(q_roped->data), mctx->workspace_, mctx->workspace_bytes_, mctx->stream_);
+        if (rc != CGLM_ERR_UNSUPPORTED) {   // an arena without the fused decode layout takes the general route below
+            CHATGLM_CHECK_CGLM(rc);
+            context_layer = mctx->new_tensor_2d(TYPE_F16, hidden_size, 1);
+            seq.q = seq.k = seq.v = static_cast<const float *>(q_roped->data);   // k and v are not read
+            seq.q_head_stride = seq.kv_head_stride = head_size_;
+            seq.q_tok_stride = seq.kv_tok_stride = hidden_size;
+            seq.kv_local = num_virtual_tokens + n_past + 1;
+            seq.flags = CGLM_SEQ_Q_ROPED | CGLM_SEQ_NO_APPEND | CGLM_SEQ_USE_KV_LOCAL | CGLM_SEQ_OUT_F16;
+            seq.out = static_cast<float *>(context_layer->data);
+            CHATGLM_CHECK_CGLM(cglm_attn_forward(mctx->arena_, &seq, 1, mctx->workspace_, mctx->workspace_bytes_, mctx->stream_));
+        }
+    }
+    if (!context_layer) {
+        Tensor *qkv = query_key_value.forward(mctx, hidden_states, TYPE_F16);                     // chatglm.cpp:629
+        context_layer = attend(mctx, qkv, attention_mask, position_ids, n_past, TYPE_F16);         // chatglm.cpp:631-717
+    }
+    return dense.forward(mctx, context_layer, TYPE_F32);                                          // chatglm.cpp:719
 }
 
 void BasicAttention::load_prefix_cache(ModelContext *mctx, const Tensor *past_kv) const {

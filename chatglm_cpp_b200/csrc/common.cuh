@@ -361,6 +361,10 @@ int qkv_linear_x_rows(int n_tok);
 int qkv_linear_k_blocks(int n_tok, int K);
 cudaError_t launch_qkv_linear(const LaunchCtx &cx, const CUtensorMap &x_map, const CUtensorMap &w_map, const int *slots,
                               const int *n_past, int n_tok, int K, int n_feat, int kb, const float *bias, float *q_out);
+// the same GEMM with a plain epilogue: out f32 / f16 [n_tok][n_feat] = x . W^T + bias, any number of tokens (x box rows
+// = qkv_linear_x_rows(min(n_tok, 128)), kb <= qkv_linear_k_blocks(min(n_tok, 128), K))
+cudaError_t launch_linear_plain(int device, cudaStream_t stream, WsHeader *hdr, const CUtensorMap &x_map, const CUtensorMap &w_map,
+                                int n_tok, int K, int n_feat, int kb, const float *bias, void *out, bool out_f16);
 int decode_max_ctas(int n_sm);
 constexpr int kDecodeMergeFan = 16;   // CTAs per group of the two-level merge
 constexpr int kDecodePartialFloats = 16 * 128 + 32;   // acc[16][128] | m[16] | l[16]

@@ -22,6 +22,12 @@
 // MMAs of a stage cost 0.03 us each: the number of TMA operations was the limiter, not the bytes in flight.  With kb
 // blocks per box: 17.3 / 18.2 / 23.1 us for 8 / 64 / 128 tokens (2.1 TB/s of weight stream at 64 tokens).  The first
 // round of the ring is filled with weights before the dependency wait; x follows after it.
+//
+// The same kernel with a plain epilogue (kPlain) is Linear::forward itself, y = x . W^T + bias written as f32 or f16
+// [token][feature]: the dense projection behind the attention path (chatglm.cpp:719, fed by the f16 context the
+// attention kernels store with CGLM_SEQ_OUT_F16) and the query_key_value projection of prompts and of shapes the fused
+// epilogue does not cover.  More than 128 tokens are a second grid dimension: every 128-token tile of a feature slice
+// streams that slice of the weight again, from L2 after the first.
 #include "common.cuh"
 
 namespace cglm {
@@ -81,15 +87,23 @@ struct QkvTable {
     int n_past[kTok];
 };
 
+// Where the plain epilogue stores: out f32 or f16 [n_tok][n_feat].
+struct PlainOut {
+    void *out;
+    int n_tok, n_feat, f16;
+};
+
+template <bool kPlain>
 __global__ void __launch_bounds__(kThreads, 1)
 qkv_linear_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constant__ CUtensorMap w_map,
                   const __grid_constant__ QkvTable tab, AttnShape sh, int K, int x_rows, int kb, int n_stages, const float *__restrict__ bias,
                   float *__restrict__ q_out, uint16_t *__restrict__ k_base, uint16_t *__restrict__ v_base,
-                  const float2 *__restrict__ rope_tab, int rope_tab_len, WsHeader *hdr) {
+                  const float2 *__restrict__ rope_tab, int rope_tab_len, WsHeader *hdr, PlainOut po) {
     extern __shared__ uint8_t smem_raw[];
     QkvSmem &sm = *reinterpret_cast<QkvSmem *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int f0 = blockIdx.x * kFeat;        // first output feature of this CTA
+    const int tok0 = kPlain ? static_cast<int>(blockIdx.y) * kTok : 0;   // first token of this CTA's tile
     const int n_k = K / (kKStep * kb);                       // stages of kb 64-k blocks each
     const int x_tile = x_rows * 128, x_bytes = kb * x_tile;   // kb x tiles, then kb W tiles
     const int stage_bytes = x_bytes + kb * kWBytes;
@@ -129,13 +143,13 @@ qkv_linear_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_consta
             asm volatile("griddepcontrol.wait;" ::: "memory");
             asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
             // rows of x past n_tok are outside the tensor map and arrive as zeros: the box is x_rows tokens
-            for (int i = 0; i < pre; ++i) tma_load_3d(sm.ring + i * stage_bytes, &x_map, 0, 0, ((i + k_first) % n_k) * kb, &sm.full[i]);
+            for (int i = 0; i < pre; ++i) tma_load_3d(sm.ring + i * stage_bytes, &x_map, 0, tok0, ((i + k_first) % n_k) * kb, &sm.full[i]);
             for (int i = pre, st = 0, round = 1; i < n_k; ++i) {
                 if (!mbar_wait_bounded(&sm.empty[st], (round - 1) & 1u, &sm.abort_flag)) break;
                 uint8_t *stage = sm.ring + st * stage_bytes;
                 mbar_arrive_expect_tx(&sm.full[st], stage_bytes);
                 const int kk = (i + k_first) % n_k;
-                tma_load_3d(stage, &x_map, 0, 0, kk * kb, &sm.full[st]);
+                tma_load_3d(stage, &x_map, 0, tok0, kk * kb, &sm.full[st]);
                 tma_load_3d(stage + x_bytes, &w_map, 0, f0, kk * kb, &sm.full[st]);
                 if (++st == n_stages) { st = 0; ++round; }
             }
@@ -181,7 +195,28 @@ qkv_linear_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_consta
 #pragma unroll
             for (int i = 0; i < kFeat; ++i) acc[i] = __uint_as_float(r[i]);
         }
-        if (ok && tok < tab.n_tok) {
+        if constexpr (kPlain) {
+            const int row = tok0 + tok;
+            if (ok && row < po.n_tok) {
+                if (bias) {
+#pragma unroll
+                    for (int i = 0; i < kFeat; ++i) acc[i] = __fadd_rn(acc[i], __ldg(bias + f0 + i));
+                }
+                const long long at = static_cast<long long>(row) * po.n_feat + f0;
+                if (po.f16) {
+                    uint4 *dst = reinterpret_cast<uint4 *>(static_cast<uint16_t *>(po.out) + at);
+#pragma unroll
+                    for (int i = 0; i < kFeat / 8; ++i) {
+                        dst[i] = make_uint4(pack_half2(acc[8 * i], acc[8 * i + 1]), pack_half2(acc[8 * i + 2], acc[8 * i + 3]),
+                                            pack_half2(acc[8 * i + 4], acc[8 * i + 5]), pack_half2(acc[8 * i + 6], acc[8 * i + 7]));
+                    }
+                } else {
+                    float4 *dst = reinterpret_cast<float4 *>(static_cast<float *>(po.out) + at);
+#pragma unroll
+                    for (int i = 0; i < kFeat / 4; ++i) dst[i] = make_float4(acc[4 * i], acc[4 * i + 1], acc[4 * i + 2], acc[4 * i + 3]);
+                }
+            }
+        } else if (ok && tok < tab.n_tok) {
             const int H = sh.H, G = sh.G, D = sh.D;
             if (bias) {
 #pragma unroll
@@ -252,23 +287,32 @@ int qkv_linear_k_blocks(int n_tok, int K) {
     return 1;
 }
 
+namespace {
+
+cudaError_t configure_once(int device) {
+    static PerDeviceOnce configured;
+    if (!configured.needed(device)) return cudaSuccess;
+    cudaError_t e = require_current_device(device);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(qkv_linear_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemPerCta);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(qkv_linear_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemPerCta);
+    if (e == cudaSuccess) configured.mark(device);
+    return e;
+}
+
+}  // namespace
+
 // x_map: f16 {64, n_tok, K/64}, box {64, qkv_linear_x_rows(n_tok), kb}; w_map: f16 {64, n_feat, K/64}, box {64, 32, kb};
 // both 128-byte swizzled.
 cudaError_t launch_qkv_linear(const LaunchCtx &cx, const CUtensorMap &x_map, const CUtensorMap &w_map, const int *slots,
                               const int *n_past, int n_tok, int K, int n_feat, int kb, const float *bias, float *q_out) {
-    static PerDeviceOnce configured;
     const int x_rows = qkv_linear_x_rows(n_tok), stage_bytes = kb * (x_rows * 128 + kWBytes);
     int n_stages = ring_stages(x_rows, kb);
     if (n_stages < 1) return cudaErrorInvalidValue;
     n_stages = n_stages > kMaxStages ? kMaxStages : n_stages;
     const int smem_bytes = 2048 + n_stages * stage_bytes + read_over_slack(x_rows, kb);
     static_assert(offsetof(QkvSmem, ring) == 1024, "header, then the ring");
-    if (configured.needed(cx.device)) {
-        cudaError_t e = require_current_device(cx.device);
-        if (e == cudaSuccess) e = cudaFuncSetAttribute(qkv_linear_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemPerCta);
-        if (e != cudaSuccess) return e;
-        configured.mark(cx.device);
-    }
+    cudaError_t e = configure_once(cx.device);
+    if (e != cudaSuccess) return e;
     static thread_local QkvTable tab;
     tab.n_tok = n_tok;
     for (int i = 0; i < n_tok; ++i) { tab.slot[i] = slots[i]; tab.n_past[i] = n_past[i]; }
@@ -282,8 +326,40 @@ cudaError_t launch_qkv_linear(const LaunchCtx &cx, const CUtensorMap &x_map, con
     cfg.stream = cx.stream;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, qkv_linear_kernel, x_map, w_map, tab, cx.shape, K, x_rows, kb, n_stages, bias, q_out, cx.k_base, cx.v_base,
-                                       cx.rope_tab, cx.rope_tab_len, cx.hdr);
+    e = cudaLaunchKernelEx(&cfg, qkv_linear_kernel<false>, x_map, w_map, tab, cx.shape, K, x_rows, kb, n_stages, bias, q_out, cx.k_base,
+                           cx.v_base, cx.rope_tab, cx.rope_tab_len, cx.hdr, PlainOut{});
+    g_launch_count += 1;
+    return e != cudaSuccess ? e : cudaGetLastError();
+}
+
+// Plain Linear: out f32 / f16 [n_tok][n_feat] = x . W^T + bias.  x_map: f16 {64, n_tok, K/64} with box
+// {64, qkv_linear_x_rows(min(n_tok, 128)), kb}; w_map as above.  n_feat a multiple of 32, K of 64 * kb.
+cudaError_t launch_linear_plain(int device, cudaStream_t stream, WsHeader *hdr, const CUtensorMap &x_map, const CUtensorMap &w_map,
+                                int n_tok, int K, int n_feat, int kb, const float *bias, void *out, bool out_f16) {
+    const int x_rows = qkv_linear_x_rows(n_tok < kTok ? n_tok : kTok), stage_bytes = kb * (x_rows * 128 + kWBytes);
+    int n_stages = ring_stages(x_rows, kb);
+    if (n_stages < 1) return cudaErrorInvalidValue;
+    n_stages = n_stages > kMaxStages ? kMaxStages : n_stages;
+    const int smem_bytes = 2048 + n_stages * stage_bytes + read_over_slack(x_rows, kb);
+    cudaError_t e = configure_once(device);
+    if (e != cudaSuccess) return e;
+    static thread_local QkvTable tab;   // the plain epilogue reads none of it
+    tab.n_tok = 0;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(n_feat / kFeat, (n_tok + kTok - 1) / kTok);
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = smem_bytes;
+    cfg.stream = stream;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    PlainOut po;
+    po.out = out; po.n_tok = n_tok; po.n_feat = n_feat; po.f16 = out_f16 ? 1 : 0;
+    e = cudaLaunchKernelEx(&cfg, qkv_linear_kernel<true>, x_map, w_map, tab, AttnShape{}, K, x_rows, kb, n_stages, bias,
+                           static_cast<float *>(nullptr), static_cast<uint16_t *>(nullptr), static_cast<uint16_t *>(nullptr),
+                           static_cast<const float2 *>(nullptr), 0, hdr, po);
     g_launch_count += 1;
     return e != cudaSuccess ? e : cudaGetLastError();
 }

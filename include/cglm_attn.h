@@ -196,6 +196,23 @@ int cglm_attn_forward(cglm_kv_arena *arena, const cglm_attn_seq *seqs, int n_seq
 int cglm_qkv_linear_forward(cglm_kv_arena *arena, const cglm_attn_seq *seqs, int n_seq, const void *x_f16, int hidden,
                             const void *weight_f16, const float *bias, float *q_roped, void *workspace,
                             size_t workspace_bytes, void *cuda_stream);
+/*
+ * Linear::forward (chatglm.cpp:418-426) on its own: out = x . weight^T + bias, the same tcgen05 GEMM with a plain
+ * epilogue.  It is the dense projection behind the attention path (chatglm.cpp:719), fed by the f16 context_layer that
+ * the attention kernels store with CGLM_SEQ_OUT_F16, and the query_key_value projection (chatglm.cpp:629) of prompts and
+ * of shapes that cglm_qkv_linear_forward does not cover.
+ *   x_f16 f16 [n_tok][in_features], weight_f16 f16 [out_features][in_features] as the model file stores it, bias f32
+ *   [out_features] or NULL, out f32 (out_is_f16 == 0) or f16 [n_tok][out_features]; all on the device, x, weight and
+ *   out 16-byte aligned; in_features a multiple of 64, out_features of 32 (else CGLM_ERR_UNSUPPORTED); any n_tok > 0.
+ * f32 accumulation; the f32 result is rounded to nearest even when out is f16.  Runs on the current device.
+ * workspace: any initialised workspace (only its status word is used).  Asynchronous on cuda_stream.
+ */
+int cglm_linear_forward(const void *x_f16, int n_tok, int in_features, const void *weight_f16, int out_features,
+                        const float *bias, void *out, int out_is_f16, void *workspace, size_t workspace_bytes,
+                        void *cuda_stream);
+/* dst_f16[i] = f16(src[i]), round to nearest even, for i in [0, n): the cast ggml applies to an f32 activation in front
+ * of an f16 matrix (device pointers; asynchronous on cuda_stream). */
+int cglm_convert_f32_to_f16(const float *src, void *dst_f16, size_t n, void *cuda_stream);
 /* n_past_dev[i] += delta for i in [0, n): the last node of a captured decode step (see CGLM_SEQ_N_PAST_DEVICE). */
 int cglm_seq_advance(int *n_past_dev, int n, int delta, void *cuda_stream);
 

@@ -8,8 +8,11 @@
 //                                                           (ctx_kv / buf_kv / backend of chatglm.h:331-348)
 //   - chatglm::Tensor                                       ne[]/nb[] shaped device tensor (ggml_tensor stand-in; ggml
 //                                                           itself is not a dependency)
+//   - chatglm::Linear                                       same constructor arguments, members and forward
+//                                                           (chatglm.h:362-377), f16 weights
 //   - chatglm::BasicAttention                               same constructor arguments, public members and forward
-//                                                           argument list (chatglm.h:440-472)
+//                                                           (chatglm.h:440-472); attend() is the part between its
+//                                                           two Linears for callers that keep them
 //   - CHATGLM_CHECK / CHATGLM_THROW                         std::runtime_error("file:line message") (chatglm.h:16-29)
 // Everything below executes through the C ABI of cglm_attn.h; there is no CPU path.
 #pragma once
@@ -94,6 +97,10 @@ class ModelContext {
     void alloc_kv();
     bool kv_allocated() const { return arena_ != nullptr; }
 
+    // parameter tensors (the reference's ctx_w): device memory, zero-filled, alive as long as the context
+    Tensor *new_weight_1d(TensorType type, int64_t ne0);
+    Tensor *new_weight_2d(TensorType type, int64_t ne0, int64_t ne1);
+
     // per-step device tensors (the reference's ctx_b scratch context); freed by reset_scratch()
     Tensor *new_tensor_1d(TensorType type, int64_t ne0);
     Tensor *new_tensor_2d(TensorType type, int64_t ne0, int64_t ne1);
@@ -110,9 +117,11 @@ class ModelContext {
   private:
     friend class BasicAttention;
     friend class DecodeStep;
+    friend class Linear;
     // creates the (still unallocated) cache tensors of one attention module and returns its arena slot
     int register_attention(const cglm_attn_desc &desc, Tensor **k_cache, Tensor **v_cache);
     void ensure_workspace(int n_seq, int max_qlen);
+    void ensure_status_workspace();   // at least the status word, for kernels that need nothing else
 
     void *stream_;
     cglm_kv_arena *arena_ = nullptr;
@@ -120,6 +129,7 @@ class ModelContext {
     bool have_desc_ = false;
     std::vector<std::unique_ptr<Tensor>> kv_tensors_;
     std::vector<std::unique_ptr<Tensor>> scratch_;
+    std::vector<std::unique_ptr<Tensor>> weights_;
     void *workspace_ = nullptr;
     size_t workspace_bytes_ = 0;
 };
@@ -130,25 +140,61 @@ std::vector<int> make_position_ids_glm2(int qlen, int n_past);
 // position ids of ChatGLM-6B v1: [min(p, n_ctx-2)] ++ [max(p-(n_ctx-2), 0)], p = n_past+i
 std::vector<int> make_position_ids_glm(int qlen, int n_past, int n_ctx);
 
+// ---- Linear (chatglm.h:362-377, chatglm.cpp:418-426) --------------------------------------------------------------
+// weight f16 [out_features, in_features] (ne = {in, out}) and bias f32 [out_features], both on the device and zero
+// until loaded (mctx->tensor_set).  forward is a tcgen05 GEMM with f32 accumulation (cglm_linear_forward);
+// in_features must be a multiple of 64 and out_features of 32.
+class Linear {
+  public:
+    Linear() = default;
+    Linear(ModelContext *mctx, int in_features, int out_features, bool use_bias = true);
+
+    int in_features() const { return weight ? static_cast<int>(weight->ne[0]) : 0; }
+    int out_features() const { return weight ? static_cast<int>(weight->ne[1]) : 0; }
+
+    // input f32 or f16 [seqlen, in_features] on the device (an f32 input is rounded to f16 first, as ggml does in
+    // front of an f16 matrix); returns [seqlen, out_features] from mctx's scratch, f32 like the reference's, or f16
+    // when the consumer takes half precision.  Enqueued on mctx's stream.
+    Tensor *forward(ModelContext *mctx, Tensor *input, TensorType out_type = TYPE_F32) const;
+
+  public:
+    Tensor *weight = nullptr;   // [out_features, in_features]
+    Tensor *bias = nullptr;     // [out_features]
+};
+
 // ---- the attention module (chatglm.h:440-472) ---------------------------------------------------------------
 class BasicAttention {
   public:
     BasicAttention() = default;
-    // Same arguments as the reference.  use_qkv_bias / use_dense_bias configure the two Linears, which stay
-    // with the caller; they are accepted and ignored here.  The caches exist once mctx->alloc_kv() ran.
+    // Same arguments as the reference.  The caches exist once mctx->alloc_kv() ran; the two Linears' parameters are
+    // allocated (zero) right away.
     BasicAttention(ModelContext *mctx, int hidden_size, int num_attention_heads, int num_key_value_heads,
                    int max_length, bool use_qkv_bias, bool use_dense_bias, bool interleaved_qkv, RopeType rope_type,
                    float rope_theta, AttentionMaskType attn_mask_type, int num_virtual_tokens);
 
-    // Everything BasicAttention::forward does between query_key_value.forward (chatglm.cpp:629) and dense.forward
-    // (chatglm.cpp:719).
-    //   qkv            f32 [qlen, (#h + 2 * #kvh) * d]: ne = {(#h + 2#kvh) * d, qlen}
+    // The reference's call (chatglm.h:457-458, chatglm.cpp:625-722): query_key_value, RoPE, cache append, attention,
+    // dense.
+    //   hidden_states  f32 or f16 [qlen, hidden] on the device
+    //   attention_mask, position_ids, n_past as for attend()
+    // Returns attn_output f32 [qlen, hidden] from mctx's scratch.  One decode token of a GLM-2/3/4 shaped module
+    // (head size 128, blocked qkv, no explicit position ids) takes three launches: the query_key_value GEMM with bias,
+    // RoPE and append in its epilogue, the decode kernel, the dense GEMM; the activations between them are roped q
+    // (f32) and the f16 context.  Everything else runs query_key_value as a plain GEMM with an f16 result, the
+    // attention kernels on f16 input and output, and dense.
+    Tensor *forward(ModelContext *mctx, Tensor *hidden_states, Tensor *attention_mask, Tensor *position_ids,
+                    int n_past) const;
+
+    // Everything forward does between query_key_value.forward (chatglm.cpp:629) and dense.forward (chatglm.cpp:719),
+    // for callers that keep the two Linears.
+    //   qkv            f32 or f16 [qlen, (#h + 2 * #kvh) * d]: ne = {(#h + 2#kvh) * d, qlen}
     //   attention_mask accepted for signature parity; the v1 mask it would carry (chatglm.cpp:1126-1140) is applied
     //                  from attn_mask_type, so the tensor may be null
     //   position_ids   i32 [qlen] (or [2 * qlen] for RopeType::CHATGLM) on the device; null derives them from
     //                  n_past (and n_ctx, see set_n_ctx)
-    // Returns context_layer f32 [qlen, hidden] allocated from mctx's scratch.  Enqueued on mctx's stream.
-    Tensor *forward(ModelContext *mctx, Tensor *qkv, Tensor *attention_mask, Tensor *position_ids, int n_past) const;
+    // Returns context_layer [qlen, hidden] (f32, or f16 on request) allocated from mctx's scratch.  Enqueued on mctx's
+    // stream.
+    Tensor *attend(ModelContext *mctx, Tensor *qkv, Tensor *attention_mask, Tensor *position_ids, int n_past,
+                   TensorType out_type = TYPE_F32) const;
 
     // prompt length of the running generation; only RopeType::CHATGLM with null position_ids reads it
     void set_n_ctx(int n_ctx) { n_ctx_ = n_ctx; }
@@ -165,6 +211,8 @@ class BasicAttention {
     float rope_theta = 10000.f;
     AttentionMaskType attn_mask_type = AttentionMaskType::CAUSAL;
     int num_virtual_tokens = 0;
+    Linear query_key_value;
+    Linear dense;
     Tensor *k_cache = nullptr;   // [#kvh, s, d]
     Tensor *v_cache = nullptr;   // [#kvh, d, s]
 

@@ -68,7 +68,7 @@ static void run_case(const Case &c) {
             ids_t = mctx.new_tensor_1d(TYPE_I32, static_cast<int64_t>(ids.size()));
             mctx.tensor_set(ids_t, ids.data(), 0, ids.size() * sizeof(int));
         }
-        Tensor *ctx = attn.forward(&mctx, qkv_t, nullptr, ids_t, n_past);
+        Tensor *ctx = attn.attend(&mctx, qkv_t, nullptr, ids_t, n_past);
         EXPECT(ctx->ne[0] == c.hidden && ctx->ne[1] == qlen, "context_layer shape");
         std::vector<float> got(static_cast<size_t>(qlen) * c.hidden);
         mctx.tensor_get(ctx, got.data(), 0, got.size() * sizeof(float));
@@ -113,16 +113,16 @@ static void run_error_cases() {
     Tensor bogus;
     bool threw = false;
     try {
-        attn.forward(&mctx, &bogus, nullptr, nullptr, 0);   // kv buffer not allocated yet
+        attn.attend(&mctx, &bogus, nullptr, nullptr, 0);   // kv buffer not allocated yet
     } catch (const std::runtime_error &e) {
         threw = std::strstr(e.what(), "chatglm_b200.cu") != nullptr;   // "file:line message", like CHATGLM_CHECK
     }
-    EXPECT(threw, "forward before alloc_kv must throw std::runtime_error with file:line");
+    EXPECT(threw, "attend before alloc_kv must throw std::runtime_error with file:line");
     mctx.alloc_kv();
     Tensor *bad = mctx.new_tensor_2d(TYPE_F32, 100, 1);   // wrong row width
     threw = false;
     try {
-        attn.forward(&mctx, bad, nullptr, nullptr, 0);
+        attn.attend(&mctx, bad, nullptr, nullptr, 0);
     } catch (const std::runtime_error &) {
         threw = true;
     }
@@ -130,7 +130,7 @@ static void run_error_cases() {
     Tensor *qkv = mctx.new_tensor_2d(TYPE_F32, 4096 + 2 * 128 * 2, 1);
     threw = false;
     try {
-        attn.forward(&mctx, qkv, nullptr, nullptr, 256);   // n_past + qlen beyond max_length
+        attn.attend(&mctx, qkv, nullptr, nullptr, 256);   // n_past + qlen beyond max_length
     } catch (const std::runtime_error &e) {
         threw = std::strstr(e.what(), "invalid argument") != nullptr;
     }
@@ -161,7 +161,7 @@ static void run_decode_step_case() {
         for (auto &x : qkv) x = dist(rng);
         Tensor *t = mctx.new_tensor_2d(TYPE_F32, width, start);
         mctx.tensor_set(t, qkv.data(), 0, qkv.size() * sizeof(float));
-        layers[l].forward(&mctx, t, nullptr, nullptr, 0);
+        layers[l].attend(&mctx, t, nullptr, nullptr, 0);
         std::vector<int> ids = make_position_ids_glm2(start, 0);
         oracle_attn_forward(&cfg, qkv.data(), width, D, qkv.data() + hidden, qkv.data() + hidden + G * D, width, D, kc[l].data(),
                             vc[l].data(), ids.data(), nullptr, start, 0, want.data(), nullptr, nullptr);
@@ -210,6 +210,101 @@ static void run_decode_step_case() {
     std::printf("case %-28s max abs err %.3g, %d graph launches\n", "decode step graph", worst, step.graph_launches());
 }
 
+// BasicAttention::forward as the reference calls it (chatglm.h:457-458): hidden_states in, attn_output out, the two
+// Linears inside.  Checked against the oracle's Linear -> attention -> Linear with the same f16 roundings between the
+// stages (f16 activations into both GEMMs, f16 cache rows).  The GEMMs sum in another order than the oracle, so an
+// appended cache value may be the neighbouring f16 value and the output carries that: max abs 6e-3 on outputs of unit
+// scale.
+struct FullCase {
+    const char *name;
+    int hidden, n_head, n_kv_head, max_length;
+    bool interleaved, qkv_bias, dense_bias;
+    RopeType rope;
+    AttentionMaskType mask;
+    int prompt;
+};
+
+static void run_full_forward_case(const FullCase &c) {
+    const int H = c.n_head, G = c.n_kv_head, D = c.hidden / c.n_head, M = c.max_length;
+    const int width = c.hidden + 2 * D * G;
+    ModelContext mctx(nullptr);
+    BasicAttention attn(&mctx, c.hidden, H, G, c.max_length, c.qkv_bias, c.dense_bias, c.interleaved, c.rope, 10000.f, c.mask, 0);
+    mctx.alloc_kv();
+    attn.set_n_ctx(c.prompt);
+    EXPECT(attn.query_key_value.in_features() == c.hidden && attn.query_key_value.out_features() == width, "qkv Linear shape");
+    EXPECT(attn.dense.in_features() == c.hidden && attn.dense.out_features() == c.hidden, "dense Linear shape");
+    EXPECT((attn.query_key_value.bias != nullptr) == c.qkv_bias && (attn.dense.bias != nullptr) == c.dense_bias, "bias presence");
+
+    std::mt19937 rng(4321);
+    std::normal_distribution<float> dist(0.f, 1.f);
+    const float w_scale = 1.f / std::sqrt(static_cast<float>(c.hidden));
+    std::vector<uint16_t> w_qkv(static_cast<size_t>(width) * c.hidden), w_dense(static_cast<size_t>(c.hidden) * c.hidden);
+    for (auto &w : w_qkv) w = oracle_f32_to_f16(dist(rng) * w_scale);
+    for (auto &w : w_dense) w = oracle_f32_to_f16(dist(rng) * w_scale);
+    std::vector<float> b_qkv(width), b_dense(c.hidden);
+    for (auto &b : b_qkv) b = dist(rng);
+    for (auto &b : b_dense) b = dist(rng);
+    mctx.tensor_set(attn.query_key_value.weight, w_qkv.data(), 0, w_qkv.size() * 2);
+    mctx.tensor_set(attn.dense.weight, w_dense.data(), 0, w_dense.size() * 2);
+    if (c.qkv_bias) mctx.tensor_set(attn.query_key_value.bias, b_qkv.data(), 0, b_qkv.size() * 4);
+    if (c.dense_bias) mctx.tensor_set(attn.dense.bias, b_dense.data(), 0, b_dense.size() * 4);
+
+    oracle_cfg cfg = {H, G, D, M, 0, static_cast<int>(c.rope), 10000.f,
+                      c.mask == AttentionMaskType::CAUSAL ? ORACLE_MASK_CAUSAL : ORACLE_MASK_CHATGLM, oracle_numerics_f32()};
+    std::vector<uint16_t> kc(static_cast<size_t>(G) * M * D, 0), vc(kc.size(), 0);
+    int n_past = 0;
+    float worst = 0.f;
+    auto round_f16 = [](std::vector<float> &v) { for (auto &x : v) x = oracle_f16_to_f32(oracle_f32_to_f16(x)); };
+    for (int qlen : {c.prompt, 1, 1}) {
+        std::vector<float> x(static_cast<size_t>(qlen) * c.hidden);
+        for (auto &e : x) e = dist(rng);
+        Tensor *x_t = mctx.new_tensor_2d(TYPE_F32, c.hidden, qlen);
+        mctx.tensor_set(x_t, x.data(), 0, x.size() * sizeof(float));
+        Tensor *out_t = attn.forward(&mctx, x_t, nullptr, nullptr, n_past);
+        EXPECT(out_t->type == TYPE_F32 && out_t->ne[0] == c.hidden && out_t->ne[1] == qlen, "attn_output shape");
+        std::vector<float> got(static_cast<size_t>(qlen) * c.hidden);
+        mctx.tensor_get(out_t, got.data(), 0, got.size() * sizeof(float));
+        mctx.synchronize();
+
+        std::vector<float> qkv(static_cast<size_t>(qlen) * width), ctx(static_cast<size_t>(qlen) * c.hidden), want(got.size()), mask;
+        oracle_linear(x.data(), qlen, c.hidden, w_qkv.data(), 1, c.qkv_bias ? b_qkv.data() : nullptr, width, 1, qkv.data());
+        round_f16(qkv);
+        const float *q = qkv.data(), *k, *v;
+        long hs;
+        if (c.interleaved) { k = q + D; v = q + 2 * D; hs = 3 * D; } else { k = q + c.hidden; v = q + c.hidden + G * D; hs = D; }
+        std::vector<int> ids = c.rope == RopeType::CHATGLM ? make_position_ids_glm(qlen, n_past, c.prompt) : make_position_ids_glm2(qlen, n_past);
+        if (n_past == 0 && c.mask == AttentionMaskType::CHATGLM) {
+            mask.resize(static_cast<size_t>(qlen) * qlen);
+            oracle_attention_mask_glm(qlen, qlen, mask.data());
+        }
+        int rc = oracle_attn_forward(&cfg, q, width, hs, k, v, width, hs, kc.data(), vc.data(), ids.data(),
+                                     mask.empty() ? nullptr : mask.data(), qlen, n_past, ctx.data(), nullptr, nullptr);
+        EXPECT(rc == 0, "oracle rejected the arguments");
+        oracle_linear(ctx.data(), qlen, c.hidden, w_dense.data(), 1, c.dense_bias ? b_dense.data() : nullptr, c.hidden, 1, want.data());
+        for (size_t i = 0; i < got.size(); i++) {
+            EXPECT(std::isfinite(got[i]), "non-finite output");
+            worst = std::fmax(worst, std::fabs(got[i] - want[i]));
+        }
+        n_past += qlen;
+        mctx.reset_scratch();
+    }
+    EXPECT(worst <= 6e-3f, "%s: max abs error %g", c.name, worst);
+    // caches: the same f16 values up to a neighbouring one where the GEMM's sum fell on the other side of a tie
+    std::vector<uint16_t> gk(kc.size()), gv(vc.size());
+    mctx.tensor_get(attn.k_cache, gk.data(), 0, gk.size() * 2);
+    mctx.tensor_get(attn.v_cache, gv.data(), 0, gv.size() * 2);
+    float cache_worst = 0.f;
+    size_t differing = 0;
+    for (size_t i = 0; i < kc.size(); i++) {
+        cache_worst = std::fmax(cache_worst, std::fabs(oracle_f16_to_f32(gk[i]) - oracle_f16_to_f32(kc[i])));
+        cache_worst = std::fmax(cache_worst, std::fabs(oracle_f16_to_f32(gv[i]) - oracle_f16_to_f32(vc[i])));
+        differing += (gk[i] != kc[i]) + (gv[i] != vc[i]);
+    }
+    EXPECT(cache_worst <= 8e-3f, "%s: cache value off by %g", c.name, cache_worst);
+    EXPECT(differing <= static_cast<size_t>(0.04 * 2 * G * D * n_past) + 4, "%s: %zu cache values differ", c.name, differing);
+    std::printf("case %-28s max abs err %.3g (caches: %zu values on a neighbouring f16)\n", c.name, worst, differing);
+}
+
 int main() {
     const Case cases[] = {
         {"glm3 gqa d128 blocked", 4096, 32, 2, 512, 0, false, RopeType::CHATGLM2, AttentionMaskType::CAUSAL, 5, false},
@@ -224,6 +319,15 @@ int main() {
         for (const Case &c : cases) run_case(c);
         run_error_cases();
         run_decode_step_case();
+        const FullCase full[] = {
+            // fused decode route after a tensor-core prefill
+            {"forward glm3 gqa d128", 4096, 32, 2, 512, false, true, false, RopeType::CHATGLM2, AttentionMaskType::CAUSAL, 130},
+            // general route: interleaved qkv, 2-D rotary, both biases
+            {"forward glm1 mha interleaved", 1024, 8, 8, 256, true, true, true, RopeType::CHATGLM, AttentionMaskType::CHATGLM, 7},
+            // head size 64: generic attention kernels behind the same GEMMs
+            {"forward d64 neox", 512, 8, 8, 128, false, false, true, RopeType::NEOX, AttentionMaskType::CAUSAL, 5},
+        };
+        for (const FullCase &c : full) run_full_forward_case(c);
     } catch (const std::exception &e) {
         std::printf("FAIL unexpected exception: %s\n", e.what());
         return 1;

@@ -780,6 +780,66 @@ def test_fused_qkv_linear_feeds_the_decode_kernel(n_seq, rope):
     arena.close()
 
 
+@pytest.mark.parametrize("n_tok,n_in,n_out,use_bias,out_f16", [
+    (1, 4096, 4096, True, False),       # dense of one decode token (chatglm.cpp:719)
+    (64, 4096, 4096, False, True),
+    (128, 256, 96, True, False),
+    (200, 512, 160, True, True),        # two token tiles, the second ragged
+    (300, 1024, 4608, True, True),      # query_key_value of a prompt
+])
+def test_linear_forward_matches_oracle(n_tok, n_in, n_out, use_bias, out_f16):
+    """cglm_linear_forward (Linear::forward, chatglm.cpp:418-426, as a tcgen05 GEMM with f16 operands and f32 sums)
+    against the oracle's Linear, which the reference's linear.data pins.  Tolerance: the two sum the same f32 products
+    in another order (2e-4 on outputs of unit variance); an f16 output adds half an f16 ulp (2e-3 at |y| < 4)."""
+    from chatglm_cpp_b200 import _lib
+    A = _A()
+    L = _lib.lib()
+    rng = np.random.default_rng(n_tok * 7 + n_out)
+    x = rng.standard_normal((n_tok, n_in)).astype(np.float16)
+    w = (rng.standard_normal((n_out, n_in)) / np.sqrt(n_in)).astype(np.float16)
+    bias = rng.standard_normal(n_out).astype(np.float32) if use_bias else None
+    x_d, w_d = torch.from_numpy(x).cuda(), torch.from_numpy(w).cuda()
+    b_d = torch.from_numpy(bias).cuda() if use_bias else None
+    # guard rows either side: the kernel must not write outside [n_tok][n_out]
+    buf = torch.full((n_tok + 2, n_out), 7.0, device="cuda", dtype=torch.float16 if out_f16 else torch.float32)
+    ws = A.Workspace(make_desc(32, 2, 128, 1024), 1, 1)
+    stream = torch.cuda.current_stream().cuda_stream
+    before = L.cglm_launch_count()
+    rc = L.cglm_linear_forward(x_d.data_ptr(), n_tok, n_in, w_d.data_ptr(), n_out, b_d.data_ptr() if use_bias else None,
+                               buf[1:].data_ptr(), int(out_f16), ws.ptr, ws.bytes, stream)
+    assert rc == 0, L.cglm_last_error_string()
+    torch.cuda.synchronize()
+    assert ws.status() == 0
+    assert L.cglm_launch_count() - before == 1
+    want = O.linear(x.astype(np.float32), w, bias)
+    got = buf[1:n_tok + 1].float().cpu().numpy()
+    tol = 2e-4 + (2e-3 * np.maximum(1.0, np.abs(want) / 4) if out_f16 else 0.0)
+    assert (np.abs(got - want) <= tol).all(), float(np.abs(got - want).max())
+    assert (buf[0] == 7).all() and (buf[n_tok + 1] == 7).all()
+    # refused, not served by another path
+    assert L.cglm_linear_forward(x_d.data_ptr(), n_tok, n_in - 32, w_d.data_ptr(), n_out, None, buf[1:].data_ptr(),
+                                 int(out_f16), ws.ptr, ws.bytes, stream) == _lib.ERR_UNSUPPORTED
+    assert L.cglm_linear_forward(x_d.data_ptr(), n_tok, n_in, w_d.data_ptr(), n_out - 8, None, buf[1:].data_ptr(),
+                                 int(out_f16), ws.ptr, ws.bytes, stream) == _lib.ERR_UNSUPPORTED
+
+
+def test_convert_f32_to_f16_rounds_like_numpy():
+    """cglm_convert_f32_to_f16 (the cast in front of an f16 Linear) against numpy's round-to-nearest-even cast, on a
+    length that is not a multiple of 4 and at an address that is not 16-byte aligned."""
+    from chatglm_cpp_b200 import _lib
+    L = _lib.lib()
+    rng = np.random.default_rng(77)
+    x = np.concatenate([rng.standard_normal(5001).astype(np.float32) * 50,
+                        np.array([0.0, -0.0, 65504.0, 1e-8, 6.1e-5, 1.00048828125], np.float32)])
+    src = torch.from_numpy(np.concatenate([[0.0], x]).astype(np.float32)).cuda()
+    dst = torch.zeros(x.size + 1, device="cuda", dtype=torch.float16)
+    stream = torch.cuda.current_stream().cuda_stream
+    assert L.cglm_convert_f32_to_f16(src[1:].data_ptr(), dst[1:].data_ptr(), x.size, stream) == 0
+    torch.cuda.synchronize()
+    np.testing.assert_array_equal(dst[1:].cpu().numpy().view(np.uint16), x.astype(np.float16).view(np.uint16))
+    assert dst[0] == 0
+
+
 def test_decode_with_settled_caches_streams_early_and_gives_the_same_bits():
     """CGLM_SEQ_CACHE_SETTLED lets a launch read cache tiles while the previous launch of the stream drains.  Eight
     layer calls back to back, each on its own slots, with and without the flag: same output bits, same caches, and
