@@ -107,7 +107,7 @@ void ModelContext::ensure_workspace(int n_seq, int max_qlen) {
 
 void ModelContext::ensure_status_workspace() {
     if (workspace_) return;
-    const size_t bytes = 4096;
+    const size_t bytes = cglm_linear_workspace_bytes();
     CHATGLM_CHECK_CUDA(cudaMalloc(&workspace_, bytes));
     workspace_bytes_ = bytes;
     CHATGLM_CHECK_CGLM(cglm_attn_workspace_init(workspace_, workspace_bytes_, stream_));

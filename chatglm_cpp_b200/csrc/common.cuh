@@ -365,6 +365,17 @@ cudaError_t launch_qkv_linear(const LaunchCtx &cx, const CUtensorMap &x_map, con
 // = qkv_linear_x_rows(min(n_tok, 128)), kb <= qkv_linear_k_blocks(min(n_tok, 128), K))
 cudaError_t launch_linear_plain(int device, cudaStream_t stream, WsHeader *hdr, const CUtensorMap &x_map, const CUtensorMap &w_map,
                                 int n_tok, int K, int n_feat, int kb, const float *bias, void *out, bool out_f16);
+// The Linear with the output features on the M side of the MMA (n_feat a multiple of 128): k split over several CTAs per
+// 128-feature tile, partial sums through `scratch` (kLinearScratchBytes at most), counters in WsHeader::reserved.
+constexpr int kLinearFmMaxSplitTiles = 60;
+constexpr size_t kLinearScratchBytes = static_cast<size_t>(148) * 128 * 128 * sizeof(float);   // 148 CTAs x [128 tokens][128 features]
+struct LinearFmPlan {
+    int n_box, tiles, token_tiles, ksplit, blocks_per_cta, kb, n_stages, tmem_cols;
+};
+bool linear_fm_plan(int n_tok, int K, int n_feat, int n_sm, size_t scratch_bytes, LinearFmPlan *plan);
+cudaError_t launch_linear_fm(const LaunchCtx &cx, const LinearFmPlan &plan, const CUtensorMap &x_map, const CUtensorMap &w_map,
+                             const int *slots, const int *n_past, int n_tok, int K, int n_feat, const float *bias, float *q_out,
+                             void *out, bool out_f16, float *scratch);
 int decode_max_ctas(int n_sm);
 constexpr int kDecodeMergeFan = 16;   // CTAs per group of the two-level merge
 constexpr int kDecodePartialFloats = 16 * 128 + 32;   // acc[16][128] | m[16] | l[16]

@@ -205,8 +205,13 @@ int cglm_qkv_linear_forward(cglm_kv_arena *arena, const cglm_attn_seq *seqs, int
  *   [out_features] or NULL, out f32 (out_is_f16 == 0) or f16 [n_tok][out_features]; all on the device, x, weight and
  *   out 16-byte aligned; in_features a multiple of 64, out_features of 32 (else CGLM_ERR_UNSUPPORTED); any n_tok > 0.
  * f32 accumulation; the f32 result is rounded to nearest even when out is f16.  Runs on the current device.
- * workspace: any initialised workspace (only its status word is used).  Asynchronous on cuda_stream.
+ * workspace: an initialised workspace of at least cglm_linear_workspace_bytes(), which every workspace sized by
+ * cglm_attn_workspace_bytes is.  Out-features that are a multiple of 128 run with the features on the M side of the MMA
+ * and k split over several thread blocks per 128-feature tile, whose partial sums pass through the workspace; with a
+ * smaller workspace (at least the 256-byte header) or other out-features the kernel with the tokens on the M side runs.
+ * Asynchronous on cuda_stream; calls that share a workspace must be ordered on one stream.
  */
+size_t cglm_linear_workspace_bytes(void);
 int cglm_linear_forward(const void *x_f16, int n_tok, int in_features, const void *weight_f16, int out_features,
                         const float *bias, void *out, int out_is_f16, void *workspace, size_t workspace_bytes,
                         void *cuda_stream);
