@@ -70,6 +70,8 @@ WORKLOADS = {
     # BasicAttention::forward as the reference calls it, per layer: fused query_key_value GEMM, decode kernel, dense GEMM
     "glm4_9b_attention_block_b64": dict(H=32, G=2, D=128, M=8192, layers=40, seqs=64, n_past=(1024, 8191), rope=8, theta=5.0e6,
                                         mask=0, interleaved=False, seed=20240603, attention_block=4096),
+    "glm4_9b_attention_block_b8": dict(H=32, G=2, D=128, M=8192, layers=40, seqs=8, n_past=(1024, 8191), rope=8, theta=5.0e6,
+                                       mask=0, interleaved=False, seed=20240603, attention_block=4096),
     "glm4_9b_qkv_linear_b8": dict(H=32, G=2, D=128, M=8192, layers=40, seqs=8, n_past=(1024, 8191), rope=8, theta=5.0e6,
                                   interleaved=False, mask=0, seed=1003, qkv_linear=4096),
     "glm4_9b_qkv_linear_b128": dict(H=32, G=2, D=128, M=8192, layers=40, seqs=128, n_past=(1024, 8191), rope=8, theta=5.0e6,
@@ -661,9 +663,9 @@ def qkv_linear_measure(dd, name, w, args, syn, steps=None):
 
 def attention_block_measure(dd, name, w, args, syn, steps=None):
     """A step is BasicAttention::forward (chatglm.cpp:625-722) of every layer for a batch of one-token sequences:
-    hidden_states f16 -> query_key_value GEMM with bias, RoPE and the K/V append in its epilogue -> decode kernel over the
-    cache (roped q in f32, context out in f16) -> dense GEMM -> attn_output f32.  Three launches per layer, each layer
-    with its own weights and caches.  Bound: KV bytes plus both weights over HBM."""
+    hidden_states f16 -> query_key_value GEMM -> decode kernel over the cache (context out in f16) -> dense GEMM ->
+    attn_output f32.  Three launches per layer, each layer with its own weights and caches.  Bound: KV bytes plus both
+    weights over HBM."""
     import torch
     from chatglm_cpp_b200 import _lib
     from chatglm_cpp_b200 import attention as A
@@ -686,7 +688,11 @@ def attention_block_measure(dd, name, w, args, syn, steps=None):
     x = torch.empty(n, hidden, device="cuda", dtype=torch.float16)
     syn.fill(x, seed, 12)
     bias = torch.zeros(n_feat, device="cuda")
-    q_roped = torch.empty(2, n, H * D, device="cuda")                       # two sets: a layer's GEMM may run ahead
+    # Up to 32 sequences the query_key_value GEMM carries bias, RoPE and the cache append in its epilogue and hands roped
+    # q (f32) to the decode kernel; beyond, the plain GEMM with an f16 qkv row and the decode kernel's own RoPE + append are
+    # faster (the fused epilogue's V^T scatter falls on two thread blocks; measured at 64 sequences).
+    fused = n <= 32
+    q_roped = torch.empty(2, n, H * D if fused else n_feat, device="cuda", dtype=torch.float32 if fused else torch.float16)
     context = torch.empty(2, n, H * D, device="cuda", dtype=torch.float16)
     out = torch.empty(layers, n, hidden, device="cuda")
     n_past = draw_n_past(w, dd.rank)
@@ -697,11 +703,17 @@ def attention_block_measure(dd, name, w, args, syn, steps=None):
             P = int(n_past[i])
             a1[i].slot, a1[i].qlen, a1[i].n_past = l * n + i, 1, P
             q = q_roped[l % 2, i].data_ptr()
-            a2[i].q = a2[i].k = a2[i].v = q                                  # k and v are not read
             a2[i].q_head_stride = a2[i].kv_head_stride = D
-            a2[i].q_tok_stride = a2[i].kv_tok_stride = H * D
-            a2[i].slot, a2[i].qlen, a2[i].n_past, a2[i].kv_local = l * n + i, 1, P, P + 1
-            a2[i].flags = _lib.SEQ_Q_ROPED | _lib.SEQ_NO_APPEND | _lib.SEQ_USE_KV_LOCAL | _lib.SEQ_OUT_F16
+            a2[i].slot, a2[i].qlen, a2[i].n_past = l * n + i, 1, P
+            if fused:
+                a2[i].q = a2[i].k = a2[i].v = q                              # k and v are not read
+                a2[i].q_tok_stride = a2[i].kv_tok_stride = H * D
+                a2[i].kv_local = P + 1
+                a2[i].flags = _lib.SEQ_Q_ROPED | _lib.SEQ_NO_APPEND | _lib.SEQ_USE_KV_LOCAL | _lib.SEQ_OUT_F16
+            else:                                                            # blocked f16 qkv row (chatglm.cpp:646-652)
+                a2[i].q, a2[i].k, a2[i].v = q, q + 2 * H * D, q + 2 * (H + G) * D
+                a2[i].q_tok_stride = a2[i].kv_tok_stride = n_feat
+                a2[i].flags = _lib.SEQ_QKV_F16 | _lib.SEQ_OUT_F16
             a2[i].out = context[l % 2, i].data_ptr()
         lin_arr.append(a1)
         att_arr.append(a2)
@@ -709,8 +721,12 @@ def attention_block_measure(dd, name, w, args, syn, steps=None):
     def step():
         stream = torch.cuda.current_stream().cuda_stream
         for l in range(layers):
-            rc = L.cglm_qkv_linear_forward(arena._h, lin_arr[l], n, x.data_ptr(), hidden, w_qkv[l].data_ptr(), bias.data_ptr(),
-                                           q_roped[l % 2].data_ptr(), ws.ptr, ws.bytes, stream)
+            if fused:
+                rc = L.cglm_qkv_linear_forward(arena._h, lin_arr[l], n, x.data_ptr(), hidden, w_qkv[l].data_ptr(), bias.data_ptr(),
+                                               q_roped[l % 2].data_ptr(), ws.ptr, ws.bytes, stream)
+            else:
+                rc = L.cglm_linear_forward(x.data_ptr(), n, hidden, w_qkv[l].data_ptr(), n_feat, bias.data_ptr(),
+                                           q_roped[l % 2].data_ptr(), 1, ws.ptr, ws.bytes, stream)
             if rc == 0:
                 rc = L.cglm_attn_forward(arena._h, att_arr[l], n, ws.ptr, ws.bytes, stream)
             if rc == 0:
@@ -748,7 +764,8 @@ def attention_block_measure(dd, name, w, args, syn, steps=None):
             "steps": steps, "launches": int(launches) // max(3, steps // 4) * steps, "tokens": n,
             "l2_policy": f"every layer streams its own caches ({kv / 1e6:.0f} MB) and weights ({w_bytes / 1e6:.1f} MB): {layers} layers > L2",
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": pk, "unit": "GB/s", "frac": achieved / pk,
-                         "peak_source": src, "kernel": "qkv_linear_kernel<false> + decode_kernel + qkv_linear_kernel<true>",
+                         "peak_source": src, "kernel": ("linear_fm_kernel<false>" if fused else "linear_fm_kernel<true>") + " + decode_kernel + linear_fm_kernel<true>",
+                         "qkv_route": "fused epilogue (RoPE + append in the GEMM)" if fused else "plain GEMM, f16 qkv row, RoPE + append in the decode kernel",
                          "algorithmic_bytes_per_layer": w_bytes + kv, "layer_us": ms * 1e3 / layers,
                          "issue": "CUDA graph of the step, replayed", "eager_layer_us": ms_eager * 1e3 / layers}}
 
