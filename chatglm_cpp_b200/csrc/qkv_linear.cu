@@ -28,6 +28,11 @@
 // attention kernels store with CGLM_SEQ_OUT_F16) and the query_key_value projection of prompts and of shapes the fused
 // epilogue does not cover.  More than 128 tokens are a second grid dimension: every 128-token tile of a feature slice
 // streams that slice of the weight again, from L2 after the first.
+//
+// Two kernels live here.  qkv_linear_kernel (tokens on the M side of the MMA, 32 features per CTA) takes any
+// out-features that are a multiple of 32 and the fused epilogue for 33 .. 128 sequences; linear_fm_kernel (features on
+// the M side, 128 per CTA, k split over the CTAs of a tile; further down) takes out-features that are a multiple of 128:
+// the plain Linear at every size and the fused epilogue up to 32 sequences.
 #include "common.cuh"
 
 namespace cglm {
