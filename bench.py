@@ -13,7 +13,7 @@ through cglm_attn_forward_host with pinned host activations (H2D and D2H inside 
 decode kernel's KV bytes per launch over its measured duration against the measured HBM copy bandwidth;
 `cpu_baseline` is the CPU restatement of the reference path timed on this box's host cores on a bounded sample, and
 `parity` compares that sample's outputs and cache rows with what the timed GPU launches produced.  With the default
-workload the line also carries `configs` (the other BASELINE configurations, short runs), `step_graph`, and under
+workload the line also carries `configs` (the other benchmark configurations, short runs), `step_graph`, and under
 N > 1 GPUs `strong` (the 64 sequences sharded over the GPUs) and `split_kv` (one 131072-token sequence cut along its
 KV length, fused exchange).  --impl reference times only the CPU path.
 
@@ -54,13 +54,13 @@ WORKLOADS = {
     # every sequence at the end of its cache: the condition the 70 %-of-HBM target is quoted on (n_past >= 8k)
     "glm4_9b_batched_decode_8k": dict(H=32, G=2, D=128, M=8192, layers=40, seqs=64, n_past=(8191, 8191), rope=8,
                                       theta=10000.0, interleaved=False, mask=0, seed=1003),
-    # BASELINE config 1: one sequence at n_past 512; 64 "layers" so that consecutive launches stream different slabs
+    # benchmark configuration 1: one sequence at n_past 512; 64 "layers" so that consecutive launches stream different slabs
     "glm3_6b_decode_512": dict(H=32, G=2, D=128, M=2048, layers=64, seqs=1, n_past=(512, 512), rope=8, theta=10000.0,
                                interleaved=False, mask=0, seed=1001),
-    # BASELINE config 4: one sequence; with N GPUs the KV length is split and the partials are exchanged over NVLink
+    # benchmark configuration 4: one sequence; with N GPUs the KV length is split and the partials are exchanged over NVLink
     "glm4_9b_long_131072": dict(H=32, G=2, D=128, M=131072 + 64, layers=1, seqs=1, n_past=(131072, 131072), rope=8,
                                 theta=5.0e6, interleaved=False, mask=0, seed=1004, split_kv=True),
-    # BASELINE config 2: one 1024-token prompt into an empty cache, causal; the tcgen05 path
+    # benchmark configuration 2: one 1024-token prompt into an empty cache, causal; the tcgen05 path
     "glm3_6b_prefill_1024": dict(H=32, G=2, D=128, M=2048, layers=1, seqs=1, n_past=(0, 0), rope=8, theta=10000.0,
                                  interleaved=False, mask=0, seed=1002, prefill=1024),
     # the query_key_value Linear in front of the path, fused with RoPE and the K/V append (decode-sized batch; a step is the
@@ -78,7 +78,7 @@ WORKLOADS = {
                                     interleaved=False, mask=0, seed=1003, qkv_linear=4096),
     "glm3_6b_prefill_8192": dict(H=32, G=2, D=128, M=8192, layers=1, seqs=1, n_past=(0, 0), rope=8, theta=10000.0,
                                  interleaved=False, mask=0, seed=1002, prefill=8192),
-    # BASELINE config 5: ChatGLM-6B v1, MHA, interleaved qkv, 2-D rope
+    # benchmark configuration 5: ChatGLM-6B v1, MHA, interleaved qkv, 2-D rope
     "glm1_6b_mha_decode": dict(H=32, G=32, D=128, M=4096, layers=28, seqs=4, n_past=(2048, 2048), rope=4,
                                theta=10000.0, interleaved=True, mask=1, seed=1005),
 }
@@ -1007,7 +1007,7 @@ def run_single(args, dd, name, w):
 
 
 def run_default(args, dd):
-    """The headline workload plus, in the same line, the other BASELINE configurations and the multi-GPU partitions."""
+    """The headline workload plus, in the same line, the other benchmark configurations and the multi-GPU partitions."""
     import torch
     name, w = HEADLINE, WORKLOADS[HEADLINE]
     syn = Synth()
@@ -1040,7 +1040,7 @@ def run_default(args, dd):
             rr = decode_measure(dd, st, nm, npast, args, seq_ids=ids, e2e=False, steps=short)
             configs[nm] = decode_summary(rr, dd.world, pk)
         if dd.world > 1:
-            # strong scaling of BASELINE config 3: the SAME 64 sequences (lengths of rank 0's draw) sharded over the GPUs
+            # strong scaling of benchmark configuration 3: the SAME 64 sequences (lengths of rank 0's draw) sharded over the GPUs
             from chatglm_cpp_b200 import sharding
             glob = draw_n_past(w, 0)
             mine = sharding.shard_sequences(len(glob), dd.world, dd.rank)

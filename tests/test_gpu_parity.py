@@ -51,7 +51,7 @@ def test_reference_fixture_through_cuda(name):
 
 
 def test_config1_glm3_decode_n_past_512():
-    """BASELINE config 1: ChatGLM3-6B layer, one decode step at n_past 512, max_length 2048."""
+    """benchmark configuration 1: ChatGLM3-6B layer, one decode step at n_past 512, max_length 2048."""
     run_decode_batch(make_desc(32, 2, 128, 2048), [512], seed=1001)
 
 
@@ -99,7 +99,7 @@ def test_decode_small_batch_fewer_tiles_than_ctas():
 
 
 def test_decode_mha_v1_2d_rope_interleaved():
-    """BASELINE config 5 shape: ChatGLM-6B v1, 32 heads with their own K/V, 2-D RoPE, interleaved qkv."""
+    """benchmark configuration 5 shape: ChatGLM-6B v1, 32 heads with their own K/V, 2-D RoPE, interleaved qkv."""
     run_decode_batch(make_desc(32, 32, 128, 4096, rope=O.ROPE_CHATGLM, mask=O.MASK_CHATGLM), [2048, 2048, 5, 300],
                      seed=1005, interleaved=True, n_ctx_list=[17, 2000, 4, 300])
 
@@ -143,7 +143,7 @@ def test_decode_generic_shapes():
 
 
 def test_long_context_rope_position_131072():
-    """BASELINE config 4's position: RoPE at 131072 with theta 5e6 stays within 2 ulp of the oracle."""
+    """benchmark configuration 4's position: RoPE at 131072 with theta 5e6 stays within 2 ulp of the oracle."""
     desc = make_desc(32, 2, 128, 131072 + 64, theta=5.0e6)
     A = _A()
     arena, ws = A.KVArena(desc, 1), A.Workspace(desc, 1, 1)
@@ -203,7 +203,7 @@ def test_prefill_then_decode(H, G, D, M, V, rope, mask, S):
 
 
 @pytest.mark.parametrize("H,G,M,V,rope,mask,S", [
-    (32, 2, 2048, 0, O.ROPE_CHATGLM2, O.MASK_CAUSAL, 1024),   # BASELINE config 2
+    (32, 2, 2048, 0, O.ROPE_CHATGLM2, O.MASK_CAUSAL, 1024),   # benchmark configuration 2
     (32, 2, 2048, 0, O.ROPE_CHATGLM2, O.MASK_CAUSAL, 128),
     (8, 2, 512, 0, O.ROPE_CHATGLM2, O.MASK_CAUSAL, 129),
     (8, 2, 512 + 8, 8, O.ROPE_CHATGLM2, O.MASK_CAUSAL, 300),  # P-Tuning prefix in front of the prompt
@@ -637,7 +637,7 @@ def test_decode_with_4_byte_aligned_activation_takes_the_generic_path_and_agrees
 
 def test_f16_hand_off_decode_configs():
     """f16 activations in, f16 context out (the hand-off to f16 Linears either side of the path) on the decode shapes
-    of BASELINE configs 1, 3 and 5 and on generic-path shapes: cache bits and RoPE as with f32 inputs of the same values."""
+    of benchmark configurations 1, 3 and 5 and on generic-path shapes: cache bits and RoPE as with f32 inputs of the same values."""
     run_decode_batch(make_desc(32, 2, 128, 2048), [512], seed=1001, f16_io=True)
     rng = np.random.default_rng(1003)
     run_decode_batch(make_desc(32, 2, 128, 8192), rng.integers(1024, 8192, 24).tolist(), seed=3, check_rope=False, f16_io=True)
@@ -651,7 +651,7 @@ def test_f16_hand_off_decode_configs():
 @pytest.mark.parametrize("S,rope,mask,H,G", [(1024, O.ROPE_CHATGLM2, O.MASK_CAUSAL, 32, 2), (200, O.ROPE_CHATGLM, O.MASK_CHATGLM, 8, 8),
                                              (37, O.ROPE_CHATGLM2, O.MASK_CAUSAL, 32, 2)])
 def test_f16_hand_off_prefill(S, rope, mask, H, G):
-    """BASELINE config 2 (and a v1 prompt, and a prompt short enough for the generic path) with f16 in / f16 out."""
+    """benchmark configuration 2 (and a v1 prompt, and a prompt short enough for the generic path) with f16 in / f16 out."""
     A = _A()
     desc = make_desc(H, G, 128, 2048, 0, rope, 10000.0, mask)
     inter = rope == O.ROPE_CHATGLM
