@@ -73,6 +73,7 @@ SYMBOLS = {
     "cglm_linear_forward": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_int,
                                       C.c_void_p, C.c_size_t, C.c_void_p]),
     "cglm_linear_workspace_bytes": (C.c_size_t, []),
+    "cglm_linear_kernel_plan": (C.c_int, [C.c_int, C.c_int, C.c_int, C.c_int, C.POINTER(C.c_int)]),
     "cglm_convert_f32_to_f16": (C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]),
     "cglm_seq_advance": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_void_p]),
     "cglm_attn_forward_host": (C.c_int, [C.c_void_p, C.POINTER(AttnSeq), C.c_int, C.c_int, C.c_void_p, C.c_void_p,

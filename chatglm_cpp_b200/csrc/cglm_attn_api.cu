@@ -1118,6 +1118,15 @@ int try_linear_fm(int device, int n_sm, cudaStream_t st, const LaunchCtx *qkv_cx
 
 size_t cglm_linear_workspace_bytes(void) { return sizeof(WsHeader) + kLinearScratchBytes; }
 
+int cglm_linear_kernel_plan(int n_tok, int in_features, int out_features, int n_sm, int plan[8]) {
+    if (!plan || n_sm <= 0) return 0;
+    LinearFmPlan p;
+    if (!linear_fm_plan(n_tok, in_features, out_features, n_sm, kLinearScratchBytes, &p)) return 0;
+    plan[0] = p.n_box; plan[1] = p.tiles; plan[2] = p.token_tiles; plan[3] = p.ksplit;
+    plan[4] = p.blocks_per_cta; plan[5] = p.kb; plan[6] = p.n_stages; plan[7] = p.tmem_cols;
+    return 1;
+}
+
 int cglm_qkv_linear_forward(cglm_kv_arena *a, const cglm_attn_seq *seqs, int n_seq, const void *x_f16, int hidden,
                             const void *weight_f16, const float *bias, float *q_roped, void *workspace, size_t workspace_bytes,
                             void *cuda_stream) {

@@ -212,6 +212,11 @@ int cglm_qkv_linear_forward(cglm_kv_arena *arena, const cglm_attn_seq *seqs, int
  * Asynchronous on cuda_stream; calls that share a workspace must be ordered on one stream.
  */
 size_t cglm_linear_workspace_bytes(void);
+/* How cglm_linear_forward would run a shape on a device of n_sm multiprocessors, without running it (host arithmetic only;
+ * for tests and tuning).  Returns 1 and fills plan[8] = {tokens per tile, feature tiles, token tiles, k splits, 64-k blocks
+ * per thread block, 64-k blocks per TMA box, ring stages, tensor-memory columns} when the kernel with the features on the
+ * M side takes the shape, 0 when the kernel with the tokens on the M side does. */
+int cglm_linear_kernel_plan(int n_tok, int in_features, int out_features, int n_sm, int plan[8]);
 int cglm_linear_forward(const void *x_f16, int n_tok, int in_features, const void *weight_f16, int out_features,
                         const float *bias, void *out, int out_is_f16, void *workspace, size_t workspace_bytes,
                         void *cuda_stream);

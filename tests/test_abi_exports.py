@@ -56,3 +56,41 @@ def test_host_only_entry_points_without_a_gpu():
         from chatglm_cpp_b200 import attention as A
         with pytest.raises(RuntimeError):
             A.KVArena(d, 1)
+
+
+def test_linear_kernel_plan_stays_inside_its_buffers():
+    """cglm_linear_kernel_plan over a grid of shapes: what the launcher would ask of shared memory, tensor memory, the
+    workspace scratch and the tile counters stays inside what exists (a plan outside them would fault on the device)."""
+    from chatglm_cpp_b200 import _lib
+    L = _lib.lib()
+    scratch = L.cglm_linear_workspace_bytes() - 256
+    smem_per_cta = 232448
+    taken = 0
+    for n_sm in (148, 132, 64):
+        for n_tok in (1, 7, 8, 16, 17, 32, 33, 64, 100, 128, 129, 200, 256, 1000, 1024, 4096, 8192):
+            for n_in in (64, 128, 512, 1024, 4096, 4160, 13696):
+                for n_out in (128, 256, 1536, 3072, 4096, 4608, 8192, 27392):
+                    plan = (C.c_int * 8)()
+                    if not L.cglm_linear_kernel_plan(n_tok, n_in, n_out, n_sm, plan):
+                        continue
+                    taken += 1
+                    n_box, tiles, ttiles, ksplit, blocks, kb, stages, cols = list(plan)
+                    what = (n_sm, n_tok, n_in, n_out, list(plan))
+                    assert n_box % 16 == 0 and 16 <= n_box <= 128 and n_box >= min(n_tok, 128), what
+                    assert tiles * 128 == n_out and ttiles == (n_tok + 127) // 128, what
+                    assert ksplit in (1, 2, 4) and blocks * ksplit * 64 == n_in, what
+                    assert kb >= 1 and blocks % kb == 0 and 1 <= stages <= 8 and stages <= blocks // kb, what
+                    stage_bytes = kb * (n_box * 128 + 128 * 128)
+                    assert 2048 + stages * stage_bytes <= smem_per_cta, what
+                    assert cols in (32, 64, 128) and cols >= n_box, what
+                    if ksplit > 1:
+                        ctas = tiles * ttiles * ksplit
+                        assert ctas <= n_sm and tiles * ttiles <= 60, what
+                        assert ctas * n_box * 128 * 4 <= scratch, what
+                    else:
+                        assert stages * stage_bytes >= n_box * 128 * 4, what       # the sums pass through the ring
+    assert taken > 500
+    # out-features that are not a multiple of 128, or in-features that are not a multiple of 64: the other kernel
+    plan = (C.c_int * 8)()
+    assert L.cglm_linear_kernel_plan(8, 4096, 96, 148, plan) == 0
+    assert L.cglm_linear_kernel_plan(8, 4000, 4096, 148, plan) == 0
