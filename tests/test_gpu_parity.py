@@ -786,7 +786,7 @@ def test_fused_qkv_linear_feeds_the_decode_kernel(n_seq, rope):
     (128, 256, 96, True, False),
     (200, 512, 160, True, True),        # two token tiles, the second ragged
     (300, 1024, 4608, True, True),      # query_key_value of a prompt: three token tiles, unsplit
-    (200, 512, 4096, True, False),      # two token tiles, k split over two thread blocks per tile
+    (200, 512, 3072, True, False),      # two token tiles, k split over two thread blocks per tile
     (129, 4096, 256, False, True),      # second token tile holds one token; k split over four
 ])
 def test_linear_forward_matches_oracle(n_tok, n_in, n_out, use_bias, out_f16):
