@@ -70,6 +70,9 @@ WORKLOADS = {
     # BasicAttention::forward as the reference calls it, per layer: fused query_key_value GEMM, decode kernel, dense GEMM
     "glm4_9b_attention_block_b64": dict(H=32, G=2, D=128, M=8192, layers=40, seqs=64, n_past=(1024, 8191), rope=8, theta=5.0e6,
                                         mask=0, interleaved=False, seed=20240603, attention_block=4096),
+    # the reference's own decode loop: one sequence, ChatGLM3-6B shape (benchmark configuration 1 with its two Linears)
+    "glm3_6b_attention_block_b1": dict(H=32, G=2, D=128, M=2048, layers=28, seqs=1, n_past=(512, 512), rope=8, theta=10000.0,
+                                       mask=0, interleaved=False, seed=20240604, attention_block=4096),
     "glm4_9b_attention_block_b8": dict(H=32, G=2, D=128, M=8192, layers=40, seqs=8, n_past=(1024, 8191), rope=8, theta=5.0e6,
                                        mask=0, interleaved=False, seed=20240603, attention_block=4096),
     "glm4_9b_qkv_linear_b8": dict(H=32, G=2, D=128, M=8192, layers=40, seqs=8, n_past=(1024, 8191), rope=8, theta=5.0e6,

@@ -367,7 +367,8 @@ void BasicAttention::load_prefix_cache(ModelContext *mctx, const Tensor *past_kv
 }
 
 // ---- DecodeStep ----------------------------------------------------------------------------------------------------
-DecodeStep::DecodeStep(ModelContext *mctx, const std::vector<const BasicAttention *> &layers) : mctx_(mctx), layers_(layers) {
+DecodeStep::DecodeStep(ModelContext *mctx, const std::vector<const BasicAttention *> &layers, bool with_linears)
+    : mctx_(mctx), layers_(layers), with_linears_(with_linears) {
     CHATGLM_CHECK(mctx && mctx->kv_allocated()) << "kv buffer not allocated";
     CHATGLM_CHECK(!layers.empty()) << "no layers";
     cudaStream_t st;
@@ -390,19 +391,36 @@ DecodeStep::DecodeStep(ModelContext *mctx, const std::vector<const BasicAttentio
     const int64_t width = hidden + 2LL * d.head_dim * d.n_kv_head;
     for (const BasicAttention *attn : layers_) {
         CHATGLM_CHECK(attn && attn->slot_ >= 0) << "layer was not built against a context";
+        // between the Linears the activations are f16 when the step runs the Linears itself, f32 when the caller does
+        const TensorType act = with_linears_ ? TYPE_F16 : TYPE_F32;
         auto in = std::make_unique<Tensor>(), out = std::make_unique<Tensor>();
-        set_contiguous(in.get(), TYPE_F32, width, 1, 1);
-        set_contiguous(out.get(), TYPE_F32, hidden, 1, 1);
-        CHATGLM_CHECK_CUDA(cudaMalloc(&in->data, nbytes(in.get())));
-        CHATGLM_CHECK_CUDA(cudaMalloc(&out->data, nbytes(out.get())));
+        set_contiguous(in.get(), act, width, 1, 1);
+        set_contiguous(out.get(), act, hidden, 1, 1);
+        CHATGLM_CHECK_CUDA(cudaMalloc(&in->data, std::max<size_t>(nbytes(in.get()), 16)));
+        CHATGLM_CHECK_CUDA(cudaMalloc(&out->data, std::max<size_t>(nbytes(out.get()), 16)));
         in->owned = out->owned = true;
+        if (with_linears_) {
+            CHATGLM_CHECK(attn->query_key_value.weight && attn->dense.weight) << "layer has no Linear parameters";
+            auto x = std::make_unique<Tensor>(), y = std::make_unique<Tensor>();
+            set_contiguous(x.get(), TYPE_F16, hidden, 1, 1);
+            set_contiguous(y.get(), TYPE_F32, hidden, 1, 1);
+            CHATGLM_CHECK_CUDA(cudaMalloc(&x->data, std::max<size_t>(nbytes(x.get()), 16)));
+            CHATGLM_CHECK_CUDA(cudaMalloc(&y->data, std::max<size_t>(nbytes(y.get()), 16)));
+            CHATGLM_CHECK_CUDA(cudaMemset(x->data, 0, nbytes(x.get())));
+            x->owned = y->owned = true;
+            hidden_.push_back(std::move(x));
+            attn_output_.push_back(std::move(y));
+        }
         cglm_attn_seq seq{};
-        const float *base = static_cast<const float *>(in->data);
+        // typed float in the descriptor; with CGLM_SEQ_QKV_F16 the same pointers address f16 values, strides in elements
+        const size_t esz = element_size(act);
+        const char *bytes = static_cast<const char *>(in->data);
+        auto at = [&](long long elems) { return reinterpret_cast<const float *>(bytes + elems * static_cast<long long>(esz)); };
         if (attn->interleaved_qkv) {   // chatglm.cpp:636-644
-            seq.q = base; seq.k = base + d.head_dim; seq.v = base + 2 * d.head_dim;
+            seq.q = at(0); seq.k = at(d.head_dim); seq.v = at(2 * d.head_dim);
             seq.q_head_stride = seq.kv_head_stride = 3 * d.head_dim;
         } else {                       // chatglm.cpp:646-652
-            seq.q = base; seq.k = base + hidden; seq.v = base + hidden + static_cast<long long>(d.head_dim) * d.n_kv_head;
+            seq.q = at(0); seq.k = at(hidden); seq.v = at(hidden + static_cast<long long>(d.head_dim) * d.n_kv_head);
             seq.q_head_stride = seq.kv_head_stride = d.head_dim;
         }
         seq.q_tok_stride = seq.kv_tok_stride = width;
@@ -411,7 +429,7 @@ DecodeStep::DecodeStep(ModelContext *mctx, const std::vector<const BasicAttentio
         seq.n_past = d.max_len - d.n_virtual - 1;   // upper bound: sizes the launch, the kernel reads the device word
         seq.n_ctx = attn->n_ctx_;
         seq.out = static_cast<float *>(out->data);
-        seq.flags = CGLM_SEQ_N_PAST_DEVICE;
+        seq.flags = CGLM_SEQ_N_PAST_DEVICE | (with_linears_ ? (CGLM_SEQ_QKV_F16 | CGLM_SEQ_OUT_F16) : 0);
         seq.n_past_dev = n_past_dev_;
         seqs_.push_back(seq);
         qkv_.push_back(std::move(in));
@@ -424,6 +442,8 @@ DecodeStep::~DecodeStep() {
     if (graph_exec_) cudaGraphExecDestroy(static_cast<cudaGraphExec_t>(graph_exec_));
     for (auto &t : qkv_) cudaFree(t->data);
     for (auto &t : context_) cudaFree(t->data);
+    for (auto &t : hidden_) cudaFree(t->data);
+    for (auto &t : attn_output_) cudaFree(t->data);
     cudaFree(n_past_dev_);
     cudaFree(workspace_);
     cudaEventDestroy(static_cast<cudaEvent_t>(ev_in_));
@@ -442,7 +462,22 @@ void DecodeStep::set_n_past(int n_past) {
 
 void DecodeStep::record(int layer, void *stream) {
     CHATGLM_CHECK(layer >= 0 && layer < static_cast<int>(seqs_.size())) << "no such layer";
-    CHATGLM_CHECK_CGLM(cglm_attn_forward(mctx_->arena_, &seqs_[layer], 1, workspace_, workspace_bytes_, stream ? stream : stream_));
+    void *st = stream ? stream : stream_;
+    if (!with_linears_) {
+        CHATGLM_CHECK_CGLM(cglm_attn_forward(mctx_->arena_, &seqs_[layer], 1, workspace_, workspace_bytes_, st));
+        return;
+    }
+    // query_key_value as a plain GEMM with an f16 result (chatglm.cpp:629); RoPE and the cache append happen in the decode
+    // kernel, which reads the position from the device word; dense (chatglm.cpp:719) on the f16 context
+    const BasicAttention *attn = layers_[layer];
+    const Linear &qkv_lin = attn->query_key_value, &dense_lin = attn->dense;
+    CHATGLM_CHECK_CGLM(cglm_linear_forward(hidden_[layer]->data, 1, qkv_lin.in_features(), qkv_lin.weight->data, qkv_lin.out_features(),
+                                           qkv_lin.bias ? static_cast<const float *>(qkv_lin.bias->data) : nullptr, qkv_[layer]->data, 1,
+                                           workspace_, workspace_bytes_, st));
+    CHATGLM_CHECK_CGLM(cglm_attn_forward(mctx_->arena_, &seqs_[layer], 1, workspace_, workspace_bytes_, st));
+    CHATGLM_CHECK_CGLM(cglm_linear_forward(context_[layer]->data, 1, dense_lin.in_features(), dense_lin.weight->data,
+                                           dense_lin.out_features(), dense_lin.bias ? static_cast<const float *>(dense_lin.bias->data) : nullptr,
+                                           attn_output_[layer]->data, 0, workspace_, workspace_bytes_, st));
 }
 
 void DecodeStep::record_advance(void *stream) {

@@ -234,13 +234,21 @@ class DecodeStep {
   public:
     // layers: the model's attention modules in order (all built against mctx, fused-decode shapes: head_dim 128, at
     // most 16 q heads per kv head, cache capacity a multiple of 8); mctx->alloc_kv() must have run.
-    DecodeStep(ModelContext *mctx, const std::vector<const BasicAttention *> &layers);
+    // with_linears: the step also runs every layer's two Linears (three launches per layer: query_key_value GEMM with an
+    // f16 result, the decode kernel, dense GEMM), i.e. the whole of BasicAttention::forward per layer in the replayed
+    // graph; the caller writes hidden(l) and reads attn_output(l).  The layers' Linear parameters must be loaded, with
+    // in-features a multiple of 64 and out-features of 32.
+    DecodeStep(ModelContext *mctx, const std::vector<const BasicAttention *> &layers, bool with_linears = false);
     ~DecodeStep();
     DecodeStep(const DecodeStep &) = delete;
     DecodeStep &operator=(const DecodeStep &) = delete;
 
-    Tensor *qkv(int layer) const { return qkv_.at(layer).get(); }           // f32 [1, (#h + 2 #kvh) * d], device
-    Tensor *context(int layer) const { return context_.at(layer).get(); }   // f32 [1, #h * d], device
+    Tensor *qkv(int layer) const { return qkv_.at(layer).get(); }           // f32 [1, (#h + 2 #kvh) * d], device (f16 with_linears)
+    Tensor *context(int layer) const { return context_.at(layer).get(); }   // f32 [1, #h * d], device (f16 with_linears)
+    // with_linears only: the layer's input (f16 [1, hidden], e.g. what the caller's input norm writes) and its result
+    // (f32 [1, hidden], chatglm.cpp:719-721)
+    Tensor *hidden(int layer) const { return hidden_.at(layer).get(); }
+    Tensor *attn_output(int layer) const { return attn_output_.at(layer).get(); }
     // position of the next token; also the value ChatGLM-6B v1 derives its 2-D ids from together with n_ctx
     void set_n_past(int n_past);
     int n_past() const { return n_past_; }
@@ -258,7 +266,8 @@ class DecodeStep {
   private:
     ModelContext *mctx_;
     std::vector<const BasicAttention *> layers_;
-    std::vector<std::unique_ptr<Tensor>> qkv_, context_;
+    bool with_linears_ = false;
+    std::vector<std::unique_ptr<Tensor>> qkv_, context_, hidden_, attn_output_;
     std::vector<cglm_attn_seq> seqs_;
     int *n_past_dev_ = nullptr;
     int n_past_ = 0;

@@ -289,6 +289,45 @@ static void run_full_forward_case(const FullCase &c) {
         mctx.reset_scratch();
     }
     EXPECT(worst <= 6e-3f, "%s: max abs error %g", c.name, worst);
+    // The same module inside a DecodeStep that runs the Linears itself: three more tokens, one eager step, one captured,
+    // one replayed (the fused decode kernel reads the position from the device word; shapes it does not take have no step).
+    float worst_step = 0.f;
+    int replays = 0;
+    if (D == 128) {
+        DecodeStep step(&mctx, {&attn}, /*with_linears=*/true);
+        step.set_n_past(n_past);
+        for (int t = 0; t < 3; t++) {
+            std::vector<float> x(c.hidden);
+            for (auto &e : x) e = dist(rng);
+            std::vector<uint16_t> x16(x.size());
+            for (size_t i = 0; i < x.size(); i++) x16[i] = oracle_f32_to_f16(x[i]);
+            mctx.tensor_set(step.hidden(0), x16.data(), 0, x16.size() * 2);
+            step.run();
+            std::vector<float> got(c.hidden);
+            mctx.tensor_get(step.attn_output(0), got.data(), 0, got.size() * sizeof(float));
+            mctx.synchronize();
+            std::vector<float> qkv(width), ctx(c.hidden), want(c.hidden);
+            oracle_linear(x.data(), 1, c.hidden, w_qkv.data(), 1, c.qkv_bias ? b_qkv.data() : nullptr, width, 1, qkv.data());
+            round_f16(qkv);
+            const float *q = qkv.data(), *k, *v;
+            long hs;
+            if (c.interleaved) { k = q + D; v = q + 2 * D; hs = 3 * D; } else { k = q + c.hidden; v = q + c.hidden + G * D; hs = D; }
+            std::vector<int> ids = c.rope == RopeType::CHATGLM ? make_position_ids_glm(1, n_past, c.prompt) : make_position_ids_glm2(1, n_past);
+            int rc = oracle_attn_forward(&cfg, q, width, hs, k, v, width, hs, kc.data(), vc.data(), ids.data(), nullptr, 1, n_past,
+                                         ctx.data(), nullptr, nullptr);
+            EXPECT(rc == 0, "oracle rejected the arguments");
+            oracle_linear(ctx.data(), 1, c.hidden, w_dense.data(), 1, c.dense_bias ? b_dense.data() : nullptr, c.hidden, 1, want.data());
+            for (size_t i = 0; i < got.size(); i++) {
+                EXPECT(std::isfinite(got[i]), "non-finite output");
+                worst_step = std::fmax(worst_step, std::fabs(got[i] - want[i]));
+            }
+            n_past += 1;
+        }
+        EXPECT(step.n_past() == n_past && step.status() == 0, "%s: step position / status", c.name);
+        replays = step.graph_launches();
+        EXPECT(replays == 2, "%s: %d graph launches", c.name, replays);
+        EXPECT(worst_step <= 6e-3f, "%s: step graph with Linears, max abs error %g", c.name, worst_step);
+    }
     // caches: the same f16 values up to a neighbouring one where the GEMM's sum fell on the other side of a tie
     std::vector<uint16_t> gk(kc.size()), gv(vc.size());
     mctx.tensor_get(attn.k_cache, gk.data(), 0, gk.size() * 2);
@@ -302,7 +341,8 @@ static void run_full_forward_case(const FullCase &c) {
     }
     EXPECT(cache_worst <= 8e-3f, "%s: cache value off by %g", c.name, cache_worst);
     EXPECT(differing <= static_cast<size_t>(0.04 * 2 * G * D * n_past) + 4, "%s: %zu cache values differ", c.name, differing);
-    std::printf("case %-28s max abs err %.3g (caches: %zu values on a neighbouring f16)\n", c.name, worst, differing);
+    std::printf("case %-28s max abs err %.3g, step graph with Linears %.3g over %d replays (caches: %zu values on a neighbouring f16)\n",
+                c.name, worst, worst_step, replays, differing);
 }
 
 int main() {
