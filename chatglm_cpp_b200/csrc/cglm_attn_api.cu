@@ -125,14 +125,20 @@ int decode_charge() {
     }();
     return v;
 }
-// When a decode CTA releases the next kernel of the stream (see DecodeTable::trigger).  CGLM_DECODE_TRIGGER overrides.
-int decode_trigger() {
-    static const int v = [] {
+// When a decode CTA releases the next kernel of the stream (see DecodeTable::trigger): late (2) in general, because a
+// kernel that is released early only sits on the SMs until its dependency wait returns; right after its own wait (0)
+// when the launch runs on settled caches and is long (at least 8192 tiles over all kv heads), because the next launch
+// of such a chain streams its cache tiles before its wait.  Measured per 40-layer step, settled caches, released early
+// against late: 64 sequences x U[1024, 8191] 2.392 / 2.424 ms, 64 x 8191 3.758 / 3.834 ms; shorter launches lose
+// (32 sequences 1.632 / 1.571 ms, 8 sequences 1.412 / 1.330 ms).  CGLM_DECODE_TRIGGER overrides (tuning knob, read once).
+constexpr long long kEarlyReleaseMinTiles = 8192;
+int decode_trigger(bool settled, long long total_tiles) {
+    static const int forced = [] {
         const char *e = std::getenv("CGLM_DECODE_TRIGGER");
-        const int x = e ? std::atoi(e) : 2;
-        return x < 0 || x > 2 ? 2 : x;
+        const int x = e ? std::atoi(e) : -1;
+        return x < 0 || x > 2 ? -1 : x;
     }();
-    return v;
+    return forced >= 0 ? forced : (settled && total_tiles >= kEarlyReleaseMinTiles ? 0 : 2);
 }
 
 // ---- workspace layout (fixed regions first, so that self-resetting counters stay where they are) ------
@@ -754,7 +760,7 @@ int forward_impl(cglm_kv_arena *a, const cglm_attn_seq *seqs, int n_seq, void *w
             if (filled == kDecodeMaxSeqPerLaunch || (i == n_seq && filled > 0)) {
                 tab.n_seq = filled;
                 tab.settled = settled && !dyn ? 1 + decode_l2_ahead() : 0;
-                tab.trigger = decode_trigger();
+                tab.trigger = decode_trigger(tab.settled != 0, static_cast<long long>(tab.prefix[filled]) * d.n_kv_head);
                 tab.charge = decode_charge();
                 for (int gi = 0; gi < 2; ++gi) {
                     tab.gate[gi] = gate_in_kernel && gates->event[gi] ? gates->word[gi] : nullptr;
@@ -1056,11 +1062,11 @@ int cglm_attn_splitkv_step(cglm_kv_arena *a, const cglm_attn_seq *seq, void *con
     o.flags = s.flags | CGLM_SEQ_PARTIAL;
     tab.n_seq = 1;
     tab.settled = (s.flags & CGLM_SEQ_CACHE_SETTLED) ? 1 + decode_l2_ahead() : 0;
-    tab.trigger = decode_trigger();
     tab.charge = decode_charge();
     tab.gate[0] = tab.gate[1] = nullptr;
     tab.prefix[0] = 0;
     tab.prefix[1] = (kv_before + appended + kDecodeTile - 1) / kDecodeTile;
+    tab.trigger = decode_trigger(tab.settled != 0, static_cast<long long>(tab.prefix[1]) * d.n_kv_head);
     CGLM_CUDA(launch_decode(cx, tab, false, &xd));
     return CGLM_OK;
 }
