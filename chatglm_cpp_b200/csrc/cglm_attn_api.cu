@@ -1099,6 +1099,7 @@ int try_linear_fm(int device, int n_sm, cudaStream_t st, const LaunchCtx *qkv_cx
                   const int *n_past, float *q_out, void *out, bool out_f16) {
     static const bool tokens_on_m = [] { const char *e = std::getenv("CGLM_LINEAR_TOKENS_ON_M"); return e && std::atoi(e) != 0; }();
     if (tokens_on_m || workspace_bytes < sizeof(WsHeader) + kLinearScratchBytes) return 1;
+    if (reinterpret_cast<uintptr_t>(bias) & 15) return 1;   // this kernel reads the bias four features at a time
     LinearFmPlan plan;
     if (!linear_fm_plan(n_tok, K, n_feat, n_sm, kLinearScratchBytes, &plan)) return 1;
     EncodeTiledFn enc = encode_tiled_fn();

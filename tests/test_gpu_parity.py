@@ -818,6 +818,18 @@ def test_linear_forward_matches_oracle(n_tok, n_in, n_out, use_bias, out_f16):
     tol = 2e-4 + (2e-3 * np.maximum(1.0, np.abs(want) / 4) if out_f16 else 0.0)
     assert (np.abs(got - want) <= tol).all(), float(np.abs(got - want).max())
     assert (buf[0] == 7).all() and (buf[n_tok + 1] == 7).all()
+    if use_bias:
+        # a bias that is only 4-byte aligned (one kernel reads it four features at a time; the call must not hand it one)
+        shifted = torch.cat([torch.zeros(1, device="cuda"), b_d])[1:]
+        assert shifted.data_ptr() % 16 == 4
+        buf.fill_(7.0)
+        rc = L.cglm_linear_forward(x_d.data_ptr(), n_tok, n_in, w_d.data_ptr(), n_out, shifted.data_ptr(), buf[1:].data_ptr(),
+                                   int(out_f16), ws.ptr, ws.bytes, stream)
+        assert rc == 0, L.cglm_last_error_string()
+        torch.cuda.synchronize()
+        assert ws.status() == 0
+        got = buf[1:n_tok + 1].float().cpu().numpy()
+        assert (np.abs(got - want) <= tol).all(), float(np.abs(got - want).max())
     # refused, not served by another path
     assert L.cglm_linear_forward(x_d.data_ptr(), n_tok, n_in - 32, w_d.data_ptr(), n_out, None, buf[1:].data_ptr(),
                                  int(out_f16), ws.ptr, ws.bytes, stream) == _lib.ERR_UNSUPPORTED
