@@ -107,6 +107,7 @@ SYMBOLS = {
     "cglm_model_file_attn_desc": (C.c_int, [C.c_void_p, C.c_int, C.POINTER(AttnDesc)]),
     "cglm_model_file_attn_weight_name": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_char_p, C.c_size_t]),
     "cglm_model_file_load_prefix": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_void_p]),
+    "cglm_model_file_load_attn_weight": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_size_t, C.c_void_p]),
 }
 
 _lib = None

@@ -360,6 +360,27 @@ Tensor *BasicAttention::forward(ModelContext *mctx, Tensor *hidden_states, Tenso
     return dense.forward(mctx, context_layer, TYPE_F32);                                          // chatglm.cpp:719
 }
 
+void BasicAttention::load_weights(ModelContext *mctx, const ModelFile &file, int layer) const {
+    CHATGLM_CHECK(mctx != nullptr) << "null context";
+    Tensor *dst[4] = {query_key_value.weight, query_key_value.bias, dense.weight, dense.bias};
+    for (int which = 0; which < 4; which++) {
+        if (!dst[which]) continue;
+        auto it = file.state_dict.kv.find(file.attn_weight_name(layer, which));
+        if (it == file.state_dict.kv.end()) {
+            CHATGLM_CHECK(which == 1 || which == 3) << "the model file has no " << file.attn_weight_name(layer, which);
+            continue;
+        }
+        const HostTensor &t = it->second;
+        const bool is_weight = which == 0 || which == 2;
+        CHATGLM_CHECK(t.dtype == (is_weight ? static_cast<int>(TYPE_F16) : static_cast<int>(TYPE_F32)))
+            << file.attn_weight_name(layer, which) << ": the Linear kernels take f16 weights and f32 biases";
+        CHATGLM_CHECK(t.nbytes == nbytes(dst[which]) && t.ne[0] == dst[which]->ne[0] && t.ne[1] == dst[which]->ne[1])
+            << file.attn_weight_name(layer, which) << ": shape does not match the module";
+        mctx->tensor_set(dst[which], t.data, 0, t.nbytes);
+    }
+    mctx->synchronize();   // the copies read the file's mapping
+}
+
 void BasicAttention::load_prefix_cache(ModelContext *mctx, const Tensor *past_kv) const {
     CHATGLM_CHECK(mctx && mctx->kv_allocated()) << "kv buffer not allocated";
     CHATGLM_CHECK(past_kv && past_kv->type == TYPE_F16 && past_kv->data) << "prefix must be an f16 device tensor";

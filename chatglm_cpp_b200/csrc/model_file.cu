@@ -388,4 +388,40 @@ int cglm_model_file_load_prefix(const cglm_model_file *f, cglm_kv_arena *arena, 
     return cglm_kv_load_prefix(arena, slot, staging_dev, cuda_stream);
 }
 
+int cglm_model_file_load_attn_weight(const cglm_model_file *f, int layer, int which, void *dst_dev, size_t dst_bytes,
+                                     void *cuda_stream) {
+    if (!f || !dst_dev || which < 0 || which > 3) return CGLM_ERR_INVALID_ARG;
+    return guarded([&] {
+        const chatglm::ModelConfig &c = f->mf->config;
+        if (layer < 0 || layer >= c.num_hidden_layers) return static_cast<int>(CGLM_ERR_INVALID_ARG);
+        auto it = f->mf->state_dict.kv.find(f->mf->attn_weight_name(layer, which));
+        if (it == f->mf->state_dict.kv.end()) {
+            cglm::set_last_error("the model file has no such tensor for this layer");
+            return static_cast<int>(CGLM_ERR_INVALID_ARG);
+        }
+        const chatglm::HostTensor &t = it->second;
+        const int64_t hidden = c.hidden_size, head = c.hidden_size / c.num_attention_heads;
+        const int64_t qkv = hidden + 2 * head * c.num_key_value_heads;
+        const bool is_weight = which == 0 || which == 2;
+        const int64_t rows = which < 2 ? qkv : hidden;
+        // weights: [out, in] = ne {in, out} in the file's matrix type; biases: f32 [out]
+        const bool shape_ok = is_weight ? (t.ndim == 2 && t.ne[0] == hidden && t.ne[1] == rows) : (t.ndim == 1 && t.ne[0] == rows);
+        if (!shape_ok) {
+            cglm::set_last_error("tensor shape does not match the configuration record");
+            return static_cast<int>(CGLM_ERR_INVALID_ARG);
+        }
+        if (t.dtype != (is_weight ? CGLM_TYPE_F16 : CGLM_TYPE_F32)) {
+            cglm::set_last_error("the Linear kernels take f16 weights and f32 biases: convert the checkpoint with type f16");
+            return static_cast<int>(CGLM_ERR_UNSUPPORTED);
+        }
+        if (dst_bytes != t.nbytes) return static_cast<int>(CGLM_ERR_INVALID_ARG);
+        cudaError_t e = cudaMemcpyAsync(dst_dev, t.data, t.nbytes, cudaMemcpyHostToDevice, static_cast<cudaStream_t>(cuda_stream));
+        if (e != cudaSuccess) {
+            cglm::set_last_error(cudaGetErrorString(e));
+            return static_cast<int>(CGLM_ERR_CUDA);
+        }
+        return static_cast<int>(CGLM_OK);
+    });
+}
+
 }  // extern "C"

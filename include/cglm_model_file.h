@@ -92,6 +92,15 @@ int cglm_model_file_attn_weight_name(const cglm_model_file *f, int layer, int wh
 int cglm_model_file_load_prefix(const cglm_model_file *f, cglm_kv_arena *arena, int layer, int slot, void *staging_dev,
                                 void *cuda_stream);
 
+/* One parameter of a layer's attention module into device memory, as load_state_dict does for the module's Linears
+ * (chatglm.cpp:1250-1313): which as for cglm_model_file_attn_weight_name.  Weights must be stored as f16 [out][in]
+ * (what cglm_linear_forward and cglm_qkv_linear_forward take), biases as f32; any other type is
+ * CGLM_ERR_UNSUPPORTED.  dst_bytes must be the tensor's size; a tensor the file does not hold (a bias the model family
+ * does not have) or a shape that contradicts the configuration record is CGLM_ERR_INVALID_ARG.  The copy is enqueued on
+ * cuda_stream from the mapping: keep the file open until it has completed. */
+int cglm_model_file_load_attn_weight(const cglm_model_file *f, int layer, int which, void *dst_dev, size_t dst_bytes,
+                                     void *cuda_stream);
+
 #ifdef __cplusplus
 }
 #endif

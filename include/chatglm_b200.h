@@ -163,6 +163,8 @@ class Linear {
 };
 
 // ---- the attention module (chatglm.h:440-472) ---------------------------------------------------------------
+class ModelFile;   // further down: the model container's reader
+
 class BasicAttention {
   public:
     BasicAttention() = default;
@@ -198,6 +200,10 @@ class BasicAttention {
 
     // prompt length of the running generation; only RopeType::CHATGLM with null position_ids reads it
     void set_n_ctx(int n_ctx) { n_ctx_ = n_ctx; }
+
+    // Parameters of the two Linears from a model file, as load_state_dict does (chatglm.cpp:1250-1313): f16 weights,
+    // f32 biases; a bias the file does not hold (GLM-2/3/4 have no dense bias) is left as it is.  Synchronous.
+    void load_weights(ModelContext *mctx, const ModelFile &file, int layer) const;
 
     // P-Tuning v2 prefix of this layer (BasicModel::load_prefix_cache, chatglm.h:580-615):
     // past_kv f16 [2, #kvh, v, d] on the device.

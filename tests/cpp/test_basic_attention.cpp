@@ -345,7 +345,75 @@ static void run_full_forward_case(const FullCase &c) {
                 c.name, worst, worst_step, replays, differing);
 }
 
-int main() {
+// A model file (written by the test driver with the converter's layout): every layer's attention module is built from
+// the configuration record, takes its Linear parameters and its P-Tuning prefix from the file, and runs forward on a
+// short prompt; checked against the oracle fed the tensors of the same file.
+static void run_model_file_case(const char *path) {
+    ModelFile file(path);
+    const ModelConfig &c = file.config;
+    const int H = c.num_attention_heads, G = c.num_key_value_heads, D = c.hidden_size / H, V = c.num_virtual_tokens;
+    const int M = c.max_length + V, width = c.hidden_size + 2 * D * G;
+    ModelContext mctx(nullptr);
+    std::vector<BasicAttention> layers;
+    for (int l = 0; l < c.num_hidden_layers; l++) {
+        layers.emplace_back(&mctx, c.hidden_size, H, G, c.max_length, c.use_qkv_bias, c.use_dense_bias, c.interleaved_qkv,
+                            c.rope_type, c.rope_theta, c.attn_mask_type, V);
+    }
+    mctx.alloc_kv();
+    const int layer = c.num_hidden_layers - 1;
+    BasicAttention &attn = layers[layer];
+    attn.load_weights(&mctx, file, layer);
+    auto tensor = [&](int which) -> const HostTensor * {
+        if (which == 3 && !c.use_dense_bias) return nullptr;
+        auto it = file.state_dict.kv.find(file.attn_weight_name(layer, which));
+        return it == file.state_dict.kv.end() ? nullptr : &it->second;
+    };
+    const HostTensor *wq = tensor(0), *bq = tensor(1), *wd = tensor(2), *bd = tensor(3);
+    EXPECT(wq && wd, "the file holds both weights");
+    oracle_cfg cfg = {H, G, D, M, V, static_cast<int>(c.rope_type), c.rope_theta,
+                      c.attn_mask_type == AttentionMaskType::CAUSAL ? ORACLE_MASK_CAUSAL : ORACLE_MASK_CHATGLM, oracle_numerics_f32()};
+    std::vector<uint16_t> kc(static_cast<size_t>(G) * M * D, 0), vc(kc.size(), 0);
+    if (V > 0) {
+        auto it = file.state_dict.kv.find("past_key_values");
+        EXPECT(it != file.state_dict.kv.end(), "prefix tensor present");
+        const size_t block = static_cast<size_t>(2) * G * V * D;
+        const uint16_t *past = static_cast<const uint16_t *>(it->second.data) + block * layer;
+        Tensor *dev = mctx.new_tensor_1d(TYPE_F16, static_cast<int64_t>(block));
+        mctx.tensor_set(dev, past, 0, block * 2);
+        attn.load_prefix_cache(&mctx, dev);
+        oracle_load_prefix_cache(&cfg, past, kc.data(), vc.data());
+    }
+    std::mt19937 rng(99);
+    std::normal_distribution<float> dist(0.f, 0.05f);   // the file's weights are N(0, 1): keep the sums of unit scale
+    const int qlen = 3;
+    std::vector<float> x(static_cast<size_t>(qlen) * c.hidden_size);
+    for (auto &e : x) e = dist(rng);
+    Tensor *x_t = mctx.new_tensor_2d(TYPE_F32, c.hidden_size, qlen);
+    mctx.tensor_set(x_t, x.data(), 0, x.size() * sizeof(float));
+    Tensor *out_t = attn.forward(&mctx, x_t, nullptr, nullptr, 0);
+    std::vector<float> got(static_cast<size_t>(qlen) * c.hidden_size);
+    mctx.tensor_get(out_t, got.data(), 0, got.size() * sizeof(float));
+    mctx.synchronize();
+    std::vector<float> qkv(static_cast<size_t>(qlen) * width), ctx(got.size()), want(got.size());
+    oracle_linear(x.data(), qlen, c.hidden_size, wq->data, 1, bq ? static_cast<const float *>(bq->data) : nullptr, width, 1, qkv.data());
+    for (auto &e : qkv) e = oracle_f16_to_f32(oracle_f32_to_f16(e));
+    const float *q = qkv.data(), *k = q + c.hidden_size, *v = q + c.hidden_size + G * D;
+    std::vector<int> ids = make_position_ids_glm2(qlen, 0);
+    int rc = oracle_attn_forward(&cfg, q, width, D, k, v, width, D, kc.data(), vc.data(), ids.data(), nullptr, qlen, 0, ctx.data(),
+                                 nullptr, nullptr);
+    EXPECT(rc == 0, "oracle rejected the arguments");
+    oracle_linear(ctx.data(), qlen, c.hidden_size, wd->data, 1, bd ? static_cast<const float *>(bd->data) : nullptr, c.hidden_size, 1,
+                  want.data());
+    float worst = 0.f, scale = 0.f;
+    for (size_t i = 0; i < got.size(); i++) {
+        worst = std::fmax(worst, std::fabs(got[i] - want[i]));
+        scale = std::fmax(scale, std::fabs(want[i]));
+    }
+    EXPECT(worst <= 6e-3f * std::fmax(1.f, scale), "model file case: max abs error %g at scale %g", worst, scale);
+    std::printf("case %-28s max abs err %.3g (output scale %.3g)\n", "forward from a model file", worst, scale);
+}
+
+int main(int argc, char **argv) {
     const Case cases[] = {
         {"glm3 gqa d128 blocked", 4096, 32, 2, 512, 0, false, RopeType::CHATGLM2, AttentionMaskType::CAUSAL, 5, false},
         {"glm3 gqa d128 long prompt", 4096, 32, 2, 512, 0, false, RopeType::CHATGLM2, AttentionMaskType::CAUSAL, 200, true},
@@ -368,6 +436,7 @@ int main() {
             {"forward d64 neox", 512, 8, 8, 128, false, false, true, RopeType::NEOX, AttentionMaskType::CAUSAL, 5},
         };
         for (const FullCase &c : full) run_full_forward_case(c);
+        if (argc > 1) run_model_file_case(argv[1]);
     } catch (const std::exception &e) {
         std::printf("FAIL unexpected exception: %s\n", e.what());
         return 1;

@@ -212,3 +212,64 @@ def test_prefix_cache_from_a_model_file_lands_in_the_arena():
     other = A.KVArena(_lib.AttnDesc(4, 2, 128, 64, 4, _lib.ROPE_CHATGLM2, 10000.0, _lib.MASK_CAUSAL), 1)
     assert L.cglm_model_file_load_prefix(h, other._h, 0, 0, staging.data_ptr(), stream) == _lib.ERR_INVALID_ARG
     L.cglm_model_file_close(h)
+
+
+@pytest.mark.gpu
+def test_attention_weights_from_a_model_file_drive_the_linears():
+    """cglm_model_file_load_attn_weight: the four parameters of a layer's attention module go from the mapping to device
+    memory with the bits the file holds (f16 weights, f32 biases), and the query_key_value Linear run on them matches
+    the oracle's Linear on the same bits.  Absent tensors, wrong sizes and f32 checkpoints are refused."""
+    import torch
+
+    from chatglm_cpp_b200 import _lib
+    from chatglm_cpp_b200 import attention as A
+    from oracle import attn_oracle as O
+    L = _lib.lib()
+    cfg = W.GLM3_PTUNING
+    blob, written = W.write_model(cfg, W.F16, 2, seed=12)
+    rc, h, keep = _open(blob)
+    assert rc == 0
+    stream = torch.cuda.current_stream().cuda_stream
+    hidden = cfg["hidden_size"]
+    loaded = {}
+    for layer in range(cfg["num_hidden_layers"]):
+        for which in range(4):
+            buf = C.create_string_buffer(256)
+            named = L.cglm_model_file_attn_weight_name(h, layer, which, buf, 256) == 0   # GLM-2/3/4 have no dense bias
+            name = buf.value.decode() if named else ""
+            probe = torch.empty(16, dtype=torch.uint8, device="cuda")
+            if name not in written:
+                assert L.cglm_model_file_load_attn_weight(h, layer, which, probe.data_ptr(), 16, stream) == _lib.ERR_INVALID_ARG
+                continue
+            x, t, _ = written[name]
+            want = x.astype(np.float16 if t == W.F16 else np.float32)
+            dst = torch.empty(want.shape, dtype=torch.float16 if t == W.F16 else torch.float32, device="cuda")
+            assert L.cglm_model_file_load_attn_weight(h, layer, which, dst.data_ptr(), want.nbytes - 4, stream) == _lib.ERR_INVALID_ARG
+            assert L.cglm_model_file_load_attn_weight(h, layer, which, dst.data_ptr(), want.nbytes, stream) == 0, L.cglm_last_error_string()
+            torch.cuda.synchronize()
+            np.testing.assert_array_equal(dst.cpu().numpy().view(np.uint8), want.view(np.uint8))
+            loaded[(layer, which)] = (dst, want)
+    assert (0, 0) in loaded and (1, 2) in loaded
+    assert L.cglm_model_file_load_attn_weight(h, cfg["num_hidden_layers"], 0, loaded[(0, 0)][0].data_ptr(), 16, stream) == _lib.ERR_INVALID_ARG
+    # the Linear on the loaded parameters
+    w_d, w = loaded[(1, 0)]
+    bias = loaded.get((1, 1))
+    rng = np.random.default_rng(5)
+    xs = rng.standard_normal((3, hidden)).astype(np.float16)
+    out = torch.empty(3, w.shape[0], device="cuda")
+    desc = _lib.AttnDesc()
+    assert L.cglm_model_file_attn_desc(h, 0, C.byref(desc)) == 0
+    ws = A.Workspace(desc, 1, 1)
+    rc = L.cglm_linear_forward(torch.from_numpy(xs).cuda().data_ptr(), 3, hidden, w_d.data_ptr(), w.shape[0],
+                               bias[0].data_ptr() if bias else None, out.data_ptr(), 0, ws.ptr, ws.bytes, stream)
+    assert rc == 0, L.cglm_last_error_string()
+    torch.cuda.synchronize()
+    want = O.linear(xs.astype(np.float32), w, bias[1] if bias else None)
+    assert np.abs(out.cpu().numpy() - want).max() <= 2e-4 * max(1.0, float(np.abs(want).max()))
+    L.cglm_model_file_close(h)
+    # an f32 checkpoint: weights are refused, not converted behind the caller's back
+    blob32, _ = W.write_model(cfg, W.F32, 2, seed=12)
+    rc, h32, keep32 = _open(blob32)
+    assert rc == 0
+    assert L.cglm_model_file_load_attn_weight(h32, 0, 0, w_d.data_ptr(), w.nbytes * 2, stream) == _lib.ERR_UNSUPPORTED
+    L.cglm_model_file_close(h32)
