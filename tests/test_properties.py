@@ -164,3 +164,21 @@ def test_prompt_fed_at_once_or_token_by_token_fills_the_cache_identically(S, fam
     np.testing.assert_array_equal(caches[0][1], caches[1][1])
     # the last row of a causal prefill sees everything, like a decode step; the v1 mask also lets the last row see all
     assert np.abs(outs[0] - outs[1]).max() <= 1e-5
+
+
+@settings(max_examples=40, deadline=None)
+@given(st.integers(1, 9), st.integers(1, 200), st.integers(1, 40), st.booleans(), st.booleans(), st.booleans(),
+       st.integers(0, 2 ** 31 - 1))
+def test_oracle_linear_matches_float64_numpy(n_tok, n_in, n_out, w_f16, round_x, use_bias, seed):
+    """Linear::forward of the oracle (chatglm.cpp:418-426) against a float64 product of the same operands: f16 weights are
+    widened exactly, round_x_f16 rounds the activation to f16 first, the bias is added once.  Bound: f32 accumulation of
+    n_in products of unit scale."""
+    rng = np.random.default_rng(seed)
+    x = rng.standard_normal((n_tok, n_in)).astype(np.float32)
+    w = rng.standard_normal((n_out, n_in)).astype(np.float16 if w_f16 else np.float32)
+    b = rng.standard_normal(n_out).astype(np.float32) if use_bias else None
+    got = O.linear(x, w, b, round_x_f16=round_x)
+    xe = x.astype(np.float16).astype(np.float64) if round_x else x.astype(np.float64)
+    want = xe @ w.astype(np.float64).T + (b.astype(np.float64) if use_bias else 0.0)
+    assert got.shape == (n_tok, n_out) and got.dtype == np.float32
+    assert np.abs(got - want).max() <= 4e-6 * n_in * max(1.0, float(np.abs(want).max()))
