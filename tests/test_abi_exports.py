@@ -94,3 +94,25 @@ def test_linear_kernel_plan_stays_inside_its_buffers():
     plan = (C.c_int * 8)()
     assert L.cglm_linear_kernel_plan(8, 4096, 96, 148, plan) == 0
     assert L.cglm_linear_kernel_plan(8, 4000, 4096, 148, plan) == 0
+
+
+def test_linear_entry_points_validate_before_they_touch_a_device():
+    """Argument checks of the Linear entry points answer on a machine without a GPU: null pointers, shapes the kernels
+    do not take, a workspace that cannot even hold the status word, misaligned operands."""
+    from chatglm_cpp_b200 import _lib
+    L = _lib.lib()
+    assert L.cglm_linear_workspace_bytes() == 256 + 148 * 128 * 128 * 4
+    ok = 0x1000   # a plausible, 16-byte aligned address; never dereferenced by the checks
+    big = L.cglm_linear_workspace_bytes()
+    assert L.cglm_linear_forward(None, 1, 64, ok, 32, None, ok, 0, ok, big, None) == _lib.ERR_INVALID_ARG
+    assert L.cglm_linear_forward(ok, 0, 64, ok, 32, None, ok, 0, ok, big, None) == _lib.ERR_INVALID_ARG
+    assert L.cglm_linear_forward(ok, 1, 64, ok, 32, None, ok, 0, None, big, None) == _lib.ERR_WORKSPACE
+    assert L.cglm_linear_forward(ok, 1, 64, ok, 32, None, ok, 0, ok, 128, None) == _lib.ERR_WORKSPACE
+    assert L.cglm_linear_forward(ok, 1, 96, ok, 32, None, ok, 0, ok, big, None) == _lib.ERR_UNSUPPORTED     # in % 64
+    assert L.cglm_linear_forward(ok, 1, 64, ok, 40, None, ok, 0, ok, big, None) == _lib.ERR_UNSUPPORTED     # out % 32
+    assert L.cglm_linear_forward(ok + 8, 1, 64, ok, 32, None, ok, 0, ok, big, None) == _lib.ERR_INVALID_ARG   # x alignment
+    assert L.cglm_linear_forward(ok, 1, 64, ok, 32, None, ok + 4, 0, ok, big, None) == _lib.ERR_INVALID_ARG   # out alignment
+    assert L.cglm_convert_f32_to_f16(None, ok, 4, None) == _lib.ERR_INVALID_ARG
+    assert L.cglm_convert_f32_to_f16(ok, ok, 0, None) == 0                                                     # nothing to do
+    plan = (C.c_int * 8)()
+    assert L.cglm_linear_kernel_plan(8, 4096, 4096, 0, plan) == 0 and L.cglm_linear_kernel_plan(8, 4096, 4096, 148, None) == 0

@@ -273,3 +273,30 @@ def test_attention_weights_from_a_model_file_drive_the_linears():
     assert rc == 0
     assert L.cglm_model_file_load_attn_weight(h32, 0, 0, w_d.data_ptr(), w.nbytes * 2, stream) == _lib.ERR_UNSUPPORTED
     L.cglm_model_file_close(h32)
+
+
+def test_attention_weight_loader_refuses_before_it_copies():
+    """cglm_model_file_load_attn_weight validates against the file on the host: layer and selector ranges, tensors the
+    model family does not have, sizes, and matrix types the Linear kernels do not take (no device is touched)."""
+    from chatglm_cpp_b200 import _lib
+    L = _lib.lib()
+    cfg = W.GLM3_PTUNING
+    dst = 0x1000   # never written: every call below is refused
+    blob, written = W.write_model(cfg, W.F16, 2, seed=3)
+    rc, h, keep = _open(blob)
+    assert rc == 0
+    n_w = written["transformer.encoder.layers.0.self_attention.query_key_value.weight"][0].size * 2
+    assert L.cglm_model_file_load_attn_weight(h, -1, 0, dst, n_w, None) == _lib.ERR_INVALID_ARG
+    assert L.cglm_model_file_load_attn_weight(h, cfg["num_hidden_layers"], 0, dst, n_w, None) == _lib.ERR_INVALID_ARG
+    assert L.cglm_model_file_load_attn_weight(h, 0, 4, dst, n_w, None) == _lib.ERR_INVALID_ARG
+    assert L.cglm_model_file_load_attn_weight(h, 0, 3, dst, 4 * cfg["hidden_size"], None) == _lib.ERR_INVALID_ARG   # no dense bias in GLM-3
+    assert L.cglm_model_file_load_attn_weight(h, 0, 0, dst, n_w - 2, None) == _lib.ERR_INVALID_ARG                  # wrong size
+    assert L.cglm_model_file_load_attn_weight(h, 0, 0, None, n_w, None) == _lib.ERR_INVALID_ARG
+    L.cglm_model_file_close(h)
+    for t in (W.F32, W.Q8_0, W.Q4_0):
+        blob, _ = W.write_model(cfg, t, 2, seed=3)
+        rc, h, keep = _open(blob)
+        assert rc == 0
+        assert L.cglm_model_file_load_attn_weight(h, 0, 0, dst, n_w, None) == _lib.ERR_UNSUPPORTED
+        assert b"f16" in L.cglm_last_error_string()
+        L.cglm_model_file_close(h)
