@@ -166,7 +166,9 @@ enum {
     CGLM_SEQ_Q_ROPED = 128
 };
 
-/* Scratch the kernels need for n_seq sequences per call with at most max_qlen tokens each. */
+/* Scratch the kernels need for n_seq sequences per call with at most max_qlen tokens each: a 256-byte header (status
+ * word, counters), 9.7 MB of scratch for the Linear kernels (see cglm_linear_forward), then the attention kernels'
+ * counters, partial results and staging.  One workspace serves one stream at a time. */
 size_t cglm_attn_workspace_bytes(const cglm_attn_desc *desc, int n_seq, int max_qlen);
 /* Zeroes the control words of a workspace.  Call once before first use and after any CGLM_ERR_TIMEOUT. */
 int cglm_attn_workspace_init(void *workspace, size_t workspace_bytes, void *cuda_stream);
