@@ -49,3 +49,26 @@ def test_reference_arm_prints_one_line_with_the_contract_keys():
     assert line["e2e"]["h2d_bytes_per_step"] == 0 and line["e2e"]["d2h_bytes_per_step"] == 0
     assert line["config"]["workload"] == "glm3_6b_decode_512" and line["value"] > 0
     assert "executes" in line["cpu_baseline"]["sample"]
+
+
+def test_workload_table_is_well_formed_and_the_default_run_names_exist():
+    """A misspelt workload name or a missing key would only show on a GPU box: every entry carries what its measurement
+    reads, the names the default run asks for exist, and every workload fits the device memory it is documented for."""
+    import inspect
+    import re
+    common = {"H", "G", "D", "M", "layers", "seqs", "n_past", "rope", "theta", "mask", "interleaved", "seed"}
+    kinds = ("prefill", "qkv_linear", "attention_block", "split_kv")
+    for name, w in bench.WORKLOADS.items():
+        assert common <= set(w), (name, common - set(w))
+        assert sum(1 for k in kinds if w.get(k)) <= 1, name
+        assert w["H"] % w["G"] == 0 and w["n_past"][0] <= w["n_past"][1] < w["M"], name
+        slots = w["layers"] * w["seqs"]
+        cache_bytes = slots * 2 * w["G"] * w["M"] * w["D"] * 2
+        assert cache_bytes <= 60e9, (name, cache_bytes)             # a third of a B200's 180 GB at most
+        if w.get("attention_block") or w.get("qkv_linear"):
+            hidden = w.get("attention_block") or w["qkv_linear"]
+            assert hidden % 64 == 0 and ((w["H"] + 2 * w["G"]) * w["D"]) % 32 == 0, name
+            assert w["layers"] * (w["H"] + 2 * w["G"]) * w["D"] * hidden * 2 > 126e6, name   # weights in rotation exceed L2
+    assert bench.HEADLINE in bench.WORKLOADS
+    asked = set(re.findall(r'"(glm[0-9a-z_]+)"', inspect.getsource(bench.run_default)))
+    assert asked and asked <= set(bench.WORKLOADS), asked - set(bench.WORKLOADS)
