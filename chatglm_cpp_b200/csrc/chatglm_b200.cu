@@ -39,6 +39,7 @@ ModelContext::ModelContext(void *cuda_stream) : stream_(cuda_stream) {}
 ModelContext::~ModelContext() {
     cudaStreamSynchronize(static_cast<cudaStream_t>(stream_));
     reset_scratch();
+    for (auto &c : pool_) cudaFree(c.base);
     for (auto &t : weights_) {
         if (t->owned && t->data) cudaFree(t->data);
     }
@@ -126,11 +127,29 @@ Tensor *ModelContext::new_weight_2d(TensorType type, int64_t ne0, int64_t ne1) {
 
 Tensor *ModelContext::new_weight_1d(TensorType type, int64_t ne0) { return new_weight_2d(type, ne0, 1); }
 
+// Per-step tensors come out of a pool that is carved front to back and rewound by reset_scratch (the reference's ctx_b
+// is the same kind of arena): no device allocation per tensor once the pool has grown to a step's needs.
+void *ModelContext::scratch_alloc(size_t bytes) {
+    const size_t need = (std::max<size_t>(bytes, 16) + 255) / 256 * 256;
+    if (pool_.empty() || pool_.back().used + need > pool_.back().size) {
+        ScratchChunk c;
+        c.size = std::max<size_t>(need, static_cast<size_t>(32) << 20);
+        c.used = 0;
+        c.base = nullptr;
+        CHATGLM_CHECK_CUDA(cudaMalloc(&c.base, c.size));
+        pool_.push_back(c);   // earlier chunks stay where they are: tensors already handed out keep their addresses
+    }
+    ScratchChunk &c = pool_.back();
+    void *p = static_cast<char *>(c.base) + c.used;
+    c.used += need;
+    return p;
+}
+
 Tensor *ModelContext::new_tensor_2d(TensorType type, int64_t ne0, int64_t ne1) {
     auto t = std::make_unique<Tensor>();
     set_contiguous(t.get(), type, ne0, ne1, 1);
-    CHATGLM_CHECK_CUDA(cudaMalloc(&t->data, std::max<size_t>(nbytes(t.get()), 16)));
-    t->owned = true;
+    t->data = scratch_alloc(nbytes(t.get()));
+    t->owned = false;   // the pool's
     scratch_.push_back(std::move(t));
     return scratch_.back().get();
 }
@@ -139,12 +158,25 @@ Tensor *ModelContext::new_tensor_1d(TensorType type, int64_t ne0) { return new_t
 
 void ModelContext::reset_scratch() {
     if (!scratch_.empty()) {
-        cudaStreamSynchronize(static_cast<cudaStream_t>(stream_));
-    }
-    for (auto &t : scratch_) {
-        if (t->owned && t->data) cudaFree(t->data);
+        cudaStreamSynchronize(static_cast<cudaStream_t>(stream_));   // kernels that still read the tensors
     }
     scratch_.clear();
+    if (pool_.size() > 1) {
+        // the step needed more than one chunk: one chunk of the whole size from now on
+        size_t total = 0;
+        for (auto &c : pool_) {
+            total += c.size;
+            cudaFree(c.base);
+        }
+        pool_.clear();
+        ScratchChunk c;
+        c.size = total;
+        c.used = 0;
+        c.base = nullptr;
+        if (cudaMalloc(&c.base, c.size) == cudaSuccess) pool_.push_back(c);   // on failure the next tensor allocates afresh
+        else cudaGetLastError();
+    }
+    for (auto &c : pool_) c.used = 0;
 }
 
 // A cache tensor of an arena whose row pitch exceeds its extent is not contiguous: such a tensor is copied whole

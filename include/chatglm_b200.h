@@ -101,7 +101,8 @@ class ModelContext {
     Tensor *new_weight_1d(TensorType type, int64_t ne0);
     Tensor *new_weight_2d(TensorType type, int64_t ne0, int64_t ne1);
 
-    // per-step device tensors (the reference's ctx_b scratch context); freed by reset_scratch()
+    // per-step device tensors (the reference's ctx_b scratch context), carved out of a pool; reset_scratch() takes them
+    // all back (after synchronising the stream) and keeps the pool
     Tensor *new_tensor_1d(TensorType type, int64_t ne0);
     Tensor *new_tensor_2d(TensorType type, int64_t ne0, int64_t ne1);
     void reset_scratch();
@@ -128,7 +129,13 @@ class ModelContext {
     cglm_attn_desc desc_{};
     bool have_desc_ = false;
     std::vector<std::unique_ptr<Tensor>> kv_tensors_;
+    struct ScratchChunk {
+        void *base;
+        size_t size, used;
+    };
+    void *scratch_alloc(size_t bytes);
     std::vector<std::unique_ptr<Tensor>> scratch_;
+    std::vector<ScratchChunk> pool_;
     std::vector<std::unique_ptr<Tensor>> weights_;
     void *workspace_ = nullptr;
     size_t workspace_bytes_ = 0;
