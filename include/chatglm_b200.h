@@ -189,8 +189,9 @@ class BasicAttention {
     // (head size 128, blocked qkv, no explicit position ids) takes three launches: the query_key_value GEMM with bias,
     // RoPE and append in its epilogue, the decode kernel, the dense GEMM; the activations between them are roped q
     // (f32) and the f16 context.  Everything else runs query_key_value as a plain GEMM with an f16 result, the
-    // attention kernels on f16 input and output, and dense.  Every intermediate tensor is a device allocation from mctx's
-    // scratch, as in the reference's per-call graph context: a token loop belongs in a DecodeStep (with_linears).
+    // attention kernels on f16 input and output, and dense.  Intermediate tensors come from mctx's scratch pool
+    // (call reset_scratch() between steps, as the reference drops its graph context); the launches are issued one by
+    // one, so a token loop is better served by a DecodeStep (with_linears), which replays them as one graph.
     Tensor *forward(ModelContext *mctx, Tensor *hidden_states, Tensor *attention_mask, Tensor *position_ids,
                     int n_past) const;
 
